@@ -1,0 +1,409 @@
+#!/usr/bin/env python3
+"""Benchmark of the weight-streaming quantized linear-layer path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (one "step" = one decoded token): 400 independent 17408 x 5120 W4A8 layers at
+M = 1 — per layer `quant_act` (fp32 activations -> int8 per 128-group) then
+`gemv_w4a8<1,false,1>` over that layer's own int4 weights and f16 group scales
+(18.4 GB of weights in total, far larger than L2, so every step streams from HBM).
+With G > 1 GPUs rank r holds rows [r*17408/G, (r+1)*17408/G) of every layer and an
+all-gather of y follows each layer (strong scaling: the job is fixed).
+
+One JSON line is printed by rank 0; see the keys at the bottom of `run_ours`.
+`--impl reference` times the reference project's CPU implementation of the same path —
+its NumPy arithmetic as restated in oracle/w4_oracle.py — on the host cores, on a
+bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures as cf
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "k100lc-kernels_b200"))
+
+N, K, GROUP = 17408, 5120, 128
+NG = K // GROUP
+W_BYTES = N * K // 2                       # packed int4 weights of one layer
+S_BYTES = N * NG * 2                       # f16 group scales of one layer
+LAYER_BYTES = W_BYTES + S_BYTES            # algorithmic bytes of one W4 layer: 45 957 120
+NVFP4_LAYER_BYTES = W_BYTES + N * (K // 16)   # E2M1 codes + E4M3 block scales: 50 135 040
+METRIC = "decode weight-stream bandwidth, 400 x (17408x5120) W4A8 layers, M=1 (us/layer and ms/token alongside)"
+WORKLOAD = "400-layer W4A8 M=1 decode weight stream, N=17408 K=5120 group=128, seed 4"
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "source": "fallback (6.65 TB/s, earlier measurement on this pool)"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.proc, self.path = device, None, f"/tmp/fm_clocks_{os.getpid()}.csv"
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, smax, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [t.strip() for t in line.split(",")]
+                if len(f) < 9 or not f[1].isdigit():
+                    continue
+                sm.append(int(f[1]))
+                smax.append(int(f[2]))
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        return {"sm_mhz": int(statistics.median(sm)), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- ours
+class Stream:
+    """The sharded 400-layer weight stream of one rank, resident in HBM."""
+
+    def __init__(self, rt, layers: int, rank: int, world: int):
+        from k100lc_kernels import synth
+        self.rt, self.layers, self.rank, self.world = rt, layers, rank, world
+        self.rows = N // world
+        blocks = synth.STREAM_ROW_BLOCKS // world
+        self.wq = rt.alloc(layers * self.rows * (K // 2))
+        self.ws = rt.alloc(layers * self.rows * NG * 2)
+        self.x = rt.alloc(layers * K * 4)
+        self.y = rt.alloc(layers * N * 4)                         # gathered outputs [layers][N]
+        self.yloc = rt.alloc(layers * self.rows * 4) if world > 1 else self.y
+        self.ae, self.ao = rt.alloc(K // 2), rt.alloc(K // 2)
+        self.asc, self.asu = rt.alloc(NG * 4), rt.alloc(NG * 4)
+        brow = N // synth.STREAM_ROW_BLOCKS
+        jobs = [(l, rank * blocks + b) for l in range(layers) for b in range(blocks)]
+        with cf.ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 8)) as ex:
+            for (l, b), blk in zip(jobs, ex.map(lambda j: synth.stream_layer_block(j[0], j[1]), jobs)):
+                lb = b - rank * blocks
+                rt.upload(self.wq + (l * self.rows + lb * brow) * (K // 2), blk["wq"])
+                rt.upload(self.ws + (l * self.rows + lb * brow) * NG * 2, blk["ws"])
+        self.x_host = rt.pinned((layers, K), np.float32)
+        for l in range(layers):
+            self.x_host[l] = synth.stream_layer_x(l)
+        self.y_host = rt.pinned((layers, N), np.float32)
+        rt.upload(self.x, self.x_host)
+
+    def wq_l(self, l): return self.wq + l * self.rows * (K // 2)
+    def ws_l(self, l): return self.ws + l * self.rows * NG * 2
+
+    def enqueue_token(self, quant=True, gemv=True, gather=True):
+        """One decoded token: per layer quant_act -> gemv_w4a8 (-> all-gather of y)."""
+        rt, rows = self.rt, self.rows
+        for l in range(self.layers):
+            if quant:
+                rt.launch("quant_act", NG, 32, [self.x + l * K * 4, self.ae, self.ao, self.asc, self.asu, 1, K])
+            if gemv:
+                dst = (self.yloc + l * rows * 4) if self.world > 1 else (self.y + l * N * 4)
+                rt.launch("gemv_w4a8<1,false,1>", rows // 4, 256,
+                          [self.wq_l(l), self.ws_l(l), self.ae, self.ao, self.asc, self.asu, dst, rows, K])
+            if gather and self.world > 1:
+                rt.allgather(self.y + l * N * 4, self.yloc + l * rows * 4, rows * 4)
+
+    def capture(self, **kw) -> int:
+        self.rt.graph_begin()
+        self.enqueue_token(**kw)
+        return self.rt.graph_end()
+
+
+def time_graph(rt, graph, steps, warmup, barrier, counter=None) -> float:
+    """ms per launch of `graph`, CUDA events on the engine stream, barrier + sync both sides.
+    `counter`, if given, receives the number of kernels launched inside the timed region."""
+    for _ in range(warmup):
+        rt.graph_launch(graph)
+    rt.sync()
+    barrier()
+    e0, e1 = rt.event(), rt.event()
+    n0 = rt.launch_count()
+    rt.record(e0)
+    for _ in range(steps):
+        rt.graph_launch(graph)
+    rt.record(e1)
+    rt.sync()
+    barrier()
+    if counter is not None:
+        counter.append(rt.launch_count() - n0)
+    return rt.elapsed_ms(e0, e1) / steps
+
+
+def path_timings(rt, st: Stream, reps: int) -> dict:
+    """us/layer and GB/s of quantiser + GEMV for W4A8, W4A4 and NVFP4 at M=1, each over a
+    rotation of distinct layers (> L2) so that the weights come from HBM."""
+    from k100lc_kernels import synth
+    out = {}
+    nl = min(st.layers, 64)
+    rows = st.rows
+    aq, asc4 = rt.alloc(K // 2), rt.alloc((K // 32) * 4)
+    qa, qb, sc16 = rt.alloc(K // 2), rt.alloc(K // 2), rt.alloc((K // 16) * 4)
+    nv_layers = min(nl, 16)
+    nvs = rt.alloc(nv_layers * rows * (K // 16))
+    rng = np.random.default_rng(2)
+    from k100lc_kernels.quant import f32_to_e4m3_bits
+    sb = f32_to_e4m3_bits(np.exp2(rng.uniform(-4.0, 2.0, size=(rows, K // 16))).astype(np.float32))
+    for l in range(nv_layers):
+        rt.upload(nvs + l * rows * (K // 16), np.roll(sb, l, axis=0))
+
+    def graph_of(fn, count):
+        rt.graph_begin()
+        for l in range(count):
+            fn(l)
+        return rt.graph_end()
+
+    def w4a8(l):
+        rt.launch("quant_act", NG, 32, [st.x + l * K * 4, st.ae, st.ao, st.asc, st.asu, 1, K])
+        rt.launch("gemv_w4a8<1,false,1>", rows // 4, 256,
+                  [st.wq_l(l), st.ws_l(l), st.ae, st.ao, st.asc, st.asu, st.y + l * N * 4, rows, K])
+
+    def w4a4(l):
+        rt.launch("quant_act4", K // 32, 32, [st.x + l * K * 4, aq, asc4, 1, K])
+        rt.launch("gemv_w4a4<1>", rows // 4, 256, [st.wq_l(l), st.ws_l(l), aq, asc4, st.y + l * N * 4, rows, K])
+
+    def nvfp4(l):
+        rt.launch("nvfp4_quant_act", K // 16, 64, [st.x + l * K * 4, qa, qb, sc16, 1, K])
+        rt.launch("nvfp4_gemv<1,1>", rows // 4, 256,
+                  [st.wq_l(l), nvs + (l % nv_layers) * rows * (K // 16), qa, qb, sc16, st.y + l * N * 4, rows, K, 0.05])
+
+    def w4a8_only(l):
+        rt.launch("gemv_w4a8<1,false,1>", rows // 4, 256,
+                  [st.wq_l(l), st.ws_l(l), st.ae, st.ao, st.asc, st.asu, st.y + l * N * 4, rows, K])
+
+    frac = rows / N
+    for name, fn, nbytes in (("w4a8_m1", w4a8, LAYER_BYTES), ("w4a4_m1", w4a4, LAYER_BYTES),
+                             ("nvfp4_m1", nvfp4, NVFP4_LAYER_BYTES), ("w4a8_m1_gemv_only", w4a8_only, LAYER_BYTES)):
+        g = graph_of(fn, nl)
+        ms = time_graph(rt, g, reps, 3, lambda: None)
+        rt.graph_free(g)
+        us = ms * 1e3 / nl
+        out[name] = {"us_per_layer": round(us, 3), "gb_per_s": round(nbytes * frac / us / 1e3, 1)}
+    for p in (aq, asc4, qa, qb, sc16, nvs):
+        rt.free(p)
+    return out
+
+
+def cpu_baseline(sample_layers: int) -> dict:
+    """The reference's CPU arithmetic (NumPy restatement in oracle/) on the host cores, on the
+    first `sample_layers` layers of the same stream."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import w4_oracle as O
+    from k100lc_kernels import synth
+    lay = []
+    for l in range(sample_layers):
+        blks = [synth.stream_layer_block(l, b) for b in range(synth.STREAM_ROW_BLOCKS)]
+        lay.append((np.concatenate([b["wq"] for b in blks]).view(np.uint32), np.concatenate([b["ws"] for b in blks]),
+                    synth.stream_layer_x(l)[None, :]))
+    t0 = time.perf_counter()
+    for wq, ws, x in lay:
+        q = O.quant_act(x)
+        O.gemv_w4(wq, ws, q["q"], q["scale"], 128)
+    dt = time.perf_counter() - t0
+    return {"value": round(sample_layers * LAYER_BYTES / dt / 1e9, 4), "unit": "GB/s", "cores": os.cpu_count(),
+            "kind": "port", "seconds_per_layer": round(dt / sample_layers, 3),
+            "sample": f"first {sample_layers} of the 400 layers (quant_act + W4A8 GEMV in NumPy; BLAS uses all host threads)"}
+
+
+def run_ours(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"bench.py --gpus {args.gpus} must be started with torch.distributed.run "
+                  f"--nproc-per-node {args.gpus}", file=sys.stderr)
+            return 2
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group(backend="gloo")
+    os.environ.setdefault("FM_DEVICE", str(local))
+    from k100lc_kernels import Runtime
+    rt = Runtime()                                  # raises when the CUDA library or a B200 is missing
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    if world > 1:
+        box = [rt.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        rt.comm_init(box[0], world, rank)
+
+    t_setup = time.perf_counter()
+    st = Stream(rt, args.layers, rank, world)
+    setup_s = time.perf_counter() - t_setup
+
+    graph = st.capture()
+    counted = []
+    with ClockSampler(rt.device_attr("device")) as clocks:
+        ms_step = time_graph(rt, graph, args.steps, args.warmup, barrier, counted)
+    gpu_launches = counted[0]                       # kernels of this library inside the timed region
+
+    # end to end through the C ABI with host buffers: x of all layers up, y of all layers back, every step
+    def e2e_step():
+        rt.upload_async(st.x, st.x_host)
+        rt.graph_launch(graph)
+        rt.download_async(st.y_host, st.y)
+    for _ in range(max(1, args.warmup)):
+        e2e_step()
+    rt.sync()
+    barrier()
+    e0, e1 = rt.event(), rt.event()
+    rt.record(e0)
+    for _ in range(args.steps):
+        e2e_step()
+    rt.record(e1)
+    rt.sync()
+    barrier()
+    ms_e2e = rt.elapsed_ms(e0, e1) / args.steps
+
+    # the dominant kernel alone (gemv_w4a8<1,false,1>), for the roofline
+    gk = st.capture(quant=False, gather=False)
+    ms_kern = time_graph(rt, gk, max(3, args.steps // 2), 3, barrier)
+
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms_step, ms_e2e, ms_kern], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, ms_e2e, ms_kern = (float(v) for v in t)
+
+    total_bytes = args.layers * LAYER_BYTES         # whole job, all ranks
+    pk = peaks()
+    us_kernel = ms_kern * 1e3 / args.layers
+    achieved = LAYER_BYTES / world / us_kernel / 1e3          # GB/s of one GPU's kernel
+    line = None
+    if rank == 0:
+        paths = path_timings(rt, st, 5) if args.paths else None
+        cpu = cpu_baseline(args.cpu_layers) if (world == 1 and args.cpu_layers > 0) else None
+        line = {
+            "metric": METRIC, "value": round(total_bytes / ms_step / 1e6, 1), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 scale",
+            "data": "synthetic (seeded uniform int4 weights, |N(0,1)|*0.01+1e-3 f16 scales, N(0,1) activations)",
+            "config": {"workload": WORKLOAD, "layers": args.layers, "rows_per_gpu": N // world,
+                       "sharding": "output rows" + (f", all-gather of y per layer (NCCL)" if world > 1 else ""),
+                       "launch": "one CUDA graph per token (quant_act + gemv_w4a8 per layer)",
+                       "l2": "inputs (18.4 GB of weights) are larger than L2; no flush needed"},
+            "ms_per_token": round(ms_step, 4), "us_per_layer": round(ms_step * 1e3 / args.layers, 3),
+            "e2e": {"value": round(total_bytes / ms_e2e / 1e6, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e, 4),
+                    "h2d_bytes_per_step": args.layers * K * 4, "d2h_bytes_per_step": args.layers * N * 4,
+                    "api": "fm_upload_async(x) + fm_graph_launch + fm_download_async(y), pinned host buffers"},
+            "gpu_launches": int(gpu_launches),
+            "roofline": {"bound": "hbm", "kernel": "gemv_w4a8<1,false,1>", "achieved": round(achieved, 1),
+                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
+                         "frac_of_nominal_8000": round(achieved / 8000.0, 4), "peak_source": pk["source"],
+                         "us_per_launch": round(us_kernel, 3), "bytes_per_launch": LAYER_BYTES // world,
+                         "traffic": None},
+            "cpu_baseline": cpu, "clocks": clocks.summary(), "paths_m1": paths, "setup_seconds": round(setup_s, 1),
+        }
+    if world > 1:
+        rt.comm_destroy()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------- reference arm
+def run_reference(args) -> int:
+    """The reference's CPU implementation of the path on the host cores: each step is a
+    bounded sample (the first `--cpu-layers` layers) of the same stream."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import w4_oracle as O
+    from k100lc_kernels import synth
+    nl = max(1, min(args.cpu_layers, 4))
+    lay = []
+    for l in range(nl):
+        blks = [synth.stream_layer_block(l, b) for b in range(synth.STREAM_ROW_BLOCKS)]
+        lay.append((np.concatenate([b["wq"] for b in blks]).view(np.uint32), np.concatenate([b["ws"] for b in blks]),
+                    synth.stream_layer_x(l)[None, :]))
+
+    def step():
+        for wq, ws, x in lay:
+            q = O.quant_act(x)
+            O.gemv_w4(wq, ws, q["q"], q["scale"], 128)
+
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    val = round(nl * LAYER_BYTES / dt / 1e9, 4)
+    sample = (f"{nl} of the 400 layers per step (quant_act + W4A8 GEMV in NumPy, all host BLAS threads); "
+              f"{steps} timed steps, {warmup} warm-up")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(dt * 1e3 * 400 / nl, 1), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 scale", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": 400, "sampled_layers": nl},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's device code targets gfx926 and cannot run here; its CPU path is the NumPy "
+                "oracle of its self-test, restated in oracle/w4_oracle.py and pinned to it by tests/golden"}), flush=True)
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=400)
+    ap.add_argument("--cpu-layers", type=int, default=6, help="layers of the stream timed on the CPU (0 = skip)")
+    ap.add_argument("--no-paths", dest="paths", action="store_false", help="skip the per-path M=1 timings")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
+    return run_reference(args) if args.impl == "reference" else run_ours(args)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,114 @@
+/* fm_engine.h — C ABI of libfm_engine.so for NVIDIA B200 (sm_100a).
+ *
+ * The first 14 entry points are a drop-in for the reference engine
+ * (Hong-agent/K100LC-kernels, runtime/fm_engine.h:10-28 and
+ * runtime/fm_engine.cpp:70-139): same names, argument meaning and return
+ * codes, so that the reference's ctypes binding
+ * (python/k100lc_kernels/runtime.py:129-163) and C++ users
+ * (examples/cpp_alloc.cpp) work unchanged.  Kernels are selected by the
+ * reference's lookup strings ("quant_act", "gemv_w4a8<1,false,1>", ...).
+ *
+ * Everything after the "extensions" banner has no counterpart in the
+ * reference (which is single-device and has no timers or collectives).
+ *
+ * Return codes of the launch family:
+ *    0  launched (asynchronously, on the engine's single in-order stream)
+ *   -1  unknown kernel name                     (reference fm_engine.cpp:83-86)
+ *   -2  explicit-argument count mismatch        (reference fm_engine.cpp:87-91)
+ *   -3  fm_launch_dyn: kernarg_size > 1024      (reference fm_engine.cpp:108)
+ *   -4  rejected before launch: a pointer argument does not lie inside a live
+ *       fm_alloc allocation for the footprint the kernel would touch, a
+ *       pointer is misaligned, or the geometry/shape is one the kernel cannot
+ *       run (the reference would read or write out of bounds instead)
+ *   -5  CUDA error; text via fm_last_error()
+ */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- reference ABI ---------------------------------------------------- */
+
+/* runtime/fm_engine.h:10, fm_engine.cpp:38-41.  `hsaco` named the kernel
+ * image in the reference; here the kernels are linked into the library and
+ * the argument is only recorded.  Idempotent.  Device = $FM_DEVICE, else
+ * $LOCAL_RANK, else 0 (unless fm_set_device was called first). */
+int   fm_init(const char* hsaco);
+/* fm_engine.h:11-12, fm_engine.cpp:43-49.  NULL when out of memory. */
+void* fm_alloc(size_t n);
+void  fm_free(void* p);
+/* fm_engine.h:13-16, fm_engine.cpp:51-65.  Ordered on the engine stream;
+ * upload/download return after the copy has completed. */
+int   fm_upload(void* dev, const void* host, size_t n);
+int   fm_download(void* host, const void* dev, size_t n);
+int   fm_copy(void* dst, const void* src, size_t n);
+int   fm_memset(void* dev, int v, size_t n);
+/* fm_engine.h:17, fm_engine.cpp:67. */
+int   fm_sync(void);
+/* fm_engine.h:19-22, fm_engine.cpp:75-101.  grid / workgroup count work-groups
+ * and threads per group as on the reference; argv[i] is the i-th explicit
+ * argument (pointers as device addresses, scalars in the low bytes, f32 as bit
+ * pattern). */
+int   fm_launch(const char* kernel, uint32_t grid, uint32_t workgroup,
+                const uint64_t* argv, int nargs);
+int   fm_launch2d(const char* kernel, uint32_t gx, uint32_t gy,
+                  uint32_t wx, uint32_t wy, const uint64_t* argv, int nargs);
+/* fm_engine.h:23-28, fm_engine.cpp:103-132.  `layout` is nargs x (off,size,kind);
+ * only its kind==0 count and kernarg_size are validated here. */
+int   fm_launch_dyn(const char* kernel, uint32_t gx, uint32_t gy,
+                    uint32_t wx, uint32_t wy,
+                    const uint32_t* layout, uint32_t nargs,
+                    uint32_t group_size, uint32_t private_size,
+                    uint32_t kernarg_size, const uint64_t* argv, int nargv);
+/* fm_engine.cpp:70-73, 134-139.  A plan is a flat uint64 array of records
+ * [kernel_id, grid, workgroup, nargs, argv...]; returns the number of records
+ * enqueued.  A plan is replayed as a CUDA graph (re-captured when its contents
+ * change). */
+int   fm_has_kernel(const char* kernel);
+int   fm_kernel_id(const char* kernel);
+int   fm_launch_batch(const uint64_t* plan, int nrec);
+
+/* ---- extensions (no counterpart in the reference) ---------------------- */
+
+const char* fm_last_error(void);
+int   fm_device_count(void);
+int   fm_set_device(int dev);          /* before fm_init */
+int   fm_device_attr(int what);        /* 0 SM count, 1 L2 bytes, 2 device ordinal,
+                                          3 total memory MiB, 4 SM clock kHz */
+int   fm_kernel_count(void);
+const char* fm_kernel_name(int id);
+int   fm_kernel_nargs(int id);
+const char* fm_kernel_sig(int id);    /* one letter per argument: p pointer, i int32, f float32 */
+unsigned long long fm_launch_count(void);   /* kernels launched so far */
+
+/* pinned host memory and asynchronous copies on the engine stream */
+void* fm_host_alloc(size_t n);
+void  fm_host_free(void* p);
+int   fm_upload_async(void* dev, const void* pinned_host, size_t n);
+int   fm_download_async(void* pinned_host, const void* dev, size_t n);
+
+/* device timers on the engine stream */
+int   fm_event_create(void);
+int   fm_event_record(int ev);
+float fm_event_elapsed_ms(int ev_start, int ev_stop);   /* <0 on error */
+
+/* explicit CUDA-graph capture of everything enqueued between begin and end */
+int   fm_graph_begin(void);
+int   fm_graph_end(void);              /* graph id >= 0, or <0 */
+int   fm_graph_launch(int graph);
+int   fm_graph_free(int graph);
+
+/* one process per GPU: NCCL communicator over NVLink/NVSwitch */
+int   fm_comm_unique_id(void* out128);
+int   fm_comm_init(const void* id128, int nranks, int rank);
+int   fm_comm_rank(void);
+int   fm_comm_size(void);
+int   fm_allgather(void* recv, const void* send, size_t bytes_per_rank);
+int   fm_comm_destroy(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,65 @@
+// Small device-side building blocks shared by the kernel files (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fm {
+
+// 128-bit streaming load of read-once data: read-only path, no L1 allocation.
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_u16(const void* p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+// signed 8-bit x 4 dot product with int32 accumulate
+__device__ __forceinline__ int dot4(uint32_t a, uint32_t b, int c) {
+    return __dp4a(static_cast<int>(a), static_cast<int>(b), c);
+}
+
+// generic byte permute; selector nibble bit 3 replicates the sign bit of the
+// selected byte (used as a "zero unless" switch with tables whose bytes are < 0x80)
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// Programmatic dependent launch: wait until the preceding kernel on the stream
+// has completed and its writes are visible / allow the next kernel to start.
+// Both are no-ops when the kernel was launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ int warp_sum(int v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Four int4 nibbles that sit in the low nibble of each byte -> four signed bytes.
+// (x & 0x08)*30 = 0xF0 exactly when the nibble is negative; no carry crosses a byte.
+__device__ __forceinline__ uint32_t sext_nibbles(uint32_t x) { return x | ((x & 0x08080808u) * 30u); }
+
+// absmax scale and round-half-even quantisation, bit-identical to
+// s = amax > 0 ? amax / qmax : 1 ; q = clip(rint(x / s)) evaluated in IEEE fp32
+__device__ __forceinline__ float absmax_scale(float amax, float qmax) {
+    return amax > 0.f ? __fdiv_rn(amax, qmax) : 1.f;
+}
+__device__ __forceinline__ int quant_rne(float x, float s, int lo, int hi) {
+    int q = __float2int_rn(__fdiv_rn(x, s));
+    return min(max(q, lo), hi);
+}
+
+}  // namespace fm

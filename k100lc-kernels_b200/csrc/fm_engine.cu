@@ -1,0 +1,637 @@
+// libfm_engine.so: the C ABI of the reference engine (runtime/fm_engine.{h,cpp},
+// by-name launch with a uint64 argv) re-implemented over the CUDA runtime for B200,
+// plus the extensions declared in include/fm_engine.h (timers, pinned copies,
+// explicit graphs, an NCCL communicator).
+//
+// Observable semantics kept from the reference runtime (runtime/hsa_rt.cpp):
+//   * one process-global engine, one in-order queue (here: one CUDA stream);
+//   * launches return immediately, fm_sync drains, copies are ordered on the queue
+//     and upload/download return when done (hsa_rt.cpp:732-761);
+//   * fm_alloc returns NULL when out of memory (hsa_rt.cpp:698-708);
+//   * fm_init is idempotent and ignores a second image name (hsa_rt.cpp:383-396);
+//   * argv is consumed before the call returns (runtime.py:169-175 relies on it).
+// Differences: errors come back as negative codes instead of ending the process, and
+// every pointer argument is checked against the live allocations before a launch.
+#include "../../include/fm_engine.h"
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "fm_internal.h"
+
+namespace fm {
+namespace {
+
+struct Graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    unsigned long long kernels = 0;      // kernel launches recorded in it
+};
+
+struct Engine {
+    std::recursive_mutex mu;
+    bool ready = false;
+    int device = -1;            // -1: choose at init
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    std::string image;
+    std::string last_error;
+    bool check_bounds = true;
+    bool pdl = false;
+    bool capturing = false;
+    unsigned long long launches = 0;          // kernels enqueued for execution so far
+    unsigned long long launches_at_capture = 0;
+    std::vector<KernelEntry> kernels;
+    std::unordered_map<std::string, int> by_name;
+    std::map<uintptr_t, size_t> allocs;          // base -> bytes
+    std::vector<cudaEvent_t> events;
+    std::vector<Graph> graphs;
+    std::unordered_map<uint64_t, int> plan_graphs;   // plan hash -> graph id
+    // NCCL (resolved with dlopen when a communicator is first asked for)
+    void* nccl_lib = nullptr;
+    void* comm = nullptr;
+    int comm_rank = 0, comm_size = 1;
+};
+
+Engine& E() {
+    static Engine e;
+    return e;
+}
+
+void set_error(const char* fmt, va_list ap) {
+    char buf[512];
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    E().last_error = buf;
+    if (getenv("FM_DEBUG")) fprintf(stderr, "fm_engine: %s\n", buf);
+}
+
+void set_errorf(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    set_error(fmt, ap);
+    va_end(ap);
+}
+
+void add_kernels(const KernelEntry* k, int n) {
+    Engine& e = E();
+    for (int i = 0; i < n; i++) {
+        e.by_name[k[i].name] = (int)e.kernels.size();
+        e.kernels.push_back(k[i]);
+    }
+}
+
+int find_kernel(const char* name) {
+    Engine& e = E();
+    auto it = e.by_name.find(name ? name : "");
+    return it == e.by_name.end() ? -1 : it->second;
+}
+
+int env_int(const char* k, int dflt) {
+    const char* v = getenv(k);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+int ensure_init() {
+    Engine& e = E();
+    if (e.ready) return 0;
+    int dev = e.device;
+    if (dev < 0) dev = env_int("FM_DEVICE", env_int("LOCAL_RANK", 0));
+    int count = 0;
+    cudaError_t err = cudaGetDeviceCount(&count);
+    if (err != cudaSuccess || count == 0) {
+        set_errorf("no CUDA device: %s", err == cudaSuccess ? "device count is 0" : cudaGetErrorString(err));
+        return FM_ECUDA;
+    }
+    if (dev >= count) dev = dev % count;
+    if ((err = cudaSetDevice(dev)) != cudaSuccess) {
+        set_errorf("cudaSetDevice(%d): %s", dev, cudaGetErrorString(err));
+        return FM_ECUDA;
+    }
+    cudaDeviceProp prop;
+    if ((err = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) {
+        set_errorf("cudaGetDeviceProperties: %s", cudaGetErrorString(err));
+        return FM_ECUDA;
+    }
+    if (prop.major != 10) {
+        set_errorf("device %d is sm_%d%d; this library carries sm_100a code only", dev, prop.major, prop.minor);
+        return FM_ECUDA;
+    }
+    if ((err = cudaStreamCreateWithFlags(&e.stream, cudaStreamNonBlocking)) != cudaSuccess) {
+        set_errorf("cudaStreamCreate: %s", cudaGetErrorString(err));
+        return FM_ECUDA;
+    }
+    e.device = dev;
+    e.sm_count = prop.multiProcessorCount;
+    e.check_bounds = env_int("FM_CHECK_BOUNDS", 1) != 0;
+    e.pdl = env_int("FM_PDL", 0) != 0;
+    if (e.kernels.empty()) {
+        int n = 0;
+        const KernelEntry* k;
+        k = quant_kernels(&n); add_kernels(k, n);
+        k = gemv_w4_kernels(&n); add_kernels(k, n);
+        k = gemv_nvfp4_kernels(&n); add_kernels(k, n);
+        k = int4_dot_kernels(&n); add_kernels(k, n);
+        k = gemm_w4_kernels(&n); add_kernels(k, n);
+    }
+    e.ready = true;
+    return 0;
+}
+
+// the kernel table is also needed without a device (fm_has_kernel, catalog generation)
+void ensure_table() {
+    Engine& e = E();
+    if (!e.kernels.empty()) return;
+    int n = 0;
+    const KernelEntry* k;
+    k = quant_kernels(&n); add_kernels(k, n);
+    k = gemv_w4_kernels(&n); add_kernels(k, n);
+    k = gemv_nvfp4_kernels(&n); add_kernels(k, n);
+    k = int4_dot_kernels(&n); add_kernels(k, n);
+    k = gemm_w4_kernels(&n); add_kernels(k, n);
+}
+
+int do_launch(int kid, uint32_t gx, uint32_t gy, uint32_t wx, uint32_t wy, const uint64_t* argv, int nargs) {
+    Engine& e = E();
+    const KernelEntry& k = e.kernels[kid];
+    if (k.nargs != nargs) {
+        set_errorf("%s takes %d explicit arguments, %d given", k.name, k.nargs, nargs);
+        return FM_ENARGS;
+    }
+    LaunchCtx ctx{gx, gy, wx, wy, e.stream, e.sm_count};
+    return k.fn(ctx, argv);
+}
+
+uint64_t fnv1a(const uint64_t* p, size_t n) {
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < n; i++) {
+        h ^= p[i];
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+
+// walks a plan, launching each record; returns records enqueued
+int run_plan(const uint64_t* plan, int nrec) {
+    Engine& e = E();
+    size_t i = 0;
+    int done = 0;
+    for (; done < nrec; done++) {
+        const int kid = (int)plan[i];
+        const uint32_t grid = (uint32_t)plan[i + 1], wg = (uint32_t)plan[i + 2];
+        const int nargs = (int)plan[i + 3];
+        if (kid < 0 || kid >= (int)e.kernels.size()) {
+            set_errorf("plan record %d: bad kernel id %d", done, kid);
+            break;
+        }
+        if (do_launch(kid, grid, 1, wg, 1, plan + i + 4, nargs) != FM_OK) break;
+        i += 4 + (size_t)nargs;
+    }
+    return done;
+}
+
+size_t plan_words(const uint64_t* plan, int nrec) {
+    size_t i = 0;
+    for (int r = 0; r < nrec; r++) i += 4 + (size_t)plan[i + 3];
+    return i;
+}
+
+// ---- NCCL through dlopen: the library loads and runs without NCCL present ----
+typedef struct { char internal[128]; } NcclUniqueId;
+typedef int (*nccl_get_uid_t)(NcclUniqueId*);
+typedef int (*nccl_init_rank_t)(void**, int, NcclUniqueId, int);
+typedef int (*nccl_allgather_t)(const void*, void*, size_t, int, void*, cudaStream_t);
+typedef int (*nccl_destroy_t)(void*);
+typedef const char* (*nccl_errstr_t)(int);
+
+void* nccl_sym(const char* name) {
+    Engine& e = E();
+    if (!e.nccl_lib) {
+        const char* names[] = {getenv("FM_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+        for (const char* n : names) {
+            if (n && *n && (e.nccl_lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL))) break;
+        }
+        if (!e.nccl_lib) {
+            set_errorf("cannot load NCCL (set FM_NCCL_LIB): %s", dlerror());
+            return nullptr;
+        }
+    }
+    void* s = dlsym(e.nccl_lib, name);
+    if (!s) set_errorf("NCCL symbol %s missing", name);
+    return s;
+}
+
+}  // namespace
+
+// ---- services for the kernel files -----------------------------------------
+bool range_ok(const void* p, size_t bytes) {
+    Engine& e = E();
+    if (!e.check_bounds) return true;
+    if (bytes == 0) return true;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    auto it = e.allocs.upper_bound(a);
+    if (it == e.allocs.begin()) return false;
+    --it;
+    return a >= it->first && a + bytes <= it->first + it->second;
+}
+
+int reject(const char* kernel, const char* fmt, ...) {
+    char msg[400];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(msg, sizeof msg, fmt, ap);
+    va_end(ap);
+    set_errorf("%s rejected: %s", kernel, msg);
+    return FM_EREJECT;
+}
+
+int cuda_fail(const char* kernel, cudaError_t err) {
+    set_errorf("%s: CUDA error %d (%s)", kernel, (int)err, cudaGetErrorString(err));
+    return FM_ECUDA;
+}
+
+int after_launch(const char* kernel) {
+    E().launches++;
+    if (E().capturing) return FM_OK;          // errors surface when the capture ends
+    cudaError_t err = cudaPeekAtLastError();
+    return err == cudaSuccess ? FM_OK : cuda_fail(kernel, cudaGetLastError());
+}
+
+bool pdl_enabled() { return E().pdl; }
+
+}  // namespace fm
+
+using namespace fm;
+#define LOCK std::lock_guard<std::recursive_mutex> lock_(E().mu)
+#define NEED_INIT(fail) do { if (ensure_init() != 0) return fail; } while (0)
+
+extern "C" {
+
+int fm_init(const char* image) {
+    LOCK;
+    if (E().ready) return 0;
+    if (image) E().image = image;
+    return ensure_init() == 0 ? 0 : -1;
+}
+
+void* fm_alloc(size_t n) {
+    LOCK;
+    NEED_INIT(nullptr);
+    void* p = nullptr;
+    if (n == 0) n = 1;
+    if (cudaMalloc(&p, n) != cudaSuccess) {
+        cudaGetLastError();
+        set_errorf("fm_alloc(%zu): out of device memory", n);
+        return nullptr;
+    }
+    E().allocs[reinterpret_cast<uintptr_t>(p)] = n;
+    return p;
+}
+
+void fm_free(void* p) {
+    LOCK;
+    if (!p || !E().ready) return;
+    cudaStreamSynchronize(E().stream);        // nothing in flight may still use it
+    E().allocs.erase(reinterpret_cast<uintptr_t>(p));
+    cudaFree(p);
+}
+
+static int copy_sync(void* dst, const void* src, size_t n, cudaMemcpyKind kind, const char* what) {
+    Engine& e = E();
+    if (n == 0) return 0;
+    cudaError_t err = cudaMemcpyAsync(dst, src, n, kind, e.stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(e.stream);
+    if (err != cudaSuccess) {
+        cuda_fail(what, err);
+        return -1;
+    }
+    return 0;
+}
+
+int fm_upload(void* dev, const void* host, size_t n) {
+    LOCK;
+    NEED_INIT(-1);
+    if (!range_ok(dev, n)) { set_errorf("fm_upload: %zu bytes at %p exceed the allocation", n, dev); return -1; }
+    return copy_sync(dev, host, n, cudaMemcpyHostToDevice, "fm_upload");
+}
+
+int fm_download(void* host, const void* dev, size_t n) {
+    LOCK;
+    NEED_INIT(-1);
+    if (!range_ok(dev, n)) { set_errorf("fm_download: %zu bytes at %p exceed the allocation", n, dev); return -1; }
+    return copy_sync(host, dev, n, cudaMemcpyDeviceToHost, "fm_download");
+}
+
+int fm_copy(void* dst, const void* src, size_t n) {
+    LOCK;
+    NEED_INIT(-1);
+    if (!range_ok(dst, n) || !range_ok(src, n)) { set_errorf("fm_copy: range exceeds an allocation"); return -1; }
+    if (n == 0) return 0;
+    cudaError_t err = cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToDevice, E().stream);
+    if (err != cudaSuccess) { cuda_fail("fm_copy", err); return -1; }
+    return 0;
+}
+
+int fm_memset(void* dev, int v, size_t n) {
+    LOCK;
+    NEED_INIT(-1);
+    if (!range_ok(dev, n)) { set_errorf("fm_memset: range exceeds the allocation"); return -1; }
+    if (n == 0) return 0;
+    cudaError_t err = cudaMemsetAsync(dev, v, n, E().stream);
+    if (err != cudaSuccess) { cuda_fail("fm_memset", err); return -1; }
+    return 0;
+}
+
+int fm_sync(void) {
+    LOCK;
+    NEED_INIT(-1);
+    cudaError_t err = cudaStreamSynchronize(E().stream);
+    if (err != cudaSuccess) { cuda_fail("fm_sync", err); return -1; }
+    return 0;
+}
+
+int fm_launch2d(const char* kernel, uint32_t gx, uint32_t gy, uint32_t wx, uint32_t wy,
+                const uint64_t* argv, int nargs) {
+    LOCK;
+    NEED_INIT(FM_ECUDA);
+    const int kid = find_kernel(kernel);
+    if (kid < 0) {
+        set_errorf("no kernel named %s", kernel ? kernel : "(null)");
+        return FM_ENOKERNEL;
+    }
+    return do_launch(kid, gx, gy, wx, wy, argv, nargs);
+}
+
+int fm_launch(const char* kernel, uint32_t grid, uint32_t workgroup, const uint64_t* argv, int nargs) {
+    return fm_launch2d(kernel, grid, 1, workgroup, 1, argv, nargs);
+}
+
+int fm_launch_dyn(const char* kernel, uint32_t gx, uint32_t gy, uint32_t wx, uint32_t wy,
+                  const uint32_t* layout, uint32_t nargs, uint32_t group_size, uint32_t private_size,
+                  uint32_t kernarg_size, const uint64_t* argv, int nargv) {
+    (void)group_size;
+    (void)private_size;
+    if (kernarg_size > 1024) return FM_EDYN;
+    int explicit_n = 0;
+    for (uint32_t i = 0; i < nargs; i++)
+        if (layout[3 * i + 2] == 0) explicit_n++;
+    if (explicit_n != nargv) return FM_ENARGS;
+    return fm_launch2d(kernel, gx, gy, wx, wy, argv, nargv);
+}
+
+int fm_has_kernel(const char* kernel) {
+    LOCK;
+    ensure_table();
+    return find_kernel(kernel) >= 0 ? 1 : 0;
+}
+
+int fm_kernel_id(const char* kernel) {
+    LOCK;
+    ensure_table();
+    return find_kernel(kernel);
+}
+
+int fm_launch_batch(const uint64_t* plan, int nrec) {
+    LOCK;
+    NEED_INIT(0);
+    Engine& e = E();
+    if (nrec <= 0) return 0;
+    if (e.capturing || getenv("FM_NO_GRAPH")) return run_plan(plan, nrec);
+    const size_t words = plan_words(plan, nrec);
+    const uint64_t h = fnv1a(plan, words) ^ ((uint64_t)nrec << 48);
+    auto it = e.plan_graphs.find(h);
+    if (it == e.plan_graphs.end()) {
+        // first sight of this exact plan: capture it (a patched plan hashes differently
+        // and is captured afresh, so LaunchPlan.set_arg/set_grid are honoured)
+        if (e.plan_graphs.size() >= 64) {          // bound the cache
+            for (auto& kv : e.plan_graphs) fm_graph_free(kv.second);
+            e.plan_graphs.clear();
+        }
+        if (fm_graph_begin() != 0) return run_plan(plan, nrec);
+        const int done = run_plan(plan, nrec);
+        const int gid = fm_graph_end();
+        if (done != nrec || gid < 0) {
+            if (gid >= 0) fm_graph_free(gid);
+            return done == nrec ? run_plan(plan, nrec) : done;   // report the failing record count
+        }
+        it = e.plan_graphs.emplace(h, gid).first;
+    }
+    return fm_graph_launch(it->second) == 0 ? nrec : 0;
+}
+
+// ---- extensions -----------------------------------------------------------
+
+const char* fm_last_error(void) { return E().last_error.c_str(); }
+
+int fm_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+int fm_set_device(int dev) {
+    LOCK;
+    if (E().ready) return E().device == dev ? 0 : -1;
+    E().device = dev;
+    return 0;
+}
+
+int fm_device_attr(int what) {
+    LOCK;
+    NEED_INIT(-1);
+    int v = 0;
+    switch (what) {
+        case 0: return E().sm_count;
+        case 1: cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, E().device); return v;
+        case 2: return E().device;
+        case 3: { size_t fr = 0, tot = 0; cudaMemGetInfo(&fr, &tot); return (int)(tot >> 20); }
+        case 4: cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, E().device); return v;
+        default: return -1;
+    }
+}
+
+int fm_kernel_count(void) { LOCK; ensure_table(); return (int)E().kernels.size(); }
+const char* fm_kernel_name(int id) {
+    LOCK; ensure_table();
+    return (id >= 0 && id < (int)E().kernels.size()) ? E().kernels[id].name : nullptr;
+}
+int fm_kernel_nargs(int id) {
+    LOCK; ensure_table();
+    return (id >= 0 && id < (int)E().kernels.size()) ? E().kernels[id].nargs : -1;
+}
+const char* fm_kernel_sig(int id) {
+    LOCK; ensure_table();
+    return (id >= 0 && id < (int)E().kernels.size()) ? E().kernels[id].sig : nullptr;
+}
+unsigned long long fm_launch_count(void) { return E().launches; }
+
+void* fm_host_alloc(size_t n) {
+    LOCK;
+    NEED_INIT(nullptr);
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, n ? n : 1, cudaHostAllocDefault) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
+}
+void fm_host_free(void* p) { if (p) cudaFreeHost(p); }
+
+int fm_upload_async(void* dev, const void* host, size_t n) {
+    LOCK;
+    NEED_INIT(-1);
+    if (!range_ok(dev, n)) { set_errorf("fm_upload_async: range exceeds the allocation"); return -1; }
+    cudaError_t err = cudaMemcpyAsync(dev, host, n, cudaMemcpyHostToDevice, E().stream);
+    if (err != cudaSuccess) { cuda_fail("fm_upload_async", err); return -1; }
+    return 0;
+}
+int fm_download_async(void* host, const void* dev, size_t n) {
+    LOCK;
+    NEED_INIT(-1);
+    if (!range_ok(dev, n)) { set_errorf("fm_download_async: range exceeds the allocation"); return -1; }
+    cudaError_t err = cudaMemcpyAsync(host, dev, n, cudaMemcpyDeviceToHost, E().stream);
+    if (err != cudaSuccess) { cuda_fail("fm_download_async", err); return -1; }
+    return 0;
+}
+
+int fm_event_create(void) {
+    LOCK;
+    NEED_INIT(-1);
+    cudaEvent_t ev;
+    if (cudaEventCreate(&ev) != cudaSuccess) { cudaGetLastError(); return -1; }
+    E().events.push_back(ev);
+    return (int)E().events.size() - 1;
+}
+int fm_event_record(int ev) {
+    LOCK;
+    if (ev < 0 || ev >= (int)E().events.size()) return -1;
+    return cudaEventRecord(E().events[ev], E().stream) == cudaSuccess ? 0 : -1;
+}
+float fm_event_elapsed_ms(int a, int b) {
+    LOCK;
+    Engine& e = E();
+    if (a < 0 || b < 0 || a >= (int)e.events.size() || b >= (int)e.events.size()) return -1.f;
+    if (cudaEventSynchronize(e.events[b]) != cudaSuccess) return -1.f;
+    float ms = -1.f;
+    if (cudaEventElapsedTime(&ms, e.events[a], e.events[b]) != cudaSuccess) { cudaGetLastError(); return -1.f; }
+    return ms;
+}
+
+int fm_graph_begin(void) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (e.capturing) { set_errorf("fm_graph_begin: a capture is already open"); return -1; }
+    cudaError_t err = cudaStreamBeginCapture(e.stream, cudaStreamCaptureModeThreadLocal);
+    if (err != cudaSuccess) { cuda_fail("fm_graph_begin", err); return -1; }
+    e.capturing = true;
+    e.launches_at_capture = e.launches;
+    return 0;
+}
+int fm_graph_end(void) {
+    LOCK;
+    Engine& e = E();
+    if (!e.capturing) { set_errorf("fm_graph_end: no capture is open"); return -1; }
+    e.capturing = false;
+    Graph g;
+    g.kernels = e.launches - e.launches_at_capture;   // recorded, not executed yet
+    e.launches = e.launches_at_capture;
+    cudaError_t err = cudaStreamEndCapture(e.stream, &g.graph);
+    if (err != cudaSuccess || !g.graph) { cuda_fail("fm_graph_end", err); cudaGetLastError(); return -1; }
+    err = cudaGraphInstantiate(&g.exec, g.graph, 0);
+    if (err != cudaSuccess) { cudaGraphDestroy(g.graph); cuda_fail("cudaGraphInstantiate", err); return -1; }
+    for (size_t i = 0; i < e.graphs.size(); i++)
+        if (!e.graphs[i].exec) { e.graphs[i] = g; return (int)i; }
+    e.graphs.push_back(g);
+    return (int)e.graphs.size() - 1;
+}
+int fm_graph_launch(int id) {
+    LOCK;
+    Engine& e = E();
+    if (id < 0 || id >= (int)e.graphs.size() || !e.graphs[id].exec) { set_errorf("bad graph id %d", id); return -1; }
+    cudaError_t err = cudaGraphLaunch(e.graphs[id].exec, e.stream);
+    if (err != cudaSuccess) { cuda_fail("fm_graph_launch", err); return -1; }
+    e.launches += e.graphs[id].kernels;
+    return 0;
+}
+int fm_graph_free(int id) {
+    LOCK;
+    Engine& e = E();
+    if (id < 0 || id >= (int)e.graphs.size() || !e.graphs[id].exec) return -1;
+    cudaStreamSynchronize(e.stream);
+    cudaGraphExecDestroy(e.graphs[id].exec);
+    cudaGraphDestroy(e.graphs[id].graph);
+    e.graphs[id] = Graph();
+    return 0;
+}
+
+int fm_comm_unique_id(void* out128) {
+    LOCK;
+    auto f = (nccl_get_uid_t)nccl_sym("ncclGetUniqueId");
+    if (!f) return -1;
+    NcclUniqueId id;
+    const int rc = f(&id);
+    if (rc != 0) { set_errorf("ncclGetUniqueId failed (%d)", rc); return -1; }
+    memcpy(out128, &id, 128);
+    return 0;
+}
+int fm_comm_init(const void* id128, int nranks, int rank) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (e.comm) { set_errorf("communicator already initialised"); return -1; }
+    auto f = (nccl_init_rank_t)nccl_sym("ncclCommInitRank");
+    if (!f) return -1;
+    NcclUniqueId id;
+    memcpy(&id, id128, 128);
+    const int rc = f(&e.comm, nranks, id, rank);
+    if (rc != 0) {
+        auto es = (nccl_errstr_t)nccl_sym("ncclGetErrorString");
+        set_errorf("ncclCommInitRank failed: %s", es ? es(rc) : "?");
+        e.comm = nullptr;
+        return -1;
+    }
+    e.comm_rank = rank;
+    e.comm_size = nranks;
+    return 0;
+}
+int fm_comm_rank(void) { return E().comm_rank; }
+int fm_comm_size(void) { return E().comm_size; }
+int fm_allgather(void* recv, const void* send, size_t bytes) {
+    LOCK;
+    Engine& e = E();
+    if (!e.comm) { set_errorf("fm_allgather: no communicator"); return -1; }
+    if (!range_ok(recv, bytes * e.comm_size) || !range_ok(send, bytes)) {
+        set_errorf("fm_allgather: range exceeds an allocation");
+        return -1;
+    }
+    auto f = (nccl_allgather_t)nccl_sym("ncclAllGather");
+    if (!f) return -1;
+    const int rc = f(send, recv, bytes, /*ncclInt8*/ 0, e.comm, e.stream);
+    if (rc != 0) {
+        auto es = (nccl_errstr_t)nccl_sym("ncclGetErrorString");
+        set_errorf("ncclAllGather failed: %s", es ? es(rc) : "?");
+        return -1;
+    }
+    return 0;
+}
+int fm_comm_destroy(void) {
+    LOCK;
+    Engine& e = E();
+    if (!e.comm) return 0;
+    cudaStreamSynchronize(e.stream);
+    auto f = (nccl_destroy_t)nccl_sym("ncclCommDestroy");
+    if (f) f(e.comm);
+    e.comm = nullptr;
+    e.comm_size = 1;
+    e.comm_rank = 0;
+    return 0;
+}
+
+}  // extern "C"

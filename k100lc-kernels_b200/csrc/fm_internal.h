@@ -1,0 +1,82 @@
+// Internal interfaces between the engine (fm_engine.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace fm {
+
+enum : int { FM_OK = 0, FM_ENOKERNEL = -1, FM_ENARGS = -2, FM_EDYN = -3, FM_EREJECT = -4, FM_ECUDA = -5 };
+
+// What a launcher receives: the caller's geometry (in the reference's units:
+// work-groups and threads per work-group), the engine stream and the device facts.
+struct LaunchCtx {
+    uint32_t gx, gy, wx, wy;
+    cudaStream_t stream;
+    int sm_count;
+};
+
+typedef int (*LaunchFn)(const LaunchCtx& ctx, const uint64_t* argv);
+
+struct KernelEntry {
+    const char* name;     // lookup string, e.g. "gemv_w4a8<1,false,1>"
+    int nargs;            // explicit arguments
+    LaunchFn fn;
+    const char* sig;      // one letter per argument: p = pointer, i = 32-bit int, f = f32
+};
+
+// Provided by the engine -------------------------------------------------
+// true when [p, p+bytes) lies inside one live fm_alloc allocation (or checks are off)
+bool range_ok(const void* p, size_t bytes);
+int reject(const char* kernel, const char* fmt, ...);   // records the message, returns FM_EREJECT
+int cuda_fail(const char* kernel, cudaError_t e);       // records the message, returns FM_ECUDA
+int after_launch(const char* kernel);                   // cudaGetLastError -> FM_OK / FM_ECUDA
+bool pdl_enabled();                                     // programmatic dependent launch on?
+
+// Registries of the kernel files -------------------------------------------
+const KernelEntry* quant_kernels(int* n);
+const KernelEntry* gemv_w4_kernels(int* n);
+const KernelEntry* gemv_nvfp4_kernels(int* n);
+const KernelEntry* int4_dot_kernels(int* n);
+const KernelEntry* gemm_w4_kernels(int* n);
+
+// argv decoding ------------------------------------------------------------
+template <typename T> static inline T* arg_ptr(uint64_t v) { return reinterpret_cast<T*>(static_cast<uintptr_t>(v)); }
+static inline int arg_i32(uint64_t v) { return static_cast<int>(static_cast<uint32_t>(v)); }
+static inline uint32_t arg_u32(uint64_t v) { return static_cast<uint32_t>(v); }
+static inline float arg_f32(uint64_t v) {
+    uint32_t b = static_cast<uint32_t>(v);
+    float f;
+    __builtin_memcpy(&f, &b, 4);
+    return f;
+}
+static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+#define FM_REQUIRE(cond, kernel, ...) \
+    do { if (!(cond)) return ::fm::reject(kernel, __VA_ARGS__); } while (0)
+#define FM_RANGE(ptr, bytes, kernel, what) \
+    do { if (!::fm::range_ok((ptr), (bytes))) \
+        return ::fm::reject(kernel, "%s: %zu bytes at %p are not inside a live fm_alloc allocation", what, (size_t)(bytes), (const void*)(ptr)); } while (0)
+
+// Launch helper: plain launch or, when enabled, with the programmatic-stream-
+// serialization attribute so the kernel may start while its predecessor drains
+// (the kernel itself calls pdl_wait() before touching anything the predecessor wrote).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+}  // namespace fm

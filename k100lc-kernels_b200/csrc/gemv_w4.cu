@@ -1,0 +1,436 @@
+// W4A8 / W4A4 decode GEMV (M = 1..4 tokens): HBM-bound weight streamers.
+//
+//   gemv_w4a8<M,SMEM,R>   reference kernels/gemv_w4a8_core.h:76-219
+//   gemv_w4a4<M>          reference kernels/gemv_w4a4_core.h:48-134
+//   gemv_w4a4_r2_k, gemv_w4a4_r2_m3_k   reference tools/gen_gemv_w4a4_r2.py:48-200
+//
+// Arithmetic (identical integers to the reference, fp32 afterwards):
+//   W4A8: I[n,g]  = sum_{k in 128-group g} w[n,k] * q[m,k]         exact int32
+//         y[m,n]  = sum_g (f16(ws[n,g]) * asc[m,g]) * float(I[n,g])
+//   W4A4: J[n,s]  = sum_{k in 32-sub-group s} w[n,k] * q[m,k]      exact int32
+//         y[m,n]  = sum_s (f16(ws[n,s/4]) * asc[m,s]) * float(J[n,s])
+// The integers are formed as sum(u*q) - 8*sum(q) with u = nibble XOR 8 in [0,15]
+// (two's-complement nibble with its sign bit flipped), four products per dp4a.
+//
+// B200 mapping.  A weight row is K/2 contiguous bytes and rows are contiguous, so a
+// warp streams one row as 16-byte words, lane l taking words l, l+32, ... (512
+// contiguous bytes per warp instruction, read-only path, no L1 allocation).  A
+// 16-byte word holds 32 weights = one int4 sub-group = a quarter of a 128-group,
+// so W4A4 needs no cross-lane traffic for its integers and W4A8 needs two
+// shuffles.  Activations (a few KB) are staged once per CTA in shared memory —
+// W4A4's packed nibbles are sign-extended to int8 there, so both paths run the same
+// dp4a inner loop — or, for one token and K = 5120, held in registers.  CTAs are
+// persistent (a multiple of the SM count) and stride over blocks of R rows; R > 1
+// shares each activation fetch between R weight rows.  The weight loads of the
+// first row block are issued before griddepcontrol.wait, so under programmatic
+// dependent launch they overlap the tail of the activation quantiser.
+#include <cuda_fp16.h>
+
+#include "device_utils.cuh"
+#include "fm_internal.h"
+
+namespace fm {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+struct GemvW4Params {
+    const uint32_t* wq;      // [N][K/8] packed two's-complement nibbles
+    const __half* ws;        // [N][K/128] f16 scales
+    const uint32_t* a0;      // A8: even-k int8 stream [M][K/2] bytes; A4: packed nibbles [M][K/2] bytes
+    const uint32_t* a1;      // A8: odd-k int8 stream; A4: unused
+    const float* asc;        // A8: [M][K/128]; A4: [M][K/32]
+    const int* asu;          // A8: [M][K/128] group sums; A4: unused
+    float* y;                // [M][N]
+    int* iacc;               // optional dump of the integer accumulators, [M][N][K/128 or K/32]
+    int N, K;
+    int rows;                // rows to compute: min(N, rows covered by the caller's grid)
+};
+
+template <bool A4>
+__device__ __forceinline__ void stage_activations(const GemvW4Params& p, int M, uint32_t* s_e, uint32_t* s_o,
+                                                  float* s_sc, int* s_su) {
+    const int KD = p.K >> 3;
+    const int nsc = A4 ? (p.K >> 5) : (p.K >> 7);
+    if (!A4) {
+        for (int i = threadIdx.x; i < M * KD; i += blockDim.x) {
+            s_e[i] = p.a0[i];
+            s_o[i] = p.a1[i];
+        }
+        for (int i = threadIdx.x; i < M * nsc; i += blockDim.x) {
+            s_sc[i] = p.asc[i];
+            s_su[i] = p.asu[i];
+        }
+        __syncthreads();
+    } else {
+        for (int i = threadIdx.x; i < M * KD; i += blockDim.x) {
+            const uint32_t a = p.a0[i];
+            s_e[i] = sext_nibbles(a & 0x0F0F0F0Fu);
+            s_o[i] = sext_nibbles((a >> 4) & 0x0F0F0F0Fu);
+        }
+        for (int i = threadIdx.x; i < M * nsc; i += blockDim.x) s_sc[i] = p.asc[i];
+        __syncthreads();
+        for (int i = threadIdx.x; i < M * nsc; i += blockDim.x) {     // sum of the 32 codes of a sub-group
+            int s = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                s = dot4(s_e[4 * i + j], 0x01010101u, s);
+                s = dot4(s_o[4 * i + j], 0x01010101u, s);
+            }
+            s_su[i] = s;
+        }
+        __syncthreads();
+    }
+}
+
+// sum over 32 weights of (nibble ^ 8) * q for one 16-byte weight word
+__device__ __forceinline__ int dot32(const uint4& w, const uint4& e, const uint4& o) {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    const uint32_t ee[4] = {e.x, e.y, e.z, e.w};
+    const uint32_t oo[4] = {o.x, o.y, o.z, o.w};
+    int v0 = 0, v1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t lo = (ww[i] & 0x0F0F0F0Fu) ^ 0x08080808u;
+        const uint32_t hi = ((ww[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+        v0 = dot4(lo, ee[i], v0);
+        v1 = dot4(hi, oo[i], v1);
+    }
+    return v0 + v1;
+}
+
+// A4     : int4 activations (32-sub-group scales) instead of int8 (128-group scales)
+// M      : tokens
+// R      : weight rows per warp step
+// KITER  : K / 1024 when K is a multiple of 1024 (fully unrolled, no tail), else 0
+// AREG   : hold the activations in registers (needs KITER > 0 and M == 1)
+// DUMP   : also store the integer accumulators
+template <bool A4, int M, int R, int KITER, bool AREG, bool DUMP>
+__global__ void __launch_bounds__(kThreads)
+gemv_w4_kernel(const GemvW4Params p) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    const int KD = p.K >> 3;                     // 32-bit words per weight row
+    const int NG = p.K >> 7;                     // weight-scale groups per row
+    const int nsc = A4 ? (p.K >> 5) : NG;        // activation scales per token
+    uint32_t* s_e = smem;
+    uint32_t* s_o = s_e + M * KD;
+    float* s_sc = reinterpret_cast<float*>(s_o + M * KD);
+    int* s_su = reinterpret_cast<int*>(s_sc + M * nsc);
+
+    const int lane = threadIdx.x & 31;
+    const int gwarp = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int nwarp = gridDim.x * kWarps;
+    const int iters = KITER > 0 ? KITER : (KD + 127) >> 7;
+    constexpr int UN = KITER > 0 ? KITER : 1;
+
+    // -- weights of the first row block: independent of the preceding kernel --
+    uint4 wreg[R][UN];
+    int rb = gwarp;
+    if (KITER > 0) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int row = rb * R + r;
+#pragma unroll
+            for (int it = 0; it < UN; it++)
+                wreg[r][it] = row < p.rows ? ld_stream_v4(p.wq + (size_t)row * KD + it * 128 + lane * 4)
+                                           : make_uint4(0, 0, 0, 0);
+        }
+    }
+
+    pdl_wait();
+    stage_activations<A4>(p, M, s_e, s_o, s_sc, s_su);
+
+    uint4 areg_e[AREG ? UN : 1], areg_o[AREG ? UN : 1];
+    float areg_sc[AREG ? UN : 1];
+    int areg_su[AREG ? UN : 1];
+    if (AREG) {
+#pragma unroll
+        for (int it = 0; it < UN; it++) {
+            const int d0 = it * 128 + lane * 4;
+            areg_e[it] = *reinterpret_cast<const uint4*>(s_e + d0);
+            areg_o[it] = *reinterpret_cast<const uint4*>(s_o + d0);
+            const int si = A4 ? (d0 >> 2) : (d0 >> 4);
+            areg_sc[it] = s_sc[si];
+            areg_su[it] = s_su[si];
+        }
+    }
+
+    for (; rb * R < p.rows; rb += nwarp) {
+        float acc[R][M];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int m = 0; m < M; m++) acc[r][m] = 0.f;
+
+        if (KITER > 0) {
+            // issue the scale loads and, for every block after the first, the weight loads
+            float sw[R][UN];
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int row = min(rb * R + r, p.rows - 1);
+#pragma unroll
+                for (int it = 0; it < UN; it++)
+                    sw[r][it] = __half2float(p.ws[(size_t)row * NG + ((it * 128 + lane * 4) >> 4)]);
+            }
+            if (rb != gwarp) {
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const int row = rb * R + r;
+#pragma unroll
+                    for (int it = 0; it < UN; it++)
+                        wreg[r][it] = row < p.rows ? ld_stream_v4(p.wq + (size_t)row * KD + it * 128 + lane * 4)
+                                                   : make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+            for (int it = 0; it < UN; it++) {
+                const int d0 = it * 128 + lane * 4;
+                const int si = A4 ? (d0 >> 2) : (d0 >> 4);
+#pragma unroll
+                for (int m = 0; m < M; m++) {
+                    const uint4 e4 = AREG ? areg_e[it] : *reinterpret_cast<const uint4*>(s_e + m * KD + d0);
+                    const uint4 o4 = AREG ? areg_o[it] : *reinterpret_cast<const uint4*>(s_o + m * KD + d0);
+                    const float sa = AREG ? areg_sc[it] : s_sc[m * nsc + si];
+                    const int su = AREG ? areg_su[it] : s_su[m * nsc + si];
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        int v = dot32(wreg[r][it], e4, o4);
+                        if (!A4) {
+                            v += __shfl_xor_sync(0xffffffffu, v, 1);
+                            v += __shfl_xor_sync(0xffffffffu, v, 2);
+                        }
+                        const int I = v - 8 * su;
+                        if (A4 || (lane & 3) == 0) {
+                            acc[r][m] += (sw[r][it] * sa) * (float)I;
+                            if (DUMP) {
+                                const int row = rb * R + r;
+                                if (row < p.rows) p.iacc[((size_t)m * p.N + row) * nsc + si] = I;
+                            }
+                        }
+                    }
+                }
+            }
+        } else {
+            for (int it = 0; it < iters; it++) {
+                const int d0 = it * 128 + lane * 4;
+                const bool ok = d0 < KD;                       // KD is a multiple of 4
+                const int dc = ok ? d0 : 0;
+                const int si = A4 ? (dc >> 2) : (dc >> 4);
+                uint4 w4[R];
+                float sw[R];
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const int row = rb * R + r;
+                    const bool live = ok && row < p.rows;
+                    w4[r] = live ? ld_stream_v4(p.wq + (size_t)row * KD + dc) : make_uint4(0, 0, 0, 0);
+                    sw[r] = live ? __half2float(p.ws[(size_t)row * NG + (dc >> 4)]) : 0.f;
+                }
+#pragma unroll
+                for (int m = 0; m < M; m++) {
+                    const uint4 e4 = *reinterpret_cast<const uint4*>(s_e + m * KD + dc);
+                    const uint4 o4 = *reinterpret_cast<const uint4*>(s_o + m * KD + dc);
+                    const float sa = ok ? s_sc[m * nsc + si] : 0.f;
+                    const int su = ok ? s_su[m * nsc + si] : 0;
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        int v = dot32(w4[r], e4, o4);
+                        if (!A4) {
+                            v += __shfl_xor_sync(0xffffffffu, v, 1);
+                            v += __shfl_xor_sync(0xffffffffu, v, 2);
+                        }
+                        const int I = v - 8 * su;
+                        if (ok && (A4 || (lane & 3) == 0)) {
+                            acc[r][m] += (sw[r] * sa) * (float)I;
+                            if (DUMP) {
+                                const int row = rb * R + r;
+                                if (row < p.rows) p.iacc[((size_t)m * p.N + row) * nsc + si] = I;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int row = rb * R + r;
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float v = warp_sum(acc[r][m]);
+                if (lane == 0 && row < p.rows) p.y[(size_t)m * p.N + row] = v;
+            }
+        }
+    }
+    pdl_launch_dependents();
+}
+
+// ------------------------------------------------------------------ host side
+struct Tuning { int ctas_per_sm; };
+
+template <bool A4, int M, int R, int KITER, bool AREG, bool DUMP>
+int run_variant(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
+    auto kern = gemv_w4_kernel<A4, M, R, KITER, AREG, DUMP>;
+    const int KD = p.K / 8;
+    const int nsc = A4 ? p.K / 32 : p.K / 128;
+    const size_t smem = (size_t)M * (2 * KD * 4 + nsc * 8);
+    FM_REQUIRE(smem <= 200 * 1024, kn, "K=%d needs %zu bytes of shared memory for %d tokens (limit 200 KiB)", p.K,
+               smem, M);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+    }
+    const int blocks_needed = (p.rows + R * kWarps - 1) / (R * kWarps);
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
+    if (e != cudaSuccess) return cuda_fail(kn, e);
+    if (per_sm < 1) per_sm = 1;
+    int grid = c.sm_count * per_sm;
+    if (grid > blocks_needed) grid = blocks_needed;
+    e = launch_kernel(kern, dim3(grid), dim3(kThreads), smem, c.stream, pdl_enabled(), p);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
+template <bool A4, int M, bool DUMP>
+int dispatch(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
+    const int kiter = (p.K % 1024 == 0) ? p.K / 1024 : 0;
+    if (DUMP) return run_variant<A4, M, 1, 0, false, true>(kn, c, p);
+    if (M == 1) {
+        if (kiter == 5) return run_variant<A4, 1, 1, 5, true, false>(kn, c, p);
+        return run_variant<A4, 1, 1, 0, false, false>(kn, c, p);
+    }
+    if (kiter == 5) return run_variant<A4, M, 2, 5, false, false>(kn, c, p);
+    return run_variant<A4, M, 2, 0, false, false>(kn, c, p);
+}
+
+// Shared checks.  `rows_per_wg` is what one 256-thread work-group of the reference
+// kernel covers (4 wave64 warps x rows per warp); the launch computes rows
+// [0, min(N, grid * rows_per_wg)) exactly like an over- or under-sized reference grid.
+template <bool A4>
+int check_and_fill(const char* kn, const LaunchCtx& c, GemvW4Params& p, int M, int rows_per_wg, bool dump) {
+    FM_REQUIRE(c.wx == 256 && c.wy == 1 && c.gy == 1, kn,
+               "work-group must be 256x1 threads on a 1-D grid (the row mapping of this kernel family is "
+               "4 warps of 64 per work-group); got %ux%u, grid y=%u", c.wx, c.wy, c.gy);
+    FM_REQUIRE(p.N > 0 && p.K > 0, kn, "N=%d K=%d must be positive", p.N, p.K);
+    FM_REQUIRE(p.K % (A4 ? 32 : 128) == 0, kn, "K=%d must be a multiple of %d", p.K, A4 ? 32 : 128);
+    const long long covered = (long long)c.gx * rows_per_wg;
+    p.rows = (int)(covered < p.N ? covered : p.N);
+    const int NG = p.K / 128, nsc = A4 ? p.K / 32 : NG;
+    FM_REQUIRE(aligned(p.wq, 16) && aligned(p.a0, 16) && aligned(p.ws, 2) && aligned(p.asc, 4) && aligned(p.y, 4) &&
+                   (A4 || (aligned(p.a1, 16) && aligned(p.asu, 4))), kn,
+               "misaligned pointer (weights and activation codes need 16 bytes, scales 2/4)");
+    if (p.rows == 0) return 1;       // nothing to do
+    FM_RANGE(p.wq, (size_t)p.rows * (p.K / 2), kn, "wq");
+    FM_RANGE(p.ws, (size_t)p.rows * NG * 2, kn, "ws");
+    FM_RANGE(p.a0, (size_t)M * (p.K / 2), kn, A4 ? "aq" : "ae");
+    if (!A4) {
+        FM_RANGE(p.a1, (size_t)M * (p.K / 2), kn, "ao");
+        FM_RANGE(p.asu, (size_t)M * NG * 4, kn, "asu");
+    }
+    FM_RANGE(p.asc, (size_t)M * nsc * 4, kn, "asc");
+    FM_RANGE(p.y, ((size_t)(M - 1) * p.N + p.rows) * 4, kn, "y");
+    if (dump) {
+        FM_REQUIRE(aligned(p.iacc, 4), kn, "misaligned accumulator dump");
+        FM_RANGE(p.iacc, (size_t)M * p.N * nsc * 4, kn, "iacc");
+    }
+    return 0;
+}
+
+// gemv_w4a8<M,SMEM,R>(wq, ws, ae, ao, asc, asu, y, N, K)
+template <int M, int RREF>
+int launch_w4a8(const LaunchCtx& c, const uint64_t* a) {
+    static const char* names[5][3] = {{0, 0, 0}, {0, "gemv_w4a8<1,*,1>", 0}, {0, 0, "gemv_w4a8<2,*,2>"},
+                                      {0, 0, "gemv_w4a8<3,*,2>"}, {0, 0, "gemv_w4a8<4,*,2>"}};
+    const char* kn = names[M][RREF];
+    GemvW4Params p = {};
+    p.wq = arg_ptr<const uint32_t>(a[0]);
+    p.ws = arg_ptr<const __half>(a[1]);
+    p.a0 = arg_ptr<const uint32_t>(a[2]);
+    p.a1 = arg_ptr<const uint32_t>(a[3]);
+    p.asc = arg_ptr<const float>(a[4]);
+    p.asu = arg_ptr<const int>(a[5]);
+    p.y = arg_ptr<float>(a[6]);
+    p.N = arg_i32(a[7]);
+    p.K = arg_i32(a[8]);
+    const int rc = check_and_fill<false>(kn, c, p, M, 4 * RREF, false);
+    if (rc) return rc < 0 ? rc : FM_OK;
+    return dispatch<false, M, false>(kn, c, p);
+}
+
+// gemv_w4a4<M>(wq, ws, aq, asc, y, N, K); RREF = 2 for the two-rows-per-warp names
+template <int M, int RREF>
+int launch_w4a4(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = RREF == 2 ? (M == 4 ? "gemv_w4a4_r2_k" : "gemv_w4a4_r2_m3_k") : "gemv_w4a4<M>";
+    GemvW4Params p = {};
+    p.wq = arg_ptr<const uint32_t>(a[0]);
+    p.ws = arg_ptr<const __half>(a[1]);
+    p.a0 = arg_ptr<const uint32_t>(a[2]);
+    p.asc = arg_ptr<const float>(a[3]);
+    p.y = arg_ptr<float>(a[4]);
+    p.N = arg_i32(a[5]);
+    p.K = arg_i32(a[6]);
+    const int rc = check_and_fill<true>(kn, c, p, M, 4 * RREF, false);
+    if (rc) return rc < 0 ? rc : FM_OK;
+    return dispatch<true, M, false>(kn, c, p);
+}
+
+// Accumulator dumps (extensions, used by the parity tests):
+//   gemv_w4a8_iacc(wq, ws, ae, ao, asc, asu, y, N, K, iacc, M)   iacc int32 [M][N][K/128]
+//   gemv_w4a4_iacc(wq, ws, aq, asc, y, N, K, iacc, M)            iacc int32 [M][N][K/32]
+// Same kernel source as the production variants with the store of I switched on.
+template <bool A4>
+int launch_iacc(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = A4 ? "gemv_w4a4_iacc" : "gemv_w4a8_iacc";
+    GemvW4Params p = {};
+    int i = 0;
+    p.wq = arg_ptr<const uint32_t>(a[i++]);
+    p.ws = arg_ptr<const __half>(a[i++]);
+    p.a0 = arg_ptr<const uint32_t>(a[i++]);
+    if (!A4) p.a1 = arg_ptr<const uint32_t>(a[i++]);
+    p.asc = arg_ptr<const float>(a[i++]);
+    if (!A4) p.asu = arg_ptr<const int>(a[i++]);
+    p.y = arg_ptr<float>(a[i++]);
+    p.N = arg_i32(a[i++]);
+    p.K = arg_i32(a[i++]);
+    p.iacc = arg_ptr<int>(a[i++]);
+    const int M = arg_i32(a[i++]);
+    FM_REQUIRE(M >= 1 && M <= 4, kn, "M=%d must be 1..4", M);
+    const int rc = check_and_fill<A4>(kn, c, p, M, 4, true);
+    if (rc) return rc < 0 ? rc : FM_OK;
+    switch (M) {
+        case 1: return dispatch<A4, 1, true>(kn, c, p);
+        case 2: return dispatch<A4, 2, true>(kn, c, p);
+        case 3: return dispatch<A4, 3, true>(kn, c, p);
+        default: return dispatch<A4, 4, true>(kn, c, p);
+    }
+}
+
+const KernelEntry kGemvW4[] = {
+    {"gemv_w4a8<1,false,1>", 9, launch_w4a8<1, 1>, "pppppppii"},
+    {"gemv_w4a8<2,false,2>", 9, launch_w4a8<2, 2>, "pppppppii"},
+    {"gemv_w4a8<3,false,2>", 9, launch_w4a8<3, 2>, "pppppppii"},
+    {"gemv_w4a8<4,false,2>", 9, launch_w4a8<4, 2>, "pppppppii"},
+    // The reference's SMEM=true instantiations differ only in how activations are
+    // fetched; they resolve to the same kernels here.
+    {"gemv_w4a8<1,true,1>", 9, launch_w4a8<1, 1>, "pppppppii"},
+    {"gemv_w4a8<2,true,2>", 9, launch_w4a8<2, 2>, "pppppppii"},
+    {"gemv_w4a8<3,true,2>", 9, launch_w4a8<3, 2>, "pppppppii"},
+    {"gemv_w4a8<4,true,2>", 9, launch_w4a8<4, 2>, "pppppppii"},
+    {"gemv_w4a4<1>", 7, launch_w4a4<1, 1>, "pppppii"},
+    {"gemv_w4a4<2>", 7, launch_w4a4<2, 1>, "pppppii"},
+    {"gemv_w4a4<3>", 7, launch_w4a4<3, 1>, "pppppii"},
+    {"gemv_w4a4<4>", 7, launch_w4a4<4, 1>, "pppppii"},
+    {"gemv_w4a4_r2_k", 7, launch_w4a4<4, 2>, "pppppii"},
+    {"gemv_w4a4_r2_m3_k", 7, launch_w4a4<3, 2>, "pppppii"},
+    {"gemv_w4a8_iacc", 11, launch_iacc<false>, "pppppppiipi"},
+    {"gemv_w4a4_iacc", 9, launch_iacc<true>, "pppppiipi"},
+};
+
+}  // namespace
+
+const KernelEntry* gemv_w4_kernels(int* n) {
+    *n = (int)(sizeof(kGemvW4) / sizeof(kGemvW4[0]));
+    return kGemvW4;
+}
+
+}  // namespace fm

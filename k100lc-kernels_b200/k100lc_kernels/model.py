@@ -1,0 +1,310 @@
+"""Model-level operators for the weight-streaming quantized linear layer.
+
+The classes keep the contract of the reference's python/k100lc_kernels/model.py:
+weights are uploaded once at construction, intermediate buffers come from a
+``Workspace`` keyed by tag, ``forward_device(x_dev, rows, sync=False, out_dev=None)``
+chains device pointers without a host round trip and ``forward(x)`` is NumPy in /
+NumPy out with a single sync (model.py:132-185, 206-310, 358-477).
+
+In scope: ``Workspace``, ``run_sequence``, ``cdiv``, ``div_magic``, ``DotLinear`` for
+the ``int4`` kind, ``RT4Linear``, ``Int4Linear`` and — an addition, the reference only
+reaches NVFP4 through raw launches — ``NVFP4Linear``.  The reference's other operators
+(norms, attention, MoE, RoPE, sampler ...) use kernels outside this path; their names
+are exported so that imports keep working and raise ``NotImplementedError`` when used.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .runtime import LaunchPlan, Runtime  # noqa: F401  (LaunchPlan re-exported like the reference)
+
+__all__ = ["cdiv", "div_magic", "Workspace", "QUANT_SPECS", "DotLinear", "RT4Linear", "Int4Linear",
+           "NVFP4Linear", "run_sequence"]
+
+
+def cdiv(a: int, b: int) -> int:
+    return -(-int(a) // int(b))
+
+
+def div_magic(d: int, max_i: int) -> int:
+    """Multiplier ``M`` with ``(i*M) >> 32 == i // d`` for ``0 <= i < max_i`` (reference
+    model.py:110-129).  ``int4_dot_k`` takes three of them in its argument list."""
+    d, max_i = int(d), int(max_i)
+    if d <= 0:
+        raise ValueError("div_magic: d must be positive")
+    if max_i <= 0:
+        return 0
+    if d == 1:
+        if max_i <= 1:
+            return 0
+        raise ValueError("div_magic: d=1 is only usable when the index is always 0")
+    m = (1 << 32) // d + 1
+    if m >> 32:
+        raise ValueError(f"div_magic: d={d} is too large")
+    i = np.arange(max_i, dtype=np.uint64)
+    if ((i * np.uint64(m)) >> np.uint64(32) != i // np.uint64(d)).any():
+        raise ValueError(f"div_magic: d={d} is not exact below {max_i}")
+    return int(m)
+
+
+class Workspace:
+    """Device buffers re-used by key: ``buffer(key, nbytes)`` returns the same block for
+    the same key and re-allocates only when it has to grow."""
+
+    def __init__(self, rt: Runtime):
+        self.rt = rt
+        self._bufs: dict[str, tuple[int, int]] = {}
+
+    def buffer(self, key: str, nbytes: int) -> int:
+        have = self._bufs.get(key)
+        if have and have[1] >= nbytes:
+            return have[0]
+        if have:
+            self.rt.free(have[0])
+        p = self.rt.alloc(int(nbytes))
+        self._bufs[key] = (p, int(nbytes))
+        return p
+
+    def upload(self, key: str, data) -> int:
+        n = len(data) if isinstance(data, (bytes, bytearray, memoryview)) else data.nbytes
+        p = self.buffer(key, n)
+        self.rt.upload(p, data)
+        return p
+
+    def size(self, key: str) -> int:
+        return self._bufs.get(key, (0, 0))[1]
+
+    def free(self) -> None:
+        for p, _n in self._bufs.values():
+            self.rt.free(p)
+        self._bufs.clear()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.free()
+
+
+def run_sequence(rt: Runtime, ops, x_dev: int, sync: bool = True) -> int:
+    """Queue a chain of device-pointer -> device-pointer operators and sync once."""
+    for op in ops:
+        x_dev = op(x_dev)
+    if sync:
+        rt.sync()
+    return x_dev
+
+
+# weight format -> kernel, block size and table pointers (only the INT4 entry of the
+# reference's table, model.py:189-203, belongs to this path)
+QUANT_SPECS: dict[str, dict] = {
+    "int4": dict(kernel="int4_dot_k", elems=128, block_bytes=64, tables=("scale",)),
+}
+
+
+def _as_rows(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    return x[None, :] if x.ndim == 1 else x
+
+
+class DotLinear:
+    """Native decode-and-dot linear layer (``int4_dot_k`` + ``reduce_blocks_k``): the
+    W4A16 path.  Weights stay in the checkpoint's bytes; ``tables`` is
+    ``(bf16_scale_bytes,)``.  One kernel pair per token row (reference model.py:260-277)."""
+
+    def __init__(self, rt: Runtime, n: int, k: int, kind: str, weight_bytes, tables=(),
+                 ws: Workspace | None = None, tag: str | None = None):
+        if kind not in QUANT_SPECS:
+            raise ValueError(f"unknown weight format {kind!r}; built here: {sorted(QUANT_SPECS)}")
+        spec = QUANT_SPECS[kind]
+        if k % spec["elems"]:
+            raise ValueError(f"{kind}: K={k} is not a multiple of the block size {spec['elems']}")
+        if len(tables) != len(spec["tables"]):
+            raise ValueError(f"{kind} takes {len(spec['tables'])} table(s), got {len(tables)}")
+        self.rt, self.n, self.k, self.kind, self.spec = rt, int(n), int(k), kind, spec
+        self.nbpr = self.k // spec["elems"]
+        self.tag = tag or f"dot_{kind}_{id(self):x}"
+        self._own_ws = ws is None
+        self.ws = ws or Workspace(rt)
+        self.w = self.ws.upload(self.tag + ".w", weight_bytes)
+        self.tables = [self.ws.upload(f"{self.tag}.t{i}", t) for i, t in enumerate(tables)]
+        self.nblocks = self.n * self.nbpr
+        self.partial = self.ws.buffer(self.tag + ".partial", self.nblocks * 4)
+        self.ids = self.ws.upload(self.tag + ".ids", np.arange(self.n, dtype=np.uint32))
+        self.m_nbpr = div_magic(self.nbpr, self.nblocks)
+        self.m_rows = div_magic(self.n, self.n)
+
+    def _argv(self, x_dev, rows_per_exp, magic_rpe, ids, stride, rows_per_w, magic_rpw):
+        return ([self.w, int(x_dev), self.partial, self.nblocks, 64, self.nbpr, self.m_nbpr,
+                 rows_per_exp, magic_rpe] + self.tables + [int(ids), stride, rows_per_w, magic_rpw])
+
+    def forward_device(self, x_dev: int, rows: int, sync: bool = False, out_dev=None) -> int:
+        out = int(out_dev) if out_dev is not None else self.ws.buffer(self.tag + ".out", rows * self.n * 4)
+        stride = self.nbpr * self.spec["block_bytes"]
+        for r in range(rows):
+            self.rt.launch(self.spec["kernel"], cdiv(self.nblocks, 64), 64,
+                           self._argv(int(x_dev) + r * self.k * 4, self.n, self.m_rows, self.ids, stride,
+                                      self.n, self.m_rows))
+            self.rt.launch("reduce_blocks_k", cdiv(self.n, 64), 64,
+                           [self.partial, out + r * self.n * 4, self.n, self.nbpr])
+        if sync:
+            self.rt.sync()
+        return out
+
+    def forward_experts(self, x_dev: int, rows: int, ids_dev: int, stride_bytes: int, rows_per_exp: int,
+                        rows_per_w: int, out_dev=None, sync: bool = False) -> int:
+        """Expert-indexed form: weight group ``ids[row // rows_per_w]``, activation row
+        ``row // rows_per_exp`` (reference model.py:279-298)."""
+        out = int(out_dev) if out_dev is not None else self.ws.buffer(self.tag + ".out", self.n * 4)
+        self.rt.launch(self.spec["kernel"], cdiv(self.nblocks, 64), 64,
+                       self._argv(x_dev, rows_per_exp, div_magic(rows_per_exp, self.n), ids_dev, stride_bytes,
+                                  rows_per_w, div_magic(rows_per_w, self.n)))
+        self.rt.launch("reduce_blocks_k", cdiv(self.n, 64), 64, [self.partial, out, self.n, self.nbpr])
+        if sync:
+            self.rt.sync()
+        return out
+
+    def forward(self, x: np.ndarray, sync: bool = True):
+        x = _as_rows(x)
+        px = self.ws.upload(self.tag + ".x", x)
+        out = self.forward_device(px, x.shape[0], sync=sync)
+        if not sync:
+            return out
+        return self.rt.download(out, x.shape[0] * self.n, np.float32).reshape(x.shape[0], self.n)
+
+
+class RT4Linear:
+    """RT4 INT4 layer already on the device (``wq``, ``ws_scale`` pointers); W4A8 or W4A4
+    decode for M = 1..4 (reference model.py:358-383)."""
+
+    def __init__(self, rt: Runtime, n: int, k: int, wq: int, ws_scale: int, path: str = "w4a8",
+                 runner=None, tag: str | None = None):
+        from .rt4 import W4Runner
+        self.rt, self.n, self.k = rt, int(n), int(k)
+        self.wq, self.ws_scale, self.path = int(wq), int(ws_scale), path
+        self.runner = runner or W4Runner(rt)
+        self.tag = tag or f"rt4_{id(self):x}"
+
+    def forward_device(self, x_dev: int, rows: int, sync: bool = False, out_dev=None) -> int:
+        return self.runner.gemv_device(self.path, self.wq, self.ws_scale, None, self.n, self.k,
+                                       x_dev=x_dev, m=rows, y_dev=out_dev, sync=sync)
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        return self.runner.gemv(self.path, self.wq, self.ws_scale, _as_rows(x), self.n, self.k)
+
+
+class Int4Linear:
+    """compressed-tensors INT4 layer with three paths (reference model.py:386-477):
+
+    ``"w4a16"``  ``int4_dot_k`` on the checkpoint bytes (fp32 activations);
+    ``"w4a8"``   ``quant_act`` + ``gemv_w4a8``;  ``"w4a4"``  ``quant_act4`` + ``gemv_w4a4``.
+
+    For the last two the codes are converted once to RT4's two's-complement nibbles and
+    the bf16 scales to f16 (GEMV) and to group-first f32 (GEMM).  Row counts that are a
+    multiple of 128 go to the prefill GEMM — W4A4 as in the reference, or W4A8 when
+    ``prefill="gemm_a8"`` — and other counts above 4 run the GEMV in chunks of 4."""
+
+    def __init__(self, rt: Runtime, n: int, k: int, packed: bytes, scales_bf16: bytes, path: str = "w4a8",
+                 ws: Workspace | None = None, tag: str | None = None, runner=None, prefill: str = "gemm"):
+        from .quant import ct_int4_to_rt4, int4_scale_group_first_f32
+        if path not in ("w4a16", "w4a8", "w4a4"):
+            raise ValueError('path must be "w4a16", "w4a8" or "w4a4"')
+        if prefill not in ("gemm", "gemm_a8", "gemv"):
+            raise ValueError('prefill must be "gemm", "gemm_a8" or "gemv"')
+        self.rt, self.n, self.k, self.path, self.prefill = rt, int(n), int(k), path, prefill
+        self.tag = tag or f"int4_{path}_{id(self):x}"
+        self._own_ws = ws is None
+        self.ws = ws or Workspace(rt)
+        self._dot = self._runner = None
+        if path == "w4a16":
+            self._dot = DotLinear(rt, n, k, "int4", packed, (scales_bf16,), self.ws, self.tag)
+            return
+        from .rt4 import W4Runner
+        q, s16 = ct_int4_to_rt4(packed, scales_bf16)
+        self.wq = self.ws.upload(self.tag + ".wq", q)
+        self.ws_f16 = self.ws.upload(self.tag + ".ws", s16)
+        self.wsc_gm = self.ws.upload(self.tag + ".wsc", int4_scale_group_first_f32(scales_bf16, self.n, self.k))
+        self._runner = runner or W4Runner(rt)
+
+    def forward_device(self, x_dev: int, rows: int, sync: bool = False, out_dev=None) -> int:
+        if self._dot is not None:
+            return self._dot.forward_device(x_dev, rows, sync=sync, out_dev=out_dev)
+        y = int(out_dev) if out_dev is not None else self.ws.buffer(self.tag + ".y", rows * self.n * 4)
+        run = self._runner
+        if rows <= 4:
+            return run.gemv_device(self.path, self.wq, self.ws_f16, None, self.n, self.k,
+                                   x_dev=x_dev, y_dev=y, m=rows, sync=sync)
+        if rows % 128 == 0 and self.n % 64 == 0 and self.prefill != "gemv":
+            return run.gemm_device(self.wq, self.wsc_gm, None, self.n, self.k, x_dev=x_dev, c_dev=y, m=rows,
+                                   sync=sync, kind="w4a8" if self.prefill == "gemm_a8" else "w4a4")
+        for r0 in range(0, rows, 4):
+            run.gemv_device(self.path, self.wq, self.ws_f16, None, self.n, self.k,
+                            x_dev=int(x_dev) + r0 * self.k * 4, y_dev=y + r0 * self.n * 4,
+                            m=min(4, rows - r0), sync=False)
+        if sync:
+            self.rt.sync()
+        return y
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = _as_rows(x)
+        px = self.ws.upload(self.tag + ".x", x)
+        out = self.forward_device(px, x.shape[0], sync=True)
+        return self.rt.download(out, x.shape[0] * self.n, np.float32).reshape(x.shape[0], self.n)
+
+
+class NVFP4Linear:
+    """NVFP4 layer: E2M1 codes ``[N,K/8]`` u32, E4M3 block scales ``[N,K/16]`` u8 and an
+    f32 global scale; activations are quantised to int8 per 16-block by
+    ``nvfp4_quant_act`` and multiplied by ``nvfp4_gemv<M,1>``.  The reference offers this
+    path only as raw launches (docs/KERNEL_CALLING.md:637-646); the class follows the
+    contract of ``Int4Linear``.  Row counts above 4 run in chunks of 4."""
+
+    def __init__(self, rt: Runtime, n: int, k: int, codes, block_scales, gscale: float,
+                 ws: Workspace | None = None, tag: str | None = None):
+        if k % 32:
+            raise ValueError(f"NVFP4 needs K to be a multiple of 32 (got {k})")
+        self.rt, self.n, self.k, self.gscale = rt, int(n), int(k), float(gscale)
+        self.tag = tag or f"nvfp4_{id(self):x}"
+        self._own_ws = ws is None
+        self.ws = ws or Workspace(rt)
+        self.wq = self.ws.upload(self.tag + ".wq", codes)
+        self.wsb = self.ws.upload(self.tag + ".ws", block_scales)
+
+    def _chunk(self, x_dev: int, m: int, y: int) -> None:
+        k, half, nb4 = self.k, self.k // 2, (self.k // 16) * 4
+        qa = self.ws.buffer(self.tag + ".qa", 4 * half)
+        qb = self.ws.buffer(self.tag + ".qb", 4 * half)
+        sc = self.ws.buffer(self.tag + ".sc", 4 * nb4)
+        for r in range(m):
+            self.rt.launch("nvfp4_quant_act", k // 16, 64,
+                           [int(x_dev) + r * k * 4, qa + r * half, qb + r * half, sc + r * nb4, 1, k])
+        self.rt.launch(f"nvfp4_gemv<{m},1>", cdiv(self.n, 4), 256,
+                       [self.wq, self.wsb, qa, qb, sc, y, self.n, k, self.gscale])
+
+    def forward_device(self, x_dev: int, rows: int, sync: bool = False, out_dev=None) -> int:
+        y = int(out_dev) if out_dev is not None else self.ws.buffer(self.tag + ".y", rows * self.n * 4)
+        for r0 in range(0, rows, 4):
+            self._chunk(int(x_dev) + r0 * self.k * 4, min(4, rows - r0), y + r0 * self.n * 4)
+        if sync:
+            self.rt.sync()
+        return y
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = _as_rows(x)
+        px = self.ws.upload(self.tag + ".x", x)
+        out = self.forward_device(px, x.shape[0], sync=True)
+        return self.rt.download(out, x.shape[0] * self.n, np.float32).reshape(x.shape[0], self.n)
+
+
+def _out_of_scope(name: str):
+    def __init__(self, *a, **kw):
+        raise NotImplementedError(
+            f"{name} belongs to the reference's norm/attention/MoE operators, which are outside the "
+            "weight-streaming quantized linear-layer path built here")
+    return type(name, (), {"__init__": __init__, "__doc__": f"Not built (outside the linear-layer path): {name}."})
+
+
+for _n in ("F32Linear", "RMSNorm", "SwiGLU", "MLP", "MoECombine", "MoEExperts", "RoPE", "KVCache", "Sampler",
+           "Attention", "FlashAttention", "TransformerLayer"):
+    globals()[_n] = _out_of_scope(_n)
+    __all__.append(_n)

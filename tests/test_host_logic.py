@@ -1,0 +1,168 @@
+"""CPU tier: host-side code of the package (no device): packers and converters against
+the reference vectors, the catalog against the library's kernel table, every symbol of
+include/fm_engine.h exported by the library, seeded generators, RT4 container round
+trip, plan packing and argument validation."""
+from __future__ import annotations
+
+import ctypes
+import json
+import pathlib
+import re
+
+import numpy as np
+import pytest
+
+import cases
+import w4_oracle as O
+from k100lc_kernels import catalog, quant, synth
+from k100lc_kernels.model import cdiv, div_magic
+from k100lc_kernels.rt4 import RT4File, _div_magic
+from k100lc_kernels.runtime import DEFAULT_LIB, _bits, load_library
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def test_host_quant_matches_reference(golden):
+    arr, meta = golden
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal((16, 256)) * 0.05).astype(np.float32)
+    assert meta["host_quant"]["inputs_sha256"] == cases.digest(w)
+    pk, sc = quant.pack_int4_group128(w)
+    assert np.array_equal(np.frombuffer(pk, np.uint8), arr["host_quant.packed"])
+    assert np.array_equal(np.frombuffer(sc, np.uint8), arr["host_quant.scales"])
+    assert np.array_equal(quant.dequant_int4_group128(pk, sc, 16, 256), arr["host_quant.dequant"])
+    q2, s2 = quant.ct_int4_to_rt4(pk, sc)
+    assert np.array_equal(np.frombuffer(q2, np.uint8), arr["host_quant.rt4_q"])
+    assert np.array_equal(np.frombuffer(s2, np.uint8), arr["host_quant.rt4_s"])
+    assert np.array_equal(quant.int4_scale_group_first_f32(sc, 16, 256), arr["host_quant.gf"])
+    # two's-complement conversion is value-preserving
+    vals = O.int4_offset(np.frombuffer(pk, np.uint32).reshape(16, -1))
+    assert np.array_equal(O.int4_twos(np.frombuffer(q2, np.uint32).reshape(16, -1)), vals)
+    with pytest.raises(ValueError):
+        quant.pack_int4_group128(np.zeros((4, 100), np.float32))
+
+
+def test_nibble_and_fp_helpers():
+    rng = np.random.default_rng(0)
+    v = rng.integers(-8, 8, size=(5, 64))
+    assert np.array_equal(quant.pack_nibbles(v), O.pack_nibbles(v))
+    assert np.array_equal(quant.unpack_nibbles(quant.pack_nibbles(v)), (v & 0xF).astype(np.uint8))
+    x = rng.standard_normal(4096).astype(np.float32)
+    b = quant.f32_to_bf16_bits(x)
+    assert np.abs(quant.bf16_bits_to_f32(b) / x - 1).max() < 2 ** -8
+    assert np.array_equal(quant.e4m3_values().view(np.uint32), O.e4m3_decode(np.arange(256, dtype=np.uint8)).view(np.uint32))
+    e = quant.f32_to_e4m3_bits(np.array([0.0625, 1.0, 1.0625, 3.9, 1000.0], np.float32))
+    assert list(e) == [0x18, 0x38, 0x38, 0x48, 0x7E]      # tie 1.0625 -> even code, 1000 saturates at 448
+
+
+def test_div_magic():
+    for d, lim in ((40, 696320), (272, 4352), (17408, 17408), (3, 1000)):
+        m = div_magic(d, lim) if d > 1 else 0
+        i = np.arange(lim, dtype=np.uint64)
+        assert np.array_equal((i * np.uint64(m)) >> np.uint64(32), i // np.uint64(d))
+    assert _div_magic(272, 4352) == div_magic(272, 4352)
+    assert div_magic(1, 1) == 0 and cdiv(7, 4) == 2
+    with pytest.raises(ValueError):
+        div_magic(1, 5)
+    with pytest.raises(ValueError):
+        _div_magic(1, 5)
+
+
+def test_catalog_matches_library():
+    """catalog.json is generated from the library's kernel table; they must not drift
+    (the reference gates the same way: tools/check_all.sh:39-45)."""
+    fresh = catalog.make_catalog()
+    assert fresh == json.loads(catalog.CATALOG.read_text())
+    names = [k["lookup"] for k in catalog.kernels()]
+    for need in ("quant_act", "quant_act4", "nvfp4_quant_act", "quant_rows_fast_k", "quant_rows_k",
+                 "gemv_w4a8<1,false,1>", "gemv_w4a8<4,false,2>", "gemv_w4a4<3>", "gemv_w4a4_r2_k",
+                 "gemv_w4a4_r2_m3_k", "nvfp4_gemv<2,1>", "nvfp4_gemv_wide<4,2>", "int4_dot_k",
+                 "reduce_blocks_k", "int4_dequant_k"):
+        assert need in names, need
+    k = catalog.info("int4_dot_k")
+    assert len(k["args"]) == 14 and k["kernarg_size"] == 80          # as in the reference catalog
+    k = catalog.info("gemv_w4a8<1,false,1>")
+    assert [a["off"] for a in k["args"]] == [0, 8, 16, 24, 32, 40, 48, 56, 60]
+    with pytest.raises(KeyError):
+        catalog.info("nope")
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "fm_engine.h").read_text()
+    declared = sorted(set(re.findall(r"\b(fm_[a-z0-9_]+)\s*\(", header)))
+    assert len(declared) >= 35
+    lib = ctypes.CDLL(str(DEFAULT_LIB))
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/fm_engine.h but not exported"
+    lib = load_library()
+    assert lib.fm_has_kernel(b"quant_act") == 1 and lib.fm_has_kernel(b"nope") == 0
+    assert lib.fm_kernel_id(b"nope") == -1
+    kid = lib.fm_kernel_id(b"gemv_w4a4<1>")
+    assert lib.fm_kernel_name(kid) == b"gemv_w4a4<1>" and lib.fm_kernel_nargs(kid) == 7
+    # argument validation that needs no device
+    layout = (ctypes.c_uint32 * 6)(0, 8, 0, 8, 4, 0)
+    argv = (ctypes.c_uint64 * 2)()
+    assert lib.fm_launch_dyn(b"quant_act", 1, 1, 32, 1, layout, 2, 0, 0, 2048, argv, 2) == -3
+    assert lib.fm_launch_dyn(b"quant_act", 1, 1, 32, 1, layout, 2, 0, 0, 64, argv, 1) == -2
+
+
+def test_argv_bit_packing():
+    assert _bits(1.0) == 0x3F800000 and _bits(np.float32(-2.0)) == 0xC0000000
+    assert _bits(np.int32(7)) == 7 and _bits(2 ** 40 + 5) == 2 ** 40 + 5
+
+
+def test_synth_is_deterministic_and_distributed_as_stated():
+    a, b = synth.rt4_layer(64, 1024, 2, seed=1), synth.rt4_layer(64, 1024, 2, seed=1)
+    assert all(np.array_equal(a[k], b[k]) for k in ("wq", "ws", "x"))
+    assert a["w"].min() == -8 and a["w"].max() == 7 and a["ws"].dtype == np.float16
+    assert np.array_equal(O.int4_twos(a["wq"]), a["w"])
+    c = synth.w4a16_layer(32, 512, seed=0)
+    assert np.array_equal(O.int4_offset(c["packed"]), c["w"]) and c["scale_bf16"].dtype == np.uint16
+    f = synth.nvfp4_layer(32, 512, 1, seed=2)
+    dec = quant.e4m3_values()[f["ws"]]
+    assert dec.min() >= 2 ** -4 * 0.9 and dec.max() <= 4.0 and not (f["ws"] == 0x7F).any()
+    g = synth.gemm_layer(64, 256, 128, seed=3)
+    assert g["wsc_gf"].shape == (2, 64) and g["x"].shape == (128, 256)
+    # stream blocks: the 8 row blocks of a layer are independent and reproducible
+    b0, b0b, b1 = (synth.stream_layer_block(3, 0, 64, 256), synth.stream_layer_block(3, 0, 64, 256),
+                   synth.stream_layer_block(3, 1, 64, 256))
+    assert np.array_equal(b0["wq"], b0b["wq"]) and not np.array_equal(b0["wq"], b1["wq"])
+    assert b0["wq"].shape == (8, 128) and b0["ws"].shape == (8, 2)
+    assert not np.array_equal(synth.stream_layer_x(0, 256), synth.stream_layer_x(1, 256))
+
+
+def test_rt4_file_roundtrip(tmp_path):
+    """Write a two-tensor RT4 container and read it back through RT4File."""
+    L = synth.rt4_layer(16, 256, 1, seed=9)
+    q, s = L["wq"].tobytes(), L["ws"].tobytes()
+    blob = q + s + b"\0" * 7
+    (tmp_path / "m.rt4").write_bytes(blob)
+    man = {"format": "RT4-v1", "group": 128, "tensors": [
+        {"name": "l0.w", "kind": "i4", "shape": [16, 256], "group": 128, "q_off": 0, "s_off": len(q),
+         "nbytes": len(q) + len(s)},
+        {"name": "l0.norm", "kind": "f32", "shape": [1, 256], "q_off": 0, "s_off": 0, "nbytes": 0}]}
+    (tmp_path / "m.rt4.json").write_text(json.dumps(man))
+    with RT4File(tmp_path / "m.rt4") as f:
+        assert f.names("i4") == ["l0.w"] and len(f.names()) == 2
+        t = f.tensor("l0.w")
+        assert (t.rows, t.cols, t.q_bytes, t.s_bytes) == (16, 256, 2048, 64)
+        assert f.weight_bytes(t) == (q, s)
+        want = L["w"].reshape(16, 2, 128).astype(np.float32) * L["ws"].astype(np.float32)[:, :, None]
+        assert np.array_equal(f.dequant(t), want.reshape(16, 256))
+        assert np.array_equal(f.dequant(t, rows=3, start=5), want.reshape(16, 256)[5:8])
+        with pytest.raises(ValueError):
+            f.weight_bytes(f.tensor("l0.norm"))
+        with pytest.raises(KeyError):
+            f.tensor("missing")
+    with pytest.raises(ValueError):
+        RT4File(tmp_path / "m.bin")
+    (tmp_path / "bad.rt4").write_bytes(b"x")
+    with pytest.raises(FileNotFoundError):
+        RT4File(tmp_path / "bad.rt4")
+
+
+def test_out_of_scope_operators_say_so():
+    import k100lc_kernels as kk
+    for name in ("RMSNorm", "Attention", "MoEExperts", "Sampler"):
+        with pytest.raises(NotImplementedError):
+            getattr(kk, name)()
