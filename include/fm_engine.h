@@ -90,6 +90,14 @@ void  fm_host_free(void* p);
 int   fm_upload_async(void* dev, const void* pinned_host, size_t n);
 int   fm_download_async(void* pinned_host, const void* dev, size_t n);
 
+/* Layer table of the fused decode stream ("w4a8_decode_stream"): host_layers holds
+ * nlayers x {wq, ws, x, y} device addresses.  Every address is checked against the live
+ * allocations for the footprint that (rows, K, row_base) implies — wq rows*K/2 bytes,
+ * ws rows*(K/128)*2, x K*4, y (row_base+rows)*4 — then the table is copied to dev_table
+ * (nlayers*32 bytes) and remembered as validated until something overwrites it.
+ * 0 ok, -4 a pointer fails the check, -1 other errors. */
+int   fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, int rows, int K, int row_base);
+
 /* device timers on the engine stream */
 int   fm_event_create(void);
 int   fm_event_record(int ev);

@@ -1,0 +1,301 @@
+// w4a8_decode_stream: one launch for the GEMVs of a whole stack of independent W4A8
+// decode layers (M = 1), software-pipelined across layers so that HBM never idles at a
+// layer boundary.  The activation codes of all layers come from one 2-D launch of the
+// ordinary quant_act kernel (grid y = layer) that precedes it.
+//
+// The reference streams its 400-layer decode benchmark as 800 back-to-back launches on
+// one in-order queue (tools/bench_decode.py:272-317).  On B200 one 17408 x 5120 layer is
+// ~6.5 us of HBM time, the same order as a kernel's launch, ramp-up and drain, so the
+// per-layer launches (which stay available by name) leave a quarter of the bandwidth
+// unused.  This kernel keeps the arithmetic of gemv_w4a8 (reference
+// kernels/gemv_w4a8_core.h:76-219) — identical int32 group accumulators, fp32 afterwards
+// — and changes only the schedule:
+//   * persistent grid, one CTA per SM; CTA c owns the contiguous rows
+//     [c*rows/G, (c+1)*rows/G) of EVERY layer, so its weight bytes are contiguous;
+//   * the last warp (one elected lane) is the producer: it walks layers and row chunks
+//     and issues 1-D bulk async copies (cp.async.bulk, no multicast) of CW rows of packed
+//     weights plus their f16 scales into a shared-memory ring, completion counted on an
+//     mbarrier per stage; once per layer it also copies that layer's int8 codes, scales
+//     and group sums (5.4 KB) into a double-buffered tile;
+//   * warps 0..CW-1 are consumers: warp w takes row w of a stage, lane l the 16-byte
+//     words l, l+32, .. of that row (LDS.128) into registers and releases the stage at
+//     once; then nibbles -> dp4a against the token's codes held in registers, two
+//     shuffles per 128-group, f16 scale * act scale * float(I), butterfly, lane 0 stores y.
+// Every wait on an mbarrier is bounded; a wait that runs out sets *status and the
+// thread leaves the kernel.
+//
+// Layers must be independent of each other (no layer reads another layer's y): the
+// kernel orders nothing between layers.
+#include <cuda_fp16.h>
+#include <stdlib.h>
+
+#include "device_utils.cuh"
+#include "fm_internal.h"
+
+namespace fm {
+namespace {
+
+constexpr int kSpinLimit = 1 << 22;
+
+struct StreamLayer {                   // one entry of the device-side layer table (32 bytes)
+    const uint8_t* wq;                 // [rows][K/2] packed two's-complement nibbles
+    const uint8_t* ws;                 // [rows][K/128] f16
+    const float* x;                    // [K] fp32 activations of this layer
+    float* y;                          // [>= row_base + rows] fp32 output of this layer
+};
+
+struct StreamParams {
+    const StreamLayer* layers;
+    const uint8_t *ae, *ao, *asc, *asu;   // quant_act outputs of all layers: [nlayers][K/2], .., [nlayers][K/128]
+    int nlayers, rows, K, row_base;
+    int npeers;                        // additional GPUs that receive y (0 on one GPU)
+    const long long* peer_delta;       // [npeers] byte offset from a local y address to the peer's copy
+    int* status;                       // 0 ok, else first failure code
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false (and *status = code) when the limit runs out
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, int code) {
+    for (int i = 0; i < kSpinLimit; i++)
+        if (mbar_try_wait(b, parity)) return true;
+    atomicCAS(status, 0, code);
+    return false;
+}
+// 1-D bulk async copy global -> this CTA's shared memory (no multicast)
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// KITER: K = KITER * 1024.  CW: consumer warps = weight rows per ring stage.  STAGES: ring depth.
+// Warp roles: 0..CW-1 consumers, CW producer (one lane).
+template <int KITER, int CW, int STAGES>
+__global__ void __launch_bounds__((CW + 1) * 32, 1)
+w4a8_stream_kernel(const StreamParams p) {
+    constexpr int K = KITER * 1024, NG = K / 128;
+    constexpr int ROWB = K / 2, SCB = NG * 2;
+    constexpr int STAGE_W = CW * ROWB, STAGE = STAGE_W + CW * SCB;
+    constexpr int ACT = K + NG * 8;                     // even codes, odd codes, scales, sums
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);      // [STAGES] weights landed
+    uint64_t* empty = full + STAGES;                          // [STAGES] weights copied to registers
+    uint64_t* act_ready = empty + STAGES;                     // [2] codes of a layer are in shared memory
+    uint64_t* act_free = act_ready + 2;                       // [2] every consumer has its register copy
+    uint8_t* ring = smem + 256;
+    uint8_t* act = ring + (size_t)STAGES * STAGE;             // [2][ACT]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CW);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&act_ready[b], 1);
+            mbar_init(&act_free[b], CW);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();                                          // the codes come from the preceding quant_act
+
+    const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const int nst = (r1 - r0 + CW - 1) / CW;             // stages per layer for this CTA
+
+    if (warp == CW) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            auto copy_codes = [&](int l) -> bool {       // layer l's codes -> act[l & 1]
+                const int b = l & 1;
+                if (l >= 2 && !mbar_wait(&act_free[b], ((l >> 1) & 1) ^ 1, p.status, 4)) return false;
+                uint8_t* ab = act + (size_t)b * ACT;
+                mbar_expect_tx(&act_ready[b], ACT);
+                bulk_g2s(ab, p.ae + (size_t)l * (K / 2), K / 2, &act_ready[b]);
+                bulk_g2s(ab + K / 2, p.ao + (size_t)l * (K / 2), K / 2, &act_ready[b]);
+                bulk_g2s(ab + K, p.asc + (size_t)l * (NG * 4), NG * 4, &act_ready[b]);
+                bulk_g2s(ab + K + NG * 4, p.asu + (size_t)l * (NG * 4), NG * 4, &act_ready[b]);
+                return true;
+            };
+            int c = 0;
+            const uint8_t* wq = p.layers[0].wq;
+            const uint8_t* ws = p.layers[0].ws;
+            if (!copy_codes(0)) return;
+            for (int l = 0; l < p.nlayers; l++) {
+                // next layer's addresses and codes are fetched while this layer's weights stream
+                const int ln = min(l + 1, p.nlayers - 1);
+                const uint8_t* wq_n = p.layers[ln].wq;
+                const uint8_t* ws_n = p.layers[ln].ws;
+                for (int j = 0; j < nst; j++, c++) {
+                    const int s = c % STAGES;
+                    if (c >= STAGES && !mbar_wait(&empty[s], ((c / STAGES) & 1) ^ 1, p.status, 1)) return;
+                    const int row = r0 + j * CW;
+                    const int nr = min(CW, r1 - row);
+                    uint8_t* dst = ring + (size_t)s * STAGE;
+                    mbar_expect_tx(&full[s], (uint32_t)(nr * (ROWB + SCB)));
+                    bulk_g2s(dst, wq + (size_t)row * ROWB, (uint32_t)(nr * ROWB), &full[s]);
+                    bulk_g2s(dst + STAGE_W, ws + (size_t)row * SCB, (uint32_t)(nr * SCB), &full[s]);
+                    if (j == 0 && l + 1 < p.nlayers && !copy_codes(l + 1)) return;
+                }
+                wq = wq_n;
+                ws = ws_n;
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    int c = 0;
+    for (int l = 0; l < p.nlayers; l++) {
+        const uint8_t* ab = act + (size_t)(l & 1) * ACT;
+        if (!mbar_wait(&act_ready[l & 1], (l >> 1) & 1, p.status, 2)) return;
+        // register copy of the token's codes for this lane's words
+        uint4 ae[KITER], ao[KITER];
+        float asc[KITER];
+        int asu8[KITER];
+#pragma unroll
+        for (int it = 0; it < KITER; it++) {
+            const int d0 = it * 128 + lane * 4;
+            ae[it] = *reinterpret_cast<const uint4*>(ab + d0 * 4);
+            ao[it] = *reinterpret_cast<const uint4*>(ab + K / 2 + d0 * 4);
+            asc[it] = *reinterpret_cast<const float*>(ab + K + (d0 >> 4) * 4);
+            asu8[it] = 8 * *reinterpret_cast<const int*>(ab + K + NG * 4 + (d0 >> 4) * 4);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&act_free[l & 1]);
+        float* y = p.layers[l].y + p.row_base;
+
+        for (int j = 0; j < nst; j++, c++) {
+            const int s = c % STAGES;
+            if (!mbar_wait(&full[s], (c / STAGES) & 1, p.status, 3)) return;
+            const int row = r0 + j * CW + warp;
+            const bool live = row < r1;
+            const uint8_t* st = ring + (size_t)s * STAGE;
+            const uint4* wrow = reinterpret_cast<const uint4*>(st + (size_t)warp * ROWB);
+            const __half* srow = reinterpret_cast<const __half*>(st + STAGE_W + (size_t)warp * SCB);
+            uint4 w[KITER];
+            float sw[KITER];
+#pragma unroll
+            for (int it = 0; it < KITER; it++) {
+                w[it] = live ? wrow[it * 32 + lane] : make_uint4(0, 0, 0, 0);
+                sw[it] = live ? __half2float(srow[(it * 128 + lane * 4) >> 4]) : 0.f;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);          // the stage may be refilled while we compute
+            float acc = 0.f;
+#pragma unroll
+            for (int it = 0; it < KITER; it++) {
+                int v = dot32_u(w[it], ae[it], ao[it]);
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                if ((lane & 3) == 0) acc += (sw[it] * asc[it]) * (float)(v - asu8[it]);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0 && live) {
+                y[row] = acc;
+                for (int q = 0; q < p.npeers; q++)           // all-gather by direct peer stores
+                    *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
+            }
+        }
+    }
+}
+
+template <int KITER, int CW, int STAGES>
+int run_stream(const char* kn, const LaunchCtx& c, const StreamParams& p) {
+    constexpr int K = KITER * 1024;
+    constexpr size_t smem = 256 + (size_t)STAGES * CW * (K / 2 + (K / 128) * 2) + 2 * (K + (K / 128) * 8);
+    static_assert(smem <= 227 * 1024, "shared memory");
+    auto kern = w4a8_stream_kernel<KITER, CW, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        configured = true;
+    }
+    int grid = c.sm_count;
+    if (grid > p.rows) grid = p.rows;
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3((CW + 1) * 32), smem, c.stream, pdl_enabled(), p);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
+// w4a8_decode_stream(layers, nlayers, rows, K, row_base, npeers, peer_delta, status, ae, ao, asc, asu)
+//   layers      device array of nlayers x {wq, ws, x, y} pointers (32 bytes each), filled by
+//               fm_stream_table (which range-checks every pointer in it)
+//   rows        weight rows held by this GPU (N, or N / number of GPUs)
+//   row_base    first output index of this GPU's rows inside each layer's y
+//   npeers      0, or the number of other GPUs whose y copies also receive the rows;
+//   peer_delta  device array of npeers signed byte offsets (peer y address - local y address)
+//   status      device int, must be 0 before the launch; non-zero afterwards = a bounded
+//               wait ran out (1 producer/ring, 2 codes not landed, 3 consumer/ring, 4 code tile not free)
+//   ae, ao, asc, asu   outputs of quant_act launched with grid y = nlayers over x [nlayers][K]:
+//               int8 codes [nlayers][K/2] twice, f32 scales and int32 sums [nlayers][K/128]
+// grid and work-group arguments are ignored (persistent: one CTA per SM).
+int launch_w4a8_stream(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = "w4a8_decode_stream";
+    StreamParams p = {};
+    p.layers = arg_ptr<const StreamLayer>(a[0]);
+    p.nlayers = arg_i32(a[1]);
+    p.rows = arg_i32(a[2]);
+    p.K = arg_i32(a[3]);
+    p.row_base = arg_i32(a[4]);
+    p.npeers = arg_i32(a[5]);
+    p.peer_delta = arg_ptr<const long long>(a[6]);
+    p.status = arg_ptr<int>(a[7]);
+    p.ae = arg_ptr<const uint8_t>(a[8]);
+    p.ao = arg_ptr<const uint8_t>(a[9]);
+    p.asc = arg_ptr<const uint8_t>(a[10]);
+    p.asu = arg_ptr<const uint8_t>(a[11]);
+    FM_REQUIRE(p.K == 5120, kn, "K=%d: the fused stream is built for K = 5120 only; launch the per-layer kernels", p.K);
+    FM_REQUIRE(p.nlayers >= 0 && p.rows > 0 && p.row_base >= 0 && p.npeers >= 0 && p.npeers <= 7, kn,
+               "bad nlayers/rows/row_base/npeers");
+    if (p.nlayers == 0) return FM_OK;
+    FM_REQUIRE(aligned(p.layers, 8) && aligned(p.status, 4), kn, "misaligned layer table or status");
+    FM_RANGE(p.layers, (size_t)p.nlayers * sizeof(StreamLayer), kn, "layers");
+    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, p.row_base), kn,
+               "the layer table at %p was not filled by fm_stream_table for nlayers=%d rows=%d K=%d row_base=%d "
+               "(or was overwritten since)", (const void*)p.layers, p.nlayers, p.rows, p.K, p.row_base);
+    FM_RANGE(p.status, 4, kn, "status");
+    if (p.npeers) FM_RANGE(p.peer_delta, (size_t)p.npeers * 8, kn, "peer_delta");
+    FM_REQUIRE(aligned(p.ae, 16) && aligned(p.ao, 16) && aligned(p.asc, 16) && aligned(p.asu, 16), kn,
+               "the activation code arrays must be 16-byte aligned");
+    FM_RANGE(p.ae, (size_t)p.nlayers * (p.K / 2), kn, "ae");
+    FM_RANGE(p.ao, (size_t)p.nlayers * (p.K / 2), kn, "ao");
+    FM_RANGE(p.asc, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asc");
+    FM_RANGE(p.asu, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asu");
+    // ring geometry: $FM_STREAM_CFG picks one of the built shapes (consumer warps x stages)
+    static const int cfg = getenv("FM_STREAM_CFG") ? atoi(getenv("FM_STREAM_CFG")) : 0;
+    switch (cfg) {
+        case 1: return run_stream<5, 16, 4>(kn, c, p);
+        case 2: return run_stream<5, 12, 6>(kn, c, p);
+        case 3: return run_stream<5, 20, 4>(kn, c, p);
+        default: return run_stream<5, 16, 5>(kn, c, p);      // 16 rows x 5 stages = 211 KB in flight per SM
+    }
+}
+
+const KernelEntry kStream[] = {
+    {"w4a8_decode_stream", 12, launch_w4a8_stream, "piiiiipppppp"},
+};
+
+}  // namespace
+
+const KernelEntry* stream_kernels(int* n) {
+    *n = (int)(sizeof(kStream) / sizeof(kStream[0]));
+    return kStream;
+}
+
+}  // namespace fm

@@ -23,6 +23,31 @@ __device__ __forceinline__ int dot4(uint32_t a, uint32_t b, int c) {
     return __dp4a(static_cast<int>(a), static_cast<int>(b), c);
 }
 
+// unsigned 8-bit (a) x signed 8-bit (b) x 4 dot product with int32 accumulate
+__device__ __forceinline__ int dot4_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// sum over the 32 int4 weights of one 16-byte word of (nibble ^ 8) * q, where e / o hold
+// the int8 activations of the even / odd k positions.  Low nibbles become bytes u (one
+// LOP3: mask and flip the sign bit); high nibbles stay in place as unsigned bytes 16*u
+// (one LOP3) and go through the unsigned-by-signed dp4a, so no shift is needed per word;
+// their sum is a multiple of 16 and is scaled back exactly at the end.
+__device__ __forceinline__ int dot32_u(const uint4& w, const uint4& e, const uint4& o) {
+    int lo = 0, hi = 0;
+    lo = dot4((w.x & 0x0F0F0F0Fu) ^ 0x08080808u, e.x, lo);
+    hi = dot4_us((w.x & 0xF0F0F0F0u) ^ 0x80808080u, o.x, hi);
+    lo = dot4((w.y & 0x0F0F0F0Fu) ^ 0x08080808u, e.y, lo);
+    hi = dot4_us((w.y & 0xF0F0F0F0u) ^ 0x80808080u, o.y, hi);
+    lo = dot4((w.z & 0x0F0F0F0Fu) ^ 0x08080808u, e.z, lo);
+    hi = dot4_us((w.z & 0xF0F0F0F0u) ^ 0x80808080u, o.z, hi);
+    lo = dot4((w.w & 0x0F0F0F0Fu) ^ 0x08080808u, e.w, lo);
+    hi = dot4_us((w.w & 0xF0F0F0F0u) ^ 0x80808080u, o.w, hi);
+    return lo + (hi >> 4);
+}
+
 // generic byte permute; selector nibble bit 3 replicates the sign bit of the
 // selected byte (used as a "zero unless" switch with tables whose bytes are < 0x80)
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {

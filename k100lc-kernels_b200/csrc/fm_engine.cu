@@ -54,6 +54,8 @@ struct Engine {
     std::vector<KernelEntry> kernels;
     std::unordered_map<std::string, int> by_name;
     std::map<uintptr_t, size_t> allocs;          // base -> bytes
+    struct Table { size_t bytes; int nlayers, rows, K, row_base; };
+    std::map<uintptr_t, Table> tables;           // validated stream layer tables
     std::vector<cudaEvent_t> events;
     std::vector<Graph> graphs;
     std::unordered_map<uint64_t, int> plan_graphs;   // plan hash -> graph id
@@ -142,6 +144,7 @@ int ensure_init() {
         k = gemv_nvfp4_kernels(&n); add_kernels(k, n);
         k = int4_dot_kernels(&n); add_kernels(k, n);
         k = gemm_w4_kernels(&n); add_kernels(k, n);
+        k = stream_kernels(&n); add_kernels(k, n);
     }
     e.ready = true;
     return 0;
@@ -158,6 +161,18 @@ void ensure_table() {
     k = gemv_nvfp4_kernels(&n); add_kernels(k, n);
     k = int4_dot_kernels(&n); add_kernels(k, n);
     k = gemm_w4_kernels(&n); add_kernels(k, n);
+    k = stream_kernels(&n); add_kernels(k, n);
+}
+
+// a write into [p, p+n) makes any validated layer table it touches unvalidated
+void touch(const void* p, size_t n) {
+    Engine& e = E();
+    if (e.tables.empty()) return;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    for (auto it = e.tables.begin(); it != e.tables.end();) {
+        if (a < it->first + it->second.bytes && it->first < a + n) it = e.tables.erase(it);
+        else ++it;
+    }
 }
 
 int do_launch(int kid, uint32_t gx, uint32_t gy, uint32_t wx, uint32_t wy, const uint64_t* argv, int nargs) {
@@ -268,6 +283,15 @@ int after_launch(const char* kernel) {
 
 bool pdl_enabled() { return E().pdl; }
 
+bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base) {
+    Engine& e = E();
+    if (!e.check_bounds) return true;
+    auto it = e.tables.find(reinterpret_cast<uintptr_t>(table));
+    if (it == e.tables.end()) return false;
+    const Engine::Table& t = it->second;
+    return t.nlayers >= nlayers && t.rows == rows && t.K == K && t.row_base == row_base;
+}
+
 }  // namespace fm
 
 using namespace fm;
@@ -301,7 +325,11 @@ void fm_free(void* p) {
     LOCK;
     if (!p || !E().ready) return;
     cudaStreamSynchronize(E().stream);        // nothing in flight may still use it
-    E().allocs.erase(reinterpret_cast<uintptr_t>(p));
+    auto it = E().allocs.find(reinterpret_cast<uintptr_t>(p));
+    if (it != E().allocs.end()) {
+        touch(p, it->second);
+        E().allocs.erase(it);
+    }
     cudaFree(p);
 }
 
@@ -321,6 +349,7 @@ int fm_upload(void* dev, const void* host, size_t n) {
     LOCK;
     NEED_INIT(-1);
     if (!range_ok(dev, n)) { set_errorf("fm_upload: %zu bytes at %p exceed the allocation", n, dev); return -1; }
+    touch(dev, n);
     return copy_sync(dev, host, n, cudaMemcpyHostToDevice, "fm_upload");
 }
 
@@ -336,6 +365,7 @@ int fm_copy(void* dst, const void* src, size_t n) {
     NEED_INIT(-1);
     if (!range_ok(dst, n) || !range_ok(src, n)) { set_errorf("fm_copy: range exceeds an allocation"); return -1; }
     if (n == 0) return 0;
+    touch(dst, n);
     cudaError_t err = cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToDevice, E().stream);
     if (err != cudaSuccess) { cuda_fail("fm_copy", err); return -1; }
     return 0;
@@ -346,6 +376,7 @@ int fm_memset(void* dev, int v, size_t n) {
     NEED_INIT(-1);
     if (!range_ok(dev, n)) { set_errorf("fm_memset: range exceeds the allocation"); return -1; }
     if (n == 0) return 0;
+    touch(dev, n);
     cudaError_t err = cudaMemsetAsync(dev, v, n, E().stream);
     if (err != cudaSuccess) { cuda_fail("fm_memset", err); return -1; }
     return 0;
@@ -487,6 +518,7 @@ int fm_upload_async(void* dev, const void* host, size_t n) {
     LOCK;
     NEED_INIT(-1);
     if (!range_ok(dev, n)) { set_errorf("fm_upload_async: range exceeds the allocation"); return -1; }
+    touch(dev, n);
     cudaError_t err = cudaMemcpyAsync(dev, host, n, cudaMemcpyHostToDevice, E().stream);
     if (err != cudaSuccess) { cuda_fail("fm_upload_async", err); return -1; }
     return 0;
@@ -497,6 +529,36 @@ int fm_download_async(void* host, const void* dev, size_t n) {
     if (!range_ok(dev, n)) { set_errorf("fm_download_async: range exceeds the allocation"); return -1; }
     cudaError_t err = cudaMemcpyAsync(host, dev, n, cudaMemcpyDeviceToHost, E().stream);
     if (err != cudaSuccess) { cuda_fail("fm_download_async", err); return -1; }
+    return 0;
+}
+
+int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, int rows, int K, int row_base) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (nlayers <= 0 || rows <= 0 || K <= 0 || K % 128 || row_base < 0) {
+        set_errorf("fm_stream_table: bad nlayers/rows/K/row_base");
+        return -1;
+    }
+    const size_t bytes = (size_t)nlayers * 32;
+    if (!range_ok(dev_table, bytes)) { set_errorf("fm_stream_table: the table does not fit its allocation"); return -1; }
+    const size_t need[4] = {(size_t)rows * (K / 2), (size_t)rows * (K / 128) * 2, (size_t)K * 4,
+                            ((size_t)row_base + rows) * 4};
+    const size_t align[4] = {16, 16, 16, 4};
+    const char* what[4] = {"wq", "ws", "x", "y"};
+    for (int l = 0; l < nlayers; l++)
+        for (int j = 0; j < 4; j++) {
+            const void* ptr = reinterpret_cast<const void*>(static_cast<uintptr_t>(host_layers[4 * l + j]));
+            if (j == 2 && ptr == nullptr) continue;      // x is informational: the kernel reads the codes
+            if (!range_ok(ptr, need[j]) || !aligned(ptr, align[j])) {
+                set_errorf("fm_stream_table: layer %d: %s (%zu bytes at %p) is misaligned or outside its allocation",
+                           l, what[j], need[j], ptr);
+                return FM_EREJECT;
+            }
+        }
+    if (copy_sync(dev_table, host_layers, bytes, cudaMemcpyHostToDevice, "fm_stream_table") != 0) return -1;
+    touch(dev_table, bytes);
+    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base};
     return 0;
 }
 

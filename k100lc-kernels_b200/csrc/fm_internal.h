@@ -32,6 +32,9 @@ int reject(const char* kernel, const char* fmt, ...);   // records the message, 
 int cuda_fail(const char* kernel, cudaError_t e);       // records the message, returns FM_ECUDA
 int after_launch(const char* kernel);                   // cudaGetLastError -> FM_OK / FM_ECUDA
 bool pdl_enabled();                                     // programmatic dependent launch on?
+// true when `table` was filled by fm_stream_table with exactly these shapes and has not been
+// overwritten since (or checks are off): every pointer inside it was range-checked then
+bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base);
 
 // Registries of the kernel files -------------------------------------------
 const KernelEntry* quant_kernels(int* n);
@@ -39,6 +42,7 @@ const KernelEntry* gemv_w4_kernels(int* n);
 const KernelEntry* gemv_nvfp4_kernels(int* n);
 const KernelEntry* int4_dot_kernels(int* n);
 const KernelEntry* gemm_w4_kernels(int* n);
+const KernelEntry* stream_kernels(int* n);
 
 // argv decoding ------------------------------------------------------------
 template <typename T> static inline T* arg_ptr(uint64_t v) { return reinterpret_cast<T*>(static_cast<uintptr_t>(v)); }

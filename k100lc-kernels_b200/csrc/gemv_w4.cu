@@ -85,20 +85,7 @@ __device__ __forceinline__ void stage_activations(const GemvW4Params& p, int M, 
 }
 
 // sum over 32 weights of (nibble ^ 8) * q for one 16-byte weight word
-__device__ __forceinline__ int dot32(const uint4& w, const uint4& e, const uint4& o) {
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-    const uint32_t ee[4] = {e.x, e.y, e.z, e.w};
-    const uint32_t oo[4] = {o.x, o.y, o.z, o.w};
-    int v0 = 0, v1 = 0;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t lo = (ww[i] & 0x0F0F0F0Fu) ^ 0x08080808u;
-        const uint32_t hi = ((ww[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
-        v0 = dot4(lo, ee[i], v0);
-        v1 = dot4(hi, oo[i], v1);
-    }
-    return v0 + v1;
-}
+__device__ __forceinline__ int dot32(const uint4& w, const uint4& e, const uint4& o) { return dot32_u(w, e, o); }
 
 // A4     : int4 activations (32-sub-group scales) instead of int8 (128-group scales)
 // M      : tokens

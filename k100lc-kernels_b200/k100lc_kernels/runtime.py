@@ -94,6 +94,7 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_comm_size": (c.c_int, []),
         "fm_allgather": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_comm_destroy": (c.c_int, []),
+        "fm_stream_table": (c.c_int, [c.c_void_p, _u64p, c.c_int, c.c_int, c.c_int, c.c_int]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)          # AttributeError here = header and library disagree
@@ -376,6 +377,16 @@ class Runtime:
 
     def graph_free(self, graph: int) -> None:
         self._lib.fm_graph_free(graph)
+
+    def stream_table(self, layers, rows: int, k: int, row_base: int = 0) -> int:
+        """Validated device table for ``w4a8_decode_stream``: ``layers`` is a list of
+        ``(wq, ws, x, y)`` device pointers; returns the table's device pointer."""
+        flat = (ctypes.c_uint64 * (4 * len(layers)))(*[int(v) for lay in layers for v in lay])
+        dev = self.alloc(32 * len(layers))
+        if self._lib.fm_stream_table(ctypes.c_void_p(dev), flat, len(layers), int(rows), int(k), int(row_base)) != 0:
+            self.free(dev)
+            self._fail("fm_stream_table")
+        return dev
 
     def comm_unique_id(self) -> bytes:
         buf = ctypes.create_string_buffer(128)

@@ -1,0 +1,102 @@
+"""GPU tier: the multi-layer decode stream (one 2-D quant_act launch over all layers, then
+w4a8_decode_stream) against the per-layer kernels and the oracle, and the validation of
+its layer table."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import w4_oracle as O
+from gpu_util import Bufs
+from k100lc_kernels import W4Runner, synth
+
+pytestmark = pytest.mark.gpu
+REL = 1e-5
+K = 5120
+
+
+class Codes:
+    """quant_act outputs of all layers: x [L][K] -> ae, ao [L][K/2], asc, asu [L][K/128]."""
+
+    def __init__(self, rt, b, layers):
+        nl = len(layers)
+        self.x = b.put(np.stack([L["x"][0] for L in layers]))
+        self.ae, self.ao = b.zeros(nl * K // 2, np.int8), b.zeros(nl * K // 2, np.int8)
+        self.asc, self.asu = b.zeros(nl * K // 128), b.zeros(nl * K // 128, np.int32)
+        self.args = [self.ae, self.ao, self.asc, self.asu]
+        self.nl = nl
+
+    def quantise(self, rt):
+        rt.launch2d("quant_act", K // 128, self.nl, 32, 1, [self.x, self.ae, self.ao, self.asc, self.asu, self.nl, K])
+
+
+def _run_stream(rt, b, layers, rows, row_base=0, n_out=None):
+    n_out = n_out or rows
+    ptrs, ys = [], []
+    codes = Codes(rt, b, layers)
+    for i, L in enumerate(layers):
+        py = b.zeros(n_out, np.float32, np.nan)
+        ys.append(py)
+        ptrs.append((b.put(L["wq"]), b.put(L["ws"]), codes.x + i * K * 4, py))
+    table = rt.stream_table(ptrs, rows, K, row_base)
+    status = b.zeros(1, np.int32)
+    codes.quantise(rt)
+    rt.launch("w4a8_decode_stream", 1, 1, [table, len(layers), rows, K, row_base, 0, 0, status] + codes.args)
+    out = [b.get(py, n_out) for py in ys]
+    assert int(b.get(status, 1, np.int32)[0]) == 0
+    rt.free(table)
+    return out, ptrs
+
+
+@pytest.mark.parametrize("rows,nlayers", [(1000, 5), (148, 3), (100, 2), (17408, 3)])
+def test_stream_matches_per_layer_and_oracle(rt, rows, nlayers):
+    layers = [synth.rt4_layer(rows, K, 1, seed=700 + i) for i in range(nlayers)]
+    runner = W4Runner(rt)
+    with Bufs(rt) as b:
+        got, ptrs = _run_stream(rt, b, layers, rows)
+        for L, y, (pwq, pws, px, _py) in zip(layers, got, ptrs):
+            q = O.quant_act(L["x"])
+            ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"][0]
+            assert O.rel_err(y, ref) < REL
+            per_layer = runner.gemv("w4a8", pwq, pws, L["x"], rows, K)[0]
+            assert O.rel_err(y, per_layer) < REL
+    runner.close()
+
+
+def test_stream_row_base_and_repeat(rt):
+    """A rank's shard writes rows [row_base, row_base+rows) of a longer y; a second launch on
+    the same table gives the same bits."""
+    rows, base, n_out = 520, 1040, 2080
+    layers = [synth.rt4_layer(rows, K, 1, seed=800 + i) for i in range(4)]
+    with Bufs(rt) as b:
+        ptrs, ys = [], []
+        codes = Codes(rt, b, layers)
+        for i, L in enumerate(layers):
+            py = b.zeros(n_out, np.float32, np.nan)
+            ys.append(py)
+            ptrs.append((b.put(L["wq"]), b.put(L["ws"]), codes.x + i * K * 4, py))
+        table = rt.stream_table(ptrs, rows, K, base)
+        status = b.zeros(1, np.int32)
+        argv = [table, 4, rows, K, base, 0, 0, status] + codes.args
+        codes.quantise(rt)
+        rt.launch("w4a8_decode_stream", 1, 1, argv)
+        first = [b.get(py, n_out) for py in ys]
+        rt.launch("w4a8_decode_stream", 1, 1, argv)
+        second = [b.get(py, n_out) for py in ys]
+        for L, y1, y2 in zip(layers, first, second):
+            q = O.quant_act(L["x"])
+            ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"][0]
+            assert O.rel_err(y1[base:base + rows], ref) < REL
+            assert np.isnan(y1[:base]).all() and np.isnan(y1[base + rows:]).all()
+            assert np.array_equal(y1[base:base + rows], y2[base:base + rows])
+        # the table is only accepted as validated, with the shapes it was validated for
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("w4a8_decode_stream", 1, 1, [table, 4, rows + 8, K, base, 0, 0, status] + codes.args)
+        rt.memset(table, 0, 32)                         # overwriting it un-validates it
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("w4a8_decode_stream", 1, 1, argv)
+        rt.free(table)
+        # a table whose y is too short for row_base + rows is refused
+        with pytest.raises(RuntimeError, match="fm_stream_table"):
+            rt.stream_table([(ptrs[0][0], ptrs[0][1], ptrs[0][2], ys[0])], rows, K, n_out)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
