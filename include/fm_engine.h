@@ -117,6 +117,22 @@ int   fm_comm_size(void);
 int   fm_allgather(void* recv, const void* send, size_t bytes_per_rank);
 int   fm_comm_destroy(void);
 
+/* No counterpart in the reference.  A whole W4A8 decode layer, y[M][N] = W . x, for callers
+ * that are not allowed to allocate device memory where they call it (code inside another
+ * component's stream capture, server plugins with a fixed memory plan, real-time loops):
+ * quant_act followed by gemv_w4a8, with the quantised activations kept in a 73 728-byte
+ * array inside the library's device image instead of a caller-allocated buffer.
+ *   wq [N][K/2] bytes (two's-complement nibbles), ws_f16 [N][K/128], x [M][K] f32, y [M][N] f32
+ *   are the caller's device buffers; `stream` is a cudaStream_t (NULL = default stream);
+ *   wait != 0 blocks until the result is ready.
+ * Limits: M 1..4; K a multiple of 128, at most 16384 — beyond that -4 with a message.
+ * The first call on a device resolves the array's address; make it outside stream capture.
+ * All calls on a GPU share the array: calls on one stream are safe, calls whose kernels
+ * overlap on the GPU race.  Does not use the engine (no fm_init needed) and makes no
+ * allocating call. */
+int   fm_w4a8_linear_static(const void* wq, const void* ws_f16, const float* x, float* y,
+                            int M, int N, int K, void* stream, int wait);
+
 #ifdef __cplusplus
 }
 #endif

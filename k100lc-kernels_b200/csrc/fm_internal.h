@@ -44,6 +44,14 @@ const KernelEntry* int4_dot_kernels(int* n);
 const KernelEntry* gemm_w4_kernels(int* n);
 const KernelEntry* stream_kernels(int* n);
 
+// Launchers without the engine (no allocation registry, no engine stream): the caller
+// owns every buffer and names the stream.  Same kernels as the by-name entries.
+cudaError_t quant_act_raw(const float* x, int8_t* ae, int8_t* ao, float* asc, int* asu, int K, int tokens,
+                          cudaStream_t stream);
+cudaError_t gemv_w4a8_raw(const uint32_t* wq, const void* ws_f16, const int8_t* ae, const int8_t* ao,
+                          const float* asc, const int* asu, float* y, int M, int N, int K, int sm_count,
+                          cudaStream_t stream);
+
 // argv decoding ------------------------------------------------------------
 template <typename T> static inline T* arg_ptr(uint64_t v) { return reinterpret_cast<T*>(static_cast<uintptr_t>(v)); }
 static inline int arg_i32(uint64_t v) { return static_cast<int>(static_cast<uint32_t>(v)); }

@@ -415,6 +415,57 @@ const KernelEntry kGemvW4[] = {
 
 }  // namespace
 
+namespace {
+template <int M, int R, int KITER, bool AREG>
+cudaError_t raw_variant(const GemvW4Params& p, int sm_count, cudaStream_t stream) {
+    auto kern = gemv_w4_kernel<false, M, R, KITER, AREG, false>;
+    const size_t smem = (size_t)M * (2 * (p.K / 8) * 4 + (p.K / 128) * 8);
+    cudaError_t e = cudaSuccess;
+    if (smem > 48 * 1024) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
+    if (e != cudaSuccess) return e;
+    const int need = (p.rows + R * kWarps - 1) / (R * kWarps);
+    int grid = sm_count * (per_sm < 1 ? 1 : per_sm);
+    if (grid > need) grid = need;
+    kern<<<grid, kThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int M>
+cudaError_t raw_for_m(const GemvW4Params& p, int sm_count, cudaStream_t stream) {
+    const bool k5 = p.K == 5120;
+    if (M == 1) return k5 ? raw_variant<1, 1, 5, true>(p, sm_count, stream) : raw_variant<1, 1, 0, false>(p, sm_count, stream);
+    return k5 ? raw_variant<M, 2, 5, false>(p, sm_count, stream) : raw_variant<M, 2, 0, false>(p, sm_count, stream);
+}
+}  // namespace
+
+cudaError_t gemv_w4a8_raw(const uint32_t* wq, const void* ws_f16, const int8_t* ae, const int8_t* ao,
+                          const float* asc, const int* asu, float* y, int M, int N, int K, int sm_count,
+                          cudaStream_t stream) {
+    GemvW4Params p = {};
+    p.wq = wq;
+    p.ws = static_cast<const __half*>(ws_f16);
+    p.a0 = reinterpret_cast<const uint32_t*>(ae);
+    p.a1 = reinterpret_cast<const uint32_t*>(ao);
+    p.asc = asc;
+    p.asu = asu;
+    p.y = y;
+    p.N = N;
+    p.K = K;
+    p.rows = N;
+    switch (M) {
+        case 1: return raw_for_m<1>(p, sm_count, stream);
+        case 2: return raw_for_m<2>(p, sm_count, stream);
+        case 3: return raw_for_m<3>(p, sm_count, stream);
+        case 4: return raw_for_m<4>(p, sm_count, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
 const KernelEntry* gemv_w4_kernels(int* n) {
     *n = (int)(sizeof(kGemvW4) / sizeof(kGemvW4[0]));
     return kGemvW4;

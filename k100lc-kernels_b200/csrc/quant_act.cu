@@ -292,6 +292,14 @@ const KernelEntry kQuant[] = {
 
 }  // namespace
 
+cudaError_t quant_act_raw(const float* x, int8_t* ae, int8_t* ao, float* asc, int* asu, int K, int tokens,
+                          cudaStream_t stream) {
+    const int groups = K / 128;
+    const int warps = groups * tokens;
+    quant_act_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(x, ae, ao, asc, asu, K, groups, tokens);
+    return cudaGetLastError();
+}
+
 const KernelEntry* quant_kernels(int* n) {
     *n = (int)(sizeof(kQuant) / sizeof(kQuant[0]));
     return kQuant;

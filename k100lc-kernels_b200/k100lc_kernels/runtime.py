@@ -95,6 +95,8 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_allgather": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_comm_destroy": (c.c_int, []),
         "fm_stream_table": (c.c_int, [c.c_void_p, _u64p, c.c_int, c.c_int, c.c_int, c.c_int]),
+        "fm_w4a8_linear_static": (c.c_int, [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
+                                            c.c_int, c.c_void_p, c.c_int]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)          # AttributeError here = header and library disagree
