@@ -43,6 +43,23 @@ METRIC = "decode weight-stream bandwidth, 400 x (17408x5120) W4A8 layers, M=1 (u
 WORKLOAD = "400-layer W4A8 M=1 decode weight stream, N=17408 K=5120 group=128, seed 4"
 
 
+def log(msg: str) -> None:
+    """Progress on stderr (rank-tagged), so that a stall can be located from the log."""
+    print(f"[bench {time.strftime('%H:%M:%S')} rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
+def watchdog(seconds: int) -> None:
+    """End the process if the whole run takes longer than `seconds` (a hung collective must not
+    hold the GPUs until someone else's limit expires)."""
+    import signal
+
+    def _fire(signum, frame):
+        log(f"watchdog: no result after {seconds} s, giving up")
+        os._exit(3)
+    signal.signal(signal.SIGALRM, _fire)
+    signal.alarm(seconds)
+
+
 def peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.is_file():
@@ -103,9 +120,9 @@ class ClockSampler:
 class Stream:
     """The sharded 400-layer weight stream of one rank, resident in HBM."""
 
-    def __init__(self, rt, layers: int, rank: int, world: int):
+    def __init__(self, rt, layers: int, rank: int, world: int, dist=None):
         from k100lc_kernels import synth
-        self.rt, self.layers, self.rank, self.world = rt, layers, rank, world
+        self.rt, self.layers, self.rank, self.world, self.dist = rt, layers, rank, world, dist
         self.rows = N // world
         blocks = synth.STREAM_ROW_BLOCKS // world
         self.wq = rt.alloc(layers * self.rows * (K // 2))
@@ -152,20 +169,36 @@ class Stream:
     def capture_fused(self) -> int:
         """One decoded token as TWO launches: quant_act over the x of all layers (grid y =
         layer), then the multi-layer stream kernel (bulk-copy ring over all layers' weights).
-        Single GPU only for now."""
+        With several GPUs the kernel's epilogue stores every y row into the y buffer of every
+        peer as well (the all-gather, over NVLink peer mappings), so no collective follows."""
         rt, nl = self.rt, self.layers
         if not hasattr(self, "table"):
+            base = self.rank * self.rows
             self.table = rt.stream_table([(self.wq_l(l), self.ws_l(l), self.x + l * K * 4, self.y + l * N * 4)
-                                          for l in range(nl)], self.rows, K, 0)
+                                          for l in range(nl)], self.rows, K, base)
             self.status = rt.alloc(4)
             rt.memset(self.status, 0, 4)
             self.ae_all, self.ao_all = rt.alloc(nl * K // 2), rt.alloc(nl * K // 2)
             self.asc_all, self.asu_all = rt.alloc(nl * NG * 4), rt.alloc(nl * NG * 4)
+            self.npeers, self.deltas = 0, 0
+            if self.world > 1:
+                from k100lc_kernels.shard import exchange_ipc
+                peers = exchange_ipc(rt, self.dist, self.y)
+                bases = [peers[r] for r in range(self.world) if r != self.rank]
+                self.deltas = rt.stream_peers(bases, self.y, nl * N * 4)
+                self.npeers = len(bases)
         rt.graph_begin()
         rt.launch2d("quant_act", NG, nl, 32, 1, [self.x, self.ae_all, self.ao_all, self.asc_all, self.asu_all, nl, K])
-        rt.launch("w4a8_decode_stream", 1, 1, [self.table, nl, self.rows, K, 0, 0, 0, self.status,
+        rt.launch("w4a8_decode_stream", 1, 1, [self.table, nl, self.rows, K, self.rank * self.rows, self.npeers,
+                                               self.deltas, self.status,
                                                self.ae_all, self.ao_all, self.asc_all, self.asu_all])
         return rt.graph_end()
+
+    def y_digest(self) -> str:
+        """SHA-1 of the gathered outputs of all layers on this rank."""
+        import hashlib
+        self.rt.sync()
+        return hashlib.sha1(self.rt.download(self.y, self.layers * N, np.float32).tobytes()).hexdigest()
 
 
 def time_graph(rt, graph, steps, warmup, barrier, counter=None) -> float:
@@ -284,22 +317,33 @@ def run_ours(args) -> int:
         if dist is not None:
             dist.barrier()
 
+    watchdog(args.watchdog)
     if world > 1:
         box = [rt.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         rt.comm_init(box[0], world, rank)
+        log("NCCL communicator ready")
 
     t_setup = time.perf_counter()
-    st = Stream(rt, args.layers, rank, world)
+    st = Stream(rt, args.layers, rank, world, dist)
     setup_s = time.perf_counter() - t_setup
+    log(f"stream resident after {setup_s:.1f} s")
+    if world > 1:
+        # NCCL sets up its connections on the first collective; do that eagerly, not inside a capture
+        rt.allgather(st.y, st.yloc, st.rows * 4)
+        rt.sync()
+        barrier()
+        log("eager all-gather done")
 
-    fused = args.mode == "fused" and world == 1
+    fused = args.mode == "fused"
     graph = st.capture_fused() if fused else st.capture()
+    log("graph captured")
     counted = []
     with ClockSampler(rt.device_attr("device")) as clocks:
         ms_step = time_graph(rt, graph, args.steps, args.warmup, barrier, counted)
     gpu_launches = counted[0]                       # kernels of this library inside the timed region
 
+    log(f"timed region done: {ms_step:.3f} ms/step")
     # end to end through the C ABI with host buffers: x of all layers up, y of all layers back, every step
     def e2e_step():
         rt.upload_async(st.x, st.x_host)
@@ -325,12 +369,27 @@ def run_ours(args) -> int:
         status = int(rt.download(st.status, 1, np.int32)[0])
         if status != 0:
             raise RuntimeError(f"w4a8_decode_stream reported status {status} (a bounded wait ran out)")
+        log("e2e done")
+        digest = st.y_digest()
+        barrier()
+        rt.memset(st.y, 0xFF, args.layers * N * 4)
+        rt.sync()
+        barrier()
         ms_alt = time_graph(rt, st.capture(), max(3, args.steps // 4), 3, barrier)   # per-layer launches, for comparison
+        log(f"per-layer launches: {ms_alt:.3f} ms/step")
+        same = digest == st.y_digest()              # both schedules must leave identical bits in y
+        if dist is not None:
+            box = [None] * world
+            dist.all_gather_object(box, (digest, same))
+            same = all(b[1] for b in box) and len({b[0] for b in box}) == 1
+        if not same:
+            raise RuntimeError("the stream kernel and the per-layer launches (or two ranks) disagree on y")
     else:
         gk = st.capture(quant=False, gather=False)
         ms_kern = time_graph(rt, gk, max(3, args.steps // 2), 3, barrier)
         ms_alt = None
 
+    log("reducing timings over ranks")
     if dist is not None:
         import torch
         t = torch.tensor([ms_step, ms_e2e, ms_kern], dtype=torch.float64)
@@ -352,7 +411,10 @@ def run_ours(args) -> int:
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 scale",
             "data": "synthetic (seeded uniform int4 weights, |N(0,1)|*0.01+1e-3 f16 scales, N(0,1) activations)",
             "config": {"workload": WORKLOAD, "layers": args.layers, "rows_per_gpu": N // world,
-                       "sharding": "output rows" + (f", all-gather of y per layer (NCCL)" if world > 1 else ""),
+                       "sharding": "output rows" + ((", all-gather of y by peer stores from the kernel epilogue (NVLink)"
+                                                     if fused else ", all-gather of y per layer (NCCL)") if world > 1 else ""),
+                       "y_check": "identical bits in y from the stream kernel and the per-layer launches on every rank"
+                                  if fused else None,
                        "launch": ("two launches per token: quant_act over the x of all layers (grid y = layer), then "
                                   "w4a8_decode_stream (gemv_w4a8 of all layers, software-pipelined)") if fused else
                                  "one CUDA graph per token (quant_act + gemv_w4a8 per layer)",
@@ -365,7 +427,8 @@ def run_ours(args) -> int:
             "per_layer_launches": None if ms_alt is None else {
                 "ms_per_token": round(ms_alt, 4), "us_per_layer": round(ms_alt * 1e3 / args.layers, 3),
                 "gb_per_s": round(total_bytes / ms_alt / 1e6, 1),
-                "what": "the same token as 800 by-name launches (quant_act, gemv_w4a8<1,false,1>) in one CUDA graph"},
+                "what": "the same token as 800 by-name launches (quant_act, gemv_w4a8<1,false,1>) in one CUDA graph"
+                        + (", plus an NCCL all-gather of y per layer" if world > 1 else "")},
             "roofline": {"bound": "hbm", "kernel": "w4a8_decode_stream" if fused else "gemv_w4a8<1,false,1>", "achieved": round(achieved, 1),
                          "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4), "peak_source": pk["source"],
@@ -373,11 +436,13 @@ def run_ours(args) -> int:
                          "traffic": None},
             "cpu_baseline": cpu, "clocks": clocks.summary(), "paths_m1": paths, "setup_seconds": round(setup_s, 1),
         }
-    if world > 1:
-        rt.comm_destroy()
-        dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line), flush=True)
+    if world > 1:
+        log("result printed; tearing down")
+        barrier()
+        rt.comm_destroy()          # also releases the captured graphs that hold NCCL collectives
+        dist.destroy_process_group()
     return 0
 
 
@@ -437,6 +502,7 @@ def main() -> int:
                     help="fused: one multi-layer kernel per token; graph: 2 by-name launches per layer")
     ap.add_argument("--cpu-layers", type=int, default=6, help="layers of the stream timed on the CPU (0 = skip)")
     ap.add_argument("--no-paths", dest="paths", action="store_false", help="skip the per-path M=1 timings")
+    ap.add_argument("--watchdog", type=int, default=600, help="give up after this many seconds")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     return run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -98,6 +98,19 @@ int   fm_download_async(void* pinned_host, const void* dev, size_t n);
  * 0 ok, -4 a pointer fails the check, -1 other errors. */
 int   fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, int rows, int K, int row_base);
 
+/* Peer memory for the row-sharded stream (one process per GPU).  fm_ipc_export gives the
+ * 64-byte CUDA IPC handle of the fm_alloc allocation that contains `dev`, the offset of
+ * `dev` in it and its size; another rank opens it with fm_ipc_import (peer access is
+ * enabled on the way) and releases it with fm_free.  fm_stream_peers checks that
+ * [peer_bases[q], +span) lies inside an imported allocation for every q and that
+ * [local_base, +span) is a local one, then writes the npeers byte offsets
+ * (peer - local) to dev_deltas for w4a8_decode_stream. */
+int   fm_ipc_export(const void* dev, void* out_handle64, unsigned long long* out_offset,
+                    unsigned long long* out_size);
+void* fm_ipc_import(const void* handle64, unsigned long long size);
+int   fm_stream_peers(void* dev_deltas, const uint64_t* peer_bases, int npeers, const void* local_base,
+                      unsigned long long span);
+
 /* device timers on the engine stream */
 int   fm_event_create(void);
 int   fm_event_record(int ev);

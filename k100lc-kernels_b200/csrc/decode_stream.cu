@@ -13,7 +13,7 @@
 //   * persistent grid, one CTA per SM; CTA c owns the contiguous rows
 //     [c*rows/G, (c+1)*rows/G) of EVERY layer, so its weight bytes are contiguous;
 //   * the last warp (one elected lane) is the producer: it walks layers and row chunks
-//     and issues 1-D bulk async copies (cp.async.bulk, no multicast) of CW rows of packed
+//     and issues 1-D bulk async copies (cp.async.bulk) of CW rows of packed
 //     weights plus their f16 scales into a shared-memory ring, completion counted on an
 //     mbarrier per stage; once per layer it also copies that layer's int8 codes, scales
 //     and group sums (5.4 KB) into a double-buffered tile;
@@ -76,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* sta
     atomicCAS(status, 0, code);
     return false;
 }
-// 1-D bulk async copy global -> this CTA's shared memory (no multicast)
+// 1-D bulk async copy global -> this CTA's shared memory
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -208,11 +208,12 @@ w4a8_stream_kernel(const StreamParams p) {
             acc = warp_sum(acc);
             if (lane == 0 && live) {
                 y[row] = acc;
-                for (int q = 0; q < p.npeers; q++)           // all-gather by direct peer stores
+                for (int q = 0; q < p.npeers; q++)           // all-gather by direct peer stores over NVLink
                     *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
             }
         }
     }
+    if (p.npeers) __threadfence_system();                    // peer stores are visible before the kernel ends
 }
 
 template <int KITER, int CW, int STAGES>
@@ -239,7 +240,8 @@ int run_stream(const char* kn, const LaunchCtx& c, const StreamParams& p) {
 //   rows        weight rows held by this GPU (N, or N / number of GPUs)
 //   row_base    first output index of this GPU's rows inside each layer's y
 //   npeers      0, or the number of other GPUs whose y copies also receive the rows;
-//   peer_delta  device array of npeers signed byte offsets (peer y address - local y address)
+//   peer_delta  device array of npeers signed byte offsets (peer y address - local y address),
+//               filled by fm_stream_peers from allocations opened with fm_ipc_import
 //   status      device int, must be 0 before the launch; non-zero afterwards = a bounded
 //               wait ran out (1 producer/ring, 2 codes not landed, 3 consumer/ring, 4 code tile not free)
 //   ae, ao, asc, asu   outputs of quant_act launched with grid y = nlayers over x [nlayers][K]:
@@ -266,9 +268,10 @@ int launch_w4a8_stream(const LaunchCtx& c, const uint64_t* a) {
     if (p.nlayers == 0) return FM_OK;
     FM_REQUIRE(aligned(p.layers, 8) && aligned(p.status, 4), kn, "misaligned layer table or status");
     FM_RANGE(p.layers, (size_t)p.nlayers * sizeof(StreamLayer), kn, "layers");
-    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, p.row_base), kn,
+    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, p.row_base, p.peer_delta, p.npeers), kn,
                "the layer table at %p was not filled by fm_stream_table for nlayers=%d rows=%d K=%d row_base=%d "
-               "(or was overwritten since)", (const void*)p.layers, p.nlayers, p.rows, p.K, p.row_base);
+               "(or was overwritten since), or the peer offsets do not come from fm_stream_peers for its outputs",
+               (const void*)p.layers, p.nlayers, p.rows, p.K, p.row_base);
     FM_RANGE(p.status, 4, kn, "status");
     if (p.npeers) FM_RANGE(p.peer_delta, (size_t)p.npeers * 8, kn, "peer_delta");
     FM_REQUIRE(aligned(p.ae, 16) && aligned(p.ao, 16) && aligned(p.asc, 16) && aligned(p.asu, 16), kn,

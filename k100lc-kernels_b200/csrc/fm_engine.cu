@@ -54,8 +54,11 @@ struct Engine {
     std::vector<KernelEntry> kernels;
     std::unordered_map<std::string, int> by_name;
     std::map<uintptr_t, size_t> allocs;          // base -> bytes
-    struct Table { size_t bytes; int nlayers, rows, K, row_base; };
+    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi; };
     std::map<uintptr_t, Table> tables;           // validated stream layer tables
+    struct Peers { int npeers; uintptr_t lo, hi; };
+    std::map<uintptr_t, Peers> peers;            // validated peer-offset arrays (device address -> window)
+    std::map<uintptr_t, size_t> imported;        // peer allocations opened through CUDA IPC
     std::vector<cudaEvent_t> events;
     std::vector<Graph> graphs;
     std::unordered_map<uint64_t, int> plan_graphs;   // plan hash -> graph id
@@ -167,10 +170,13 @@ void ensure_table() {
 // a write into [p, p+n) makes any validated layer table it touches unvalidated
 void touch(const void* p, size_t n) {
     Engine& e = E();
-    if (e.tables.empty()) return;
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
     for (auto it = e.tables.begin(); it != e.tables.end();) {
         if (a < it->first + it->second.bytes && it->first < a + n) it = e.tables.erase(it);
+        else ++it;
+    }
+    for (auto it = e.peers.begin(); it != e.peers.end();) {
+        if (a < it->first + (size_t)it->second.npeers * 8 && it->first < a + n) it = e.peers.erase(it);
         else ++it;
     }
 }
@@ -283,13 +289,19 @@ int after_launch(const char* kernel) {
 
 bool pdl_enabled() { return E().pdl; }
 
-bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base) {
+bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
+                     int npeers) {
     Engine& e = E();
     if (!e.check_bounds) return true;
     auto it = e.tables.find(reinterpret_cast<uintptr_t>(table));
     if (it == e.tables.end()) return false;
     const Engine::Table& t = it->second;
-    return t.nlayers >= nlayers && t.rows == rows && t.K == K && t.row_base == row_base;
+    if (!(t.nlayers >= nlayers && t.rows == rows && t.K == K && t.row_base == row_base)) return false;
+    if (npeers == 0) return true;
+    // every y of the table must lie inside the window the peer offsets were validated for
+    auto ip = e.peers.find(reinterpret_cast<uintptr_t>(peer_delta));
+    if (ip == e.peers.end() || ip->second.npeers != npeers) return false;
+    return t.y_lo >= ip->second.lo && t.y_hi <= ip->second.hi;
 }
 
 }  // namespace fm
@@ -329,6 +341,12 @@ void fm_free(void* p) {
     if (it != E().allocs.end()) {
         touch(p, it->second);
         E().allocs.erase(it);
+    }
+    auto im = E().imported.find(reinterpret_cast<uintptr_t>(p));
+    if (im != E().imported.end()) {              // a peer's allocation: unmap, do not free
+        E().imported.erase(im);
+        cudaIpcCloseMemHandle(p);
+        return;
     }
     cudaFree(p);
 }
@@ -544,6 +562,7 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
     if (!range_ok(dev_table, bytes)) { set_errorf("fm_stream_table: the table does not fit its allocation"); return -1; }
     const size_t need[4] = {(size_t)rows * (K / 2), (size_t)rows * (K / 128) * 2, (size_t)K * 4,
                             ((size_t)row_base + rows) * 4};
+    uintptr_t y_lo = ~(uintptr_t)0, y_hi = 0;
     const size_t align[4] = {16, 16, 16, 4};
     const char* what[4] = {"wq", "ws", "x", "y"};
     for (int l = 0; l < nlayers; l++)
@@ -555,10 +574,83 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
                            l, what[j], need[j], ptr);
                 return FM_EREJECT;
             }
+            if (j == 3) {
+                const uintptr_t y = static_cast<uintptr_t>(host_layers[4 * l + j]);
+                if (y + (size_t)row_base * 4 < y_lo) y_lo = y + (size_t)row_base * 4;
+                if (y + need[3] > y_hi) y_hi = y + need[3];
+            }
         }
     if (copy_sync(dev_table, host_layers, bytes, cudaMemcpyHostToDevice, "fm_stream_table") != 0) return -1;
     touch(dev_table, bytes);
-    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base};
+    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi};
+    return 0;
+}
+
+int fm_ipc_export(const void* dev, void* out_handle64, unsigned long long* out_offset, unsigned long long* out_size) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    const uintptr_t a = reinterpret_cast<uintptr_t>(dev);
+    auto it = e.allocs.upper_bound(a);
+    if (it == e.allocs.begin()) { set_errorf("fm_ipc_export: %p is not inside an fm_alloc allocation", dev); return -1; }
+    --it;
+    if (a >= it->first + it->second || e.imported.count(it->first)) {
+        set_errorf("fm_ipc_export: %p is not inside a local fm_alloc allocation", dev);
+        return -1;
+    }
+    cudaIpcMemHandle_t h;
+    cudaError_t err = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(it->first));
+    if (err != cudaSuccess) { cuda_fail("fm_ipc_export", err); return -1; }
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    memcpy(out_handle64, &h, 64);
+    *out_offset = a - it->first;
+    *out_size = it->second;
+    return 0;
+}
+
+void* fm_ipc_import(const void* handle64, unsigned long long size) {
+    LOCK;
+    NEED_INIT(nullptr);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    cudaError_t err = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (err != cudaSuccess) { cuda_fail("fm_ipc_import", err); return nullptr; }
+    E().allocs[reinterpret_cast<uintptr_t>(p)] = (size_t)size;
+    E().imported[reinterpret_cast<uintptr_t>(p)] = (size_t)size;
+    return p;
+}
+
+int fm_stream_peers(void* dev_deltas, const uint64_t* peer_bases, int npeers, const void* local_base,
+                    unsigned long long span) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (npeers < 1 || npeers > 7) { set_errorf("fm_stream_peers: npeers must be 1..7"); return -1; }
+    if (!range_ok(dev_deltas, (size_t)npeers * 8) || !range_ok(local_base, span)) {
+        set_errorf("fm_stream_peers: the offset array or the local window is outside its allocation");
+        return FM_EREJECT;
+    }
+    long long delta[7];
+    for (int q = 0; q < npeers; q++) {
+        const uintptr_t pb = static_cast<uintptr_t>(peer_bases[q]);
+        auto it = e.imported.upper_bound(pb);
+        bool ok = it != e.imported.begin();
+        if (ok) {
+            --it;
+            ok = pb >= it->first && pb + span <= it->first + it->second;
+        }
+        if (!ok) {
+            set_errorf("fm_stream_peers: peer window %d (%llu bytes at %p) is not inside an imported allocation", q, span,
+                       reinterpret_cast<void*>(pb));
+            return FM_EREJECT;
+        }
+        delta[q] = (long long)pb - (long long)reinterpret_cast<uintptr_t>(local_base);
+    }
+    if (copy_sync(dev_deltas, delta, (size_t)npeers * 8, cudaMemcpyHostToDevice, "fm_stream_peers") != 0) return -1;
+    touch(dev_deltas, (size_t)npeers * 8);
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(local_base);
+    e.peers[reinterpret_cast<uintptr_t>(dev_deltas)] = Engine::Peers{npeers, lo, lo + (uintptr_t)span};
     return 0;
 }
 
@@ -688,6 +780,15 @@ int fm_comm_destroy(void) {
     Engine& e = E();
     if (!e.comm) return 0;
     cudaStreamSynchronize(e.stream);
+    // captured graphs may hold collectives of this communicator; NCCL waits for them to be
+    // released before it lets the communicator go, so every graph is destroyed first
+    for (size_t i = 0; i < e.graphs.size(); i++)
+        if (e.graphs[i].exec) {
+            cudaGraphExecDestroy(e.graphs[i].exec);
+            cudaGraphDestroy(e.graphs[i].graph);
+            e.graphs[i] = Graph();
+        }
+    e.plan_graphs.clear();
     auto f = (nccl_destroy_t)nccl_sym("ncclCommDestroy");
     if (f) f(e.comm);
     e.comm = nullptr;

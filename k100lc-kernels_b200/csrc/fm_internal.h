@@ -33,8 +33,10 @@ int cuda_fail(const char* kernel, cudaError_t e);       // records the message, 
 int after_launch(const char* kernel);                   // cudaGetLastError -> FM_OK / FM_ECUDA
 bool pdl_enabled();                                     // programmatic dependent launch on?
 // true when `table` was filled by fm_stream_table with exactly these shapes and has not been
-// overwritten since (or checks are off): every pointer inside it was range-checked then
-bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base);
+// overwritten since (or checks are off): every pointer inside it was range-checked then; with
+// npeers > 0 the offset array must come from fm_stream_peers and cover every y of the table
+bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
+                     int npeers);
 
 // Registries of the kernel files -------------------------------------------
 const KernelEntry* quant_kernels(int* n);

@@ -95,6 +95,9 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_allgather": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_comm_destroy": (c.c_int, []),
         "fm_stream_table": (c.c_int, [c.c_void_p, _u64p, c.c_int, c.c_int, c.c_int, c.c_int]),
+        "fm_ipc_export": (c.c_int, [c.c_void_p, c.c_void_p, c.POINTER(c.c_ulonglong), c.POINTER(c.c_ulonglong)]),
+        "fm_ipc_import": (c.c_void_p, [c.c_void_p, c.c_ulonglong]),
+        "fm_stream_peers": (c.c_int, [c.c_void_p, _u64p, c.c_int, c.c_void_p, c.c_ulonglong]),
         "fm_w4a8_linear_static": (c.c_int, [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
                                             c.c_int, c.c_void_p, c.c_int]),
     }
@@ -388,6 +391,30 @@ class Runtime:
         if self._lib.fm_stream_table(ctypes.c_void_p(dev), flat, len(layers), int(rows), int(k), int(row_base)) != 0:
             self.free(dev)
             self._fail("fm_stream_table")
+        return dev
+
+    def ipc_export(self, ptr: int) -> tuple[bytes, int, int]:
+        """(64-byte IPC handle, offset of ptr in its allocation, allocation size)."""
+        h = ctypes.create_string_buffer(64)
+        off, size = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+        if self._lib.fm_ipc_export(ctypes.c_void_p(int(ptr)), h, ctypes.byref(off), ctypes.byref(size)) != 0:
+            self._fail("fm_ipc_export")
+        return h.raw, int(off.value), int(size.value)
+
+    def ipc_import(self, handle: bytes, size: int) -> int:
+        p = self._lib.fm_ipc_import(ctypes.c_char_p(handle), int(size))
+        if not p:
+            self._fail("fm_ipc_import")
+        return int(p)
+
+    def stream_peers(self, peer_bases, local_base: int, span: int) -> int:
+        """Validated device array of byte offsets (peer - local) for ``w4a8_decode_stream``."""
+        n = len(peer_bases)
+        dev = self.alloc(8 * n)
+        arr = (ctypes.c_uint64 * n)(*[int(b) for b in peer_bases])
+        if self._lib.fm_stream_peers(ctypes.c_void_p(dev), arr, n, ctypes.c_void_p(int(local_base)), int(span)) != 0:
+            self.free(dev)
+            self._fail("fm_stream_peers")
         return dev
 
     def comm_unique_id(self) -> bytes:
