@@ -188,15 +188,20 @@ w4a8_stream_kernel(const StreamParams p) {
             const uint8_t* st = ring + (size_t)s * STAGE;
             const uint4* wrow = reinterpret_cast<const uint4*>(st + (size_t)warp * ROWB);
             const __half* srow = reinterpret_cast<const __half*>(st + STAGE_W + (size_t)warp * SCB);
+            // `live` is uniform over the warp (one row per warp), so dead rows of a partial last
+            // stage skip the loads and the arithmetic altogether
             uint4 w[KITER];
             float sw[KITER];
+            if (live) {
 #pragma unroll
-            for (int it = 0; it < KITER; it++) {
-                w[it] = live ? wrow[it * 32 + lane] : make_uint4(0, 0, 0, 0);
-                sw[it] = live ? __half2float(srow[(it * 128 + lane * 4) >> 4]) : 0.f;
+                for (int it = 0; it < KITER; it++) {
+                    w[it] = wrow[it * 32 + lane];
+                    sw[it] = __half2float(srow[(it * 128 + lane * 4) >> 4]);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);          // the stage may be refilled while we compute
+            if (!live) continue;
             float acc = 0.f;
 #pragma unroll
             for (int it = 0; it < KITER; it++) {
@@ -206,7 +211,7 @@ w4a8_stream_kernel(const StreamParams p) {
                 if ((lane & 3) == 0) acc += (sw[it] * asc[it]) * (float)(v - asu8[it]);
             }
             acc = warp_sum(acc);
-            if (lane == 0 && live) {
+            if (lane == 0) {
                 y[row] = acc;
                 for (int q = 0; q < p.npeers; q++)           // all-gather by direct peer stores over NVLink
                     *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
