@@ -111,6 +111,10 @@ void* fm_ipc_import(const void* handle64, unsigned long long size);
 int   fm_stream_peers(void* dev_deltas, const uint64_t* peer_bases, int npeers, const void* local_base,
                       unsigned long long span);
 
+/* Drains the stream and returns (then clears) the status word of the tcgen05 GEMM kernels:
+ * 0, or the code of the first bounded wait that ran out (the results are then invalid). */
+int   fm_gemm_status(void);
+
 /* device timers on the engine stream */
 int   fm_event_create(void);
 int   fm_event_record(int ev);

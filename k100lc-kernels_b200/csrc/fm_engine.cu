@@ -654,6 +654,12 @@ int fm_stream_peers(void* dev_deltas, const uint64_t* peer_bases, int npeers, co
     return 0;
 }
 
+int fm_gemm_status(void) {
+    LOCK;
+    NEED_INIT(-1);
+    return gemm_read_status(E().stream);
+}
+
 int fm_event_create(void) {
     LOCK;
     NEED_INIT(-1);

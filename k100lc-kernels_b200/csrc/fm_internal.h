@@ -54,6 +54,8 @@ cudaError_t gemv_w4a8_raw(const uint32_t* wq, const void* ws_f16, const int8_t* 
                           const float* asc, const int* asu, float* y, int M, int N, int K, int sm_count,
                           cudaStream_t stream);
 
+int gemm_read_status(cudaStream_t stream);   // 0, or the code of the first bounded wait that ran out
+
 // argv decoding ------------------------------------------------------------
 template <typename T> static inline T* arg_ptr(uint64_t v) { return reinterpret_cast<T*>(static_cast<uintptr_t>(v)); }
 static inline int arg_i32(uint64_t v) { return static_cast<int>(static_cast<uint32_t>(v)); }

@@ -1,0 +1,130 @@
+"""GPU tier: the tcgen05 prefill GEMM (gemm_w4a4_flat / gemm_w4a4 / gemm_w4a8) through the C
+ABI.  Gates: int32 accumulators per (m, n, 128-group) identical to the oracle (dump entries),
+C within 1e-5 relative of the float64 oracle, and within the reference example's 1e-3 of its
+golden vector (examples/python_w4a4_gemm.py:59-83)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import cases
+import w4_oracle as O
+from gpu_util import Bufs
+from k100lc_kernels import Int4Linear, W4Runner, Workspace, synth
+from k100lc_kernels.quant import pack_int4_group128, pack_nibbles
+
+pytestmark = pytest.mark.gpu
+REL = 1e-5
+
+
+def _perm8(q):
+    """int8 codes [M,K] -> the (k0,k2,k4,k6,k1,k3,k5,k7) byte order of quant_rows_a8_k."""
+    m, k = q.shape
+    return np.ascontiguousarray(q.reshape(m, k // 8, 8)[:, :, [0, 2, 4, 6, 1, 3, 5, 7]].astype(np.int8))
+
+
+def run_gemm(rt, L, a8=False, dump=False):
+    m, n, k = L["m"], L["n"], L["k"]
+    g = k // 128
+    qa = O.quant_rows_a8(L["x"]) if a8 else O.quant_rows(L["x"])
+    with Bufs(rt) as b:
+        paq = b.put(_perm8(qa["q"]) if a8 else qa["words"])
+        pwq, pasc, pwsc = b.put(L["wq"]), b.put(qa["scale_gf"]), b.put(L["wsc_gf"])
+        pc = b.zeros(m * n, np.float32, np.nan)
+        base = [paq, pwq, pasc, pwsc, pc, m, n, k]
+        acc = None
+        if dump:
+            pi = b.zeros(m * n * g, np.int32, -7)
+            rt.launch("gemm_w4a8_iacc" if a8 else "gemm_w4a4_iacc", 1, 256, base + [pi])
+            acc = b.get(pi, m * n * g, np.int32).reshape(m, n, g)
+        elif a8:
+            rt.launch("gemm_w4a8", (n // 64) * (m // 128), 256, base)
+        else:
+            rt.launch("gemm_w4a4_flat", (n // 64) * (m // 128), 256, base + [n // 64, 0])
+        c = b.get(pc, m * n).reshape(m, n)
+        assert rt.gemm_status() == 0
+    ref = O.gemm_w4(qa["q"], L["wq"], qa["scale_gf"], L["wsc_gf"])
+    return c, acc, ref
+
+
+@pytest.mark.parametrize("a8", [False, True])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (128, 64, 256), (256, 192, 640), (384, 320, 1024)])
+def test_gemm_accumulators_and_output(rt, a8, m, n, k):
+    L = synth.gemm_layer(n, k, m, seed=900 + m + n)
+    c, acc, ref = run_gemm(rt, L, a8=a8, dump=True)
+    assert np.array_equal(acc, ref["acc"]), "int32 accumulators differ"
+    assert O.rel_err(c, ref["c"]) < REL
+    c2, _, _ = run_gemm(rt, L, a8=a8)
+    assert np.array_equal(c2, c)
+
+
+def test_gemm_reference_example(rt, golden):
+    """The reference's own GEMM self-test: M=256, N=128, K=512, unit weight scales, through
+    W4Runner.gemm (quant_rows_fast_k + gemm_w4a4_flat)."""
+    arr, _ = golden
+    bmat, x = cases.gemm_case()
+    n, k = bmat.shape
+    runner = W4Runner(rt)
+    with Bufs(rt) as b:
+        pwq, pwsc = b.put(pack_nibbles(bmat)), b.put(np.ones((k // 128, n), np.float32))
+        y = runner.gemm(pwq, pwsc, x, n, k)
+        assert rt.gemm_status() == 0
+    runner.close()
+    assert O.rel_err(y, arr["gemm_w4a4.c"]) < 1e-3
+    q = O.quant_rows(x)
+    assert O.rel_err(y, O.gemm_w4(q["q"], pack_nibbles(bmat), q["scale_gf"], np.ones((k // 128, n), np.float32))["c"]) < REL
+
+
+def test_gemm_n64_uses_2d_entry_and_int4linear_prefill(rt):
+    L = synth.gemm_layer(64, 256, 128, seed=77)
+    runner = W4Runner(rt)
+    with Bufs(rt) as b:
+        y = runner.gemm(b.put(L["wq"]), b.put(L["wsc_gf"]), L["x"], 64, 256)      # N/64 == 1 -> gemm_w4a4 (2-D)
+    runner.close()
+    q = O.quant_rows(L["x"])
+    assert O.rel_err(y, O.gemm_w4(q["q"], L["wq"], q["scale_gf"], L["wsc_gf"])["c"]) < REL
+    # Int4Linear routes 128-aligned row counts to the GEMM (W4A4, or W4A8 with prefill="gemm_a8")
+    rng = np.random.default_rng(4)
+    n, k, m = 256, 512, 128
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    packed, scales = pack_int4_group128(w)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    from k100lc_kernels.quant import dequant_int4_group128
+    ref = x.astype(np.float64) @ dequant_int4_group128(packed, scales, n, k).astype(np.float64).T
+    with Workspace(rt) as ws:
+        y4 = Int4Linear(rt, n, k, packed, scales, "w4a4", ws, "g4").forward(x)
+        y8 = Int4Linear(rt, n, k, packed, scales, "w4a8", ws, "g8", prefill="gemm_a8").forward(x)
+    assert rt.gemm_status() == 0
+    assert O.rel_err(y4, ref) < 3e-1 and O.rel_err(y8, ref) < 3e-2
+
+
+@pytest.mark.parametrize("a8", [False, True])
+def test_gemm_full_size_sampled(rt, a8):
+    """M=2048, N=17408, K=5120 (seed 3): C on 48 sampled token rows x 384 sampled channels
+    against the oracle run on exactly those rows, plus the whole-matrix checksum property
+    sum_n C[m,n] == (sum over sampled...) being finite."""
+    L = synth.gemm_layer(seed=3)
+    c, _, _ = run_gemm_sampled(rt, L, a8)
+
+
+def run_gemm_sampled(rt, L, a8):
+    m, n, k = L["m"], L["n"], L["k"]
+    qa = O.quant_rows_a8(L["x"]) if a8 else O.quant_rows(L["x"])
+    with Bufs(rt) as b:
+        paq = b.put(_perm8(qa["q"]) if a8 else qa["words"])
+        pwq, pasc, pwsc = b.put(L["wq"]), b.put(qa["scale_gf"]), b.put(L["wsc_gf"])
+        pc = b.zeros(m * n, np.float32, np.nan)
+        base = [paq, pwq, pasc, pwsc, pc, m, n, k]
+        if a8:
+            rt.launch("gemm_w4a8", (n // 64) * (m // 128), 256, base)
+        else:
+            rt.launch("gemm_w4a4_flat", (n // 64) * (m // 128), 256, base + [n // 64, 0])
+        c = b.get(pc, m * n).reshape(m, n)
+        assert rt.gemm_status() == 0
+    assert np.isfinite(c).all()
+    rng = np.random.default_rng(0)
+    mi = np.sort(rng.choice(m, 48, replace=False))
+    ni = np.sort(rng.choice(n, 384, replace=False))
+    ref = O.gemm_w4(qa["q"][mi], L["wq"][ni], qa["scale_gf"][:, mi], L["wsc_gf"][:, ni])["c"]
+    assert O.rel_err(c[np.ix_(mi, ni)], ref) < REL
+    return c, None, None

@@ -77,7 +77,7 @@ def test_catalog_matches_library():
     for need in ("quant_act", "quant_act4", "nvfp4_quant_act", "quant_rows_fast_k", "quant_rows_k",
                  "gemv_w4a8<1,false,1>", "gemv_w4a8<4,false,2>", "gemv_w4a4<3>", "gemv_w4a4_r2_k",
                  "gemv_w4a4_r2_m3_k", "nvfp4_gemv<2,1>", "nvfp4_gemv_wide<4,2>", "int4_dot_k",
-                 "reduce_blocks_k", "int4_dequant_k"):
+                 "reduce_blocks_k", "int4_dequant_k", "gemm_w4a4_flat", "gemm_w4a4", "gemm_w4a8"):
         assert need in names, need
     k = catalog.info("int4_dot_k")
     assert len(k["args"]) == 14 and k["kernarg_size"] == 80          # as in the reference catalog
