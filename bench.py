@@ -275,6 +275,51 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
     return out
 
 
+def gemm_timings(rt, st: "Stream", reps: int = 5) -> dict:
+    """Prefill GEMM at M = 2048 (N = 17408, K = 5120): row quantiser + tcgen05 GEMM, W4A4 and W4A8,
+    over a rotation of 8 distinct weight layers of the stream (356 MB, larger than L2)."""
+    m, nl = 2048, min(8, st.layers)
+    ops = 2.0 * m * N * K
+    rng = np.random.default_rng(3)
+    x = rt.alloc(m * K * 4)
+    rt.upload(x, rng.standard_normal((m, K)).astype(np.float32))
+    wsc = rt.alloc(NG * N * 4)
+    rt.upload(wsc, (np.abs(rng.standard_normal((NG, N))) * 0.01 + 1e-3).astype(np.float32))
+    aq4, aq8, asc, c = rt.alloc(m * K // 2), rt.alloc(m * K), rt.alloc(NG * m * 4), rt.alloc(m * N * 4)
+    out = {}
+
+    def timed(fn):
+        rt.graph_begin()
+        for l in range(nl):
+            fn(l)
+        g = rt.graph_end()
+        ms = time_graph(rt, g, reps, 3, lambda: None) / nl
+        rt.graph_free(g)
+        return ms
+
+    grid = (N // 64) * (m // 128)
+    q4 = lambda l: rt.launch("quant_rows_fast_k", m, 256, [aq4, asc, x, K, 128, m, K, 0, NG])
+    g4 = lambda l: rt.launch("gemm_w4a4_flat", grid, 256, [aq4, st.wq_l(l), asc, wsc, c, m, N, K, N // 64, 0])
+    q8 = lambda l: rt.launch("quant_rows_a8_k", m, 256, [aq8, 0, asc, 0, x, K, 128, m, K, 0])
+    g8 = lambda l: rt.launch("gemm_w4a8", grid, 256, [aq8, st.wq_l(l), asc, wsc, c, m, N, K])
+    q4(0), q8(0)
+    pk_int8 = 2 * json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"] if (ROOT / "MEASURED_PEAKS.json").is_file() else 2 * 1590.0
+    for name, qf, gf in (("w4a4", q4, g4), ("w4a8", q8, g8)):
+        ms_g = timed(gf)
+        ms_all = timed(lambda l: (qf(l), gf(l)))
+        out[name] = {"gemm_ms": round(ms_g, 4), "quant_plus_gemm_ms": round(ms_all, 4),
+                     "gemm_tmac_per_s": round(ops / 2 / ms_g / 1e9, 1), "quant_plus_gemm_tmac_per_s": round(ops / 2 / ms_all / 1e9, 1),
+                     "gemm_tops": round(ops / ms_g / 1e9, 1),
+                     "frac_of_int8_peak": round(ops / ms_g / 1e9 / pk_int8, 4)}
+    out["int8_peak_tops_assumed"] = pk_int8
+    out["note"] = "int8 peak assumed = 2 x the measured dense bf16 figure (no int8 peak is measured on this pool)"
+    if rt.gemm_status() != 0:
+        raise RuntimeError("a bounded wait ran out in the GEMM kernel")
+    for ptr in (x, wsc, aq4, aq8, asc, c):
+        rt.free(ptr)
+    return out
+
+
 def cpu_baseline(sample_layers: int) -> dict:
     """The reference's CPU arithmetic (NumPy restatement in oracle/) on the host cores, on the
     first `sample_layers` layers of the same stream."""
@@ -404,6 +449,7 @@ def run_ours(args) -> int:
     line = None
     if rank == 0:
         paths = path_timings(rt, st, 5) if args.paths else None
+        gemm = gemm_timings(rt, st) if (args.paths and world == 1) else None
         cpu = cpu_baseline(args.cpu_layers) if (world == 1 and args.cpu_layers > 0) else None
         line = {
             "metric": METRIC, "value": round(total_bytes / ms_step / 1e6, 1), "unit": "GB/s",
@@ -434,7 +480,7 @@ def run_ours(args) -> int:
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4), "peak_source": pk["source"],
                          "us_per_launch": round(us_kernel, 3), "bytes_per_launch": bytes_per_launch,
                          "traffic": None},
-            "cpu_baseline": cpu, "clocks": clocks.summary(), "paths_m1": paths, "setup_seconds": round(setup_s, 1),
+            "cpu_baseline": cpu, "clocks": clocks.summary(), "paths_m1": paths, "prefill_gemm_m2048": gemm, "setup_seconds": round(setup_s, 1),
         }
     if line is not None:
         print(json.dumps(line), flush=True)

@@ -22,9 +22,9 @@
 //     (k0,k2,k4,k6,k1,k3,k5,k7); int8 activations arrive in that order from
 //     quant_rows_a8_k and are copied.  A 4-deep ring of such stages feeds the tensor core;
 //   * one thread issues four tcgen05.mma.kind::i8 (M=128, N=128, K=32) per group into one
-//     of two int32 accumulators in tensor memory and commits to mbarriers;
-//   * four epilogue warps (one TMEM lane = one token row each) drain the accumulator with
-//     tcgen05.ld, convert, and fold it into 128 fp32 running sums per thread with the
+//     of four int32 accumulators in tensor memory (all 512 columns) and commits to an mbarrier;
+//   * eight epilogue warps (one TMEM lane = one token row, half of the columns each) drain the
+//     accumulator with tcgen05.ld, convert, and fold it into 64 fp32 running sums per thread with the
 //     group's scale product.  The integer in TMEM is 256*I (W4A4) or 16*I (W4A8); the
 //     power of two is divided out of the scale, which leaves the fused multiply-add
 //     bit-identical to fmaf(float(I), sa*sb, C).
@@ -41,13 +41,18 @@ namespace {
 
 constexpr int BM = 128, BN = 128, GK = 128;       // tile and quantisation group
 constexpr int STAGES = 4;
-constexpr int SCALE_SLOTS = 8;                     // > STAGES + 2 accumulators in flight
-constexpr int kThreads = 9 * 32;                   // 4 epilogue + 1 MMA + 4 producer warps
+constexpr int NACC = 4;                            // int32 accumulators in tensor memory (4 x 128 columns = all of it)
+constexpr int SCALE_SLOTS = 16;                    // > STAGES + NACC groups in flight
+constexpr int EPI_WARPS = 8;                       // two per TMEM lane quarter: each takes half of the columns
+constexpr int MMA_WARP = EPI_WARPS;                // warp index of the MMA issuer
+constexpr int PROD_WARP0 = EPI_WARPS + 1;          // first of the 4 producer warps
+constexpr int kThreads = (EPI_WARPS + 1 + 4) * 32;
+static_assert(STAGES == NACC, "stage and accumulator share one completion barrier");
 constexpr int TILE_BYTES = BM * GK;                // one int8 operand tile of one group: 16 KB
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;
 constexpr int LBO = (BM / 8) * 128;                // bytes between core matrices adjacent in K
 constexpr int SBO = 128;                           // bytes between 8-row groups
-constexpr int kSpin = 1 << 20;
+constexpr int kSpin = 1 << 17;
 
 struct GemmParams {
     const uint32_t* aq;     // A4: [M][K/8] packed nibbles; A8: [M][K] int8, 8-permuted
@@ -57,14 +62,12 @@ struct GemmParams {
     float* C;               // [M][N]
     int* dump;              // optional [M][N][K/128]
     int M, N, K;
-    int* status;            // optional device int: non-zero after a wait ran out
 };
 
 struct __align__(16) Control {          // head of the dynamic shared memory
     uint64_t full[STAGES];               // producers -> MMA: stage written
-    uint64_t empty[STAGES];              // MMA -> producers: stage consumed
-    uint64_t acc_full[2];                // MMA -> epilogue: accumulator complete
-    uint64_t acc_empty[2];               // epilogue -> MMA: accumulator drained
+    uint64_t acc_full[NACC];             // MMA -> epilogue: accumulator complete; -> producers: stage consumed
+    uint64_t acc_empty[NACC];            // epilogue -> MMA: accumulator drained
     uint64_t sc_full[SCALE_SLOTS];       // producers -> epilogue: scales of a group written
     uint32_t tmem_base;
     volatile int abort;
@@ -83,10 +86,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+#ifndef FM_GEMM_SPIN
+#define FM_GEMM_SPIN 0
+#endif
 // bounded wait that also gives up when another role has raised the abort flag
 __device__ __forceinline__ bool wait_or_abort(uint64_t* b, uint32_t parity, Control* ctl, int* status, int code) {
     for (int i = 0; i < kSpin; i++) {
-        if (mbar_try_wait(b, parity)) return true;
+        if (FM_GEMM_SPIN ? mbar_test_wait(b, parity) : mbar_try_wait(b, parity)) return true;
         if ((i & 63) == 63 && ctl->abort) return false;
     }
     ctl->abort = 1;
@@ -125,6 +137,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// two fp32 lanes per instruction (sm_100 packed fp32): per lane identical to fmul / fmaf
+__device__ __forceinline__ void mul2(float& d0, float& d1, float a, float b0, float b1) {
+    asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2,%2};\nmov.b64 rb, {%3,%4};\nmul.rn.f32x2 rd, ra, rb;\nmov.b64 {%0,%1}, rd;\n}"
+        : "=f"(d0), "=f"(d1) : "f"(a), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void fma2(float& c0, float& c1, float a0, float a1, float b0, float b1) {
+    asm("{\n.reg .b64 ra, rb, rc;\nmov.b64 ra, {%2,%3};\nmov.b64 rb, {%4,%5};\nmov.b64 rc, {%0,%1};\n"
+        "fma.rn.f32x2 rc, ra, rb, rc;\nmov.b64 {%0,%1}, rc;\n}"
+        : "+f"(c0), "+f"(c1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+
 // K-major, no swizzle: start address, LBO (next core matrix in K), SBO (next 8-row group)
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
     uint64_t d = 0;
@@ -153,6 +176,24 @@ __device__ int g_gemm_status;
 __device__ __forceinline__ uint32_t even16(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }   // 16*v of k0,k2,k4,k6
 __device__ __forceinline__ uint32_t odd16(uint32_t w) { return w & 0xF0F0F0F0u; }           // 16*v of k1,k3,k5,k7
 
+// Position of a role in its sequence of (tile, group) steps.  The divisions that turn a tile
+// index into coordinates run once per tile; per group only the counter moves (each role's loop
+// is a serial chain of dependent instructions, so per-step index arithmetic is on the critical path).
+struct Cursor {
+    int g, m0, n0, t;
+    __device__ __forceinline__ void set_tile(int tile, int tiles_m) {
+        t = tile;
+        m0 = (tile % tiles_m) * BM;
+        n0 = (tile / tiles_m) * BN;
+    }
+    __device__ __forceinline__ void next(int G, int tiles_m, int stride) {
+        if (++g == G) {
+            g = 0;
+            set_tile(t + stride, tiles_m);
+        }
+    }
+};
+
 // A8: activations are int8 (quant_rows_a8_k) instead of packed int4.  DUMP: store the integers.
 template <bool A8, bool DUMP>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -170,41 +211,36 @@ gemm_w4_kernel(const GemmParams p) {
     int* status = &g_gemm_status;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(&ctl->full[s], 128);
-            mbar_init(&ctl->empty[s], 1);
-        }
-        for (int b = 0; b < 2; b++) {
+        // one arrival per WARP on the software barriers (hundreds of per-thread arrivals on one
+        // barrier word would serialise)
+        for (int s = 0; s < STAGES; s++) mbar_init(&ctl->full[s], 4);
+        for (int b = 0; b < NACC; b++) {
             mbar_init(&ctl->acc_full[b], 1);
-            mbar_init(&ctl->acc_empty[b], 128);
+            mbar_init(&ctl->acc_empty[b], EPI_WARPS);
         }
-        for (int s = 0; s < SCALE_SLOTS; s++) mbar_init(&ctl->sc_full[s], 128);
+        for (int s = 0; s < SCALE_SLOTS; s++) mbar_init(&ctl->sc_full[s], 4);
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) tmem_alloc(&ctl->tmem_base, 256);                 // two 128-column int32 accumulators
+    if (warp == MMA_WARP) tmem_alloc(&ctl->tmem_base, NACC * BN);    // NACC 128-column int32 accumulators
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
     pdl_wait();
 
-    if (warp >= 5) {
+    if (warp >= PROD_WARP0) {
         // ================================================================ producers
-        const int pw = warp - 5, q = lane >> 3, rr = lane & 7, pt = pw * 32 + lane;
+        const int pw = warp - PROD_WARP0, q = lane >> 3, rr = lane & 7, pt = pw * 32 + lane;
         const int KW = p.K >> 3;                                     // packed words per row
         constexpr int NA = A8 ? 8 : 4;
         uint4 bufA[2][NA], bufB[2][4];
         float fsa[2], fsb[2];
-        auto coords = [&](int it, int& m0, int& n0, int& g) {
-            const int t = (int)blockIdx.x + (it / G) * (int)gridDim.x;
-            g = it % G;
-            m0 = (t % tiles_m) * BM;
-            n0 = (t / tiles_m) * BN;
-        };
-        auto issue = [&](int it, uint4* a, uint4* b, float& sa, float& sb) {
-            int m0, n0, g;
-            coords(it, m0, n0, g);
+        Cursor ld;                                                   // position of the loads (one step ahead)
+        ld.g = 0;
+        ld.set_tile((int)blockIdx.x, tiles_m);
+        auto issue = [&](uint4* a, uint4* b, float& sa, float& sb) {  // loads of the step at `ld`, then advance
+            const int m0 = ld.m0, n0 = ld.n0, g = ld.g;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int row = (i * 4 + pw) * 8 + rr;
@@ -220,6 +256,7 @@ gemm_w4_kernel(const GemmParams p) {
             }
             sa = p.sa[(size_t)g * p.M + m0 + pt];
             sb = (n0 + pt < p.N) ? p.sb[(size_t)g * p.N + n0 + pt] : 0.f;
+            ld.next(G, tiles_m, (int)gridDim.x);
         };
         auto expand_store = [&](uint8_t* tile, int r8, const uint4& w) {   // 4 packed words -> 32 int8
             uint8_t* dst = tile + (2 * q) * LBO + r8 * SBO + rr * 16;
@@ -228,7 +265,7 @@ gemm_w4_kernel(const GemmParams p) {
         };
         auto step = [&](int it, const uint4* a, const uint4* b, float sa, float sb) -> bool {
             const int s = it % STAGES;
-            if (it >= STAGES && !wait_or_abort(&ctl->empty[s], ((it / STAGES) & 1) ^ 1, ctl, status, 1)) return false;
+            if (it >= STAGES && !wait_or_abort(&ctl->acc_full[s], ((it / STAGES) & 1) ^ 1, ctl, status, 1)) return false;
             uint8_t* At = stages + s * STAGE_BYTES;
             uint8_t* Bt = At + TILE_BYTES;
 #pragma unroll
@@ -242,88 +279,112 @@ gemm_w4_kernel(const GemmParams p) {
                 }
                 expand_store(Bt, r8, b[i]);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core's reads
-            mbar_arrive(&ctl->full[s]);
             const int slot = it % SCALE_SLOTS;
             sc_ring[slot * 256 + pt] = sa;
             sc_ring[slot * 256 + 128 + pt] = sb;
-            mbar_arrive(&ctl->sc_full[slot]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&ctl->full[s]);
+                mbar_arrive(&ctl->sc_full[slot]);
+            }
             return true;
         };
-        if (total > 0) issue(0, bufA[0], bufB[0], fsa[0], fsb[0]);
+        if (total > 0) issue(bufA[0], bufB[0], fsa[0], fsb[0]);
         for (int it = 0; it < total; it += 2) {
-            if (it + 1 < total) issue(it + 1, bufA[1], bufB[1], fsa[1], fsb[1]);
+            if (it + 1 < total) issue(bufA[1], bufB[1], fsa[1], fsb[1]);
             if (!step(it, bufA[0], bufB[0], fsa[0], fsb[0])) break;
             if (it + 1 >= total) break;
-            if (it + 2 < total) issue(it + 2, bufA[0], bufB[0], fsa[0], fsb[0]);
+            if (it + 2 < total) issue(bufA[0], bufB[0], fsa[0], fsb[0]);
             if (!step(it + 1, bufA[1], bufB[1], fsa[1], fsb[1])) break;
         }
-    } else if (warp == 4) {
+    } else if (warp == MMA_WARP) {
         // ================================================================ MMA issuer
         if (lane == 0) {
+            // everything that does not depend on the step is computed once: this single thread is
+            // on the critical path of every group, so its loop body is kept to a few instructions
             const uint32_t idesc = instr_desc();
+            const uint64_t adesc0 = smem_desc(smem_u32(stages));
+            const uint64_t bdesc0 = smem_desc(smem_u32(stages) + TILE_BYTES);
+            constexpr uint64_t kStageStep = STAGE_BYTES >> 4, kKStep = (2 * LBO) >> 4;   // descriptor units of 16 bytes
             for (int it = 0; it < total; it++) {
-                const int s = it % STAGES, b = it & 1;
-                if (it >= 2 && !wait_or_abort(&ctl->acc_empty[b], ((it >> 1) & 1) ^ 1, ctl, status, 3)) break;
-                if (!wait_or_abort(&ctl->full[s], (it / STAGES) & 1, ctl, status, 2)) break;
+                const int s = it % STAGES;                  // == accumulator index (STAGES == NACC)
+                const uint32_t ph = (it / STAGES) & 1;
+                if (it >= NACC && !wait_or_abort(&ctl->acc_empty[s], ph ^ 1, ctl, status, 3)) break;
+                if (!wait_or_abort(&ctl->full[s], ph, ctl, status, 2)) break;
                 tc_fence_after();
-                const uint32_t a0 = smem_u32(stages + s * STAGE_BYTES), b0 = a0 + TILE_BYTES;
-#pragma unroll
-                for (int k = 0; k < GK / 32; k++)
-                    tc_mma_i8(tmem_base + b * BN, smem_desc(a0 + k * 2 * LBO), smem_desc(b0 + k * 2 * LBO), idesc, k > 0);
-                tc_commit(&ctl->empty[s]);           // the stage may be overwritten once these MMAs have read it
-                tc_commit(&ctl->acc_full[b]);        // and the accumulator is complete
+                const uint64_t ad = adesc0 + s * kStageStep, bd = bdesc0 + s * kStageStep;
+                const uint32_t d = tmem_base + s * BN;
+                tc_mma_i8(d, ad, bd, idesc, 0);
+                tc_mma_i8(d, ad + kKStep, bd + kKStep, idesc, 1);
+                tc_mma_i8(d, ad + 2 * kKStep, bd + 2 * kKStep, idesc, 1);
+                tc_mma_i8(d, ad + 3 * kKStep, bd + 3 * kKStep, idesc, 1);
+                // one commit per group: STAGES == NACC, so one barrier tells the producers "stage
+                // consumed" and the epilogue "accumulator complete"
+                tc_commit(&ctl->acc_full[s]);
             }
         }
     } else {
         // ================================================================ epilogue
-        const int mrow = warp * 32 + lane;                           // TMEM lane = row of the tile
+        // warp w drains TMEM lanes 32*(w%4).. (a hardware rule) and columns 64*(w/4)..+63
+        constexpr int CPW = BN / (EPI_WARPS / 4);                    // columns per warp: 64
+        const int lq = warp & 3, ch = warp >> 2;
+        const int mrow = lq * 32 + lane;                             // TMEM lane = row of the tile
         const float inv = A8 ? (1.0f / 16.0f) : (1.0f / 256.0f);     // the integer in TMEM is 16*I or 256*I
-        float facc[BN];
+        float facc[CPW];
 #pragma unroll
-        for (int j = 0; j < BN; j++) facc[j] = 0.f;
-        for (int it = 0; it < total; it++) {
-            const int b = it & 1, slot = it % SCALE_SLOTS, g = it % G;
-            const int t = (int)blockIdx.x + (it / G) * (int)gridDim.x;
-            const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+        for (int j = 0; j < CPW; j++) facc[j] = 0.f;
+        Cursor cur;
+        cur.g = 0;
+        cur.set_tile((int)blockIdx.x, tiles_m);
+        for (int it = 0; it < total; it++, cur.next(G, tiles_m, (int)gridDim.x)) {
+            const int b = it % NACC, slot = it % SCALE_SLOTS, g = cur.g;
+            const int m0 = cur.m0, n0 = cur.n0 + ch * CPW;
             if (!wait_or_abort(&ctl->sc_full[slot], (it / SCALE_SLOTS) & 1, ctl, status, 5)) break;
-            if (!wait_or_abort(&ctl->acc_full[b], (it >> 1) & 1, ctl, status, 4)) break;
+            if (!wait_or_abort(&ctl->acc_full[b], (it / NACC) & 1, ctl, status, 4)) break;
             tc_fence_after();
             const float sa = sc_ring[slot * 256 + mrow] * inv;
-            const float* sbv = sc_ring + slot * 256 + 128;
+            const float* sbv = sc_ring + slot * 256 + 128 + ch * CPW;
 #pragma unroll
-            for (int c = 0; c < BN / 32; c++) {
+            for (int c = 0; c < CPW / 32; c++) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * BN + c * 32, r);
+                tmem_ld32(tmem_base + ((uint32_t)(lq * 32) << 16) + b * BN + ch * CPW + c * 32, r);
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    const int v = (int)r[j];
-                    facc[c * 32 + j] = fmaf((float)v, sa * sbv[c * 32 + j], facc[c * 32 + j]);
-                    if (DUMP && n0 + c * 32 + j < p.N)
-                        p.dump[((size_t)(m0 + mrow) * p.N + n0 + c * 32 + j) * G + g] = v >> (A8 ? 4 : 8);
+                for (int j = 0; j < 32; j += 2) {
+                    const int col = c * 32 + j;
+                    const float2 sb2 = *reinterpret_cast<const float2*>(sbv + col);
+                    float s0, s1;
+                    mul2(s0, s1, sa, sb2.x, sb2.y);                  // scale product, rounded to fp32 first
+                    fma2(facc[col], facc[col + 1], (float)(int)r[j], (float)(int)r[j + 1], s0, s1);
+                    if (DUMP) {
+                        int* d = p.dump + ((size_t)(m0 + mrow) * p.N + n0 + col) * G + g;
+                        if (n0 + col < p.N) d[0] = (int)r[j] >> (A8 ? 4 : 8);
+                        if (n0 + col + 1 < p.N) d[G] = (int)r[j + 1] >> (A8 ? 4 : 8);
+                    }
                 }
             }
             tc_fence_before();
-            mbar_arrive(&ctl->acc_empty[b]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->acc_empty[b]);
             if (g == G - 1) {                                        // tile finished: write C and clear
                 float* crow = p.C + (size_t)(m0 + mrow) * p.N + n0;
-                if (n0 + BN <= p.N) {
+                if (n0 + CPW <= p.N) {
 #pragma unroll
-                    for (int j = 0; j < BN; j += 4)
+                    for (int j = 0; j < CPW; j += 4)
                         *reinterpret_cast<float4*>(crow + j) = make_float4(facc[j], facc[j + 1], facc[j + 2], facc[j + 3]);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < BN; j++)
+                    for (int j = 0; j < CPW; j++)
                         if (n0 + j < p.N) crow[j] = facc[j];
                 }
 #pragma unroll
-                for (int j = 0; j < BN; j++) facc[j] = 0.f;
+                for (int j = 0; j < CPW; j++) facc[j] = 0.f;
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem_base, 256);
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, NACC * BN);
     pdl_launch_dependents();
 }
 
