@@ -179,7 +179,7 @@ class Runtime:
 
     def __init__(self, hsaco=None, lib=None, catalog=None):
         global _BOUND_IMAGE
-        image = pathlib.Path(os.environ.get("RT_HSACO") or hsaco or lib or DEFAULT_HSACO)
+        image = pathlib.Path(os.environ.get("RT_HSACO") or hsaco or lib or os.environ.get("FM_ENGINE_LIB") or DEFAULT_HSACO)
         self._lib = load_library(lib or (image if image.suffix == ".so" else None))
         if _BOUND_IMAGE is not None and _BOUND_IMAGE.resolve() != image.resolve():
             raise RuntimeError(
