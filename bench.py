@@ -270,7 +270,31 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         rt.graph_free(g)
         us = ms * 1e3 / nl
         out[name] = {"us_per_layer": round(us, 3), "gb_per_s": round(nbytes * frac / us / 1e3, 1)}
-    for p in (aq, asc4, qa, qb, sc16, nvs):
+    # the same layers through the multi-layer stream kernels (two launches for all nl layers)
+    table = rt.stream_table([(st.wq_l(l), st.ws_l(l), st.x + l * K * 4, st.y + l * N * 4) for l in range(nl)], rows, K, 0)
+    status = rt.alloc(4)
+    rt.memset(status, 0, 4)
+    ae, ao, sc8, su8 = rt.alloc(nl * K // 2), rt.alloc(nl * K // 2), rt.alloc(nl * NG * 4), rt.alloc(nl * NG * 4)
+    aq4, sc4 = rt.alloc(nl * K // 2), rt.alloc(nl * (K // 32) * 4)
+
+    def s8():
+        rt.launch2d("quant_act", NG, nl, 32, 1, [st.x, ae, ao, sc8, su8, nl, K])
+        rt.launch("w4a8_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, ae, ao, sc8, su8])
+
+    def s4():
+        rt.launch2d("quant_act4", K // 32, nl, 32, 1, [st.x, aq4, sc4, nl, K])
+        rt.launch("w4a4_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, aq4, sc4])
+
+    for name, fn in (("w4a8_m1_stream", s8), ("w4a4_m1_stream", s4)):
+        rt.graph_begin()
+        fn()
+        g = rt.graph_end()
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
+        rt.graph_free(g)
+        out[name] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
+    if int(rt.download(status, 1, np.int32)[0]) != 0:
+        raise RuntimeError("a bounded wait ran out in a stream kernel")
+    for p in (aq, asc4, qa, qb, sc16, nvs, table, status, ae, ao, sc8, su8, aq4, sc4):
         rt.free(p)
     return out
 

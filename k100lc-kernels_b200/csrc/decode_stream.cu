@@ -1,4 +1,4 @@
-// w4a8_decode_stream: one launch for the GEMVs of a whole stack of independent W4A8
+// w4a8_decode_stream / w4a4_decode_stream: one launch for the GEMVs of a whole stack of independent W4A8
 // decode layers (M = 1), software-pipelined across layers so that HBM never idles at a
 // layer boundary.  The activation codes of all layers come from one 2-D launch of the
 // ordinary quant_act kernel (grid y = layer) that precedes it.
@@ -21,6 +21,11 @@
 //     words l, l+32, .. of that row (LDS.128) into registers and releases the stage at
 //     once; then nibbles -> dp4a against the token's codes held in registers, two
 //     shuffles per 128-group, f16 scale * act scale * float(I), butterfly, lane 0 stores y.
+//   * W4A8 has a second consumer (the default) that feeds a stage of 16 rows to the tensor
+//     cores as one m16 tile (mma.sync int8), described at w4a8_stream_mma_kernel below: 40 %
+//     fewer instructions per weight byte, which matters because a sustained stream runs at
+//     the board's power limit, where every instruction saved is SM clock (and with it L2 and
+//     fabric bandwidth) kept.
 // Every wait on an mbarrier is bounded; a wait that runs out sets *status and the
 // thread leaves the kernel.
 //
@@ -84,13 +89,17 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 
 // KITER: K = KITER * 1024.  CW: consumer warps = weight rows per ring stage.  STAGES: ring depth.
 // Warp roles: 0..CW-1 consumers, CW producer (one lane).
-template <int KITER, int CW, int STAGES>
+// A4: int4 activations of quant_act4 (packed nibbles + one scale per 32 k) instead of the int8
+//     codes of quant_act; the nibbles are sign-extended to int8 in registers at each layer start
+//     and the integers are lane-private (a 16-byte word is one 32-sub-group).
+template <bool A4, int KITER, int CW, int STAGES>
 __global__ void __launch_bounds__((CW + 1) * 32, 1)
-w4a8_stream_kernel(const StreamParams p) {
+w4_stream_kernel(const StreamParams p) {
     constexpr int K = KITER * 1024, NG = K / 128;
     constexpr int ROWB = K / 2, SCB = NG * 2;
     constexpr int STAGE_W = CW * ROWB, STAGE = STAGE_W + CW * SCB;
-    constexpr int ACT = K + NG * 8;                     // even codes, odd codes, scales, sums
+    constexpr int ACT = A4 ? K / 2 + (K / 32) * 4        // packed nibbles, sub-group scales
+                           : K + NG * 8;               // even codes, odd codes, scales, sums
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);      // [STAGES] weights landed
     uint64_t* empty = full + STAGES;                          // [STAGES] weights copied to registers
@@ -126,10 +135,15 @@ w4a8_stream_kernel(const StreamParams p) {
                 if (l >= 2 && !mbar_wait(&act_free[b], ((l >> 1) & 1) ^ 1, p.status, 4)) return false;
                 uint8_t* ab = act + (size_t)b * ACT;
                 mbar_expect_tx(&act_ready[b], ACT);
-                bulk_g2s(ab, p.ae + (size_t)l * (K / 2), K / 2, &act_ready[b]);
-                bulk_g2s(ab + K / 2, p.ao + (size_t)l * (K / 2), K / 2, &act_ready[b]);
-                bulk_g2s(ab + K, p.asc + (size_t)l * (NG * 4), NG * 4, &act_ready[b]);
-                bulk_g2s(ab + K + NG * 4, p.asu + (size_t)l * (NG * 4), NG * 4, &act_ready[b]);
+                if (A4) {
+                    bulk_g2s(ab, p.ae + (size_t)l * (K / 2), K / 2, &act_ready[b]);                  // aq
+                    bulk_g2s(ab + K / 2, p.asc + (size_t)l * (K / 32 * 4), K / 32 * 4, &act_ready[b]);
+                } else {
+                    bulk_g2s(ab, p.ae + (size_t)l * (K / 2), K / 2, &act_ready[b]);
+                    bulk_g2s(ab + K / 2, p.ao + (size_t)l * (K / 2), K / 2, &act_ready[b]);
+                    bulk_g2s(ab + K, p.asc + (size_t)l * (NG * 4), NG * 4, &act_ready[b]);
+                    bulk_g2s(ab + K + NG * 4, p.asu + (size_t)l * (NG * 4), NG * 4, &act_ready[b]);
+                }
                 return true;
             };
             int c = 0;
@@ -171,10 +185,25 @@ w4a8_stream_kernel(const StreamParams p) {
 #pragma unroll
         for (int it = 0; it < KITER; it++) {
             const int d0 = it * 128 + lane * 4;
-            ae[it] = *reinterpret_cast<const uint4*>(ab + d0 * 4);
-            ao[it] = *reinterpret_cast<const uint4*>(ab + K / 2 + d0 * 4);
-            asc[it] = *reinterpret_cast<const float*>(ab + K + (d0 >> 4) * 4);
-            asu8[it] = 8 * *reinterpret_cast<const int*>(ab + K + NG * 4 + (d0 >> 4) * 4);
+            if (A4) {
+                const uint4 a = *reinterpret_cast<const uint4*>(ab + d0 * 4);      // 32 nibbles = one sub-group
+                ae[it] = make_uint4(sext_nibbles(a.x & 0x0F0F0F0Fu), sext_nibbles(a.y & 0x0F0F0F0Fu),
+                                    sext_nibbles(a.z & 0x0F0F0F0Fu), sext_nibbles(a.w & 0x0F0F0F0Fu));
+                ao[it] = make_uint4(sext_nibbles((a.x >> 4) & 0x0F0F0F0Fu), sext_nibbles((a.y >> 4) & 0x0F0F0F0Fu),
+                                    sext_nibbles((a.z >> 4) & 0x0F0F0F0Fu), sext_nibbles((a.w >> 4) & 0x0F0F0F0Fu));
+                asc[it] = *reinterpret_cast<const float*>(ab + K / 2 + (d0 >> 2) * 4);
+                int su = 0;
+                su = dot4(ae[it].x, 0x01010101u, su); su = dot4(ao[it].x, 0x01010101u, su);
+                su = dot4(ae[it].y, 0x01010101u, su); su = dot4(ao[it].y, 0x01010101u, su);
+                su = dot4(ae[it].z, 0x01010101u, su); su = dot4(ao[it].z, 0x01010101u, su);
+                su = dot4(ae[it].w, 0x01010101u, su); su = dot4(ao[it].w, 0x01010101u, su);
+                asu8[it] = 8 * su;
+            } else {
+                ae[it] = *reinterpret_cast<const uint4*>(ab + d0 * 4);
+                ao[it] = *reinterpret_cast<const uint4*>(ab + K / 2 + d0 * 4);
+                asc[it] = *reinterpret_cast<const float*>(ab + K + (d0 >> 4) * 4);
+                asu8[it] = 8 * *reinterpret_cast<const int*>(ab + K + NG * 4 + (d0 >> 4) * 4);
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&act_free[l & 1]);
@@ -206,9 +235,11 @@ w4a8_stream_kernel(const StreamParams p) {
 #pragma unroll
             for (int it = 0; it < KITER; it++) {
                 int v = dot32_u(w[it], ae[it], ao[it]);
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                if ((lane & 3) == 0) acc += (sw[it] * asc[it]) * (float)(v - asu8[it]);
+                if (!A4) {
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                }
+                if (A4 || (lane & 3) == 0) acc += (sw[it] * asc[it]) * (float)(v - asu8[it]);
             }
             acc = warp_sum(acc);
             if (lane == 0) {
@@ -221,12 +252,216 @@ w4a8_stream_kernel(const StreamParams p) {
     if (p.npeers) __threadfence_system();                    // peer stores are visible before the kernel ends
 }
 
-template <int KITER, int CW, int STAGES>
+// ------------------------------------------------------------------------------------
+// Tensor-core consumer (W4A8, one token).  The dp4a consumer above is bound by the ALU pipe
+// (two LOP3 and two dp4a per packed word, plus shuffles).  Here a stage of 16 weight rows is
+// one m16 tile: each of the 8 consumer warps takes 5 of the 40 groups of all 16 rows and
+// multiplies them with mma.sync m16n8k32 (int8 x int8 -> int32; the token is column 0 of B).
+// Per packed word only the two nibble masks remain: low nibbles as bytes u = n ^ 8 (signed
+// operand), high nibbles in place as unsigned bytes 16*u (the u8 x s8 form), two accumulators,
+//   I[n,g] = acc_lo + (acc_hi >> 4) - 8 * sum(q)        exactly, no shuffles,
+// because the MMA itself adds over the four lanes that share a group.  Warp w scales groups
+// w, w+8, ..., w+32 in fp32 and the eight per-warp partial sums of a row are added by one
+// warp per stage (rotating) through a small shared-memory tile, as the tree
+// ((p0+p4)+(p2+p6)) + ((p1+p5)+(p3+p7)): the association of the dp4a consumer's lane
+// partials and xor-butterfly, so both variants (and gemv_w4a8) give the same bits.
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(9 * 32, 1)
+w4a8_stream_mma_kernel(const StreamParams p) {
+    constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;   // 8 consumer warps x 5 groups, 16 rows per stage
+    constexpr int ROWB = K / 2, SCB = NG * 2;
+    constexpr int STAGE_W = ROWS * ROWB, STAGE = STAGE_W + ROWS * SCB;
+    constexpr int ACT = K + NG * 8;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + STAGES;
+    uint64_t* act_ready = empty + STAGES;     // [2]
+    uint64_t* act_free = act_ready + 2;       // [2]
+    uint64_t* red_full = act_free + 2;        // [2] all eight partial sums of a stage are written
+    uint64_t* red_free = red_full + 2;        // [2] the reducer has read them
+    uint8_t* ring = smem + 256;
+    uint8_t* act = ring + (size_t)STAGES * STAGE;
+    float* red = reinterpret_cast<float*>(act + 2 * ACT);             // [2][CW][ROWS]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CW);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&act_ready[b], 1);
+            mbar_init(&act_free[b], CW);
+            mbar_init(&red_full[b], CW);
+            mbar_init(&red_free[b], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();
+
+    const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const int nst = (r1 - r0 + ROWS - 1) / ROWS;
+
+    if (warp == CW) {
+        if (lane == 0) {                                   // producer: identical to the dp4a kernel's
+            auto copy_codes = [&](int l) -> bool {
+                const int b = l & 1;
+                if (l >= 2 && !mbar_wait(&act_free[b], ((l >> 1) & 1) ^ 1, p.status, 4)) return false;
+                uint8_t* ab = act + (size_t)b * ACT;
+                mbar_expect_tx(&act_ready[b], ACT);
+                bulk_g2s(ab, p.ae + (size_t)l * (K / 2), K / 2, &act_ready[b]);
+                bulk_g2s(ab + K / 2, p.ao + (size_t)l * (K / 2), K / 2, &act_ready[b]);
+                bulk_g2s(ab + K, p.asc + (size_t)l * (NG * 4), NG * 4, &act_ready[b]);
+                bulk_g2s(ab + K + NG * 4, p.asu + (size_t)l * (NG * 4), NG * 4, &act_ready[b]);
+                return true;
+            };
+            int c = 0;
+            const uint8_t* wq = p.layers[0].wq;
+            const uint8_t* ws = p.layers[0].ws;
+            if (!copy_codes(0)) return;
+            for (int l = 0; l < p.nlayers; l++) {
+                const int ln = min(l + 1, p.nlayers - 1);
+                const uint8_t* wq_n = p.layers[ln].wq;
+                const uint8_t* ws_n = p.layers[ln].ws;
+                for (int j = 0; j < nst; j++, c++) {
+                    const int s = c % STAGES;
+                    if (c >= STAGES && !mbar_wait(&empty[s], ((c / STAGES) & 1) ^ 1, p.status, 1)) return;
+                    const int row = r0 + j * ROWS;
+                    const int nr = min(ROWS, r1 - row);
+                    uint8_t* dst = ring + (size_t)s * STAGE;
+                    mbar_expect_tx(&full[s], (uint32_t)(nr * (ROWB + SCB)));
+                    bulk_g2s(dst, wq + (size_t)row * ROWB, (uint32_t)(nr * ROWB), &full[s]);
+                    bulk_g2s(dst + STAGE_W, ws + (size_t)row * SCB, (uint32_t)(nr * SCB), &full[s]);
+                    if (j == 0 && l + 1 < p.nlayers && !copy_codes(l + 1)) return;
+                }
+                wq = wq_n;
+                ws = ws_n;
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;                 // fragment coordinates: rows g and g+8, k slot t
+    int c = 0;
+    for (int l = 0; l < p.nlayers; l++) {
+        const uint8_t* ab = act + (size_t)(l & 1) * ACT;
+        if (!mbar_wait(&act_ready[l & 1], (l >> 1) & 1, p.status, 2)) return;
+        uint4 be[GPW], bo[GPW];                            // B fragments: codes of the token for this lane's k slots
+        float sa[GPW];
+        int su8[GPW];
+#pragma unroll
+        for (int j = 0; j < GPW; j++) {
+            const int gg = j * CW + warp;                   // this warp's groups: warp, warp + 8, ...
+            be[j] = *reinterpret_cast<const uint4*>(ab + (gg * 16 + 4 * t) * 4);
+            bo[j] = *reinterpret_cast<const uint4*>(ab + K / 2 + (gg * 16 + 4 * t) * 4);
+            sa[j] = *reinterpret_cast<const float*>(ab + K + gg * 4);
+            su8[j] = 8 * *reinterpret_cast<const int*>(ab + K + NG * 4 + gg * 4);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&act_free[l & 1]);
+        float* y = p.layers[l].y + p.row_base;
+
+        for (int jst = 0; jst < nst; jst++, c++) {
+            const int s = c % STAGES;
+            if (!mbar_wait(&full[s], (c / STAGES) & 1, p.status, 3)) return;
+            const uint8_t* st = ring + (size_t)s * STAGE;
+            uint4 xa[GPW], xb[GPW];                        // packed words of rows g and g+8
+            float swa[GPW], swb[GPW];
+#pragma unroll
+            for (int j = 0; j < GPW; j++) {
+                const int gg = j * CW + warp;                   // this warp's groups: warp, warp + 8, ...
+                xa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * ROWB + gg * 64 + t * 16);
+                xb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * ROWB + gg * 64 + t * 16);
+                swa[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + g * SCB + gg * 2));
+                swb[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + (g + 8) * SCB + gg * 2));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);          // registers hold the stage: refill may start
+            float fa = 0.f, fb = 0.f;                       // partial y of rows g and g+8 over this warp's groups
+#pragma unroll
+            for (int j = 0; j < GPW; j++) {
+                int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+                const uint32_t m_lo = 0x0F0F0F0Fu, x_lo = 0x08080808u, m_hi = 0xF0F0F0F0u, x_hi = 0x80808080u;
+                mma_s8(lo, (xa[j].x & m_lo) ^ x_lo, (xb[j].x & m_lo) ^ x_lo, (xa[j].y & m_lo) ^ x_lo, (xb[j].y & m_lo) ^ x_lo,
+                       be[j].x, be[j].y);
+                mma_s8(lo, (xa[j].z & m_lo) ^ x_lo, (xb[j].z & m_lo) ^ x_lo, (xa[j].w & m_lo) ^ x_lo, (xb[j].w & m_lo) ^ x_lo,
+                       be[j].z, be[j].w);
+                mma_u8(hi, (xa[j].x & m_hi) ^ x_hi, (xb[j].x & m_hi) ^ x_hi, (xa[j].y & m_hi) ^ x_hi, (xb[j].y & m_hi) ^ x_hi,
+                       bo[j].x, bo[j].y);
+                mma_u8(hi, (xa[j].z & m_hi) ^ x_hi, (xb[j].z & m_hi) ^ x_hi, (xa[j].w & m_hi) ^ x_hi, (xb[j].w & m_hi) ^ x_hi,
+                       bo[j].z, bo[j].w);
+                // column 0 (the token) of the accumulator tile sits in the lanes with t == 0
+                const int ia = lo[0] + (hi[0] >> 4) - su8[j];
+                const int ib = lo[2] + (hi[2] >> 4) - su8[j];
+                fa += (swa[j] * sa[j]) * (float)ia;
+                fb += (swb[j] * sa[j]) * (float)ib;
+            }
+            const int rb = c & 1;
+            if (c >= 2 && !mbar_wait(&red_free[rb], ((c >> 1) & 1) ^ 1, p.status, 5)) return;
+            if (t == 0) {
+                red[(rb * CW + warp) * ROWS + g] = fa;
+                red[(rb * CW + warp) * ROWS + g + 8] = fb;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_full[rb]);
+            if (warp == (c % CW)) {                         // this stage's reducer: fixed order over the warps
+                if (!mbar_wait(&red_full[rb], (c >> 1) & 1, p.status, 6)) return;
+                const int row = r0 + jst * ROWS + lane;
+                float acc = 0.f;
+                if (lane < ROWS) {
+                    const float* pr = red + rb * CW * ROWS + lane;
+                    acc = ((pr[0 * ROWS] + pr[4 * ROWS]) + (pr[2 * ROWS] + pr[6 * ROWS])) +
+                          ((pr[1 * ROWS] + pr[5 * ROWS]) + (pr[3 * ROWS] + pr[7 * ROWS]));
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_free[rb]);
+                if (lane < ROWS && row < r1) {
+                    y[row] = acc;
+                    for (int q = 0; q < p.npeers; q++)
+                        *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
+                }
+            }
+        }
+    }
+    if (p.npeers) __threadfence_system();
+}
+
+template <int STAGES>
+int run_stream_mma(const char* kn, const LaunchCtx& c, const StreamParams& p) {
+    constexpr int K = 5120;
+    constexpr size_t smem = 256 + (size_t)STAGES * 16 * (K / 2 + 80) + 2 * (K + 320) + 2 * 8 * 16 * 4;
+    static_assert(smem <= 227 * 1024, "shared memory");
+    auto kern = w4a8_stream_mma_kernel<STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        configured = true;
+    }
+    int grid = c.sm_count;
+    if (grid > p.rows) grid = p.rows;
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(9 * 32), smem, c.stream, pdl_enabled(), p);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
+template <bool A4, int KITER, int CW, int STAGES>
 int run_stream(const char* kn, const LaunchCtx& c, const StreamParams& p) {
     constexpr int K = KITER * 1024;
     constexpr size_t smem = 256 + (size_t)STAGES * CW * (K / 2 + (K / 128) * 2) + 2 * (K + (K / 128) * 8);
     static_assert(smem <= 227 * 1024, "shared memory");
-    auto kern = w4a8_stream_kernel<KITER, CW, STAGES>;
+    auto kern = w4_stream_kernel<A4, KITER, CW, STAGES>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -248,12 +483,16 @@ int run_stream(const char* kn, const LaunchCtx& c, const StreamParams& p) {
 //   peer_delta  device array of npeers signed byte offsets (peer y address - local y address),
 //               filled by fm_stream_peers from allocations opened with fm_ipc_import
 //   status      device int, must be 0 before the launch; non-zero afterwards = a bounded
-//               wait ran out (1 producer/ring, 2 codes not landed, 3 consumer/ring, 4 code tile not free)
+//               wait ran out (1 producer/ring, 2 codes not landed, 3 consumer/ring, 4 code tile not free,
+//               5 / 6 partial-sum tile of the tensor-core variant)
 //   ae, ao, asc, asu   outputs of quant_act launched with grid y = nlayers over x [nlayers][K]:
 //               int8 codes [nlayers][K/2] twice, f32 scales and int32 sums [nlayers][K/128]
 // grid and work-group arguments are ignored (persistent: one CTA per SM).
-int launch_w4a8_stream(const LaunchCtx& c, const uint64_t* a) {
-    const char* kn = "w4a8_decode_stream";
+// w4a4_decode_stream(layers, nlayers, rows, K, row_base, npeers, peer_delta, status, aq, asc): the same
+// with the outputs of quant_act4 (grid y = nlayers): packed nibbles [nlayers][K/2], scales [nlayers][K/32].
+template <bool A4>
+int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = A4 ? "w4a4_decode_stream" : "w4a8_decode_stream";
     StreamParams p = {};
     p.layers = arg_ptr<const StreamLayer>(a[0]);
     p.nlayers = arg_i32(a[1]);
@@ -264,9 +503,13 @@ int launch_w4a8_stream(const LaunchCtx& c, const uint64_t* a) {
     p.peer_delta = arg_ptr<const long long>(a[6]);
     p.status = arg_ptr<int>(a[7]);
     p.ae = arg_ptr<const uint8_t>(a[8]);
-    p.ao = arg_ptr<const uint8_t>(a[9]);
-    p.asc = arg_ptr<const uint8_t>(a[10]);
-    p.asu = arg_ptr<const uint8_t>(a[11]);
+    if (A4) {
+        p.asc = arg_ptr<const uint8_t>(a[9]);
+    } else {
+        p.ao = arg_ptr<const uint8_t>(a[9]);
+        p.asc = arg_ptr<const uint8_t>(a[10]);
+        p.asu = arg_ptr<const uint8_t>(a[11]);
+    }
     FM_REQUIRE(p.K == 5120, kn, "K=%d: the fused stream is built for K = 5120 only; launch the per-layer kernels", p.K);
     FM_REQUIRE(p.nlayers >= 0 && p.rows > 0 && p.row_base >= 0 && p.npeers >= 0 && p.npeers <= 7, kn,
                "bad nlayers/rows/row_base/npeers");
@@ -279,24 +522,24 @@ int launch_w4a8_stream(const LaunchCtx& c, const uint64_t* a) {
                (const void*)p.layers, p.nlayers, p.rows, p.K, p.row_base);
     FM_RANGE(p.status, 4, kn, "status");
     if (p.npeers) FM_RANGE(p.peer_delta, (size_t)p.npeers * 8, kn, "peer_delta");
-    FM_REQUIRE(aligned(p.ae, 16) && aligned(p.ao, 16) && aligned(p.asc, 16) && aligned(p.asu, 16), kn,
+    FM_REQUIRE(aligned(p.ae, 16) && aligned(p.asc, 16) && (A4 || (aligned(p.ao, 16) && aligned(p.asu, 16))), kn,
                "the activation code arrays must be 16-byte aligned");
-    FM_RANGE(p.ae, (size_t)p.nlayers * (p.K / 2), kn, "ae");
-    FM_RANGE(p.ao, (size_t)p.nlayers * (p.K / 2), kn, "ao");
-    FM_RANGE(p.asc, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asc");
-    FM_RANGE(p.asu, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asu");
-    // ring geometry: $FM_STREAM_CFG picks one of the built shapes (consumer warps x stages)
-    static const int cfg = getenv("FM_STREAM_CFG") ? atoi(getenv("FM_STREAM_CFG")) : 0;
-    switch (cfg) {
-        case 1: return run_stream<5, 16, 4>(kn, c, p);
-        case 2: return run_stream<5, 12, 6>(kn, c, p);
-        case 3: return run_stream<5, 20, 4>(kn, c, p);
-        default: return run_stream<5, 16, 5>(kn, c, p);      // 16 rows x 5 stages = 211 KB in flight per SM
+    FM_RANGE(p.ae, (size_t)p.nlayers * (p.K / 2), kn, A4 ? "aq" : "ae");
+    FM_RANGE(p.asc, (size_t)p.nlayers * (p.K / (A4 ? 32 : 128)) * 4, kn, "asc");
+    if (!A4) {
+        FM_RANGE(p.ao, (size_t)p.nlayers * (p.K / 2), kn, "ao");
+        FM_RANGE(p.asu, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asu");
     }
+    // consumer: W4A8 defaults to the tensor-core variant; $FM_STREAM_CFG=1 (and W4A4 always) takes
+    // the dp4a consumer.  Both keep 16 rows x 5 stages = 211 KB in flight per SM and give the same bits.
+    static const int cfg = getenv("FM_STREAM_CFG") ? atoi(getenv("FM_STREAM_CFG")) : 0;
+    if (!A4 && cfg != 1) return run_stream_mma<5>(kn, c, p);
+    return run_stream<A4, 5, 16, 5>(kn, c, p);
 }
 
 const KernelEntry kStream[] = {
-    {"w4a8_decode_stream", 12, launch_w4a8_stream, "piiiiipppppp"},
+    {"w4a8_decode_stream", 12, launch_w4_stream<false>, "piiiiipppppp"},
+    {"w4a4_decode_stream", 10, launch_w4_stream<true>, "piiiiipppp"},
 };
 
 }  // namespace

@@ -100,3 +100,27 @@ def test_stream_row_base_and_repeat(rt):
         with pytest.raises(RuntimeError, match="fm_stream_table"):
             rt.stream_table([(ptrs[0][0], ptrs[0][1], ptrs[0][2], ys[0])], rows, K, n_out)
         assert int(b.get(status, 1, np.int32)[0]) == 0
+
+
+def test_w4a4_stream_matches_oracle(rt):
+    """The int4-activation variant: one 2-D quant_act4 launch, then w4a4_decode_stream."""
+    rows, nl = 1000, 4
+    layers = [synth.rt4_layer(rows, K, 1, seed=850 + i) for i in range(nl)]
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"][0] for L in layers]))
+        aq, asc = b.zeros(nl * K // 2, np.uint8), b.zeros(nl * K // 32)
+        ptrs, ys = [], []
+        for i, L in enumerate(layers):
+            py = b.zeros(rows, np.float32, np.nan)
+            ys.append(py)
+            ptrs.append((b.put(L["wq"]), b.put(L["ws"]), x + i * K * 4, py))
+        table = rt.stream_table(ptrs, rows, K, 0)
+        status = b.zeros(1, np.int32)
+        rt.launch2d("quant_act4", K // 32, nl, 32, 1, [x, aq, asc, nl, K])
+        rt.launch("w4a4_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, aq, asc])
+        got = [b.get(py, rows) for py in ys]
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+    for L, y in zip(layers, got):
+        q = O.quant_act4(L["x"])
+        assert O.rel_err(y, O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 32)["y"][0]) < REL

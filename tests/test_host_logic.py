@@ -166,3 +166,33 @@ def test_out_of_scope_operators_say_so():
     for name in ("RMSNorm", "Attention", "MoEExperts", "Sampler"):
         with pytest.raises(NotImplementedError):
             getattr(kk, name)()
+
+
+def test_ct_int4_safetensors_reader(tmp_path):
+    """A synthetic compressed-tensors checkpoint split over two files is read back row by row."""
+    from k100lc_kernels.ct_int4 import CTInt4Layer, SafeTensors, write_safetensors
+    rng = np.random.default_rng(3)
+    n, k = 24, 256
+    w = (rng.standard_normal((n, k)) * 0.03).astype(np.float32)
+    packed, scales = quant.pack_int4_group128(w)
+    pre = "model.layers.0.mlp.gate_proj"
+    write_safetensors(tmp_path / "a.safetensors", {
+        pre + ".weight_packed": ("I32", np.frombuffer(packed, np.int32).reshape(n, k // 8)),
+        "other.bias": ("F32", np.zeros(7, np.float32))})
+    write_safetensors(tmp_path / "b.safetensors", {
+        pre + ".weight_scale": ("BF16", np.frombuffer(scales, np.uint16).reshape(n, k // 128)),
+        pre + ".weight_shape": ("I64", np.array([n, k], np.int64))})
+    lay = CTInt4Layer(pre, tmp_path)
+    assert (lay.n, lay.k, lay.nbpr) == (n, k, 2) and "N=24" in repr(lay)
+    assert lay.packed_rows() == packed and lay.scale_rows() == scales
+    assert lay.packed_rows(5, 3) == packed[5 * k // 2: 8 * k // 2]
+    assert np.array_equal(lay.dequant_rows(), quant.dequant_int4_group128(packed, scales, n, k))
+    assert np.array_equal(lay.dequant_rows(20, 4), quant.dequant_int4_group128(packed, scales, n, k)[20:])
+    st = SafeTensors(tmp_path / "a.safetensors")
+    assert st.array("other.bias").shape == (7,) and pre + ".weight_packed" in st
+    with pytest.raises(ValueError):
+        lay.packed_rows(20, 9)
+    with pytest.raises(KeyError):
+        CTInt4Layer("missing.layer", tmp_path)
+    with pytest.raises(ValueError):
+        st.read("other.bias", 20, 20)
