@@ -26,6 +26,7 @@ import pathlib
 import statistics
 import subprocess
 import sys
+import threading
 import time
 
 import numpy as np
@@ -69,51 +70,70 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    """SM clock, power and throttle-reason samples taken while the timed region runs.
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    A thread polls NVML (read-only queries) every 2 ms, so that even a 50 ms timed region gets
+    tens of samples; `window(t0, t1)` keeps the samples whose host time lies inside the region.
+    Without NVML the summary says so instead of inventing numbers."""
+
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
     def __init__(self, device: int):
-        self.device, self.proc, self.path = device, None, f"/tmp/fm_clocks_{os.getpid()}.csv"
+        self.samples, self.t0, self.t1 = [], None, None
+        self._stop, self._thread, self._h, self._nv = threading.Event(), None, None, None
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        ids = [v for v in vis.split(",") if v.strip().isdigit()]
+        self.index = int(ids[device]) if device < len(ids) else device
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+            import pynvml as nv
+            nv.nvmlInit()
+            self._nv, self._h = nv, nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.smax = nv.nvmlDeviceGetMaxClockInfo(self._h, nv.NVML_CLOCK_SM)
+        except Exception as e:                        # no NVML on this host
+            self._why = f"NVML unavailable: {type(e).__name__}"
+            return self
+        self._thread = threading.Thread(target=self._poll, daemon=True)
+        self._thread.start()
         return self
 
-    def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
+    def _poll(self):
+        nv, h = self._nv, self._h
+        reasons_of = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
             try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+                self.samples.append((time.perf_counter(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+                                     int(reasons_of(h)), nv.nvmlDeviceGetPowerUsage(h) / 1000.0))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def window(self, t0: float, t1: float) -> None:
+        self.t0, self.t1 = t0, t1
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+            try:
+                self._nv.nvmlShutdown()
+            except Exception:
+                pass
 
     def summary(self) -> dict:
-        sm, smax, reasons = [], [], set()
-        try:
-            for line in open(self.path):
-                f = [t.strip() for t in line.split(",")]
-                if len(f) < 9 or not f[1].isdigit():
-                    continue
-                sm.append(int(f[1]))
-                smax.append(int(f[2]))
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
-        except OSError:
-            pass
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
-        return {"sm_mhz": int(statistics.median(sm)), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        rows = [r for r in self.samples if self.t0 is None or self.t0 <= r[0] <= self.t1]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [getattr(self, "_why", "no NVML sample inside the timed region")],
+                    "samples": 0}
+        bits = 0
+        for r in rows:
+            bits |= r[2]
+        return {"sm_mhz": int(statistics.median(r[1] for r in rows)), "sm_min_mhz": min(r[1] for r in rows),
+                "sm_max_mhz": int(self.smax), "power_w": round(statistics.median(r[3] for r in rows), 1),
+                "reasons": [name for name, bit in self.REASONS if bits & bit], "samples": len(rows),
+                "how": "NVML polled every 2 ms by a host thread during the timed region"}
 
 
 # --------------------------------------------------------------------------- ours
@@ -166,11 +186,13 @@ class Stream:
         self.enqueue_token(**kw)
         return self.rt.graph_end()
 
-    def capture_fused(self) -> int:
+    def capture_fused(self, host_mirror: bool = False) -> int:
         """One decoded token as TWO launches: quant_act over the x of all layers (grid y =
         layer), then the multi-layer stream kernel (bulk-copy ring over all layers' weights).
         With several GPUs the kernel's epilogue stores every y row into the y buffer of every
-        peer as well (the all-gather, over NVLink peer mappings), so no collective follows."""
+        peer as well (the all-gather, over NVLink peer mappings), so no collective follows.
+        With `host_mirror` the pinned host array y_host is one more receiver of this rank's
+        rows: the result reaches the host while the kernel runs, with no copy afterwards."""
         rt, nl = self.rt, self.layers
         if not hasattr(self, "table"):
             base = self.rank * self.rows
@@ -187,10 +209,16 @@ class Stream:
                 bases = [peers[r] for r in range(self.world) if r != self.rank]
                 self.deltas = rt.stream_peers(bases, self.y, nl * N * 4)
                 self.npeers = len(bases)
+            self.bases = bases if self.world > 1 else []
+        npeers, deltas = self.npeers, self.deltas
+        if host_mirror:
+            if not hasattr(self, "deltas_host"):
+                self.deltas_host = rt.stream_peers(self.bases + [self.y_host.ctypes.data], self.y, nl * N * 4)
+            npeers, deltas = self.npeers + 1, self.deltas_host
         rt.graph_begin()
         rt.launch2d("quant_act", NG, nl, 32, 1, [self.x, self.ae_all, self.ao_all, self.asc_all, self.asu_all, nl, K])
-        rt.launch("w4a8_decode_stream", 1, 1, [self.table, nl, self.rows, K, self.rank * self.rows, self.npeers,
-                                               self.deltas, self.status,
+        rt.launch("w4a8_decode_stream", 1, 1, [self.table, nl, self.rows, K, self.rank * self.rows, npeers,
+                                               deltas, self.status,
                                                self.ae_all, self.ao_all, self.asc_all, self.asu_all])
         return rt.graph_end()
 
@@ -201,20 +229,24 @@ class Stream:
         return hashlib.sha1(self.rt.download(self.y, self.layers * N, np.float32).tobytes()).hexdigest()
 
 
-def time_graph(rt, graph, steps, warmup, barrier, counter=None) -> float:
+def time_graph(rt, graph, steps, warmup, barrier, counter=None, clocks=None) -> float:
     """ms per launch of `graph`, CUDA events on the engine stream, barrier + sync both sides.
-    `counter`, if given, receives the number of kernels launched inside the timed region."""
+    `counter`, if given, receives the number of kernels launched inside the timed region;
+    `clocks` (a ClockSampler) is told the host-time window of the region."""
     for _ in range(warmup):
         rt.graph_launch(graph)
     rt.sync()
     barrier()
     e0, e1 = rt.event(), rt.event()
     n0 = rt.launch_count()
+    t0 = time.perf_counter()
     rt.record(e0)
     for _ in range(steps):
         rt.graph_launch(graph)
     rt.record(e1)
     rt.sync()
+    if clocks is not None:
+        clocks.window(t0, time.perf_counter())
     barrier()
     if counter is not None:
         counter.append(rt.launch_count() - n0)
@@ -409,15 +441,20 @@ def run_ours(args) -> int:
     log("graph captured")
     counted = []
     with ClockSampler(rt.device_attr("device")) as clocks:
-        ms_step = time_graph(rt, graph, args.steps, args.warmup, barrier, counted)
+        ms_step = time_graph(rt, graph, args.steps, args.warmup, barrier, counted, clocks)
     gpu_launches = counted[0]                       # kernels of this library inside the timed region
 
     log(f"timed region done: {ms_step:.3f} ms/step")
     # end to end through the C ABI with host buffers: x of all layers up, y of all layers back, every step
+    # (fused: the kernel itself delivers this rank's rows of y to the pinned host array; per-layer
+    # mode copies the gathered y back after the graph)
+    graph_e2e = st.capture_fused(host_mirror=True) if fused else graph
+    st.y_host[:] = np.nan
     def e2e_step():
         rt.upload_async(st.x, st.x_host)
-        rt.graph_launch(graph)
-        rt.download_async(st.y_host, st.y)
+        rt.graph_launch(graph_e2e)
+        if not fused:
+            rt.download_async(st.y_host, st.y)
     for _ in range(max(1, args.warmup)):
         e2e_step()
     rt.sync()
@@ -430,6 +467,11 @@ def run_ours(args) -> int:
     rt.sync()
     barrier()
     ms_e2e = rt.elapsed_ms(e0, e1) / args.steps
+    if fused:                                       # what the host received is what the device holds
+        lo = rank * st.rows
+        dev_y = rt.download(st.y, args.layers * N, np.float32).reshape(args.layers, N)
+        if not np.array_equal(st.y_host[:, lo:lo + st.rows].view(np.uint32), dev_y[:, lo:lo + st.rows].view(np.uint32)):
+            raise RuntimeError("the host copy of y written by the stream kernel differs from the device copy")
 
     # the dominant kernel alone, for the roofline: the fused stream kernel is the whole step;
     # in per-layer mode it is gemv_w4a8<1,false,1> without the quantiser
@@ -491,8 +533,11 @@ def run_ours(args) -> int:
                        "l2": "inputs (18.4 GB of weights) are larger than L2; no flush needed"},
             "ms_per_token": round(ms_step, 4), "us_per_layer": round(ms_step * 1e3 / args.layers, 3),
             "e2e": {"value": round(total_bytes / ms_e2e / 1e6, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e, 4),
-                    "h2d_bytes_per_step": args.layers * K * 4, "d2h_bytes_per_step": args.layers * N * 4,
-                    "api": "fm_upload_async(x) + fm_graph_launch + fm_download_async(y), pinned host buffers"},
+                    "h2d_bytes_per_step": world * args.layers * K * 4, "d2h_bytes_per_step": args.layers * N * 4,
+                    "api": ("fm_upload_async(x of all layers, every rank) + fm_graph_launch; the stream kernel stores each "
+                            "rank's rows of y into a pinned host array (fm_host_alloc, registered through fm_stream_peers) "
+                            "while it runs; fm_sync ends the step") if fused else
+                           "fm_upload_async(x) + fm_graph_launch + fm_download_async(y), pinned host buffers"},
             "gpu_launches": int(gpu_launches),
             "per_layer_launches": None if ms_alt is None else {
                 "ms_per_token": round(ms_alt, 4), "us_per_layer": round(ms_alt * 1e3 / args.layers, 3),

@@ -102,9 +102,11 @@ int   fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers,
  * 64-byte CUDA IPC handle of the fm_alloc allocation that contains `dev`, the offset of
  * `dev` in it and its size; another rank opens it with fm_ipc_import (peer access is
  * enabled on the way) and releases it with fm_free.  fm_stream_peers checks that
- * [peer_bases[q], +span) lies inside an imported allocation for every q and that
- * [local_base, +span) is a local one, then writes the npeers byte offsets
- * (peer - local) to dev_deltas for w4a8_decode_stream. */
+ * [peer_bases[q], +span) lies inside an imported allocation — or inside a pinned host buffer from
+ * fm_host_alloc, which makes the kernel deliver y to the host while it runs instead of a
+ * device-to-host copy afterwards — for every q (npeers 1..8) and that [local_base, +span) is a
+ * local allocation, then writes the npeers byte offsets (copy - local) to dev_deltas for
+ * w4a8_decode_stream / w4a4_decode_stream. */
 int   fm_ipc_export(const void* dev, void* out_handle64, unsigned long long* out_offset,
                     unsigned long long* out_size);
 void* fm_ipc_import(const void* handle64, unsigned long long size);

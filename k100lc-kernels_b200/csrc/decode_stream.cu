@@ -41,6 +41,7 @@ namespace fm {
 namespace {
 
 constexpr int kSpinLimit = 1 << 22;
+constexpr int kOutCap = 512;           // rows of one CTA whose y values of a layer are collected in shared memory
 
 struct StreamLayer {                   // one entry of the device-side layer table (32 bytes)
     const uint8_t* wq;                 // [rows][K/2] packed two's-complement nibbles
@@ -87,13 +88,29 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// Output tile.  A CTA's y values of one layer (at most kOutCap rows, else they are stored one by
+// one) are collected in shared memory and written out once per layer by one warp as coalesced
+// 128-byte stores: to the local y and to every additional copy (other GPUs' y over NVLink, a
+// pinned host buffer over PCIe).  Per-row 4- or 64-byte stores are fine for HBM but throttle
+// the kernel when they cross a link.  ydone[b] counts the consumer warps that have finished the
+// layer, yfree[b] is set by the writer when the tile may be overwritten (two tiles alternate).
+// The writer is a warp of its own, so that a slow link never holds up a consumer.
+__device__ __forceinline__ void write_out(const StreamParams& p, const float* tile, float* y, int n, int lane) {
+    for (int i = lane; i < n; i += 32) {
+        const float v = tile[i];
+        y[i] = v;
+        for (int q = 0; q < p.npeers; q++)
+            *reinterpret_cast<float*>(reinterpret_cast<char*>(y + i) + p.peer_delta[q]) = v;
+    }
+}
+
 // KITER: K = KITER * 1024.  CW: consumer warps = weight rows per ring stage.  STAGES: ring depth.
-// Warp roles: 0..CW-1 consumers, CW producer (one lane).
+// Warp roles: 0..CW-1 consumers, CW producer (one lane), CW+1 writer of the output tile.
 // A4: int4 activations of quant_act4 (packed nibbles + one scale per 32 k) instead of the int8
 //     codes of quant_act; the nibbles are sign-extended to int8 in registers at each layer start
 //     and the integers are lane-private (a 16-byte word is one 32-sub-group).
 template <bool A4, int KITER, int CW, int STAGES>
-__global__ void __launch_bounds__((CW + 1) * 32, 1)
+__global__ void __launch_bounds__((CW + 2) * 32, 1)
 w4_stream_kernel(const StreamParams p) {
     constexpr int K = KITER * 1024, NG = K / 128;
     constexpr int ROWB = K / 2, SCB = NG * 2;
@@ -105,8 +122,11 @@ w4_stream_kernel(const StreamParams p) {
     uint64_t* empty = full + STAGES;                          // [STAGES] weights copied to registers
     uint64_t* act_ready = empty + STAGES;                     // [2] codes of a layer are in shared memory
     uint64_t* act_free = act_ready + 2;                       // [2] every consumer has its register copy
+    uint64_t* ydone = act_free + 2;                           // [2] output tile complete
+    uint64_t* yfree = ydone + 2;                              // [2] output tile written out
     uint8_t* ring = smem + 256;
     uint8_t* act = ring + (size_t)STAGES * STAGE;             // [2][ACT]
+    float* ytile = reinterpret_cast<float*>(act + 2 * ACT);   // [2][kOutCap]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -117,6 +137,8 @@ w4_stream_kernel(const StreamParams p) {
         for (int b = 0; b < 2; b++) {
             mbar_init(&act_ready[b], 1);
             mbar_init(&act_free[b], CW);
+            mbar_init(&ydone[b], CW);
+            mbar_init(&yfree[b], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -126,6 +148,7 @@ w4_stream_kernel(const StreamParams p) {
     const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
     const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
     const int nst = (r1 - r0 + CW - 1) / CW;             // stages per layer for this CTA
+    const bool tiled = (r1 - r0) <= kOutCap;
 
     if (warp == CW) {
         // ------------------------------------------------------------ producer
@@ -173,10 +196,24 @@ w4_stream_kernel(const StreamParams p) {
         return;
     }
 
+    if (warp == CW + 1) {                                    // writer: one coalesced pass per layer over the output tile
+        if (!tiled) return;
+        for (int l = 0; l < p.nlayers; l++) {
+            if (!mbar_wait(&ydone[l & 1], (l >> 1) & 1, p.status, 8)) return;
+            write_out(p, ytile + (l & 1) * kOutCap, p.layers[l].y + p.row_base + r0, r1 - r0, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&yfree[l & 1]);
+        }
+        if (p.npeers) __threadfence_system();
+        return;
+    }
+
     // ---------------------------------------------------------------- consumers
     int c = 0;
     for (int l = 0; l < p.nlayers; l++) {
         const uint8_t* ab = act + (size_t)(l & 1) * ACT;
+        float* yt = ytile + (l & 1) * kOutCap;
+        if (tiled && l >= 2 && !mbar_wait(&yfree[l & 1], ((l >> 1) & 1) ^ 1, p.status, 7)) return;
         if (!mbar_wait(&act_ready[l & 1], (l >> 1) & 1, p.status, 2)) return;
         // register copy of the token's codes for this lane's words
         uint4 ae[KITER], ao[KITER];
@@ -243,10 +280,18 @@ w4_stream_kernel(const StreamParams p) {
             }
             acc = warp_sum(acc);
             if (lane == 0) {
-                y[row] = acc;
-                for (int q = 0; q < p.npeers; q++)           // all-gather by direct peer stores over NVLink
-                    *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
+                if (tiled) {
+                    yt[row - r0] = acc;
+                } else {
+                    y[row] = acc;
+                    for (int q = 0; q < p.npeers; q++)       // all-gather by direct peer stores over NVLink
+                        *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
+                }
             }
+        }
+        if (tiled) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ydone[l & 1]);
         }
     }
     if (p.npeers) __threadfence_system();                    // peer stores are visible before the kernel ends
@@ -275,7 +320,7 @@ __device__ __forceinline__ void mma_u8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 }
 
 template <int STAGES>
-__global__ void __launch_bounds__(9 * 32, 1)
+__global__ void __launch_bounds__(10 * 32, 1)
 w4a8_stream_mma_kernel(const StreamParams p) {
     constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;   // 8 consumer warps x 5 groups, 16 rows per stage
     constexpr int ROWB = K / 2, SCB = NG * 2;
@@ -288,9 +333,12 @@ w4a8_stream_mma_kernel(const StreamParams p) {
     uint64_t* act_free = act_ready + 2;       // [2]
     uint64_t* red_full = act_free + 2;        // [2] all eight partial sums of a stage are written
     uint64_t* red_free = red_full + 2;        // [2] the reducer has read them
+    uint64_t* ydone = red_free + 2;           // [2] output tile complete
+    uint64_t* yfree = ydone + 2;              // [2] output tile written out
     uint8_t* ring = smem + 256;
     uint8_t* act = ring + (size_t)STAGES * STAGE;
     float* red = reinterpret_cast<float*>(act + 2 * ACT);             // [2][CW][ROWS]
+    float* ytile = red + 2 * CW * ROWS;                               // [2][kOutCap]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -303,6 +351,8 @@ w4a8_stream_mma_kernel(const StreamParams p) {
             mbar_init(&act_free[b], CW);
             mbar_init(&red_full[b], CW);
             mbar_init(&red_free[b], 1);
+            mbar_init(&ydone[b], CW);
+            mbar_init(&yfree[b], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -312,6 +362,7 @@ w4a8_stream_mma_kernel(const StreamParams p) {
     const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
     const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
     const int nst = (r1 - r0 + ROWS - 1) / ROWS;
+    const bool tiled = (r1 - r0) <= kOutCap;
 
     if (warp == CW) {
         if (lane == 0) {                                   // producer: identical to the dp4a kernel's
@@ -352,11 +403,25 @@ w4a8_stream_mma_kernel(const StreamParams p) {
         return;
     }
 
+    if (warp == CW + 1) {                                    // writer: one coalesced pass per layer over the output tile
+        if (!tiled) return;
+        for (int l = 0; l < p.nlayers; l++) {
+            if (!mbar_wait(&ydone[l & 1], (l >> 1) & 1, p.status, 8)) return;
+            write_out(p, ytile + (l & 1) * kOutCap, p.layers[l].y + p.row_base + r0, r1 - r0, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&yfree[l & 1]);
+        }
+        if (p.npeers) __threadfence_system();
+        return;
+    }
+
     // ---------------------------------------------------------------- consumers
     const int g = lane >> 2, t = lane & 3;                 // fragment coordinates: rows g and g+8, k slot t
     int c = 0;
     for (int l = 0; l < p.nlayers; l++) {
         const uint8_t* ab = act + (size_t)(l & 1) * ACT;
+        float* yt = ytile + (l & 1) * kOutCap;
+        if (tiled && l >= 2 && !mbar_wait(&yfree[l & 1], ((l >> 1) & 1) ^ 1, p.status, 7)) return;
         if (!mbar_wait(&act_ready[l & 1], (l >> 1) & 1, p.status, 2)) return;
         uint4 be[GPW], bo[GPW];                            // B fragments: codes of the token for this lane's k slots
         float sa[GPW];
@@ -428,11 +493,19 @@ w4a8_stream_mma_kernel(const StreamParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_free[rb]);
                 if (lane < ROWS && row < r1) {
-                    y[row] = acc;
-                    for (int q = 0; q < p.npeers; q++)
-                        *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
+                    if (tiled) {
+                        yt[row - r0] = acc;
+                    } else {
+                        y[row] = acc;
+                        for (int q = 0; q < p.npeers; q++)
+                            *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
+                    }
                 }
             }
+        }
+        if (tiled) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ydone[l & 1]);
         }
     }
     if (p.npeers) __threadfence_system();
@@ -441,7 +514,7 @@ w4a8_stream_mma_kernel(const StreamParams p) {
 template <int STAGES>
 int run_stream_mma(const char* kn, const LaunchCtx& c, const StreamParams& p) {
     constexpr int K = 5120;
-    constexpr size_t smem = 256 + (size_t)STAGES * 16 * (K / 2 + 80) + 2 * (K + 320) + 2 * 8 * 16 * 4;
+    constexpr size_t smem = 256 + (size_t)STAGES * 16 * (K / 2 + 80) + 2 * (K + 320) + 2 * 8 * 16 * 4 + 2 * kOutCap * 4;
     static_assert(smem <= 227 * 1024, "shared memory");
     auto kern = w4a8_stream_mma_kernel<STAGES>;
     static bool configured = false;
@@ -452,14 +525,14 @@ int run_stream_mma(const char* kn, const LaunchCtx& c, const StreamParams& p) {
     }
     int grid = c.sm_count;
     if (grid > p.rows) grid = p.rows;
-    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(9 * 32), smem, c.stream, pdl_enabled(), p);
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(10 * 32), smem, c.stream, pdl_enabled(), p);
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
 template <bool A4, int KITER, int CW, int STAGES>
 int run_stream(const char* kn, const LaunchCtx& c, const StreamParams& p) {
     constexpr int K = KITER * 1024;
-    constexpr size_t smem = 256 + (size_t)STAGES * CW * (K / 2 + (K / 128) * 2) + 2 * (K + (K / 128) * 8);
+    constexpr size_t smem = 256 + (size_t)STAGES * CW * (K / 2 + (K / 128) * 2) + 2 * (K + (K / 128) * 8) + 2 * kOutCap * 4;
     static_assert(smem <= 227 * 1024, "shared memory");
     auto kern = w4_stream_kernel<A4, KITER, CW, STAGES>;
     static bool configured = false;
@@ -470,7 +543,7 @@ int run_stream(const char* kn, const LaunchCtx& c, const StreamParams& p) {
     }
     int grid = c.sm_count;
     if (grid > p.rows) grid = p.rows;
-    cudaError_t e = launch_kernel(kern, dim3(grid), dim3((CW + 1) * 32), smem, c.stream, pdl_enabled(), p);
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3((CW + 2) * 32), smem, c.stream, pdl_enabled(), p);
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
@@ -479,7 +552,8 @@ int run_stream(const char* kn, const LaunchCtx& c, const StreamParams& p) {
 //               fm_stream_table (which range-checks every pointer in it)
 //   rows        weight rows held by this GPU (N, or N / number of GPUs)
 //   row_base    first output index of this GPU's rows inside each layer's y
-//   npeers      0, or the number of other GPUs whose y copies also receive the rows;
+//   npeers      0, or the number of other copies of y that also receive the rows (other GPUs'
+//               buffers and/or a pinned host buffer: up to 8);
 //   peer_delta  device array of npeers signed byte offsets (peer y address - local y address),
 //               filled by fm_stream_peers from allocations opened with fm_ipc_import
 //   status      device int, must be 0 before the launch; non-zero afterwards = a bounded
@@ -511,7 +585,7 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
         p.asu = arg_ptr<const uint8_t>(a[11]);
     }
     FM_REQUIRE(p.K == 5120, kn, "K=%d: the fused stream is built for K = 5120 only; launch the per-layer kernels", p.K);
-    FM_REQUIRE(p.nlayers >= 0 && p.rows > 0 && p.row_base >= 0 && p.npeers >= 0 && p.npeers <= 7, kn,
+    FM_REQUIRE(p.nlayers >= 0 && p.rows > 0 && p.row_base >= 0 && p.npeers >= 0 && p.npeers <= 8, kn,
                "bad nlayers/rows/row_base/npeers");
     if (p.nlayers == 0) return FM_OK;
     FM_REQUIRE(aligned(p.layers, 8) && aligned(p.status, 4), kn, "misaligned layer table or status");

@@ -59,6 +59,7 @@ struct Engine {
     struct Peers { int npeers; uintptr_t lo, hi; };
     std::map<uintptr_t, Peers> peers;            // validated peer-offset arrays (device address -> window)
     std::map<uintptr_t, size_t> imported;        // peer allocations opened through CUDA IPC
+    std::map<uintptr_t, size_t> pinned;          // fm_host_alloc buffers (device-addressable host memory)
     std::vector<cudaEvent_t> events;
     std::vector<Graph> graphs;
     std::unordered_map<uint64_t, int> plan_graphs;   // plan hash -> graph id
@@ -527,10 +528,21 @@ void* fm_host_alloc(size_t n) {
     LOCK;
     NEED_INIT(nullptr);
     void* p = nullptr;
-    if (cudaHostAlloc(&p, n ? n : 1, cudaHostAllocDefault) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (cudaHostAlloc(&p, n ? n : 1, cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    E().pinned[reinterpret_cast<uintptr_t>(p)] = n ? n : 1;
     return p;
 }
-void fm_host_free(void* p) { if (p) cudaFreeHost(p); }
+void fm_host_free(void* p) {
+    if (!p) return;
+    {
+        LOCK;
+        E().pinned.erase(reinterpret_cast<uintptr_t>(p));
+    }
+    cudaFreeHost(p);
+}
 
 int fm_upload_async(void* dev, const void* host, size_t n) {
     LOCK;
@@ -626,23 +638,24 @@ int fm_stream_peers(void* dev_deltas, const uint64_t* peer_bases, int npeers, co
     LOCK;
     NEED_INIT(-1);
     Engine& e = E();
-    if (npeers < 1 || npeers > 7) { set_errorf("fm_stream_peers: npeers must be 1..7"); return -1; }
+    if (npeers < 1 || npeers > 8) { set_errorf("fm_stream_peers: npeers must be 1..8"); return -1; }
     if (!range_ok(dev_deltas, (size_t)npeers * 8) || !range_ok(local_base, span)) {
         set_errorf("fm_stream_peers: the offset array or the local window is outside its allocation");
         return FM_EREJECT;
     }
-    long long delta[7];
+    long long delta[8];
     for (int q = 0; q < npeers; q++) {
         const uintptr_t pb = static_cast<uintptr_t>(peer_bases[q]);
-        auto it = e.imported.upper_bound(pb);
-        bool ok = it != e.imported.begin();
-        if (ok) {
+        bool ok = false;                             // a peer GPU's imported allocation, or a pinned host buffer
+        for (const auto* m : {&e.imported, &e.pinned}) {
+            auto it = m->upper_bound(pb);
+            if (it == m->begin()) continue;
             --it;
-            ok = pb >= it->first && pb + span <= it->first + it->second;
+            ok = ok || (pb >= it->first && pb + span <= it->first + it->second);
         }
         if (!ok) {
-            set_errorf("fm_stream_peers: peer window %d (%llu bytes at %p) is not inside an imported allocation", q, span,
-                       reinterpret_cast<void*>(pb));
+            set_errorf("fm_stream_peers: window %d (%llu bytes at %p) is neither inside an imported allocation nor "
+                       "inside an fm_host_alloc buffer", q, span, reinterpret_cast<void*>(pb));
             return FM_EREJECT;
         }
         delta[q] = (long long)pb - (long long)reinterpret_cast<uintptr_t>(local_base);
