@@ -124,3 +124,64 @@ def test_w4a4_stream_matches_oracle(rt):
     for L, y in zip(layers, got):
         q = O.quant_act4(L["x"])
         assert O.rel_err(y, O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 32)["y"][0]) < REL
+
+
+@pytest.mark.parametrize("kernel", ["w4a8_decode_stream", "w4a4_decode_stream"])
+def test_stream_delivers_y_to_pinned_host_memory(rt, kernel):
+    """A pinned host buffer registered through fm_stream_peers is one more receiver of y: after
+    fm_sync it holds the bits of the device copy, rows outside the shard untouched."""
+    rows, base, n_out, nl = 1500, 500, 2500, 5
+    a4 = kernel.startswith("w4a4")
+    layers = [synth.rt4_layer(rows, K, 1, seed=870 + i) for i in range(nl)]
+    host = rt.pinned((nl, n_out), np.float32)
+    host[:] = np.nan
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"][0] for L in layers]))
+        y = b.zeros(nl * n_out, np.float32, np.nan)
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), x + i * K * 4, y + i * n_out * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, base)
+        status = b.zeros(1, np.int32)
+        # ordinary (pageable) host memory is not an accepted receiver
+        with pytest.raises(RuntimeError, match="fm_stream_peers"):
+            rt.stream_peers([np.zeros(nl * n_out, np.float32).ctypes.data], y, nl * n_out * 4)
+        deltas = rt.stream_peers([host.ctypes.data], y, nl * n_out * 4)
+        if a4:
+            aq, asc = b.zeros(nl * K // 2, np.uint8), b.zeros(nl * K // 32)
+            rt.launch2d("quant_act4", K // 32, nl, 32, 1, [x, aq, asc, nl, K])
+            rt.launch(kernel, 1, 1, [table, nl, rows, K, base, 1, deltas, status, aq, asc])
+        else:
+            ae, ao = b.zeros(nl * K // 2, np.int8), b.zeros(nl * K // 2, np.int8)
+            asc, asu = b.zeros(nl * K // 128), b.zeros(nl * K // 128, np.int32)
+            rt.launch2d("quant_act", K // 128, nl, 32, 1, [x, ae, ao, asc, asu, nl, K])
+            rt.launch(kernel, 1, 1, [table, nl, rows, K, base, 1, deltas, status, ae, ao, asc, asu])
+        dev = b.get(y, nl * n_out).reshape(nl, n_out)          # drains the stream
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+        rt.free(deltas)
+    assert np.array_equal(host.view(np.uint32), dev.view(np.uint32))
+    assert np.isnan(host[:, :base]).all() and np.isnan(host[:, base + rows:]).all()
+    for i, L in enumerate(layers):
+        q = O.quant_act4(L["x"]) if a4 else O.quant_act(L["x"])
+        ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 32 if a4 else 128)["y"][0]
+        assert O.rel_err(host[i, base:base + rows], ref) < REL
+
+
+def test_stream_many_rows_per_cta(rt):
+    """More rows per CTA than the shared-memory output tile holds (512): y is then stored row by
+    row.  The oracle checks the first and last rows, the per-layer kernel all of them."""
+    sms = rt.device_attr("sm_count")
+    rows = sms * 512 + 64
+    rng = np.random.default_rng(890)                       # (synth.rt4_layer is too slow for 75 840 rows)
+    L = {"wq": rng.integers(0, 2**32, size=(rows, K // 8), dtype=np.uint32),
+         "ws": (np.abs(rng.standard_normal((rows, K // 128))) * 0.01 + 1e-3).astype(np.float16),
+         "x": rng.standard_normal((1, K)).astype(np.float32)}
+    runner = W4Runner(rt)
+    with Bufs(rt) as b:
+        got, ptrs = _run_stream(rt, b, [L], rows)
+        per_layer = runner.gemv("w4a8", ptrs[0][0], ptrs[0][1], L["x"], rows, K)[0]
+        assert np.array_equal(got[0].view(np.uint32), per_layer.view(np.uint32))
+    runner.close()
+    q = O.quant_act(L["x"])
+    for sl in (slice(0, 1024), slice(rows - 1024, rows)):
+        ref = O.gemv_w4(L["wq"][sl], L["ws"][sl], q["q"], q["scale"], 128)["y"][0]
+        assert O.rel_err(got[0][sl], ref) < REL
