@@ -26,6 +26,8 @@
 // dependent launch they overlap the tail of the activation quantiser.
 #include <cuda_fp16.h>
 
+#include <stdlib.h>
+
 #include "device_utils.cuh"
 #include "fm_internal.h"
 
@@ -94,7 +96,7 @@ __device__ __forceinline__ int dot32(const uint4& w, const uint4& e, const uint4
 // AREG   : hold the activations in registers (needs KITER > 0 and M == 1)
 // DUMP   : also store the integer accumulators
 template <bool A4, int M, int R, int KITER, bool AREG, bool DUMP>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 gemv_w4_kernel(const GemvW4Params p) {
     extern __shared__ __align__(16) uint32_t smem[];
     const int KD = p.K >> 3;                     // 32-bit words per weight row
@@ -111,23 +113,31 @@ gemv_w4_kernel(const GemvW4Params p) {
     const int iters = KITER > 0 ? KITER : (KD + 127) >> 7;
     constexpr int UN = KITER > 0 ? KITER : 1;
 
-    // -- weights of the first row block: independent of the preceding kernel --
+    // -- weights and scales of the first row block: independent of the preceding kernel --
+    // (one block is always in flight: the loads of block rb + nwarp are issued right after block rb
+    //  has been consumed, so HBM latency overlaps the arithmetic and the reduction)
     uint4 wreg[R][UN];
-    int rb = gwarp;
-    if (KITER > 0) {
+    float swreg[R][UN];
+    auto fetch = [&](int blk) {
 #pragma unroll
         for (int r = 0; r < R; r++) {
-            const int row = rb * R + r;
+            const int row = blk * R + r;
+            const bool live = row < p.rows;
 #pragma unroll
-            for (int it = 0; it < UN; it++)
-                wreg[r][it] = row < p.rows ? ld_stream_v4(p.wq + (size_t)row * KD + it * 128 + lane * 4)
-                                           : make_uint4(0, 0, 0, 0);
+            for (int it = 0; it < UN; it++) {
+                const int d0 = it * 128 + lane * 4;
+                wreg[r][it] = live ? ld_stream_v4(p.wq + (size_t)row * KD + d0) : make_uint4(0, 0, 0, 0);
+                swreg[r][it] = live ? __half2float(p.ws[(size_t)row * NG + (d0 >> 4)]) : 0.f;
+            }
         }
-    }
+    };
+    int rb = gwarp;
+    if (KITER > 0) fetch(rb);
 
     pdl_wait();
-    stage_activations<A4>(p, M, s_e, s_o, s_sc, s_su);
 
+    // one token and K = 5120: the codes of the token go straight from global memory (L2) into
+    // registers; otherwise they are staged in shared memory for all warps of the CTA
     uint4 areg_e[AREG ? UN : 1], areg_o[AREG ? UN : 1];
     float areg_sc[AREG ? UN : 1];
     int areg_su[AREG ? UN : 1];
@@ -135,12 +145,28 @@ gemv_w4_kernel(const GemvW4Params p) {
 #pragma unroll
         for (int it = 0; it < UN; it++) {
             const int d0 = it * 128 + lane * 4;
-            areg_e[it] = *reinterpret_cast<const uint4*>(s_e + d0);
-            areg_o[it] = *reinterpret_cast<const uint4*>(s_o + d0);
-            const int si = A4 ? (d0 >> 2) : (d0 >> 4);
-            areg_sc[it] = s_sc[si];
-            areg_su[it] = s_su[si];
+            if (A4) {                                       // 32 nibbles = one 32-sub-group per lane and step
+                const uint4 a = *reinterpret_cast<const uint4*>(p.a0 + d0);
+                areg_e[it] = make_uint4(sext_nibbles(a.x & 0x0F0F0F0Fu), sext_nibbles(a.y & 0x0F0F0F0Fu),
+                                        sext_nibbles(a.z & 0x0F0F0F0Fu), sext_nibbles(a.w & 0x0F0F0F0Fu));
+                areg_o[it] = make_uint4(sext_nibbles((a.x >> 4) & 0x0F0F0F0Fu), sext_nibbles((a.y >> 4) & 0x0F0F0F0Fu),
+                                        sext_nibbles((a.z >> 4) & 0x0F0F0F0Fu), sext_nibbles((a.w >> 4) & 0x0F0F0F0Fu));
+                areg_sc[it] = p.asc[d0 >> 2];
+                int su = 0;
+                su = dot4(areg_e[it].x, 0x01010101u, su); su = dot4(areg_o[it].x, 0x01010101u, su);
+                su = dot4(areg_e[it].y, 0x01010101u, su); su = dot4(areg_o[it].y, 0x01010101u, su);
+                su = dot4(areg_e[it].z, 0x01010101u, su); su = dot4(areg_o[it].z, 0x01010101u, su);
+                su = dot4(areg_e[it].w, 0x01010101u, su); su = dot4(areg_o[it].w, 0x01010101u, su);
+                areg_su[it] = su;
+            } else {
+                areg_e[it] = *reinterpret_cast<const uint4*>(p.a0 + d0);
+                areg_o[it] = *reinterpret_cast<const uint4*>(p.a1 + d0);
+                areg_sc[it] = p.asc[d0 >> 4];
+                areg_su[it] = p.asu[d0 >> 4];
+            }
         }
+    } else {
+        stage_activations<A4>(p, M, s_e, s_o, s_sc, s_su);
     }
 
     for (; rb * R < p.rows; rb += nwarp) {
@@ -151,25 +177,6 @@ gemv_w4_kernel(const GemvW4Params p) {
             for (int m = 0; m < M; m++) acc[r][m] = 0.f;
 
         if (KITER > 0) {
-            // issue the scale loads and, for every block after the first, the weight loads
-            float sw[R][UN];
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int row = min(rb * R + r, p.rows - 1);
-#pragma unroll
-                for (int it = 0; it < UN; it++)
-                    sw[r][it] = __half2float(p.ws[(size_t)row * NG + ((it * 128 + lane * 4) >> 4)]);
-            }
-            if (rb != gwarp) {
-#pragma unroll
-                for (int r = 0; r < R; r++) {
-                    const int row = rb * R + r;
-#pragma unroll
-                    for (int it = 0; it < UN; it++)
-                        wreg[r][it] = row < p.rows ? ld_stream_v4(p.wq + (size_t)row * KD + it * 128 + lane * 4)
-                                                   : make_uint4(0, 0, 0, 0);
-                }
-            }
 #pragma unroll
             for (int it = 0; it < UN; it++) {
                 const int d0 = it * 128 + lane * 4;
@@ -189,7 +196,7 @@ gemv_w4_kernel(const GemvW4Params p) {
                         }
                         const int I = v - 8 * su;
                         if (A4 || (lane & 3) == 0) {
-                            acc[r][m] += (sw[r][it] * sa) * (float)I;
+                            acc[r][m] += (swreg[r][it] * sa) * (float)I;
                             if (DUMP) {
                                 const int row = rb * R + r;
                                 if (row < p.rows) p.iacc[((size_t)m * p.N + row) * nsc + si] = I;
@@ -198,6 +205,7 @@ gemv_w4_kernel(const GemvW4Params p) {
                     }
                 }
             }
+            fetch(rb + nwarp);                              // next block of this warp (no loads past the end)
         } else {
             for (int it = 0; it < iters; it++) {
                 const int d0 = it * 128 + lane * 4;
@@ -260,7 +268,7 @@ int run_variant(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
     auto kern = gemv_w4_kernel<A4, M, R, KITER, AREG, DUMP>;
     const int KD = p.K / 8;
     const int nsc = A4 ? p.K / 32 : p.K / 128;
-    const size_t smem = (size_t)M * (2 * KD * 4 + nsc * 8);
+    const size_t smem = AREG ? 0 : (size_t)M * (2 * KD * 4 + nsc * 8);
     FM_REQUIRE(smem <= 200 * 1024, kn, "K=%d needs %zu bytes of shared memory for %d tokens (limit 200 KiB)", p.K,
                smem, M);
     if (smem > 48 * 1024) {
@@ -272,6 +280,8 @@ int run_variant(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
     if (e != cudaSuccess) return cuda_fail(kn, e);
     if (per_sm < 1) per_sm = 1;
+    static const int cap = getenv("FM_GEMV_CTAS") ? atoi(getenv("FM_GEMV_CTAS")) : 0;
+    if (cap > 0 && per_sm > cap) per_sm = cap;
     int grid = c.sm_count * per_sm;
     if (grid > blocks_needed) grid = blocks_needed;
     e = launch_kernel(kern, dim3(grid), dim3(kThreads), smem, c.stream, pdl_enabled(), p);
