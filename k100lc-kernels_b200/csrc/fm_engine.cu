@@ -60,6 +60,8 @@ struct Engine {
     std::map<uintptr_t, Peers> peers;            // validated peer-offset arrays (device address -> window)
     std::map<uintptr_t, size_t> imported;        // peer allocations opened through CUDA IPC
     std::map<uintptr_t, size_t> pinned;          // fm_host_alloc buffers (device-addressable host memory)
+    void* scratch = nullptr;                     // kernel-internal workspace (grows on demand)
+    size_t scratch_bytes = 0;
     std::vector<cudaEvent_t> events;
     std::vector<Graph> graphs;
     std::unordered_map<uint64_t, int> plan_graphs;   // plan hash -> graph id
@@ -289,6 +291,27 @@ int after_launch(const char* kernel) {
 }
 
 bool pdl_enabled() { return E().pdl; }
+
+// Device workspace owned by the engine for intermediates that the reference ABI has no argument
+// for.  It only grows, and growing means a synchronising free + allocation, which a stream
+// capture forbids: inside a capture a request beyond the current size returns nullptr.
+void* engine_scratch(size_t bytes) {
+    Engine& e = E();
+    if (bytes <= e.scratch_bytes) return e.scratch;
+    if (e.capturing) return nullptr;
+    cudaStreamSynchronize(e.stream);
+    if (e.scratch) cudaFree(e.scratch);
+    e.scratch = nullptr;
+    e.scratch_bytes = 0;
+    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    if (cudaMalloc(&e.scratch, want) != cudaSuccess) {
+        cudaGetLastError();
+        e.scratch = nullptr;
+        return nullptr;
+    }
+    e.scratch_bytes = want;
+    return e.scratch;
+}
 
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
                      int npeers) {

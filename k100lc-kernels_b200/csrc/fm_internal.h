@@ -32,6 +32,9 @@ int reject(const char* kernel, const char* fmt, ...);   // records the message, 
 int cuda_fail(const char* kernel, cudaError_t e);       // records the message, returns FM_ECUDA
 int after_launch(const char* kernel);                   // cudaGetLastError -> FM_OK / FM_ECUDA
 bool pdl_enabled();                                     // programmatic dependent launch on?
+// engine-owned device workspace of at least `bytes` (contents undefined); nullptr when it would
+// have to grow inside a stream capture or the allocation fails
+void* engine_scratch(size_t bytes);
 // true when `table` was filled by fm_stream_table with exactly these shapes and has not been
 // overwritten since (or checks are off): every pointer inside it was range-checked then; with
 // npeers > 0 the offset array must come from fm_stream_peers and cover every y of the table

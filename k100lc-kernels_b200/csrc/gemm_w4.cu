@@ -12,15 +12,19 @@
 //   C[m,n] = fmaf(float(I), sa[g*M+m] * sb[g*N+n], C[m,n])   (scale product rounded first).
 //
 // Mapping.  One persistent CTA per SM walks 128 x 128 output tiles (m fastest, so the CTAs
-// that run together share a weight tile in L2).  Per tile and per group:
-//   * four producer warps read the packed rows of A and W for this group (64 B per row),
-//     turn every nibble into the int8 value 16*v by masking it in place in the high half
-//     of its byte ((w & 0xF0F0F0F0) for odd k, ((w << 4) & 0xF0F0F0F0) for even k — the
-//     two's-complement nibble is then the byte's sign and magnitude), and store the bytes
-//     in the K-major core-matrix layout tcgen05.mma reads (8 rows x 16 bytes per core
-//     matrix, no swizzle).  Both operands use the same k order inside a word
-//     (k0,k2,k4,k6,k1,k3,k5,k7); int8 activations arrive in that order from
-//     quant_rows_a8_k and are copied.  A 4-deep ring of such stages feeds the tensor core;
+// that run together share a weight tile in L2).  Per tile and per 128-k group:
+//   * one thread (the copy lane) issues TMA copies into a 4-deep ring: the int8 activation
+//     tile (128 rows x 128 bytes, 128-byte swizzle — exactly the K-major layout tcgen05.mma
+//     reads), the packed weight tile (128 rows x 64 bytes, 64-byte swizzle) and the two
+//     scale vectors of the group.  int4 activations are widened to int8 (16*v) once per call by
+//     a small kernel in front, into an engine-owned workspace, so the GEMM never repeats
+//     that for every column tile;
+//   * four producer warps turn every weight nibble into the int8 value 16*v by masking it
+//     in place in the high half of its byte ((w & 0xF0F0F0F0) for odd k,
+//     ((w << 4) & 0xF0F0F0F0) for even k — the two's-complement nibble is then the byte's
+//     sign and magnitude), shared memory to shared memory, into the un-swizzled core-matrix
+//     layout (8 rows x 16 bytes).  Both operands use the same k order inside a word
+//     (k0,k2,k4,k6,k1,k3,k5,k7); int8 activations arrive in that order from quant_rows_a8_k;
 //   * one thread issues four tcgen05.mma.kind::i8 (M=128, N=128, K=32) per group into one
 //     of four int32 accumulators in tensor memory (all 512 columns) and commits to an mbarrier;
 //   * eight epilogue warps (one TMEM lane = one token row, half of the columns each) drain the
@@ -31,6 +35,7 @@
 // Every mbarrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, the
 // status word is set, all roles leave their loops, tensor memory is released and the
 // kernel returns.
+#include <cuda.h>          // CUtensorMap and its enums; the encoder itself is resolved at run time
 #include <stdlib.h>
 
 #include "device_utils.cuh"
@@ -42,33 +47,37 @@ namespace {
 constexpr int BM = 128, BN = 128, GK = 128;       // tile and quantisation group
 constexpr int STAGES = 4;
 constexpr int NACC = 4;                            // int32 accumulators in tensor memory (4 x 128 columns = all of it)
-constexpr int SCALE_SLOTS = 16;                    // > STAGES + NACC groups in flight
+constexpr int SCALE_SLOTS = 16;                    // > 2 * NACC groups between a slot's write and its reuse
 constexpr int EPI_WARPS = 8;                       // two per TMEM lane quarter: each takes half of the columns
 constexpr int MMA_WARP = EPI_WARPS;                // warp index of the MMA issuer
-constexpr int PROD_WARP0 = EPI_WARPS + 1;          // first of the 4 producer warps
-constexpr int kThreads = (EPI_WARPS + 1 + 4) * 32;
+constexpr int TMA_WARP = EPI_WARPS + 1;            // warp whose lane 0 issues the copies
+constexpr int PROD_WARP0 = EPI_WARPS + 2;          // first of the 4 producer warps
+constexpr int kThreads = (EPI_WARPS + 2 + 4) * 32;
 static_assert(STAGES == NACC, "stage and accumulator share one completion barrier");
-constexpr int TILE_BYTES = BM * GK;                // one int8 operand tile of one group: 16 KB
-constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-constexpr int LBO = (BM / 8) * 128;                // bytes between core matrices adjacent in K
-constexpr int SBO = 128;                           // bytes between 8-row groups
+constexpr int A_BYTES = BM * GK;                   // int8 activation tile of one group, 128-byte swizzle
+constexpr int BX_BYTES = BN * GK;                  // expanded int8 weight tile, core-matrix layout
+constexpr int BP_BYTES = BN * GK / 2;              // packed weight tile as copied, 64-byte swizzle
+constexpr int STAGE_BYTES = A_BYTES + BX_BYTES + BP_BYTES;
+constexpr int LBO = (BN / 8) * 128;                // weights: bytes between core matrices adjacent in K
+constexpr int SBO = 128;                           // weights: bytes between 8-row groups
 constexpr int kSpin = 1 << 17;
 
 struct GemmParams {
-    const uint32_t* aq;     // A4: [M][K/8] packed nibbles; A8: [M][K] int8, 8-permuted
-    const uint32_t* wq;     // [N][K/8] packed nibbles
     const float* sa;        // [K/128][M]
     const float* sb;        // [K/128][N]
     float* C;               // [M][N]
     int* dump;              // optional [M][N][K/128]
     int M, N, K;
+    float inv;              // 1/16 (int8 activations) or 1/256 (int4 activations widened to 16*v)
+    int shift;              // log2 of the same factor, for the integer dump
 };
 
 struct __align__(16) Control {          // head of the dynamic shared memory
-    uint64_t full[STAGES];               // producers -> MMA: stage written
-    uint64_t acc_full[NACC];             // MMA -> epilogue: accumulator complete; -> producers: stage consumed
+    uint64_t ld_full[STAGES];            // copy lane -> producers, MMA: tiles of a stage landed
+    uint64_t full[STAGES];               // producers -> MMA: weight tile expanded
+    uint64_t acc_full[NACC];             // MMA -> epilogue: accumulator complete; -> copy lane: stage consumed
     uint64_t acc_empty[NACC];            // epilogue -> MMA: accumulator drained
-    uint64_t sc_full[SCALE_SLOTS];       // producers -> epilogue: scales of a group written
+    uint64_t sc_full[SCALE_SLOTS];       // copy lane -> epilogue: scales of a group landed
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -79,6 +88,18 @@ __device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+// 1-D bulk copy and 2-D tiled TMA copy, global -> this CTA's shared memory, completion on an mbarrier
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
     uint32_t ok;
@@ -148,7 +169,7 @@ __device__ __forceinline__ void fma2(float& c0, float& c1, float a0, float a1, f
         : "+f"(c0), "+f"(c1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
 
-// K-major, no swizzle: start address, LBO (next core matrix in K), SBO (next 8-row group)
+// Weights: K-major, no swizzle: start address, LBO (next core matrix in K), SBO (next 8-row group)
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3FFF);
@@ -156,6 +177,17 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
     d |= (uint64_t)((SBO >> 4) & 0x3FFF) << 32;
     d |= (uint64_t)1 << 46;                       // descriptor version of sm_100
     return d;                                     // layout type 0 (no swizzle), base offset 0
+}
+// Activations: K-major rows of 128 bytes with the 128-byte swizzle TMA wrote (tile base 1024-aligned):
+// 8-row groups are 1024 bytes apart; a K step of 32 bytes is an offset of the start address
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                       // leading byte offset: not used by this layout
+    d |= (uint64_t)((1024 >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;                       // layout type: 128-byte swizzle
+    return d;
 }
 // kind::i8, signed x signed -> s32, both operands K-major, M = 128, N = 128
 __device__ __forceinline__ uint32_t instr_desc() {
@@ -169,8 +201,8 @@ __device__ __forceinline__ uint32_t instr_desc() {
 }
 
 // 0 while every bounded wait of the GEMM kernels has been satisfied; otherwise the code of
-// the first one that ran out (1 stage not free, 2 stage not full, 3 accumulator not drained,
-// 4 accumulator not complete, 5 scales not written).  Read and cleared by fm_gemm_status().
+// the first one that ran out (1 stage not free, 2 weights not expanded, 3 accumulator not drained,
+// 4 accumulator not complete, 5 scales not landed, 6 / 7 tiles not landed).  Read and cleared by fm_gemm_status().
 __device__ int g_gemm_status;
 
 __device__ __forceinline__ uint32_t even16(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }   // 16*v of k0,k2,k4,k6
@@ -194,13 +226,29 @@ struct Cursor {
     }
 };
 
-// A8: activations are int8 (quant_rows_a8_k) instead of packed int4.  DUMP: store the integers.
-template <bool A8, bool DUMP>
+// int4 activations [M][K/8] packed words -> int8 16*v in the word-internal order k0,k2,k4,k6,k1,k3,k5,k7
+__global__ void __launch_bounds__(256)
+expand_a4_kernel(const uint4* __restrict__ aq, uint4* __restrict__ out, size_t n16) {
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 w = aq[i];
+        out[2 * i] = make_uint4(even16(w.x), odd16(w.x), even16(w.y), odd16(w.y));
+        out[2 * i + 1] = make_uint4(even16(w.z), odd16(w.z), even16(w.w), odd16(w.w));
+    }
+    pdl_launch_dependents();
+}
+
+// tmA: int8 activations [M][K], box 128 bytes x 128 rows, 128-byte swizzle.
+// tmB: packed weights [N][K/2] bytes, box 64 bytes x 128 rows, 64-byte swizzle (rows past N read as 0).
+// DUMP: also store the integers.
+template <bool DUMP>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_w4_kernel(const GemmParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
+gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // the swizzled tiles need a 1024-byte aligned base whatever the offset of the dynamic window is
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     Control* ctl = reinterpret_cast<Control*>(smem);
-    uint8_t* stages = smem + 1024;                                   // STAGES x (A tile, B tile)
+    uint8_t* stages = smem + 1024;                                   // STAGES x (A, expanded W, packed W)
     float* sc_ring = reinterpret_cast<float*>(stages + STAGES * STAGE_BYTES);   // [SLOTS][2][128]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.K / GK;
@@ -213,12 +261,15 @@ gemm_w4_kernel(const GemmParams p) {
     if (threadIdx.x == 0) {
         // one arrival per WARP on the software barriers (hundreds of per-thread arrivals on one
         // barrier word would serialise)
-        for (int s = 0; s < STAGES; s++) mbar_init(&ctl->full[s], 4);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&ctl->ld_full[s], 1);
+            mbar_init(&ctl->full[s], 4);
+        }
         for (int b = 0; b < NACC; b++) {
             mbar_init(&ctl->acc_full[b], 1);
             mbar_init(&ctl->acc_empty[b], EPI_WARPS);
         }
-        for (int s = 0; s < SCALE_SLOTS; s++) mbar_init(&ctl->sc_full[s], 4);
+        for (int s = 0; s < SCALE_SLOTS; s++) mbar_init(&ctl->sc_full[s], 1);
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -229,74 +280,64 @@ gemm_w4_kernel(const GemmParams p) {
     const uint32_t tmem_base = ctl->tmem_base;
     pdl_wait();
 
-    if (warp >= PROD_WARP0) {
+    if (warp == TMA_WARP) {
+        // ================================================================ copy lane
+        if (lane == 0) {
+            Cursor ld;
+            ld.g = 0;
+            ld.set_tile((int)blockIdx.x, tiles_m);
+            int issued = 0;
+            for (int it = 0; it < total; it++, ld.next(G, tiles_m, (int)gridDim.x)) {
+                const int s = it % STAGES, slot = it % SCALE_SLOTS;
+                // stage s was read by the MMAs of step it - STAGES; a scale slot is reused 16 steps later,
+                // by when the epilogue of its previous user is long done (the MMA of step it - 4 waited for
+                // the epilogue of step it - 8)
+                if (it >= STAGES && !wait_or_abort(&ctl->acc_full[s], ((it / STAGES) & 1) ^ 1, ctl, status, 1)) break;
+                const uint32_t nb = (uint32_t)min(BN, p.N - ld.n0) * 4u;
+                float* sc = sc_ring + slot * 256;
+                mbar_expect_tx(&ctl->sc_full[slot], BM * 4 + nb);
+                bulk_g2s(sc, p.sa + (size_t)ld.g * p.M + ld.m0, BM * 4, &ctl->sc_full[slot]);
+                bulk_g2s(sc + 128, p.sb + (size_t)ld.g * p.N + ld.n0, nb, &ctl->sc_full[slot]);
+                uint8_t* st = stages + s * STAGE_BYTES;
+                mbar_expect_tx(&ctl->ld_full[s], A_BYTES + BP_BYTES);
+                tma_2d(st, &tmA, ld.g * GK, ld.m0, &ctl->ld_full[s]);
+                tma_2d(st + A_BYTES + BX_BYTES, &tmB, ld.g * (GK / 2), ld.n0, &ctl->ld_full[s]);
+                issued = it + 1;
+            }
+            if (ctl->abort) {
+                // leaving early: the copies already issued must have landed before the CTA's shared
+                // memory is given up (bounded like every other wait; nothing is reported twice)
+                for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; j++) {
+                    for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->ld_full[j % STAGES], (j / STAGES) & 1); i++) {}
+                    for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->sc_full[j % SCALE_SLOTS], (j / SCALE_SLOTS) & 1); i++) {}
+                }
+            }
+        }
+    } else if (warp >= PROD_WARP0) {
         // ================================================================ producers
-        const int pw = warp - PROD_WARP0, q = lane >> 3, rr = lane & 7, pt = pw * 32 + lane;
-        const int KW = p.K >> 3;                                     // packed words per row
-        constexpr int NA = A8 ? 8 : 4;
-        uint4 bufA[2][NA], bufB[2][4];
-        float fsa[2], fsb[2];
-        Cursor ld;                                                   // position of the loads (one step ahead)
-        ld.g = 0;
-        ld.set_tile((int)blockIdx.x, tiles_m);
-        auto issue = [&](uint4* a, uint4* b, float& sa, float& sb) {  // loads of the step at `ld`, then advance
-            const int m0 = ld.m0, n0 = ld.n0, g = ld.g;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int row = (i * 4 + pw) * 8 + rr;
-                if (A8) {
-                    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.aq) + (size_t)(m0 + row) * p.K + g * GK;
-                    a[2 * i] = *reinterpret_cast<const uint4*>(src + q * 16);
-                    a[2 * i + 1] = *reinterpret_cast<const uint4*>(src + (q + 4) * 16);
-                } else {
-                    a[i] = *reinterpret_cast<const uint4*>(p.aq + (size_t)(m0 + row) * KW + g * 16 + q * 4);
-                }
-                b[i] = (n0 + row < p.N) ? ld_stream_v4(p.wq + (size_t)(n0 + row) * KW + g * 16 + q * 4)
-                                        : make_uint4(0, 0, 0, 0);
-            }
-            sa = p.sa[(size_t)g * p.M + m0 + pt];
-            sb = (n0 + pt < p.N) ? p.sb[(size_t)g * p.N + n0 + pt] : 0.f;
-            ld.next(G, tiles_m, (int)gridDim.x);
-        };
-        auto expand_store = [&](uint8_t* tile, int r8, const uint4& w) {   // 4 packed words -> 32 int8
-            uint8_t* dst = tile + (2 * q) * LBO + r8 * SBO + rr * 16;
-            *reinterpret_cast<uint4*>(dst) = make_uint4(even16(w.x), odd16(w.x), even16(w.y), odd16(w.y));
-            *reinterpret_cast<uint4*>(dst + LBO) = make_uint4(even16(w.z), odd16(w.z), even16(w.w), odd16(w.w));
-        };
-        auto step = [&](int it, const uint4* a, const uint4* b, float sa, float sb) -> bool {
+        // lane -> (q: which 16 packed bytes = 32 k of the row, rr: row inside an 8-row group); warp pw takes
+        // the 8-row groups pw, pw + 4, pw + 8, pw + 12
+        const int pw = warp - PROD_WARP0, q = lane >> 3, rr = lane & 7;
+        for (int it = 0; it < total; it++) {
             const int s = it % STAGES;
-            if (it >= STAGES && !wait_or_abort(&ctl->acc_full[s], ((it / STAGES) & 1) ^ 1, ctl, status, 1)) return false;
-            uint8_t* At = stages + s * STAGE_BYTES;
-            uint8_t* Bt = At + TILE_BYTES;
+            if (!wait_or_abort(&ctl->ld_full[s], (it / STAGES) & 1, ctl, status, 6)) break;
+            uint8_t* Bx = stages + s * STAGE_BYTES + A_BYTES;
+            const uint8_t* Bp = Bx + BX_BYTES;
+            uint4 w[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const int r8 = i * 4 + pw;
-                if (A8) {
-                    *reinterpret_cast<uint4*>(At + q * LBO + r8 * SBO + rr * 16) = a[2 * i];
-                    *reinterpret_cast<uint4*>(At + (q + 4) * LBO + r8 * SBO + rr * 16) = a[2 * i + 1];
-                } else {
-                    expand_store(At, r8, a[i]);
-                }
-                expand_store(Bt, r8, b[i]);
+                const int row = (i * 4 + pw) * 8 + rr;               // 64-byte swizzle: chunk ^= (row / 2) % 4
+                w[i] = *reinterpret_cast<const uint4*>(Bp + row * 64 + ((q ^ ((row >> 1) & 3)) << 4));
             }
-            const int slot = it % SCALE_SLOTS;
-            sc_ring[slot * 256 + pt] = sa;
-            sc_ring[slot * 256 + 128 + pt] = sb;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint8_t* dst = Bx + (2 * q) * LBO + (i * 4 + pw) * SBO + rr * 16;
+                *reinterpret_cast<uint4*>(dst) = make_uint4(even16(w[i].x), odd16(w[i].x), even16(w[i].y), odd16(w[i].y));
+                *reinterpret_cast<uint4*>(dst + LBO) = make_uint4(even16(w[i].z), odd16(w[i].z), even16(w[i].w), odd16(w[i].w));
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core's reads
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&ctl->full[s]);
-                mbar_arrive(&ctl->sc_full[slot]);
-            }
-            return true;
-        };
-        if (total > 0) issue(bufA[0], bufB[0], fsa[0], fsb[0]);
-        for (int it = 0; it < total; it += 2) {
-            if (it + 1 < total) issue(bufA[1], bufB[1], fsa[1], fsb[1]);
-            if (!step(it, bufA[0], bufB[0], fsa[0], fsb[0])) break;
-            if (it + 1 >= total) break;
-            if (it + 2 < total) issue(bufA[0], bufB[0], fsa[0], fsb[0]);
-            if (!step(it + 1, bufA[1], bufB[1], fsa[1], fsb[1])) break;
+            if (lane == 0) mbar_arrive(&ctl->full[s]);
         }
     } else if (warp == MMA_WARP) {
         // ================================================================ MMA issuer
@@ -304,22 +345,24 @@ gemm_w4_kernel(const GemmParams p) {
             // everything that does not depend on the step is computed once: this single thread is
             // on the critical path of every group, so its loop body is kept to a few instructions
             const uint32_t idesc = instr_desc();
-            const uint64_t adesc0 = smem_desc(smem_u32(stages));
-            const uint64_t bdesc0 = smem_desc(smem_u32(stages) + TILE_BYTES);
-            constexpr uint64_t kStageStep = STAGE_BYTES >> 4, kKStep = (2 * LBO) >> 4;   // descriptor units of 16 bytes
+            const uint64_t adesc0 = smem_desc_sw128(smem_u32(stages));
+            const uint64_t bdesc0 = smem_desc(smem_u32(stages) + A_BYTES);
+            constexpr uint64_t kStageStep = STAGE_BYTES >> 4;        // descriptor units of 16 bytes
+            constexpr uint64_t kAStep = 32 >> 4, kBStep = (2 * LBO) >> 4;   // 32 k further along the row
             for (int it = 0; it < total; it++) {
                 const int s = it % STAGES;                  // == accumulator index (STAGES == NACC)
                 const uint32_t ph = (it / STAGES) & 1;
                 if (it >= NACC && !wait_or_abort(&ctl->acc_empty[s], ph ^ 1, ctl, status, 3)) break;
                 if (!wait_or_abort(&ctl->full[s], ph, ctl, status, 2)) break;
+                if (!wait_or_abort(&ctl->ld_full[s], ph, ctl, status, 7)) break;   // complete already: the producers waited for it
                 tc_fence_after();
                 const uint64_t ad = adesc0 + s * kStageStep, bd = bdesc0 + s * kStageStep;
                 const uint32_t d = tmem_base + s * BN;
                 tc_mma_i8(d, ad, bd, idesc, 0);
-                tc_mma_i8(d, ad + kKStep, bd + kKStep, idesc, 1);
-                tc_mma_i8(d, ad + 2 * kKStep, bd + 2 * kKStep, idesc, 1);
-                tc_mma_i8(d, ad + 3 * kKStep, bd + 3 * kKStep, idesc, 1);
-                // one commit per group: STAGES == NACC, so one barrier tells the producers "stage
+                tc_mma_i8(d, ad + kAStep, bd + kBStep, idesc, 1);
+                tc_mma_i8(d, ad + 2 * kAStep, bd + 2 * kBStep, idesc, 1);
+                tc_mma_i8(d, ad + 3 * kAStep, bd + 3 * kBStep, idesc, 1);
+                // one commit per group: STAGES == NACC, so one barrier tells the copy lane "stage
                 // consumed" and the epilogue "accumulator complete"
                 tc_commit(&ctl->acc_full[s]);
             }
@@ -330,7 +373,7 @@ gemm_w4_kernel(const GemmParams p) {
         constexpr int CPW = BN / (EPI_WARPS / 4);                    // columns per warp: 64
         const int lq = warp & 3, ch = warp >> 2;
         const int mrow = lq * 32 + lane;                             // TMEM lane = row of the tile
-        const float inv = A8 ? (1.0f / 16.0f) : (1.0f / 256.0f);     // the integer in TMEM is 16*I or 256*I
+        const float inv = p.inv;                                     // the integer in TMEM is 16*I or 256*I
         float facc[CPW];
 #pragma unroll
         for (int j = 0; j < CPW; j++) facc[j] = 0.f;
@@ -358,8 +401,8 @@ gemm_w4_kernel(const GemmParams p) {
                     fma2(facc[col], facc[col + 1], (float)(int)r[j], (float)(int)r[j + 1], s0, s1);
                     if (DUMP) {
                         int* d = p.dump + ((size_t)(m0 + mrow) * p.N + n0 + col) * G + g;
-                        if (n0 + col < p.N) d[0] = (int)r[j] >> (A8 ? 4 : 8);
-                        if (n0 + col + 1 < p.N) d[G] = (int)r[j + 1] >> (A8 ? 4 : 8);
+                        if (n0 + col < p.N) d[0] = (int)r[j] >> p.shift;
+                        if (n0 + col + 1 < p.N) d[G] = (int)r[j + 1] >> p.shift;
                     }
                 }
             }
@@ -389,37 +432,94 @@ gemm_w4_kernel(const GemmParams p) {
 }
 
 // ------------------------------------------------------------------------- host side
-constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * STAGE_BYTES + SCALE_SLOTS * 256 * 4 + 16 * 1024;
+constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * STAGE_BYTES + SCALE_SLOTS * 256 * 4 + 1024;
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// the driver's tensor-map encoder, looked up through the runtime (no link against the driver library)
+EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+// bytes [rows][row_bytes], row-major and dense; box = box_bytes x 128 rows
+bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes, CUtensorMapSwizzle sw) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_bytes, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// aq: packed int4 [M][K/8] words (A8 false) or int8 [M][K] (A8 true)
 template <bool A8, bool DUMP>
-int run_gemm(const char* kn, const LaunchCtx& c, const GemmParams& p) {
-    auto kern = gemm_w4_kernel<A8, DUMP>;
+int run_gemm(const char* kn, const LaunchCtx& c, const GemmParams& p, const void* aq, const void* wq) {
+    auto kern = gemm_w4_kernel<DUMP>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return cuda_fail(kn, e);
         configured = true;
     }
+    const void* a8 = aq;
+    if (!A8) {                                       // widen the int4 codes once, in front of the GEMM
+        const size_t bytes = (size_t)p.M * p.K;
+        void* ws = engine_scratch(bytes);
+        FM_REQUIRE(ws != nullptr, kn,
+                   "the %zu-byte workspace for the widened activations cannot be allocated here (inside a graph "
+                   "capture it must exist already: run this shape once outside the capture)", bytes);
+        const size_t n16 = bytes / 32;
+        const int blocks = (int)((n16 + 255) / 256 < (size_t)c.sm_count * 8 ? (n16 + 255) / 256 : (size_t)c.sm_count * 8);
+        cudaError_t e = launch_kernel(expand_a4_kernel, dim3(blocks), dim3(256), 0, c.stream, pdl_enabled(),
+                                      static_cast<const uint4*>(aq), static_cast<uint4*>(ws), n16);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        after_launch(kn);
+        a8 = ws;
+    }
+    CUtensorMap tmA, tmB;
+    FM_REQUIRE(make_map(&tmA, a8, p.M, p.K, 128, CU_TENSOR_MAP_SWIZZLE_128B) &&
+               make_map(&tmB, wq, p.N, p.K / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B), kn,
+               "cuTensorMapEncodeTiled is unavailable or refused M=%d N=%d K=%d", p.M, p.N, p.K);
     const int ntiles = (p.M / BM) * ((p.N + BN - 1) / BN);
     const int grid = ntiles < c.sm_count ? ntiles : c.sm_count;
-    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kThreads), kSmemBytes, c.stream, pdl_enabled(), p);
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kThreads), kSmemBytes, c.stream, pdl_enabled(), tmA, tmB, p);
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
+struct GemmArgs {                                   // the by-name arguments before they are split up
+    const uint32_t* aq;
+    const uint32_t* wq;
+    GemmParams p;
+};
+
 // shared checks; tiles_needed = number of reference work-groups (128 x 64 tiles) the grid must cover
 template <bool A8>
-int check_gemm(const char* kn, const LaunchCtx& c, GemmParams& p, long long groups_given, bool dump) {
+int check_gemm(const char* kn, const LaunchCtx& c, GemmArgs& ga, long long groups_given, bool dump) {
+    GemmParams& p = ga.p;
     FM_REQUIRE(c.wx == 256 && c.wy == 1, kn, "work-group must be 256 threads (got %ux%u)", c.wx, c.wy);
     FM_REQUIRE(p.M > 0 && p.N > 0 && p.K > 0 && p.M % 128 == 0 && p.N % 64 == 0 && p.K % 128 == 0, kn,
                "M=%d N=%d K=%d: M must be a multiple of 128, N of 64, K of 128", p.M, p.N, p.K);
     const long long need = (long long)(p.N / 64) * (p.M / 128);
     FM_REQUIRE(groups_given >= need, kn, "the grid covers %lld of the %lld 128x64 tiles; partial grids are not built",
                groups_given, need);
-    FM_REQUIRE(aligned(p.aq, 16) && aligned(p.wq, 16) && aligned(p.sa, 4) && aligned(p.sb, 4) && aligned(p.C, 16), kn,
-               "misaligned pointer (codes and C need 16 bytes)");
+    FM_REQUIRE(aligned(ga.aq, 16) && aligned(ga.wq, 16) && aligned(p.sa, 16) && aligned(p.sb, 16) && aligned(p.C, 16), kn,
+               "misaligned pointer (codes, scales and C need 16 bytes)");
     const int G = p.K / 128;
-    FM_RANGE(p.aq, A8 ? (size_t)p.M * p.K : (size_t)p.M * (p.K / 2), kn, "aq");
-    FM_RANGE(p.wq, (size_t)p.N * (p.K / 2), kn, "wq");
+    FM_RANGE(ga.aq, A8 ? (size_t)p.M * p.K : (size_t)p.M * (p.K / 2), kn, "aq");
+    FM_RANGE(ga.wq, (size_t)p.N * (p.K / 2), kn, "wq");
+    p.inv = A8 ? (1.0f / 16.0f) : (1.0f / 256.0f);
+    p.shift = A8 ? 4 : 8;
     FM_RANGE(p.sa, (size_t)G * p.M * 4, kn, "asc");
     FM_RANGE(p.sb, (size_t)G * p.N * 4, kn, "wsc");
     FM_RANGE(p.C, (size_t)p.M * p.N * 4, kn, "C");
@@ -430,9 +530,10 @@ int check_gemm(const char* kn, const LaunchCtx& c, GemmParams& p, long long grou
     return FM_OK;
 }
 
-void fill(GemmParams& p, const uint64_t* a) {
-    p.aq = arg_ptr<const uint32_t>(a[0]);
-    p.wq = arg_ptr<const uint32_t>(a[1]);
+void fill(GemmArgs& ga, const uint64_t* a) {
+    GemmParams& p = ga.p;
+    ga.aq = arg_ptr<const uint32_t>(a[0]);
+    ga.wq = arg_ptr<const uint32_t>(a[1]);
     p.sa = arg_ptr<const float>(a[2]);
     p.sb = arg_ptr<const float>(a[3]);
     p.C = arg_ptr<float>(a[4]);
@@ -445,44 +546,48 @@ void fill(GemmParams& p, const uint64_t* a) {
 // nbn must be N/64; the magic multiplier is accepted and ignored.
 int launch_gemm_flat(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = "gemm_w4a4_flat";
-    GemmParams p = {};
-    fill(p, a);
+    GemmArgs ga = {};
+    GemmParams& p = ga.p;
+    fill(ga, a);
     FM_REQUIRE(c.gy == 1, kn, "1-D grid expected");
     FM_REQUIRE(p.N > 0 && arg_i32(a[8]) == p.N / 64, kn, "nbn=%d must equal N/64=%d", arg_i32(a[8]), p.N / 64);
-    const int rc = check_gemm<false>(kn, c, p, c.gx, false);
-    return rc ? rc : run_gemm<false, false>(kn, c, p);
+    const int rc = check_gemm<false>(kn, c, ga, c.gx, false);
+    return rc ? rc : run_gemm<false, false>(kn, c, p, ga.aq, ga.wq);
 }
 
 // gemm_w4a4(aq, wq, asc, wsc, C, M, N, K): grid x = N/64, grid y = M/128 (a 1-D launch covers M = 128)
 int launch_gemm_2d(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = "gemm_w4a4";
-    GemmParams p = {};
-    fill(p, a);
+    GemmArgs ga = {};
+    GemmParams& p = ga.p;
+    fill(ga, a);
     FM_REQUIRE(p.N > 0 && p.M > 0 && (long long)c.gx >= p.N / 64 && (long long)c.gy >= p.M / 128, kn,
                "grid %ux%u does not cover N/64=%d by M/128=%d work-groups", c.gx, c.gy, p.N / 64, p.M / 128);
-    const int rc = check_gemm<false>(kn, c, p, (long long)(p.N / 64) * (p.M / 128), false);
-    return rc ? rc : run_gemm<false, false>(kn, c, p);
+    const int rc = check_gemm<false>(kn, c, ga, (long long)(p.N / 64) * (p.M / 128), false);
+    return rc ? rc : run_gemm<false, false>(kn, c, p, ga.aq, ga.wq);
 }
 
 // gemm_w4a8(aq8, wq, asc, wsc, C, M, N, K): aq8 = int8 codes of quant_rows_a8_k; 1-D grid of N/64 * M/128
 int launch_gemm_a8(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = "gemm_w4a8";
-    GemmParams p = {};
-    fill(p, a);
+    GemmArgs ga = {};
+    GemmParams& p = ga.p;
+    fill(ga, a);
     FM_REQUIRE(c.gy == 1, kn, "1-D grid expected");
-    const int rc = check_gemm<true>(kn, c, p, c.gx, false);
-    return rc ? rc : run_gemm<true, false>(kn, c, p);
+    const int rc = check_gemm<true>(kn, c, ga, c.gx, false);
+    return rc ? rc : run_gemm<true, false>(kn, c, p, ga.aq, ga.wq);
 }
 
 // gemm_w4a4_iacc / gemm_w4a8_iacc (aq, wq, asc, wsc, C, M, N, K, iacc): iacc int32 [M][N][K/128]
 template <bool A8>
 int launch_gemm_iacc(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = A8 ? "gemm_w4a8_iacc" : "gemm_w4a4_iacc";
-    GemmParams p = {};
-    fill(p, a);
+    GemmArgs ga = {};
+    GemmParams& p = ga.p;
+    fill(ga, a);
     p.dump = arg_ptr<int>(a[8]);
-    const int rc = check_gemm<A8>(kn, c, p, 1LL << 40, true);
-    return rc ? rc : run_gemm<A8, true>(kn, c, p);
+    const int rc = check_gemm<A8>(kn, c, ga, 1LL << 40, true);
+    return rc ? rc : run_gemm<A8, true>(kn, c, p, ga.aq, ga.wq);
 }
 
 const KernelEntry kGemm[] = {
