@@ -142,6 +142,12 @@ int ensure_init() {
     e.sm_count = prop.multiProcessorCount;
     e.check_bounds = env_int("FM_CHECK_BOUNDS", 1) != 0;
     e.pdl = env_int("FM_PDL", 0) != 0;
+    {   // workspace for kernel-internal intermediates, reserved up front so that a first use inside a
+        // stream capture finds it ($FM_SCRATCH_MB, default 64: int4 activations of M x K <= 64 Mi widened)
+        const size_t mb = (size_t)env_int("FM_SCRATCH_MB", 64);
+        if (mb > 0 && cudaMalloc(&e.scratch, mb << 20) == cudaSuccess) e.scratch_bytes = mb << 20;
+        else { cudaGetLastError(); e.scratch = nullptr; e.scratch_bytes = 0; }
+    }
     if (e.kernels.empty()) {
         int n = 0;
         const KernelEntry* k;
