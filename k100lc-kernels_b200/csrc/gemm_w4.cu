@@ -25,10 +25,10 @@
 //     sign and magnitude), shared memory to shared memory, into the un-swizzled core-matrix
 //     layout (8 rows x 16 bytes).  Both operands use the same k order inside a word
 //     (k0,k2,k4,k6,k1,k3,k5,k7); int8 activations arrive in that order from quant_rows_a8_k;
-//   * one thread issues four tcgen05.mma.kind::i8 (M=128, N=128, K=32) per group into one
-//     of four int32 accumulators in tensor memory (all 512 columns) and commits to an mbarrier;
-//   * eight epilogue warps (one TMEM lane = one token row, half of the columns each) drain the
-//     accumulator with tcgen05.ld, convert, and fold it into 64 fp32 running sums per thread with the
+//   * two threads (even and odd steps) issue four tcgen05.mma.kind::i8 (M=128, N=128, K=32) per group
+//     into one of four int32 accumulators in tensor memory (all 512 columns) and commit to an mbarrier;
+//   * sixteen epilogue warps (one TMEM lane = one token row, a quarter of the columns each) drain the
+//     accumulator with tcgen05.ld, convert, and fold it into 32 fp32 running sums per thread with the
 //     group's scale product.  The integer in TMEM is 256*I (W4A4) or 16*I (W4A8); the
 //     power of two is divided out of the scale, which leaves the fused multiply-add
 //     bit-identical to fmaf(float(I), sa*sb, C).
@@ -48,11 +48,16 @@ constexpr int BM = 128, BN = 128, GK = 128;       // tile and quantisation group
 constexpr int STAGES = 4;
 constexpr int NACC = 4;                            // int32 accumulators in tensor memory (4 x 128 columns = all of it)
 constexpr int SCALE_SLOTS = 16;                    // > 2 * NACC groups between a slot's write and its reuse
-constexpr int EPI_WARPS = 8;                       // two per TMEM lane quarter: each takes half of the columns
-constexpr int MMA_WARP = EPI_WARPS;                // warp index of the MMA issuer
-constexpr int TMA_WARP = EPI_WARPS + 1;            // warp whose lane 0 issues the copies
-constexpr int PROD_WARP0 = EPI_WARPS + 2;          // first of the 4 producer warps
-constexpr int kThreads = (EPI_WARPS + 2 + 4) * 32;
+// Warps come in groups of four (the unit of setmaxnreg): four groups of epilogue warps, one group
+// with the two MMA issuers and the copy lane, one group of producers.
+constexpr int EPI_WARPS = 16;                      // four per TMEM lane quarter: each takes a quarter of the columns
+constexpr int MMA_WARP = EPI_WARPS;                // first of the two MMA issuer warps (even / odd steps)
+constexpr int TMA_WARP = EPI_WARPS + 2;            // warp whose lane 0 issues the copies (warp EPI_WARPS + 3 idles)
+constexpr int PROD_WARP0 = EPI_WARPS + 4;          // first of the 4 producer warps
+constexpr int kThreads = (EPI_WARPS + 4 + 4) * 32;
+// 768 threads start with 80 registers each; the epilogue (32 running sums + 32 loaded integers per
+// thread) takes 96, the other two groups shrink to 48: 4*128*96 + 2*128*48 = 61440 of 65536
+constexpr int kRegsEpilogue = 96, kRegsOther = 48;
 static_assert(STAGES == NACC, "stage and accumulator share one completion barrier");
 constexpr int A_BYTES = BM * GK;                   // int8 activation tile of one group, 128-byte swizzle
 constexpr int BX_BYTES = BN * GK;                  // expanded int8 weight tile, core-matrix layout
@@ -73,8 +78,10 @@ struct GemmParams {
 };
 
 struct __align__(16) Control {          // head of the dynamic shared memory
-    uint64_t ld_full[STAGES];            // copy lane -> producers, MMA: tiles of a stage landed
-    uint64_t full[STAGES];               // producers -> MMA: weight tile expanded
+    uint64_t ldb_full[STAGES];           // copy lane -> producers: packed weight tile landed
+    uint64_t full[STAGES];               // -> MMA: activation tile landed (copy, byte count) and weight tile
+                                         //    expanded (one arrival per producer warp)
+    uint64_t drain[2];                   // MMA issuers: everything they issued has completed
     uint64_t acc_full[NACC];             // MMA -> epilogue: accumulator complete; -> copy lane: stage consumed
     uint64_t acc_empty[NACC];            // epilogue -> MMA: accumulator drained
     uint64_t sc_full[SCALE_SLOTS];       // copy lane -> epilogue: scales of a group landed
@@ -202,7 +209,7 @@ __device__ __forceinline__ uint32_t instr_desc() {
 
 // 0 while every bounded wait of the GEMM kernels has been satisfied; otherwise the code of
 // the first one that ran out (1 stage not free, 2 weights not expanded, 3 accumulator not drained,
-// 4 accumulator not complete, 5 scales not landed, 6 / 7 tiles not landed).  Read and cleared by fm_gemm_status().
+// 4 accumulator not complete, 5 scales not landed, 6 packed weights not landed).  Read and cleared by fm_gemm_status().
 __device__ int g_gemm_status;
 
 __device__ __forceinline__ uint32_t even16(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }   // 16*v of k0,k2,k4,k6
@@ -262,9 +269,11 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // one arrival per WARP on the software barriers (hundreds of per-thread arrivals on one
         // barrier word would serialise)
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&ctl->ld_full[s], 1);
-            mbar_init(&ctl->full[s], 4);
+            mbar_init(&ctl->ldb_full[s], 1);
+            mbar_init(&ctl->full[s], 5);
         }
+        mbar_init(&ctl->drain[0], 1);
+        mbar_init(&ctl->drain[1], 1);
         for (int b = 0; b < NACC; b++) {
             mbar_init(&ctl->acc_full[b], 1);
             mbar_init(&ctl->acc_empty[b], EPI_WARPS);
@@ -280,47 +289,17 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t tmem_base = ctl->tmem_base;
     pdl_wait();
 
-    if (warp == TMA_WARP) {
-        // ================================================================ copy lane
-        if (lane == 0) {
-            Cursor ld;
-            ld.g = 0;
-            ld.set_tile((int)blockIdx.x, tiles_m);
-            int issued = 0;
-            for (int it = 0; it < total; it++, ld.next(G, tiles_m, (int)gridDim.x)) {
-                const int s = it % STAGES, slot = it % SCALE_SLOTS;
-                // stage s was read by the MMAs of step it - STAGES; a scale slot is reused 16 steps later,
-                // by when the epilogue of its previous user is long done (the MMA of step it - 4 waited for
-                // the epilogue of step it - 8)
-                if (it >= STAGES && !wait_or_abort(&ctl->acc_full[s], ((it / STAGES) & 1) ^ 1, ctl, status, 1)) break;
-                const uint32_t nb = (uint32_t)min(BN, p.N - ld.n0) * 4u;
-                float* sc = sc_ring + slot * 256;
-                mbar_expect_tx(&ctl->sc_full[slot], BM * 4 + nb);
-                bulk_g2s(sc, p.sa + (size_t)ld.g * p.M + ld.m0, BM * 4, &ctl->sc_full[slot]);
-                bulk_g2s(sc + 128, p.sb + (size_t)ld.g * p.N + ld.n0, nb, &ctl->sc_full[slot]);
-                uint8_t* st = stages + s * STAGE_BYTES;
-                mbar_expect_tx(&ctl->ld_full[s], A_BYTES + BP_BYTES);
-                tma_2d(st, &tmA, ld.g * GK, ld.m0, &ctl->ld_full[s]);
-                tma_2d(st + A_BYTES + BX_BYTES, &tmB, ld.g * (GK / 2), ld.n0, &ctl->ld_full[s]);
-                issued = it + 1;
-            }
-            if (ctl->abort) {
-                // leaving early: the copies already issued must have landed before the CTA's shared
-                // memory is given up (bounded like every other wait; nothing is reported twice)
-                for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; j++) {
-                    for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->ld_full[j % STAGES], (j / STAGES) & 1); i++) {}
-                    for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->sc_full[j % SCALE_SLOTS], (j / SCALE_SLOTS) & 1); i++) {}
-                }
-            }
-        }
-    } else if (warp >= PROD_WARP0) {
+    // Every group of four warps begins by resizing its register file; all four warps of a group run the
+    // same setmaxnreg instruction before they split into their roles.
+    if (warp >= PROD_WARP0) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
         // ================================================================ producers
         // lane -> (q: which 16 packed bytes = 32 k of the row, rr: row inside an 8-row group); warp pw takes
         // the 8-row groups pw, pw + 4, pw + 8, pw + 12
         const int pw = warp - PROD_WARP0, q = lane >> 3, rr = lane & 7;
         for (int it = 0; it < total; it++) {
             const int s = it % STAGES;
-            if (!wait_or_abort(&ctl->ld_full[s], (it / STAGES) & 1, ctl, status, 6)) break;
+            if (!wait_or_abort(&ctl->ldb_full[s], (it / STAGES) & 1, ctl, status, 6)) break;
             uint8_t* Bx = stages + s * STAGE_BYTES + A_BYTES;
             const uint8_t* Bp = Bx + BX_BYTES;
             uint4 w[4];
@@ -339,38 +318,84 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->full[s]);
         }
-    } else if (warp == MMA_WARP) {
-        // ================================================================ MMA issuer
-        if (lane == 0) {
-            // everything that does not depend on the step is computed once: this single thread is
-            // on the critical path of every group, so its loop body is kept to a few instructions
-            const uint32_t idesc = instr_desc();
-            const uint64_t adesc0 = smem_desc_sw128(smem_u32(stages));
-            const uint64_t bdesc0 = smem_desc(smem_u32(stages) + A_BYTES);
-            constexpr uint64_t kStageStep = STAGE_BYTES >> 4;        // descriptor units of 16 bytes
-            constexpr uint64_t kAStep = 32 >> 4, kBStep = (2 * LBO) >> 4;   // 32 k further along the row
-            for (int it = 0; it < total; it++) {
-                const int s = it % STAGES;                  // == accumulator index (STAGES == NACC)
-                const uint32_t ph = (it / STAGES) & 1;
-                if (it >= NACC && !wait_or_abort(&ctl->acc_empty[s], ph ^ 1, ctl, status, 3)) break;
-                if (!wait_or_abort(&ctl->full[s], ph, ctl, status, 2)) break;
-                if (!wait_or_abort(&ctl->ld_full[s], ph, ctl, status, 7)) break;   // complete already: the producers waited for it
-                tc_fence_after();
-                const uint64_t ad = adesc0 + s * kStageStep, bd = bdesc0 + s * kStageStep;
-                const uint32_t d = tmem_base + s * BN;
-                tc_mma_i8(d, ad, bd, idesc, 0);
-                tc_mma_i8(d, ad + kAStep, bd + kBStep, idesc, 1);
-                tc_mma_i8(d, ad + 2 * kAStep, bd + 2 * kBStep, idesc, 1);
-                tc_mma_i8(d, ad + 3 * kAStep, bd + 3 * kBStep, idesc, 1);
-                // one commit per group: STAGES == NACC, so one barrier tells the copy lane "stage
-                // consumed" and the epilogue "accumulator complete"
-                tc_commit(&ctl->acc_full[s]);
+    } else if (warp >= EPI_WARPS) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+        if (warp == TMA_WARP) {
+            // ================================================================ copy lane
+            if (lane == 0) {
+                Cursor ld;
+                ld.g = 0;
+                ld.set_tile((int)blockIdx.x, tiles_m);
+                int issued = 0;
+                for (int it = 0; it < total; it++, ld.next(G, tiles_m, (int)gridDim.x)) {
+                    const int s = it % STAGES, slot = it % SCALE_SLOTS;
+                    // stage s was read by the MMAs of step it - STAGES; a scale slot is reused 16 steps later,
+                    // by when the epilogue of its previous user is long done (the MMA of step it - 4 waited for
+                    // the epilogue of step it - 8)
+                    if (it >= STAGES && !wait_or_abort(&ctl->acc_full[s], ((it / STAGES) & 1) ^ 1, ctl, status, 1)) break;
+                    const uint32_t nb = (uint32_t)min(BN, p.N - ld.n0) * 4u;
+                    float* sc = sc_ring + slot * 256;
+                    mbar_expect_tx(&ctl->sc_full[slot], BM * 4 + nb);
+                    bulk_g2s(sc, p.sa + (size_t)ld.g * p.M + ld.m0, BM * 4, &ctl->sc_full[slot]);
+                    bulk_g2s(sc + 128, p.sb + (size_t)ld.g * p.N + ld.n0, nb, &ctl->sc_full[slot]);
+                    uint8_t* st = stages + s * STAGE_BYTES;
+                    mbar_expect_tx(&ctl->ldb_full[s], BP_BYTES);
+                    tma_2d(st + A_BYTES + BX_BYTES, &tmB, ld.g * (GK / 2), ld.n0, &ctl->ldb_full[s]);
+                    mbar_expect_tx(&ctl->full[s], A_BYTES);
+                    tma_2d(st, &tmA, ld.g * GK, ld.m0, &ctl->full[s]);
+                    issued = it + 1;
+                }
+                if (ctl->abort) {
+                    // leaving early: the copies already issued must have landed before the CTA's shared
+                    // memory is given up (bounded like every other wait; nothing is reported twice)
+                    for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; j++) {
+                        for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->ldb_full[j % STAGES], (j / STAGES) & 1); i++) {}
+                        for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->sc_full[j % SCALE_SLOTS], (j / SCALE_SLOTS) & 1); i++) {}
+                    }
+                }
+            }
+        } else if (warp < TMA_WARP) {
+            // ================================================================ MMA issuers
+            // Two threads, one for the even and one for the odd steps: a step is two barrier waits (each a
+            // few hundred cycles of latency even when the barrier is ready) around 256 cycles of MMA, so
+            // one thread alone would keep the tensor pipe idle three quarters of the time.  Steps use
+            // distinct stages and accumulators, and every thread commits its own MMAs.
+            if (lane == 0) {
+                const int par = warp - MMA_WARP;
+                // everything that does not depend on the step is computed once: this single thread is
+                // on the critical path of every group, so its loop body is kept to a few instructions
+                const uint32_t idesc = instr_desc();
+                const uint64_t adesc0 = smem_desc_sw128(smem_u32(stages));
+                const uint64_t bdesc0 = smem_desc(smem_u32(stages) + A_BYTES);
+                constexpr uint64_t kStageStep = STAGE_BYTES >> 4;        // descriptor units of 16 bytes
+                constexpr uint64_t kAStep = 32 >> 4, kBStep = (2 * LBO) >> 4;   // 32 k further along the row
+                for (int it = par; it < total; it += 2) {
+                    const int s = it % STAGES;                  // == accumulator index (STAGES == NACC)
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (it >= NACC && !wait_or_abort(&ctl->acc_empty[s], ph ^ 1, ctl, status, 3)) break;
+                    if (!wait_or_abort(&ctl->full[s], ph, ctl, status, 2)) break;
+                    tc_fence_after();
+                    const uint64_t ad = adesc0 + s * kStageStep, bd = bdesc0 + s * kStageStep;
+                    const uint32_t d = tmem_base + s * BN;
+                    tc_mma_i8(d, ad, bd, idesc, 0);
+                    tc_mma_i8(d, ad + kAStep, bd + kBStep, idesc, 1);
+                    tc_mma_i8(d, ad + 2 * kAStep, bd + 2 * kBStep, idesc, 1);
+                    tc_mma_i8(d, ad + 3 * kAStep, bd + 3 * kBStep, idesc, 1);
+                    // one commit per group: STAGES == NACC, so one barrier tells the copy lane "stage
+                    // consumed" and the epilogue "accumulator complete"
+                    tc_commit(&ctl->acc_full[s]);
+                }
+                // nothing this thread issued may still be running when tensor memory is released (the
+                // epilogue has consumed every step unless the kernel is aborting)
+                tc_commit(&ctl->drain[par]);
+                for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->drain[par], 0); i++) {}
             }
         }
     } else {
         // ================================================================ epilogue
-        // warp w drains TMEM lanes 32*(w%4).. (a hardware rule) and columns 64*(w/4)..+63
-        constexpr int CPW = BN / (EPI_WARPS / 4);                    // columns per warp: 64
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
+        // warp w drains TMEM lanes 32*(w%4).. (a hardware rule) and columns 32*(w/4)..+31
+        constexpr int CPW = BN / (EPI_WARPS / 4);                    // columns per warp: 32
         const int lq = warp & 3, ch = warp >> 2;
         const int mrow = lq * 32 + lane;                             // TMEM lane = row of the tile
         const float inv = p.inv;                                     // the integer in TMEM is 16*I or 256*I
@@ -393,16 +418,21 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(lq * 32) << 16) + b * BN + ch * CPW + c * 32, r);
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
+                for (int j = 0; j < 32; j += 4) {
                     const int col = c * 32 + j;
-                    const float2 sb2 = *reinterpret_cast<const float2*>(sbv + col);
-                    float s0, s1;
-                    mul2(s0, s1, sa, sb2.x, sb2.y);                  // scale product, rounded to fp32 first
+                    // one 16-byte broadcast load for four columns: shared-memory bandwidth is what this
+                    // kernel runs out of (the MMA alone reads 128 bytes per clock)
+                    const float4 sb4 = *reinterpret_cast<const float4*>(sbv + col);
+                    float s0, s1, s2, s3;
+                    mul2(s0, s1, sa, sb4.x, sb4.y);                  // scale products, rounded to fp32 first
+                    mul2(s2, s3, sa, sb4.z, sb4.w);
                     fma2(facc[col], facc[col + 1], (float)(int)r[j], (float)(int)r[j + 1], s0, s1);
+                    fma2(facc[col + 2], facc[col + 3], (float)(int)r[j + 2], (float)(int)r[j + 3], s2, s3);
                     if (DUMP) {
                         int* d = p.dump + ((size_t)(m0 + mrow) * p.N + n0 + col) * G + g;
-                        if (n0 + col < p.N) d[0] = (int)r[j] >> p.shift;
-                        if (n0 + col + 1 < p.N) d[G] = (int)r[j + 1] >> p.shift;
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+                            if (n0 + col + u < p.N) d[u * G] = (int)r[j + u] >> p.shift;
                     }
                 }
             }
