@@ -13,10 +13,10 @@
 //
 // Mapping.  One persistent CTA per SM walks 128 x 128 output tiles (m fastest, so the CTAs
 // that run together share a weight tile in L2).  Per tile and per 128-k group:
-//   * one thread (the copy lane) issues TMA copies into a 4-deep ring: the int8 activation
-//     tile (128 rows x 128 bytes, 128-byte swizzle — exactly the K-major layout tcgen05.mma
-//     reads), the packed weight tile (128 rows x 64 bytes, 64-byte swizzle) and the two
-//     scale vectors of the group.  int4 activations are widened to int8 (16*v) once per call by
+//   * two threads issue TMA copies: one the int8 activation tile (128 rows x 128 bytes, 128-byte
+//     swizzle — exactly the K-major layout tcgen05.mma reads) into a 4-deep ring together with
+//     the two scale vectors of the group, the other the packed weight tile (128 rows x 64 bytes,
+//     64-byte swizzle) into an 8-deep ring of its own that the producers free early.  int4 activations are widened to int8 (16*v) once per call by
 //     a small kernel in front, into an engine-owned workspace, so the GEMM never repeats
 //     that for every column tile;
 //   * four producer warps turn every weight nibble into the int8 value 16*v by masking it
@@ -52,17 +52,18 @@ constexpr int SCALE_SLOTS = 16;                    // > 2 * NACC groups between 
 // with the two MMA issuers and the copy lane, one group of producers.
 constexpr int EPI_WARPS = 16;                      // four per TMEM lane quarter: each takes a quarter of the columns
 constexpr int MMA_WARP = EPI_WARPS;                // first of the two MMA issuer warps (even / odd steps)
-constexpr int TMA_WARP = EPI_WARPS + 2;            // warp whose lane 0 issues the copies (warp EPI_WARPS + 3 idles)
+constexpr int TMA_WARP = EPI_WARPS + 2;            // lane 0 copies activations and scales; warp EPI_WARPS + 3 the packed weights
 constexpr int PROD_WARP0 = EPI_WARPS + 4;          // first of the 4 producer warps
 constexpr int kThreads = (EPI_WARPS + 4 + 4) * 32;
 // 768 threads start with 80 registers each; the epilogue (32 running sums + 32 loaded integers per
 // thread) takes 96, the other two groups shrink to 48: 4*128*96 + 2*128*48 = 61440 of 65536
 constexpr int kRegsEpilogue = 96, kRegsOther = 48;
 static_assert(STAGES == NACC, "stage and accumulator share one completion barrier");
+constexpr int BP_STAGES = 8;                       // ring of packed weight tiles: fetched far ahead, freed by the producers
 constexpr int A_BYTES = BM * GK;                   // int8 activation tile of one group, 128-byte swizzle
 constexpr int BX_BYTES = BN * GK;                  // expanded int8 weight tile, core-matrix layout
 constexpr int BP_BYTES = BN * GK / 2;              // packed weight tile as copied, 64-byte swizzle
-constexpr int STAGE_BYTES = A_BYTES + BX_BYTES + BP_BYTES;
+constexpr int STAGE_BYTES = A_BYTES + BX_BYTES;    // what the MMA reads: freed when its MMAs have completed
 constexpr int LBO = (BN / 8) * 128;                // weights: bytes between core matrices adjacent in K
 constexpr int SBO = 128;                           // weights: bytes between 8-row groups
 constexpr int kSpin = 1 << 17;
@@ -78,7 +79,8 @@ struct GemmParams {
 };
 
 struct __align__(16) Control {          // head of the dynamic shared memory
-    uint64_t ldb_full[STAGES];           // copy lane -> producers: packed weight tile landed
+    uint64_t bp_full[BP_STAGES];         // weight copy lane -> producers: packed weight tile landed
+    uint64_t bp_free[BP_STAGES];         // producers -> weight copy lane: packed tile is in registers
     uint64_t full[STAGES];               // -> MMA: activation tile landed (copy, byte count) and weight tile
                                          //    expanded (one arrival per producer warp)
     uint64_t drain[2];                   // MMA issuers: everything they issued has completed
@@ -209,7 +211,8 @@ __device__ __forceinline__ uint32_t instr_desc() {
 
 // 0 while every bounded wait of the GEMM kernels has been satisfied; otherwise the code of
 // the first one that ran out (1 stage not free, 2 weights not expanded, 3 accumulator not drained,
-// 4 accumulator not complete, 5 scales not landed, 6 packed weights not landed).  Read and cleared by fm_gemm_status().
+// 4 accumulator not complete, 5 scales not landed, 6 packed weights not landed, 7 expanded tile
+// not free, 8 packed tile not free).  Read and cleared by fm_gemm_status().
 __device__ int g_gemm_status;
 
 __device__ __forceinline__ uint32_t even16(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }   // 16*v of k0,k2,k4,k6
@@ -255,8 +258,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // the swizzled tiles need a 1024-byte aligned base whatever the offset of the dynamic window is
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     Control* ctl = reinterpret_cast<Control*>(smem);
-    uint8_t* stages = smem + 1024;                                   // STAGES x (A, expanded W, packed W)
-    float* sc_ring = reinterpret_cast<float*>(stages + STAGES * STAGE_BYTES);   // [SLOTS][2][128]
+    uint8_t* stages = smem + 1024;                                   // STAGES x (A, expanded W)
+    uint8_t* bp_ring = stages + STAGES * STAGE_BYTES;                // BP_STAGES x packed W
+    float* sc_ring = reinterpret_cast<float*>(bp_ring + BP_STAGES * BP_BYTES);   // [SLOTS][2][128]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.K / GK;
     const int tiles_m = p.M / BM, tiles_n = (p.N + BN - 1) / BN;
@@ -269,8 +273,11 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // one arrival per WARP on the software barriers (hundreds of per-thread arrivals on one
         // barrier word would serialise)
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&ctl->ldb_full[s], 1);
             mbar_init(&ctl->full[s], 5);
+        }
+        for (int s = 0; s < BP_STAGES; s++) {
+            mbar_init(&ctl->bp_full[s], 1);
+            mbar_init(&ctl->bp_free[s], 4);
         }
         mbar_init(&ctl->drain[0], 1);
         mbar_init(&ctl->drain[1], 1);
@@ -298,16 +305,18 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // the 8-row groups pw, pw + 4, pw + 8, pw + 12
         const int pw = warp - PROD_WARP0, q = lane >> 3, rr = lane & 7;
         for (int it = 0; it < total; it++) {
-            const int s = it % STAGES;
-            if (!wait_or_abort(&ctl->ldb_full[s], (it / STAGES) & 1, ctl, status, 6)) break;
+            const int s = it % STAGES, sp = it % BP_STAGES;
+            if (!wait_or_abort(&ctl->bp_full[sp], (it / BP_STAGES) & 1, ctl, status, 6)) break;
             uint8_t* Bx = stages + s * STAGE_BYTES + A_BYTES;
-            const uint8_t* Bp = Bx + BX_BYTES;
+            const uint8_t* Bp = bp_ring + sp * BP_BYTES;
             uint4 w[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int row = (i * 4 + pw) * 8 + rr;               // 64-byte swizzle: chunk ^= (row / 2) % 4
                 w[i] = *reinterpret_cast<const uint4*>(Bp + row * 64 + ((q ^ ((row >> 1) & 3)) << 4));
             }
+            // the expanded tile of stage s was read by the MMAs of step it - STAGES
+            if (it >= STAGES && !wait_or_abort(&ctl->acc_full[s], ((it / STAGES) & 1) ^ 1, ctl, status, 7)) break;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 uint8_t* dst = Bx + (2 * q) * LBO + (i * 4 + pw) * SBO + rr * 16;
@@ -316,7 +325,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core's reads
             __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl->full[s]);
+            if (lane == 0) {
+                mbar_arrive(&ctl->full[s]);
+                mbar_arrive(&ctl->bp_free[sp]);                      // the packed tile may be refilled
+            }
         }
     } else if (warp >= EPI_WARPS) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
@@ -339,8 +351,6 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     bulk_g2s(sc, p.sa + (size_t)ld.g * p.M + ld.m0, BM * 4, &ctl->sc_full[slot]);
                     bulk_g2s(sc + 128, p.sb + (size_t)ld.g * p.N + ld.n0, nb, &ctl->sc_full[slot]);
                     uint8_t* st = stages + s * STAGE_BYTES;
-                    mbar_expect_tx(&ctl->ldb_full[s], BP_BYTES);
-                    tma_2d(st + A_BYTES + BX_BYTES, &tmB, ld.g * (GK / 2), ld.n0, &ctl->ldb_full[s]);
                     mbar_expect_tx(&ctl->full[s], A_BYTES);
                     tma_2d(st, &tmA, ld.g * GK, ld.m0, &ctl->full[s]);
                     issued = it + 1;
@@ -349,9 +359,30 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // leaving early: the copies already issued must have landed before the CTA's shared
                     // memory is given up (bounded like every other wait; nothing is reported twice)
                     for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; j++) {
-                        for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->ldb_full[j % STAGES], (j / STAGES) & 1); i++) {}
+                        for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->full[j % STAGES], (j / STAGES) & 1); i++) {}
                         for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->sc_full[j % SCALE_SLOTS], (j / SCALE_SLOTS) & 1); i++) {}
                     }
+                }
+            }
+        } else if (warp == TMA_WARP + 1) {
+            // ================================================================ weight copy lane
+            // the packed weight tiles run up to BP_STAGES steps ahead of the producers, so their trip
+            // from L2 is off the critical path
+            if (lane == 0) {
+                Cursor ld;
+                ld.g = 0;
+                ld.set_tile((int)blockIdx.x, tiles_m);
+                int issued = 0;
+                for (int it = 0; it < total; it++, ld.next(G, tiles_m, (int)gridDim.x)) {
+                    const int sp = it % BP_STAGES;
+                    if (it >= BP_STAGES && !wait_or_abort(&ctl->bp_free[sp], ((it / BP_STAGES) & 1) ^ 1, ctl, status, 8)) break;
+                    mbar_expect_tx(&ctl->bp_full[sp], BP_BYTES);
+                    tma_2d(bp_ring + sp * BP_BYTES, &tmB, ld.g * (GK / 2), ld.n0, &ctl->bp_full[sp]);
+                    issued = it + 1;
+                }
+                if (ctl->abort) {
+                    for (int j = issued > BP_STAGES ? issued - BP_STAGES : 0; j < issued; j++)
+                        for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->bp_full[j % BP_STAGES], (j / BP_STAGES) & 1); i++) {}
                 }
             }
         } else if (warp < TMA_WARP) {
@@ -462,7 +493,8 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------- host side
-constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * STAGE_BYTES + SCALE_SLOTS * 256 * 4 + 1024;
+constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)BP_STAGES * BP_BYTES + SCALE_SLOTS * 256 * 4 + 1024;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
