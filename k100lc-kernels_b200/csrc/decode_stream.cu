@@ -18,8 +18,7 @@
 //     mbarrier per stage; once per layer it also copies that layer's int8 codes, scales
 //     and group sums (5.4 KB) into a double-buffered tile;
 //   * warps 0..CW-1 are consumers: warp w takes row w of a stage, lane l the 16-byte
-//     words l, l+32, .. of that row (LDS.128) into registers and releases the stage at
-//     once; then nibbles -> dp4a against the token's codes held in registers, two
+//     words l, l+32, .. of that row (LDS.128) into registers; nibbles -> dp4a against the token's codes held in registers, two
 //     shuffles per 128-group, f16 scale * act scale * float(I), butterfly, lane 0 stores y.
 //   * W4A8 has a second consumer (the default) that feeds a stage of 16 rows to the tensor
 //     cores as one m16 tile (mma.sync int8), described at w4a8_stream_mma_kernel below: 40 %
@@ -242,8 +241,6 @@ w4_stream_kernel(const StreamParams p) {
                 asu8[it] = 8 * *reinterpret_cast<const int*>(ab + K + NG * 4 + (d0 >> 4) * 4);
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&act_free[l & 1]);
         float* y = p.layers[l].y + p.row_base;
 
         for (int j = 0; j < nst; j++, c++) {
@@ -265,19 +262,27 @@ w4_stream_kernel(const StreamParams p) {
                     sw[it] = __half2float(srow[(it * 128 + lane * 4) >> 4]);
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);          // the stage may be refilled while we compute
-            if (!live) continue;
             float acc = 0.f;
+            if (live) {
 #pragma unroll
-            for (int it = 0; it < KITER; it++) {
-                int v = dot32_u(w[it], ae[it], ao[it]);
-                if (!A4) {
-                    v += __shfl_xor_sync(0xffffffffu, v, 1);
-                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                for (int it = 0; it < KITER; it++) {
+                    int v = dot32_u(w[it], ae[it], ao[it]);
+                    if (!A4) {
+                        v += __shfl_xor_sync(0xffffffffu, v, 1);
+                        v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    }
+                    if (A4 || (lane & 3) == 0) acc += (sw[it] * asc[it]) * (float)(v - asu8[it]);
                 }
-                if (A4 || (lane & 3) == 0) acc += (sw[it] * asc[it]) * (float)(v - asu8[it]);
             }
+            // Release only now: the arithmetic above has consumed every register loaded from the stage
+            // (and, in a layer's first stage, from the code tile), so those loads have completed.  An
+            // arrive issued right behind the loads can overtake them, and the refill would race with them.
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&empty[s]);
+                if (j == 0) mbar_arrive(&act_free[l & 1]);
+            }
+            if (!live) continue;
             acc = warp_sum(acc);
             if (lane == 0) {
                 if (tiled) {
@@ -434,8 +439,6 @@ w4a8_stream_mma_kernel(const StreamParams p) {
             sa[j] = *reinterpret_cast<const float*>(ab + K + gg * 4);
             su8[j] = 8 * *reinterpret_cast<const int*>(ab + K + NG * 4 + gg * 4);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&act_free[l & 1]);
         float* y = p.layers[l].y + p.row_base;
 
         for (int jst = 0; jst < nst; jst++, c++) {
@@ -452,8 +455,6 @@ w4a8_stream_mma_kernel(const StreamParams p) {
                 swa[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + g * SCB + gg * 2));
                 swb[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + (g + 8) * SCB + gg * 2));
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);          // registers hold the stage: refill may start
             float fa = 0.f, fb = 0.f;                       // partial y of rows g and g+8 over this warp's groups
 #pragma unroll
             for (int j = 0; j < GPW; j++) {
@@ -472,6 +473,14 @@ w4a8_stream_mma_kernel(const StreamParams p) {
                 const int ib = lo[2] + (hi[2] >> 4) - su8[j];
                 fa += (swa[j] * sa[j]) * (float)ia;
                 fb += (swb[j] * sa[j]) * (float)ib;
+            }
+            // Release only now: the MMAs and multiplies above have consumed every register loaded from
+            // the stage (and, in a layer's first stage, from the code tile), so those loads have
+            // completed.  An arrive issued right behind the loads can overtake them.
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&empty[s]);
+                if (jst == 0) mbar_arrive(&act_free[l & 1]);
             }
             const int rb = c & 1;
             if (c >= 2 && !mbar_wait(&red_free[rb], ((c >> 1) & 1) ^ 1, p.status, 5)) return;
