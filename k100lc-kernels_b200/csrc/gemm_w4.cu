@@ -56,10 +56,12 @@ constexpr int TMA_WARP = EPI_WARPS + 2;            // lane 0 copies activations 
 constexpr int PROD_WARP0 = EPI_WARPS + 4;          // first of the 4 producer warps
 constexpr int kThreads = (EPI_WARPS + 4 + 4) * 32;
 // 768 threads start with 80 registers each; the epilogue (32 running sums + 32 loaded integers per
-// thread) takes 96, the other two groups shrink to 48: 4*128*96 + 2*128*48 = 61440 of 65536
+// thread, and half of the scale products) takes 96, the other two groups shrink to 48: 4*128*96 + 2*128*48 =
+// 61440 of 65536.  (Asking for all of the register file, 104, made setmaxnreg.inc wait forever.)
 constexpr int kRegsEpilogue = 96, kRegsOther = 48;
 static_assert(STAGES == NACC, "stage and accumulator share one completion barrier");
 constexpr int BP_STAGES = 8;                       // ring of packed weight tiles: fetched far ahead, freed by the producers
+static_assert(SCALE_SLOTS >= BP_STAGES + 2 * NACC, "scale slot reuse distance (see the weight copy lane)");
 constexpr int A_BYTES = BM * GK;                   // int8 activation tile of one group, 128-byte swizzle
 constexpr int BX_BYTES = BN * GK;                  // expanded int8 weight tile, core-matrix layout
 constexpr int BP_BYTES = BN * GK / 2;              // packed weight tile as copied, 64-byte swizzle
@@ -86,7 +88,6 @@ struct __align__(16) Control {          // head of the dynamic shared memory
     uint64_t drain[2];                   // MMA issuers: everything they issued has completed
     uint64_t acc_full[NACC];             // MMA -> epilogue: accumulator complete; -> copy lane: stage consumed
     uint64_t acc_empty[NACC];            // epilogue -> MMA: accumulator drained
-    uint64_t sc_full[SCALE_SLOTS];       // copy lane -> epilogue: scales of a group landed
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -154,7 +155,8 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint6
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-// 32 lanes x 32 columns of 32-bit: thread t of the warp gets lane t, columns c..c+31
+// 32 lanes x 32 columns of 32-bit: thread t of the warp gets lane t, columns c..c+31 (asynchronous:
+// the registers are valid after tmem_ld_wait)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -164,13 +166,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                    "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// the loaded registers are operands of the wait, so that no use of them can be scheduled ahead of it
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
 }
 
 // two fp32 lanes per instruction (sm_100 packed fp32): per lane identical to fmul / fmaf
 __device__ __forceinline__ void mul2(float& d0, float& d1, float a, float b0, float b1) {
     asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2,%2};\nmov.b64 rb, {%3,%4};\nmul.rn.f32x2 rd, ra, rb;\nmov.b64 {%0,%1}, rd;\n}"
         : "=f"(d0), "=f"(d1) : "f"(a), "f"(b0), "f"(b1));
+}
+// float(i) for |i| < 2^22 without the conversion unit: 1.5 * 2^23 + i is exact in the mantissa of a
+// float, and subtracting 1.5 * 2^23 again is exact too (two lanes per instruction)
+__device__ __forceinline__ void int2float2(float& f0, float& f1, uint32_t i0, uint32_t i1) {
+    const float a0 = __uint_as_float(0x4B400000u + i0), a1 = __uint_as_float(0x4B400000u + i1);
+    asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2,%3};\nmov.b64 rb, {%4,%4};\nadd.rn.f32x2 rd, ra, rb;\nmov.b64 {%0,%1}, rd;\n}"
+        : "=f"(f0), "=f"(f1) : "f"(a0), "f"(a1), "f"(-12582912.0f));
 }
 __device__ __forceinline__ void fma2(float& c0, float& c1, float a0, float a1, float b0, float b1) {
     asm("{\n.reg .b64 ra, rb, rc;\nmov.b64 ra, {%2,%3};\nmov.b64 rb, {%4,%5};\nmov.b64 rc, {%0,%1};\n"
@@ -211,7 +225,7 @@ __device__ __forceinline__ uint32_t instr_desc() {
 
 // 0 while every bounded wait of the GEMM kernels has been satisfied; otherwise the code of
 // the first one that ran out (1 stage not free, 2 weights not expanded, 3 accumulator not drained,
-// 4 accumulator not complete, 5 scales not landed, 6 packed weights not landed, 7 expanded tile
+// 4 accumulator not complete, 6 packed weights and scales not landed, 7 expanded tile
 // not free, 8 packed tile not free).  Read and cleared by fm_gemm_status().
 __device__ int g_gemm_status;
 
@@ -285,7 +299,6 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mbar_init(&ctl->acc_full[b], 1);
             mbar_init(&ctl->acc_empty[b], EPI_WARPS);
         }
-        for (int s = 0; s < SCALE_SLOTS; s++) mbar_init(&ctl->sc_full[s], 1);
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -340,16 +353,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 ld.set_tile((int)blockIdx.x, tiles_m);
                 int issued = 0;
                 for (int it = 0; it < total; it++, ld.next(G, tiles_m, (int)gridDim.x)) {
-                    const int s = it % STAGES, slot = it % SCALE_SLOTS;
-                    // stage s was read by the MMAs of step it - STAGES; a scale slot is reused 16 steps later,
-                    // by when the epilogue of its previous user is long done (the MMA of step it - 4 waited for
-                    // the epilogue of step it - 8)
+                    const int s = it % STAGES;
+                    // stage s was read by the MMAs of step it - STAGES
                     if (it >= STAGES && !wait_or_abort(&ctl->acc_full[s], ((it / STAGES) & 1) ^ 1, ctl, status, 1)) break;
-                    const uint32_t nb = (uint32_t)min(BN, p.N - ld.n0) * 4u;
-                    float* sc = sc_ring + slot * 256;
-                    mbar_expect_tx(&ctl->sc_full[slot], BM * 4 + nb);
-                    bulk_g2s(sc, p.sa + (size_t)ld.g * p.M + ld.m0, BM * 4, &ctl->sc_full[slot]);
-                    bulk_g2s(sc + 128, p.sb + (size_t)ld.g * p.N + ld.n0, nb, &ctl->sc_full[slot]);
                     uint8_t* st = stages + s * STAGE_BYTES;
                     mbar_expect_tx(&ctl->full[s], A_BYTES);
                     tma_2d(st, &tmA, ld.g * GK, ld.m0, &ctl->full[s]);
@@ -360,7 +366,6 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // memory is given up (bounded like every other wait; nothing is reported twice)
                     for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; j++) {
                         for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->full[j % STAGES], (j / STAGES) & 1); i++) {}
-                        for (int i = 0; i < kSpin && !mbar_try_wait(&ctl->sc_full[j % SCALE_SLOTS], (j / SCALE_SLOTS) & 1); i++) {}
                     }
                 }
             }
@@ -376,8 +381,17 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int it = 0; it < total; it++, ld.next(G, tiles_m, (int)gridDim.x)) {
                     const int sp = it % BP_STAGES;
                     if (it >= BP_STAGES && !wait_or_abort(&ctl->bp_free[sp], ((it / BP_STAGES) & 1) ^ 1, ctl, status, 8)) break;
-                    mbar_expect_tx(&ctl->bp_full[sp], BP_BYTES);
+                    const uint32_t nb = (uint32_t)min(BN, p.N - ld.n0) * 4u;
+                    mbar_expect_tx(&ctl->bp_full[sp], BP_BYTES + BM * 4 + nb);
                     tma_2d(bp_ring + sp * BP_BYTES, &tmB, ld.g * (GK / 2), ld.n0, &ctl->bp_full[sp]);
+                    // The scales of the step travel with it.  Slot it % 16 was last used by step it - 16: the
+                    // producers have finished step it - 8 (bp_free), for which they waited for the MMAs of step
+                    // it - 12, which were issued after the epilogue had drained step it - 16.
+                    // They complete on the packed tile's barrier: the producers wait for it, the MMAs wait for
+                    // the producers and the epilogue waits for the MMAs.
+                    float* sc = sc_ring + (it % SCALE_SLOTS) * 256;
+                    bulk_g2s(sc, p.sa + (size_t)ld.g * p.M + ld.m0, BM * 4, &ctl->bp_full[sp]);
+                    bulk_g2s(sc + 128, p.sb + (size_t)ld.g * p.N + ld.n0, nb, &ctl->bp_full[sp]);
                     issued = it + 1;
                 }
                 if (ctl->abort) {
@@ -439,32 +453,43 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int it = 0; it < total; it++, cur.next(G, tiles_m, (int)gridDim.x)) {
             const int b = it % NACC, slot = it % SCALE_SLOTS, g = cur.g;
             const int m0 = cur.m0, n0 = cur.n0 + ch * CPW;
-            if (!wait_or_abort(&ctl->sc_full[slot], (it / SCALE_SLOTS) & 1, ctl, status, 5)) break;
             if (!wait_or_abort(&ctl->acc_full[b], (it / NACC) & 1, ctl, status, 4)) break;
             tc_fence_after();
+            // (the scales landed with the packed weight tile, before the producers expanded it for these MMAs)
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(lq * 32) << 16) + b * BN + ch * CPW, r);
+            // while the accumulator is on its way: the scale products, rounded to fp32 first
             const float sa = sc_ring[slot * 256 + mrow] * inv;
             const float* sbv = sc_ring + slot * 256 + 128 + ch * CPW;
+            constexpr int PRE = CPW / 2;                            // products computed ahead (register budget)
+            float sc[PRE];
 #pragma unroll
-            for (int c = 0; c < CPW / 32; c++) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(lq * 32) << 16) + b * BN + ch * CPW + c * 32, r);
+            for (int j = 0; j < PRE; j += 4) {
+                const float4 sb4 = *reinterpret_cast<const float4*>(sbv + j);   // one broadcast load for four columns
+                mul2(sc[j], sc[j + 1], sa, sb4.x, sb4.y);
+                mul2(sc[j + 2], sc[j + 3], sa, sb4.z, sb4.w);
+            }
+            tmem_ld_wait(r);
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    const int col = c * 32 + j;
-                    // one 16-byte broadcast load for four columns: shared-memory bandwidth is what this
-                    // kernel runs out of (the MMA alone reads 128 bytes per clock)
-                    const float4 sb4 = *reinterpret_cast<const float4*>(sbv + col);
-                    float s0, s1, s2, s3;
-                    mul2(s0, s1, sa, sb4.x, sb4.y);                  // scale products, rounded to fp32 first
+            for (int j = 0; j < CPW; j += 4) {
+                float s0, s1, s2, s3;
+                if (j < PRE) {
+                    s0 = sc[j]; s1 = sc[j + 1]; s2 = sc[j + 2]; s3 = sc[j + 3];
+                } else {
+                    const float4 sb4 = *reinterpret_cast<const float4*>(sbv + j);
+                    mul2(s0, s1, sa, sb4.x, sb4.y);
                     mul2(s2, s3, sa, sb4.z, sb4.w);
-                    fma2(facc[col], facc[col + 1], (float)(int)r[j], (float)(int)r[j + 1], s0, s1);
-                    fma2(facc[col + 2], facc[col + 3], (float)(int)r[j + 2], (float)(int)r[j + 3], s2, s3);
-                    if (DUMP) {
-                        int* d = p.dump + ((size_t)(m0 + mrow) * p.N + n0 + col) * G + g;
+                }
+                float f0, f1, f2, f3;
+                int2float2(f0, f1, r[j], r[j + 1]);                 // |256 * I| <= 2^21
+                int2float2(f2, f3, r[j + 2], r[j + 3]);
+                fma2(facc[j], facc[j + 1], f0, f1, s0, s1);
+                fma2(facc[j + 2], facc[j + 3], f2, f3, s2, s3);
+                if (DUMP) {
+                    int* d = p.dump + ((size_t)(m0 + mrow) * p.N + n0 + j) * G + g;
 #pragma unroll
-                        for (int u = 0; u < 4; u++)
-                            if (n0 + col + u < p.N) d[u * G] = (int)r[j + u] >> p.shift;
-                    }
+                    for (int u = 0; u < 4; u++)
+                        if (n0 + j + u < p.N) d[u * G] = (int)r[j + u] >> p.shift;
                 }
             }
             tc_fence_before();
