@@ -368,7 +368,14 @@ def gemm_timings(rt, st: "Stream", reps: int = 5) -> dict:
                      "gemm_tops": round(ops / ms_g / 1e9, 1),
                      "frac_of_int8_peak": round(ops / ms_g / 1e9 / pk_int8, 4)}
     out["int8_peak_tops_assumed"] = pk_int8
-    out["note"] = "int8 peak assumed = 2 x the measured dense bf16 figure (no int8 peak is measured on this pool)"
+    # tcgen05.mma.kind::i8 M128 N128 K32 issued back to back from shared memory completes one MMA per 64.2
+    # clocks on these B200s (8172 MAC per clock per SM, measured once with a stand-alone loop)
+    issue_tops = 2 * 8172.0 * rt.device_attr("sm_count") * rt.device_attr("clock_khz") * 1e3 / 1e12
+    out["int8_mma_issue_rate_tops"] = round(issue_tops, 1)
+    for name in ("w4a4", "w4a8"):
+        out[name]["frac_of_mma_issue_rate"] = round(out[name]["gemm_tops"] / issue_tops, 4)
+    out["note"] = ("no int8 peak is measured on this pool: frac_of_int8_peak uses 2 x the measured dense bf16 figure, "
+                   "frac_of_mma_issue_rate the tensor core's own int8 rate at the maximum SM clock")
     if rt.gemm_status() != 0:
         raise RuntimeError("a bounded wait ran out in the GEMM kernel")
     for ptr in (x, wsc, aq4, aq8, asc, c):

@@ -179,13 +179,6 @@ __device__ __forceinline__ void mul2(float& d0, float& d1, float a, float b0, fl
     asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2,%2};\nmov.b64 rb, {%3,%4};\nmul.rn.f32x2 rd, ra, rb;\nmov.b64 {%0,%1}, rd;\n}"
         : "=f"(d0), "=f"(d1) : "f"(a), "f"(b0), "f"(b1));
 }
-// float(i) for |i| < 2^22 without the conversion unit: 1.5 * 2^23 + i is exact in the mantissa of a
-// float, and subtracting 1.5 * 2^23 again is exact too (two lanes per instruction)
-__device__ __forceinline__ void int2float2(float& f0, float& f1, uint32_t i0, uint32_t i1) {
-    const float a0 = __uint_as_float(0x4B400000u + i0), a1 = __uint_as_float(0x4B400000u + i1);
-    asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2,%3};\nmov.b64 rb, {%4,%4};\nadd.rn.f32x2 rd, ra, rb;\nmov.b64 {%0,%1}, rd;\n}"
-        : "=f"(f0), "=f"(f1) : "f"(a0), "f"(a1), "f"(-12582912.0f));
-}
 __device__ __forceinline__ void fma2(float& c0, float& c1, float a0, float a1, float b0, float b1) {
     asm("{\n.reg .b64 ra, rb, rc;\nmov.b64 ra, {%2,%3};\nmov.b64 rb, {%4,%5};\nmov.b64 rc, {%0,%1};\n"
         "fma.rn.f32x2 rc, ra, rb, rc;\nmov.b64 {%0,%1}, rc;\n}"
@@ -480,9 +473,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     mul2(s0, s1, sa, sb4.x, sb4.y);
                     mul2(s2, s3, sa, sb4.z, sb4.w);
                 }
-                float f0, f1, f2, f3;
-                int2float2(f0, f1, r[j], r[j + 1]);                 // |256 * I| <= 2^21
-                int2float2(f2, f3, r[j + 2], r[j + 3]);
+                // (a magic-number conversion on the FMA pipe was measured slower: the epilogue is bound by
+                //  issue slots, and the conversion unit is otherwise idle)
+                const float f0 = (float)(int)r[j], f1 = (float)(int)r[j + 1];
+                const float f2 = (float)(int)r[j + 2], f3 = (float)(int)r[j + 3];
                 fma2(facc[j], facc[j + 1], f0, f1, s0, s1);
                 fma2(facc[j + 2], facc[j + 3], f2, f3, s2, s3);
                 if (DUMP) {
