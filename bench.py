@@ -302,6 +302,37 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         rt.graph_free(g)
         us = ms * 1e3 / nl
         out[name] = {"us_per_layer": round(us, 3), "gb_per_s": round(nbytes * frac / us / 1e3, 1)}
+    # four tokens per layer (the reference's launch sequence: one quantiser launch per token, one GEMV)
+    from k100lc_kernels import W4Runner
+    runner = W4Runner(rt)
+    m4 = lambda kind: (lambda l: runner.gemv_device(kind, st.wq_l(l), st.ws_l(l), None, rows, K, x_dev=st.x + min(l, st.layers - 4) * K * 4,
+                                                    y_dev=st.y + min(l, st.layers - 4) * N * 4, m=4, sync=False))
+    for name, kind in (("w4a8_m4", "w4a8"), ("w4a4_m4", "w4a4")):
+        if st.layers < 4:
+            break
+        fn = m4(kind)
+        fn(0)                                           # the runner's scratch buffers exist before the capture
+        rt.sync()
+        g = graph_of(fn, nl)
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
+        rt.graph_free(g)
+        out[name] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
+    runner.close()
+    # W4A16: compressed-tensors bytes (offset-binary nibbles, bf16 group scales), fp32 activations
+    from k100lc_kernels import DotLinear, Workspace
+    nd = min(nl, 8)
+    bf16_bits = lambda a: (a.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    with Workspace(rt) as dws:
+        dots = [DotLinear(rt, rows, K, "int4", rng.integers(0, 256, size=(rows, K // 2), dtype=np.uint8),
+                          (bf16_bits(np.abs(rng.standard_normal((rows, NG))) * 0.01 + 1e-3),), ws=dws, tag=f"bench_dot{i}")
+                for i in range(nd)]
+        for d in dots:
+            d.forward_device(st.x, 1)                   # output buffers exist before the capture
+        rt.sync()
+        g = graph_of(lambda l: dots[l % nd].forward_device(st.x + l * K * 4, 1), nl)
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
+        rt.graph_free(g)
+        out["w4a16_m1"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
     # the same layers through the multi-layer stream kernels (two launches for all nl layers)
     table = rt.stream_table([(st.wq_l(l), st.ws_l(l), st.x + l * K * 4, st.y + l * N * 4) for l in range(nl)], rows, K, 0)
     status = rt.alloc(4)

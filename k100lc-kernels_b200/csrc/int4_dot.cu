@@ -18,6 +18,9 @@
 // float without an integer conversion: PRMT drops the code into the low byte of
 // 0x4B000000 (= 2^23 + code) and one fp32 subtract of 2^23 + 8 gives code - 8 exactly.
 // The path is fp32 throughout (no integer accumulator exists on it).
+#include <cuda_bf16.h>
+#include <stdlib.h>
+
 #include "device_utils.cuh"
 #include "fm_internal.h"
 
@@ -38,28 +41,81 @@ struct DotParams {
 };
 
 // eight codes of one packed word times eight activations, added into acc[0..3]
-// (code j goes to accumulator j % 4, as in the reference)
+// (code j goes to accumulator j % 4, as in the reference); two fp32 lanes per instruction
+__device__ __forceinline__ void sub2(float& d0, float& d1, float a0, float a1, float b) {
+    asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2,%3};\nmov.b64 rb, {%4,%4};\nadd.rn.f32x2 rd, ra, rb;\nmov.b64 {%0,%1}, rd;\n}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b));
+}
+__device__ __forceinline__ void fma2(float& c0, float& c1, float a0, float a1, float b0, float b1) {
+    asm("{\n.reg .b64 ra, rb, rc;\nmov.b64 ra, {%2,%3};\nmov.b64 rb, {%4,%5};\nmov.b64 rc, {%0,%1};\n"
+        "fma.rn.f32x2 rc, ra, rb, rc;\nmov.b64 {%0,%1}, rc;\n}"
+        : "+f"(c0), "+f"(c1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
 __device__ __forceinline__ void fma_word(uint32_t w, const float4& xa, const float4& xb, float acc[4]) {
     const uint32_t lo = w & 0x0F0F0F0Fu;            // codes 0,2,4,6
     const uint32_t hi = (w >> 4) & 0x0F0F0F0Fu;     // codes 1,3,5,7
     const uint32_t magic = 0x4B000000u;             // 2^23
-    const float bias = 8388616.0f;                  // 2^23 + 8
-    const float c0 = __uint_as_float(prmt(lo, magic, 0x7540u)) - bias;
-    const float c1 = __uint_as_float(prmt(hi, magic, 0x7540u)) - bias;
-    const float c2 = __uint_as_float(prmt(lo, magic, 0x7541u)) - bias;
-    const float c3 = __uint_as_float(prmt(hi, magic, 0x7541u)) - bias;
-    const float c4 = __uint_as_float(prmt(lo, magic, 0x7542u)) - bias;
-    const float c5 = __uint_as_float(prmt(hi, magic, 0x7542u)) - bias;
-    const float c6 = __uint_as_float(prmt(lo, magic, 0x7543u)) - bias;
-    const float c7 = __uint_as_float(prmt(hi, magic, 0x7543u)) - bias;
-    acc[0] = fmaf(c0, xa.x, acc[0]);
-    acc[1] = fmaf(c1, xa.y, acc[1]);
-    acc[2] = fmaf(c2, xa.z, acc[2]);
-    acc[3] = fmaf(c3, xa.w, acc[3]);
-    acc[0] = fmaf(c4, xb.x, acc[0]);
-    acc[1] = fmaf(c5, xb.y, acc[1]);
-    acc[2] = fmaf(c6, xb.z, acc[2]);
-    acc[3] = fmaf(c7, xb.w, acc[3]);
+    const float nbias = -8388616.0f;                // -(2^23 + 8)
+    float c0, c1, c2, c3, c4, c5, c6, c7;
+    sub2(c0, c1, __uint_as_float(prmt(lo, magic, 0x7540u)), __uint_as_float(prmt(hi, magic, 0x7540u)), nbias);
+    sub2(c2, c3, __uint_as_float(prmt(lo, magic, 0x7541u)), __uint_as_float(prmt(hi, magic, 0x7541u)), nbias);
+    sub2(c4, c5, __uint_as_float(prmt(lo, magic, 0x7542u)), __uint_as_float(prmt(hi, magic, 0x7542u)), nbias);
+    sub2(c6, c7, __uint_as_float(prmt(lo, magic, 0x7543u)), __uint_as_float(prmt(hi, magic, 0x7543u)), nbias);
+    fma2(acc[0], acc[1], c0, c1, xa.x, xa.y);
+    fma2(acc[2], acc[3], c2, c3, xa.z, xa.w);
+    fma2(acc[0], acc[1], c4, c5, xb.x, xb.y);
+    fma2(acc[2], acc[3], c6, c7, xb.z, xb.w);
+}
+
+// Dense layout (one weight table, every row reads activation row 0): activation-stationary.
+// A warp owns one 512-byte slice of every weight row (8 blocks of 128 weights; lane l the 16-byte
+// word l of the slice, a block is 4 lanes) and keeps the 32 activations its lane needs in registers
+// for the whole kernel: no shared memory, one 16-byte load per lane and row, UN rows in flight.
+// The CTA has one warp per slice and walks rows blockIdx.x, blockIdx.x + gridDim.x, ...
+template <int UN>
+__global__ void __launch_bounds__(1024)
+int4_dot_dense_kernel(const DotParams p) {
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const uint32_t nbpr = p.nbpr;
+    const uint32_t rows = (p.items + nbpr - 1) / nbpr;       // the last row may be partial
+    const uint32_t word = slice * 32 + lane;                 // 16-byte word of the row
+    const bool live = word < nbpr * 4;
+    const uint32_t b = word >> 2;                            // block inside the row
+    const size_t base = (size_t)p.ids[0] * p.stride;
+    const uint8_t* w = p.w + base + (size_t)word * 16;
+    const uint16_t* sc = reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(p.scale) + base / 32) + b;
+    const size_t row_bytes = (size_t)nbpr * 64;
+    pdl_wait();
+    float4 xv[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        xv[j] = live ? *reinterpret_cast<const float4*>(p.x + (size_t)word * 32 + j * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t r0 = blockIdx.x; r0 < rows; r0 += gridDim.x * UN) {
+        uint4 w4[UN];
+        uint32_t sb[UN];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const uint32_t r = r0 + u * gridDim.x;
+            const bool ok = live && r < rows;
+            w4[u] = ok ? ld_stream_v4(w + (size_t)r * row_bytes) : make_uint4(0, 0, 0, 0);
+            sb[u] = ok ? sc[(size_t)r * nbpr] : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const uint32_t r = r0 + u * gridDim.x;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            fma_word(w4[u].x, xv[0], xv[1], acc);
+            fma_word(w4[u].y, xv[2], xv[3], acc);
+            fma_word(w4[u].z, xv[4], xv[5], acc);
+            fma_word(w4[u].w, xv[6], xv[7], acc);
+            float v = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            const uint32_t item = r * nbpr + b;
+            if ((lane & 3) == 0 && live && r < rows && item < p.items) p.partial[item] = v * __uint_as_float(sb[u] << 16);
+        }
+    }
+    pdl_launch_dependents();
 }
 
 // SHARED_X: all rows use activation row 0, staged in shared memory; R rows per warp step.
@@ -127,8 +183,162 @@ int4_dot_kernel(const DotParams p) {
     pdl_launch_dependents();
 }
 
+// Dense layout on the tensor cores.  The fp32 activations are split into three bf16 terms
+// (x = x1 + x2 + x3 carries all 24 mantissa bits), the weights code - 8 are exact in bf16, so
+// mma.sync m16n8k16 (bf16 in, fp32 accumulate) with the three terms as three columns of B gives
+// the fp32 dot product to within accumulation rounding, and the add over the four lanes of a
+// 128-block happens inside the MMA.  A warp owns one block index (so its B fragments — 32
+// activations per lane — stay in registers) and walks 16-row units; lane (g, t) reads word t of
+// a block for rows g and g + 8 (one 16-byte load each) and converts nibbles to bf16 two at a time:
+// PRMT drops two codes into the low bytes of two 0x43xx halves (128 + code), one packed
+// subtract of 136 gives code - 8.  6 instructions per 8 weights instead of 19.
+__device__ __forceinline__ uint32_t bf16x2_sub136(uint32_t v) {
+    uint32_t d;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(v), "r"(0x43084308u));     // 136.0 twice
+    return d;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// term `which` (0, 1, 2) of the three-way bf16 split of x, as the upper 16 bits of a float
+__device__ __forceinline__ uint32_t bf16_term(float x, int which) {
+    float r = x;
+    uint32_t t = 0;
+    for (int i = 0; i <= which; i++) {
+        t = __float_as_uint(__bfloat162float(__float2bfloat16_rn(r))) >> 16;
+        r -= __uint_as_float(t << 16);
+    }
+    return t;
+}
+
+// A CTA has one warp per block index of a group of eight adjacent blocks (512 contiguous bytes of
+// every row) and walks 16-row units; the loads of the next two units are in flight while the
+// current two are multiplied (HBM latency under load is several microseconds — a warp that
+// loads, waits and then computes leaves the memory system idle half of the time).
+constexpr int kDotWarps = 8;
+
+// B fragments of int4_dot_mma_kernel, computed once per launch instead of once per warp:
+// out[((b * 3 + term) * 4 + t) * 16 + (q * 4 + h * 2 + i)] = bf16 pair of the split term of
+// x[128 b + 32 t + 8 q + 4 i + h] (low half) and x[... + 2] (high half)
+__global__ void __launch_bounds__(256)
+int4_dot_split_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, uint32_t nbpr) {
+    pdl_wait();
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < nbpr * 192) {
+        const uint32_t e = idx & 15, t = (idx >> 4) & 3, term = (idx >> 6) % 3, b = idx / 192;
+        const uint32_t q = e >> 2, h = (e >> 1) & 1, i = e & 1;
+        const float* xs = x + (size_t)b * 128 + t * 32 + 8 * q + 4 * i + h;
+        out[idx] = bf16_term(xs[0], (int)term) | (bf16_term(xs[2], (int)term) << 16);
+    }
+    pdl_launch_dependents();
+}
+
+template <int UN>
+__global__ void __launch_bounds__(kDotWarps * 32)
+int4_dot_mma_kernel(const DotParams p, const uint32_t* __restrict__ frags) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t nbpr = p.nbpr;
+    const uint32_t rows = (p.items + nbpr - 1) / nbpr;       // the last row may be partial
+    const uint32_t bgroups = (nbpr + kDotWarps - 1) / kDotWarps;
+    const uint32_t b = (blockIdx.x % bgroups) * kDotWarps + (threadIdx.x >> 5);   // this warp's block
+    const uint32_t ucta = blockIdx.x / bgroups, nucta = gridDim.x / bgroups;       // row-unit walk of the CTA
+    if (b >= nbpr || ucta >= nucta) return;
+    const size_t base = (size_t)p.ids[0] * p.stride;
+    const size_t row_bytes = (size_t)nbpr * 64;
+    const uint8_t* w = p.w + base + (size_t)b * 64 + t * 16;
+    const uint16_t* sc = reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(p.scale) + base / 32) + b;
+    const uint32_t nunits = (rows + 15) / 16;
+    const uint4 zero8 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);   // code 8 = weight 0
+    uint4 wa[UN], wb[UN];
+    const uint8_t* wnext = w + (size_t)(ucta * 16 + g) * row_bytes;   // row g of the next unit to fetch
+    const size_t ustep = (size_t)nucta * 16 * row_bytes;
+    auto fetch = [&](uint32_t u0) {
+#pragma unroll
+        for (int k = 0; k < UN; k++) {
+            const uint32_t unit = u0 + k * nucta;
+            const uint32_t ra = unit * 16 + g, rb = ra + 8;
+            wa[k] = (unit < nunits && ra < rows) ? ld_stream_v4(wnext) : zero8;
+            wb[k] = (unit < nunits && rb < rows) ? ld_stream_v4(wnext + 8 * row_bytes) : zero8;
+            wnext += ustep;
+        }
+    };
+    fetch(ucta);                                             // weights do not depend on the preceding kernel
+    pdl_wait();
+
+    // B fragments: MMA (q, h) uses, of the lane's 32 codes, codes 8q+h, 8q+2+h (b0) and 8q+4+h, 8q+6+h (b1);
+    // column g of B is term g of the split (columns 3..7 are zero)
+    uint32_t bf[4][2][2];
+    {
+        const uint4* fp = reinterpret_cast<const uint4*>(frags + ((size_t)(b * 3 + (g < 3 ? g : 0)) * 4 + t) * 16);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint4 v = g < 3 ? fp[q] : make_uint4(0, 0, 0, 0);
+            bf[q][0][0] = v.x; bf[q][0][1] = v.y; bf[q][1][0] = v.z; bf[q][1][1] = v.w;
+        }
+    }
+    for (uint32_t u0 = ucta; u0 < nunits; u0 += nucta * UN) {
+        uint4 ca[UN], cb[UN];
+#pragma unroll
+        for (int k = 0; k < UN; k++) {
+            ca[k] = wa[k];
+            cb[k] = wb[k];
+        }
+        fetch(u0 + nucta * UN);                              // next round (no loads past the end)
+#pragma unroll
+        for (int k = 0; k < UN; k++) {
+            const uint32_t unit = u0 + k * nucta;
+            if (unit >= nunits) break;
+            const uint32_t ra = unit * 16 + g, rb = ra + 8;
+            const uint32_t wav[4] = {ca[k].x, ca[k].y, ca[k].z, ca[k].w}, wbv[4] = {cb[k].x, cb[k].y, cb[k].z, cb[k].w};
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint32_t la = wav[q] & 0x0F0F0F0Fu, ha = (wav[q] >> 4) & 0x0F0F0F0Fu;
+                const uint32_t lb = wbv[q] & 0x0F0F0F0Fu, hb = (wbv[q] >> 4) & 0x0F0F0F0Fu;
+                const uint32_t m = 0x43434343u;
+                // even codes (0,2 | 4,6), then odd codes (1,3 | 5,7)
+                mma_bf16(c, bf16x2_sub136(prmt(la, m, 0x5140u)), bf16x2_sub136(prmt(lb, m, 0x5140u)),
+                         bf16x2_sub136(prmt(la, m, 0x5342u)), bf16x2_sub136(prmt(lb, m, 0x5342u)), bf[q][0][0], bf[q][0][1]);
+                mma_bf16(c, bf16x2_sub136(prmt(ha, m, 0x5140u)), bf16x2_sub136(prmt(hb, m, 0x5140u)),
+                         bf16x2_sub136(prmt(ha, m, 0x5342u)), bf16x2_sub136(prmt(hb, m, 0x5342u)), bf[q][1][0], bf[q][1][1]);
+            }
+            // columns 0, 1 (lane t = 0) and 2 (lane t = 1) hold the three terms: smallest first
+            const float va = __shfl_down_sync(0xffffffffu, c[0], 1), vb = __shfl_down_sync(0xffffffffu, c[2], 1);
+            if (t == 0) {
+                if (ra < rows && ra * nbpr + b < p.items)
+                    p.partial[(size_t)ra * nbpr + b] = ((va + c[1]) + c[0]) * __uint_as_float((uint32_t)sc[(size_t)ra * nbpr] << 16);
+                if (rb < rows && rb * nbpr + b < p.items)
+                    p.partial[(size_t)rb * nbpr + b] = ((vb + c[3]) + c[2]) * __uint_as_float((uint32_t)sc[(size_t)rb * nbpr] << 16);
+            }
+        }
+    }
+    pdl_launch_dependents();
+}
+
+// 128 rows per CTA: their nbpr partial sums are one contiguous range, fetched coalesced into shared
+// memory (row stride nbpr + 1 words: conflict-free), then every thread adds its row in index order.
 __global__ void __launch_bounds__(128)
 reduce_blocks_kernel(const float* __restrict__ partial, float* __restrict__ y, uint32_t rows, uint32_t nbpr) {
+    extern __shared__ float s_part[];
+    pdl_wait();
+    const uint32_t row0 = blockIdx.x * 128;
+    const uint32_t nrow = min(128u, rows - row0);
+    const float* src = partial + (size_t)row0 * nbpr;
+    for (uint32_t i = threadIdx.x; i < nrow * nbpr; i += 128) s_part[(i / nbpr) * (nbpr + 1) + i % nbpr] = src[i];
+    __syncthreads();
+    if (threadIdx.x < nrow) {
+        const float* q = s_part + threadIdx.x * (nbpr + 1);
+        float s = 0.f;
+        for (uint32_t j = 0; j < nbpr; j++) s += q[j];
+        y[row0 + threadIdx.x] = s;
+    }
+    pdl_launch_dependents();
+}
+
+// rows too long for the shared-memory tile: one thread per row straight from global memory
+__global__ void __launch_bounds__(128)
+reduce_blocks_long_kernel(const float* __restrict__ partial, float* __restrict__ y, uint32_t rows, uint32_t nbpr) {
     pdl_wait();
     const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r < rows) {
@@ -198,9 +408,40 @@ int launch_int4_dot(const LaunchCtx& c, const uint64_t* a) {
     }
     const bool shared_x = n_x == 1;
     const size_t smem = shared_x ? (size_t)p.nbpr * 512 : 0;
-    FM_REQUIRE(smem <= 200 * 1024, kn, "K=%u is too large for the shared-memory activation row", p.nbpr * 128);
     cudaError_t e;
-    if (shared_x) {
+    if (shared_x && n_w == 1 && p.nbpr <= 256) {
+        // dense layer: one warp per 8 blocks of the row, rows strided over the CTAs
+        static const int cfg = getenv("FM_DOT_CFG") ? atoi(getenv("FM_DOT_CFG")) : 0;
+        if (cfg != 1) {                              // tensor-core kernel: one warp per block index, 16-row units
+            auto kern = int4_dot_mma_kernel<2>;
+            const int bgroups = (int)((p.nbpr + kDotWarps - 1) / kDotWarps);
+            int per_sm = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kDotWarps * 32, 0);
+            if (e != cudaSuccess) return cuda_fail(kn, e);
+            const int units = (int)((rows + 15) / 16);
+            int ucta = c.sm_count * (per_sm < 1 ? 1 : per_sm) / bgroups;
+            if (ucta < 1) ucta = 1;
+            if (ucta > units) ucta = units;
+            uint32_t* frags = static_cast<uint32_t*>(engine_scratch((size_t)p.nbpr * 192 * 4));
+            FM_REQUIRE(frags != nullptr, kn, "the engine workspace is not available (FM_SCRATCH_MB=0?)");
+            e = launch_kernel(int4_dot_split_kernel, dim3((p.nbpr * 192 + 255) / 256), dim3(256), 0, c.stream, pdl_enabled(),
+                              p.x, frags, p.nbpr);
+            if (e != cudaSuccess) return cuda_fail(kn, e);
+            after_launch(kn);
+            e = launch_kernel(kern, dim3(ucta * bgroups), dim3(kDotWarps * 32), 0, c.stream, pdl_enabled(), p,
+                              static_cast<const uint32_t*>(frags));
+            return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+        }
+        const int warps = (int)((p.nbpr + 7) / 8);
+        auto kern = int4_dot_dense_kernel<4>;
+        int per_sm = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, warps * 32, 0);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        int grid = c.sm_count * (per_sm < 1 ? 1 : per_sm);
+        if ((uint32_t)grid > rows) grid = (int)rows;
+        e = launch_kernel(kern, dim3(grid), dim3(warps * 32), 0, c.stream, pdl_enabled(), p);
+    } else if (shared_x) {
+        FM_REQUIRE(smem <= 200 * 1024, kn, "K=%u is too large for the shared-memory activation row", p.nbpr * 128);
         auto kern = int4_dot_kernel<true, 4>;
         if (smem > 48 * 1024) {
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -236,8 +477,12 @@ int launch_reduce_blocks(const LaunchCtx& c, const uint64_t* a) {
     FM_REQUIRE(aligned(partial, 4) && aligned(y, 4), kn, "misaligned pointer");
     FM_RANGE(partial, (size_t)rows * nbpr * 4, kn, "partial");
     FM_RANGE(y, (size_t)rows * 4, kn, "y");
-    cudaError_t e = launch_kernel(reduce_blocks_kernel, dim3((rows + 127) / 128), dim3(128), 0, c.stream,
-                                  pdl_enabled(), partial, y, rows, nbpr);
+    const size_t smem = (size_t)128 * (nbpr + 1) * 4;
+    cudaError_t e = smem <= 48 * 1024
+        ? launch_kernel(reduce_blocks_kernel, dim3((rows + 127) / 128), dim3(128), smem, c.stream, pdl_enabled(),
+                        partial, y, rows, nbpr)
+        : launch_kernel(reduce_blocks_long_kernel, dim3((rows + 127) / 128), dim3(128), 0, c.stream, pdl_enabled(),
+                        partial, y, rows, nbpr);
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
