@@ -260,6 +260,141 @@ gemv_w4_kernel(const GemvW4Params p) {
     pdl_launch_dependents();
 }
 
+// ------------------------------------------------------------------ W4A8, 2..4 tokens, tensor cores
+// The tokens are the columns of the MMA, so two to eight tokens cost what one costs.  A warp owns
+// 16-row tiles (rows g and g + 8 per lane group, as in mma.sync m16n8k32): per 128-group it loads
+// the 16-byte word t of the group for both rows, masks the nibbles in place (low nibbles as signed
+// bytes n ^ 8, high nibbles as unsigned bytes 16 * (n ^ 8): the u8 x s8 form) and multiplies them
+// with the tokens' codes read from shared memory; the add over the four lanes of a group happens in
+// the MMA, so there are no shuffles.  I = lo + (hi >> 4) - 8 * sum(q) is the exact integer of the
+// dp4a kernel; lane (g, t) then owns rows g, g + 8 of tokens 2t, 2t + 1 and adds
+// (sw * sa) * float(I) group by group in fp32.  Loads run GC groups ahead of the arithmetic.
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int M>
+__global__ void __launch_bounds__(kThreads, 2)
+gemv_w4a8_mma_kernel(const GemvW4Params p) {
+    constexpr int GC = 4;                         // groups fetched per step: 2 x GC x 16 bytes in flight per lane
+    extern __shared__ __align__(16) uint32_t smem[];
+    const int KD = p.K >> 3, NG = p.K >> 7;
+    uint32_t* s_e = smem;
+    uint32_t* s_o = s_e + M * KD;
+    float* s_sc = reinterpret_cast<float*>(s_o + M * KD);
+    int* s_su = reinterpret_cast<int*>(s_sc + M * NG);
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int gwarp = blockIdx.x * kWarps + (threadIdx.x >> 5), nwarp = gridDim.x * kWarps;
+    const int ntiles = (p.rows + 15) >> 4;
+    const int nchunks = (NG + GC - 1) / GC;
+    const long long total = (long long)((ntiles - gwarp + nwarp - 1) / nwarp) * nchunks;   // (tile, chunk) steps of this warp
+    const int tk = g < M ? g : M - 1;             // token whose codes this lane feeds as column g (columns >= M are unused)
+    const int t0 = 2 * t, t1 = 2 * t + 1;         // tokens of this lane's accumulator columns
+
+    uint4 na[GC], nb[GC];                         // next step's words of rows g, g + 8
+    uint32_t nsa[GC], nsb[GC];                    // and their f16 scales
+    int ftile = gwarp, fchunk = 0;                // position of the fetch
+    auto fetch = [&]() {
+        const int ra = min(ftile * 16 + g, p.rows - 1), rb = min(ftile * 16 + g + 8, p.rows - 1);
+        const bool live = ftile < ntiles;
+#pragma unroll
+        for (int j = 0; j < GC; j++) {
+            const int gg = fchunk * GC + j;
+            const bool ok = live && gg < NG;
+            na[j] = ok ? ld_stream_v4(p.wq + (size_t)ra * KD + gg * 16 + t * 4) : make_uint4(0, 0, 0, 0);
+            nb[j] = ok ? ld_stream_v4(p.wq + (size_t)rb * KD + gg * 16 + t * 4) : make_uint4(0, 0, 0, 0);
+            nsa[j] = ok ? ld_stream_u16(p.ws + (size_t)ra * NG + gg) : 0u;
+            nsb[j] = ok ? ld_stream_u16(p.ws + (size_t)rb * NG + gg) : 0u;
+        }
+        if (++fchunk == nchunks) {
+            fchunk = 0;
+            ftile += nwarp;
+        }
+    };
+    if (total > 0) fetch();                       // weights do not depend on the preceding kernel
+    pdl_wait();
+    stage_activations<false>(p, M, s_e, s_o, s_sc, s_su);
+
+    int tile = gwarp, chunk = 0;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};          // (row g, token 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
+    for (long long it = 0; it < total; it++) {
+        uint4 ca[GC], cb[GC];
+        float swa[GC], swb[GC];
+#pragma unroll
+        for (int j = 0; j < GC; j++) {
+            ca[j] = na[j];
+            cb[j] = nb[j];
+            swa[j] = __half2float(__ushort_as_half((unsigned short)nsa[j]));
+            swb[j] = __half2float(__ushort_as_half((unsigned short)nsb[j]));
+        }
+        if (it + 1 < total) fetch();
+#pragma unroll
+        for (int j = 0; j < GC; j++) {
+            const int gg = chunk * GC + j;
+            if (gg >= NG) break;
+            const uint4 be = *reinterpret_cast<const uint4*>(s_e + tk * KD + gg * 16 + t * 4);
+            const uint4 bo = *reinterpret_cast<const uint4*>(s_o + tk * KD + gg * 16 + t * 4);
+            int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+            const uint32_t m_lo = 0x0F0F0F0Fu, x_lo = 0x08080808u, m_hi = 0xF0F0F0F0u, x_hi = 0x80808080u;
+            mma_s8s8(lo, (ca[j].x & m_lo) ^ x_lo, (cb[j].x & m_lo) ^ x_lo, (ca[j].y & m_lo) ^ x_lo, (cb[j].y & m_lo) ^ x_lo, be.x, be.y);
+            mma_s8s8(lo, (ca[j].z & m_lo) ^ x_lo, (cb[j].z & m_lo) ^ x_lo, (ca[j].w & m_lo) ^ x_lo, (cb[j].w & m_lo) ^ x_lo, be.z, be.w);
+            mma_u8s8(hi, (ca[j].x & m_hi) ^ x_hi, (cb[j].x & m_hi) ^ x_hi, (ca[j].y & m_hi) ^ x_hi, (cb[j].y & m_hi) ^ x_hi, bo.x, bo.y);
+            mma_u8s8(hi, (ca[j].z & m_hi) ^ x_hi, (cb[j].z & m_hi) ^ x_hi, (ca[j].w & m_hi) ^ x_hi, (cb[j].w & m_hi) ^ x_hi, bo.z, bo.w);
+            if (t0 < M) {
+                const float sa = s_sc[t0 * NG + gg];
+                const int su8 = 8 * s_su[t0 * NG + gg];
+                acc[0] += (swa[j] * sa) * (float)(lo[0] + (hi[0] >> 4) - su8);
+                acc[2] += (swb[j] * sa) * (float)(lo[2] + (hi[2] >> 4) - su8);
+            }
+            if (t1 < M) {
+                const float sa = s_sc[t1 * NG + gg];
+                const int su8 = 8 * s_su[t1 * NG + gg];
+                acc[1] += (swa[j] * sa) * (float)(lo[1] + (hi[1] >> 4) - su8);
+                acc[3] += (swb[j] * sa) * (float)(lo[3] + (hi[3] >> 4) - su8);
+            }
+        }
+        if (++chunk == nchunks) {                 // tile finished
+            const int ra = tile * 16 + g, rb = ra + 8;
+            if (t0 < M) {
+                if (ra < p.rows) p.y[(size_t)t0 * p.N + ra] = acc[0];
+                if (rb < p.rows) p.y[(size_t)t0 * p.N + rb] = acc[2];
+            }
+            if (t1 < M) {
+                if (ra < p.rows) p.y[(size_t)t1 * p.N + ra] = acc[1];
+                if (rb < p.rows) p.y[(size_t)t1 * p.N + rb] = acc[3];
+            }
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            chunk = 0;
+            tile += nwarp;
+        }
+    }
+    pdl_launch_dependents();
+}
+
+template <int M>
+int run_mma(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
+    auto kern = gemv_w4a8_mma_kernel<M>;
+    const size_t smem = (size_t)M * (2 * (p.K / 8) * 4 + (p.K / 128) * 8);
+    FM_REQUIRE(smem <= 200 * 1024, kn, "K=%d needs %zu bytes of shared memory for %d tokens (limit 200 KiB)", p.K, smem, M);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+    }
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
+    if (e != cudaSuccess) return cuda_fail(kn, e);
+    const int blocks_needed = ((p.rows + 15) / 16 + kWarps - 1) / kWarps;
+    int grid = c.sm_count * (per_sm < 1 ? 1 : per_sm);
+    if (grid > blocks_needed) grid = blocks_needed;
+    e = launch_kernel(kern, dim3(grid), dim3(kThreads), smem, c.stream, pdl_enabled(), p);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
 // ------------------------------------------------------------------ host side
 struct Tuning { int ctas_per_sm; };
 
@@ -296,6 +431,9 @@ int dispatch(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
         if (kiter == 5) return run_variant<A4, 1, 1, 5, true, false>(kn, c, p);
         return run_variant<A4, 1, 1, 0, false, false>(kn, c, p);
     }
+    // several tokens with int8 activations: the tensor-core kernel ($FM_GEMV_CFG=1 keeps the dp4a one)
+    static const int cfg = getenv("FM_GEMV_CFG") ? atoi(getenv("FM_GEMV_CFG")) : 0;
+    if (!A4 && cfg != 1) return run_mma<M>(kn, c, p);
     if (kiter == 5) return run_variant<A4, M, 2, 5, false, false>(kn, c, p);
     return run_variant<A4, M, 2, 0, false, false>(kn, c, p);
 }

@@ -203,9 +203,9 @@ class W4Runner:
             half, ng4 = k // 2, (k // GRP) * 4
             ae, ao = self._buf("w4a8_ae", m * half), self._buf("w4a8_ao", m * half)
             asc, asu = self._buf("w4a8_asc", m * ng4), self._buf("w4a8_asu", m * ng4)
-            for r in range(m):         # one 1-D launch per token row, as the reference does
-                rt.launch("quant_act", k // GRP, 32,
-                          [px + r * k * 4, ae + r * half, ao + r * half, asc + r * ng4, asu + r * ng4, 1, k])
+            # one 2-D launch, grid y = token row (the reference's runner issues one 1-D launch per row;
+            # the kernel's own contract covers both)
+            rt.launch2d("quant_act", k // GRP, m, 32, 1, [px, ae, ao, asc, asu, m, k])
             rows_per_wg = 4 * (1 if m == 1 else 2)
             rt.launch(W4A8_KERNEL[m], -(-n // rows_per_wg), threads, [wq, ws, ae, ao, asc, asu, py, n, k])
         elif kind == "w4a4":
@@ -213,8 +213,7 @@ class W4Runner:
                 raise ValueError(f"W4A4 needs K to be a multiple of {SG} (got {k})")
             half, ns4 = k // 2, (k // SG) * 4
             aq, asc = self._buf("w4a4_aq", m * half), self._buf("w4a4_asc", m * ns4)
-            for r in range(m):
-                rt.launch("quant_act4", k // SG, 32, [px + r * k * 4, aq + r * half, asc + r * ns4, 1, k])
+            rt.launch2d("quant_act4", k // SG, m, 32, 1, [px, aq, asc, m, k])
             rt.launch(W4A4_KERNEL[m], -(-n // 4), threads, [wq, ws, aq, asc, py, n, k])
         else:
             raise ValueError(f"unknown W4 path {kind!r} (use 'w4a8' or 'w4a4')")
