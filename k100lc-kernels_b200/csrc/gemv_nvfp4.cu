@@ -74,26 +74,47 @@ nvfp4_gemv_kernel(const Nvfp4Params p) {
     const int iters = KITER > 0 ? KITER : (KD + 127) >> 7;
     constexpr int UN = KITER > 0 ? KITER : 1;
 
+    // one row block is always in flight: the loads of block rb + nwarp are issued right after block rb
+    // has been consumed (weights and block scales do not depend on the preceding kernel)
     uint4 wreg[R][UN];
-    int rb = gwarp;
-    if (KITER > 0) {
+    uint32_t sbyte[R][UN];
+    auto fetch = [&](int blk) {
 #pragma unroll
         for (int r = 0; r < R; r++) {
-            const int row = rb * R + r;
+            const int row = blk * R + r;
+            const bool live = row < p.rows;
 #pragma unroll
-            for (int it = 0; it < UN; it++)
-                wreg[r][it] = row < p.rows ? ld_stream_v4(p.wq + (size_t)row * KD + it * 128 + lane * 4)
-                                           : make_uint4(0, 0, 0, 0);
+            for (int it = 0; it < UN; it++) {
+                const int d0 = it * 128 + lane * 4;
+                wreg[r][it] = live ? ld_stream_v4(p.wq + (size_t)row * KD + d0) : make_uint4(0, 0, 0, 0);
+                sbyte[r][it] = live ? ld_stream_u16(p.ws + (size_t)row * NB + (d0 >> 1)) : 0u;
+            }
         }
-    }
+    };
+    int rb = gwarp;
+    if (KITER > 0) fetch(rb);
 
     pdl_wait();
-    for (int i = threadIdx.x; i < M * KD; i += blockDim.x) {
-        const uint32_t e = p.qa[i], o = p.qb[i];
-        s_a[2 * i] = prmt(e, o, 0x5140u);        // k0 k1 k2 k3
-        s_a[2 * i + 1] = prmt(e, o, 0x7362u);    // k4 k5 k6 k7
+    constexpr bool AREG = M == 1 && KITER > 0;   // one token: its codes go straight from L2 into registers
+    uint4 ra0[AREG ? UN : 1], ra1[AREG ? UN : 1];
+    float2 rsc[AREG ? UN : 1];
+    if (AREG) {
+#pragma unroll
+        for (int it = 0; it < UN; it++) {
+            const int d0 = it * 128 + lane * 4;
+            const uint4 e = *reinterpret_cast<const uint4*>(p.qa + d0), o = *reinterpret_cast<const uint4*>(p.qb + d0);
+            ra0[it] = make_uint4(prmt(e.x, o.x, 0x5140u), prmt(e.x, o.x, 0x7362u), prmt(e.y, o.y, 0x5140u), prmt(e.y, o.y, 0x7362u));
+            ra1[it] = make_uint4(prmt(e.z, o.z, 0x5140u), prmt(e.z, o.z, 0x7362u), prmt(e.w, o.w, 0x5140u), prmt(e.w, o.w, 0x7362u));
+            rsc[it] = *reinterpret_cast<const float2*>(p.sc + (d0 >> 1));
+        }
+    } else {
+        for (int i = threadIdx.x; i < M * KD; i += blockDim.x) {
+            const uint32_t e = p.qa[i], o = p.qb[i];
+            s_a[2 * i] = prmt(e, o, 0x5140u);        // k0 k1 k2 k3
+            s_a[2 * i + 1] = prmt(e, o, 0x7362u);    // k4 k5 k6 k7
+        }
+        for (int i = threadIdx.x; i < M * NB; i += blockDim.x) s_sc[i] = p.sc[i];
     }
-    for (int i = threadIdx.x; i < M * NB; i += blockDim.x) s_sc[i] = p.sc[i];
     for (int i = threadIdx.x; i < 256; i += blockDim.x) s_lut[i] = (0.5f * p.gscale) * e4m3_to_f32(i);
     __syncthreads();
 
@@ -104,26 +125,6 @@ nvfp4_gemv_kernel(const Nvfp4Params p) {
 #pragma unroll
             for (int m = 0; m < M; m++) acc[r][m] = 0.f;
 
-        if (KITER > 0 && rb != gwarp) {
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int row = rb * R + r;
-#pragma unroll
-                for (int it = 0; it < UN; it++)
-                    wreg[r][it] = row < p.rows ? ld_stream_v4(p.wq + (size_t)row * KD + it * 128 + lane * 4)
-                                               : make_uint4(0, 0, 0, 0);
-            }
-        }
-        uint32_t sbyte[R][UN];
-        if (KITER > 0) {
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int row = min(rb * R + r, p.rows - 1);
-#pragma unroll
-                for (int it = 0; it < UN; it++)
-                    sbyte[r][it] = ld_stream_u16(p.ws + (size_t)row * NB + ((it * 128 + lane * 4) >> 1));
-            }
-        }
 
 #pragma unroll 1
         for (int it0 = 0; it0 < iters; it0 += UN) {
@@ -150,9 +151,9 @@ nvfp4_gemv_kernel(const Nvfp4Params p) {
                 }
 #pragma unroll
                 for (int m = 0; m < M; m++) {
-                    const uint4 a0 = *reinterpret_cast<const uint4*>(s_a + m * (p.K >> 2) + 2 * dc);
-                    const uint4 a1 = *reinterpret_cast<const uint4*>(s_a + m * (p.K >> 2) + 2 * dc + 4);
-                    const float2 as = *reinterpret_cast<const float2*>(s_sc + m * NB + b0);
+                    const uint4 a0 = AREG ? ra0[u] : *reinterpret_cast<const uint4*>(s_a + m * (p.K >> 2) + 2 * dc);
+                    const uint4 a1 = AREG ? ra1[u] : *reinterpret_cast<const uint4*>(s_a + m * (p.K >> 2) + 2 * dc + 4);
+                    const float2 as = AREG ? rsc[u] : *reinterpret_cast<const float2*>(s_sc + m * NB + b0);
 #pragma unroll
                     for (int r = 0; r < R; r++) {
                         int i0 = dot8_e2m1(w4[r].x, a0.x, a0.y, 0);
@@ -175,6 +176,7 @@ nvfp4_gemv_kernel(const Nvfp4Params p) {
                 }
             }
         }
+        if (KITER > 0) fetch(rb + nwarp);                   // next block of this warp (no loads past the end)
 
 #pragma unroll
         for (int r = 0; r < R; r++) {
@@ -215,7 +217,8 @@ int dispatch(const char* kn, const LaunchCtx& c, const Nvfp4Params& p) {
     const int kiter = (p.K % 1024 == 0) ? p.K / 1024 : 0;
     if (DUMP) return run_variant<M, 1, 0, true>(kn, c, p);
     if (M == 1) {
-        if (kiter == 5) return run_variant<1, 1, 5, false>(kn, c, p);
+        // (the register path reads the codes as 16-byte words)
+        if (kiter == 5 && aligned(p.qa, 16) && aligned(p.qb, 16)) return run_variant<1, 1, 5, false>(kn, c, p);
         return run_variant<1, 1, 0, false>(kn, c, p);
     }
     if (kiter == 5) return run_variant<M, 2, 5, false>(kn, c, p);
