@@ -124,8 +124,15 @@ class ClockSampler:
 
     def summary(self) -> dict:
         rows = [r for r in self.samples if self.t0 is None or self.t0 <= r[0] <= self.t1]
+        note = None
+        if not rows and self.samples:
+            # a region of a few milliseconds can fall between two polls (each poll is three NVML calls):
+            # take the sample closest to it and say how far away it was
+            near = min(self.samples, key=lambda r: min(abs(r[0] - self.t0), abs(r[0] - self.t1)))
+            rows = [near]
+            note = f"closest sample, {1e3 * min(abs(near[0] - self.t0), abs(near[0] - self.t1)):.1f} ms outside the timed region"
         if not rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [getattr(self, "_why", "no NVML sample inside the timed region")],
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [getattr(self, "_why", "no NVML sample")],
                     "samples": 0}
         bits = 0
         for r in rows:
@@ -133,7 +140,7 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(r[1] for r in rows)), "sm_min_mhz": min(r[1] for r in rows),
                 "sm_max_mhz": int(self.smax), "power_w": round(statistics.median(r[3] for r in rows), 1),
                 "reasons": [name for name, bit in self.REASONS if bits & bit], "samples": len(rows),
-                "how": "NVML polled every 2 ms by a host thread during the timed region"}
+                "how": "NVML polled every 2 ms by a host thread during the timed region" + (f" ({note})" if note else "")}
 
 
 # --------------------------------------------------------------------------- ours
