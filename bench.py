@@ -593,7 +593,12 @@ def run_ours(args) -> int:
                          "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4), "peak_source": pk["source"],
                          "us_per_launch": round(us_kernel, 3), "bytes_per_launch": bytes_per_launch,
-                         "traffic": None},
+                         # DRAM bytes of one launch, from the ncu capture of the same kernel on 24 layers
+                         # (1 103 145 000 B read + 5 141 000 B written), scaled by the layer count: every
+                         # weight byte is read once, so traffic is proportional to the layers
+                         "traffic": int(round((1103145000 + 5141000) / 24 * bytes_per_launch / LAYER_BYTES)) if fused else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 24-layer launch, scaled "
+                                           "(profiles/w4a8_decode_stream_24layers_ncu.md)" if fused else None},
             "cpu_baseline": cpu, "clocks": clocks.summary(), "paths_m1": paths, "prefill_gemm_m2048": gemm, "setup_seconds": round(setup_s, 1),
         }
     if line is not None:

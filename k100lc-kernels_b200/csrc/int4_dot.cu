@@ -223,6 +223,9 @@ constexpr int kDotWarps = 8;
 // x[128 b + 32 t + 8 q + 4 i + h] (low half) and x[... + 2] (high half)
 __global__ void __launch_bounds__(256)
 int4_dot_split_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, uint32_t nbpr) {
+    // the multiply kernel behind this one is launched as a programmatic dependent: it may start now and
+    // fetch its first weights; it waits for this grid before it reads the fragments
+    pdl_launch_dependents();
     pdl_wait();
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < nbpr * 192) {
@@ -231,7 +234,6 @@ int4_dot_split_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, u
         const float* xs = x + (size_t)b * 128 + t * 32 + 8 * q + 4 * i + h;
         out[idx] = bf16_term(xs[0], (int)term) | (bf16_term(xs[2], (int)term) << 16);
     }
-    pdl_launch_dependents();
 }
 
 template <int UN>
@@ -428,7 +430,7 @@ int launch_int4_dot(const LaunchCtx& c, const uint64_t* a) {
                               p.x, frags, p.nbpr);
             if (e != cudaSuccess) return cuda_fail(kn, e);
             after_launch(kn);
-            e = launch_kernel(kern, dim3(ucta * bgroups), dim3(kDotWarps * 32), 0, c.stream, pdl_enabled(), p,
+            e = launch_kernel(kern, dim3(ucta * bgroups), dim3(kDotWarps * 32), 0, c.stream, true, p,
                               static_cast<const uint32_t*>(frags));
             return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
         }

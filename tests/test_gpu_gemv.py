@@ -67,7 +67,7 @@ def test_w4_golden(rt, golden, name, seed, m, kernel):
     dev = w4a8_device if "w4a8" in kernel else w4a4_device
     y, _, _ = dev(rt, pack_nibbles(wv), ws, x, name=kernel)
     ref = arr[f"{name}.y"]
-    assert np.abs(y - ref).max() <= 1e-4 + 1e-5 * max(1.0, float(np.abs(ref).max()))   # the reference's judge()
+    assert np.abs(y - ref).max() <= 1e-4 + 1e-5 * max(1.0, float(np.abs(ref).max()))   # the tolerance of the reference's own acceptance check
     assert O.rel_err(y, ref) < REL
 
 
