@@ -278,51 +278,52 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// One warp = one 16-row tile x one half of K (two warps per tile, four tiles per CTA): 17408 rows are
+// only 1088 tiles, and a warp that walked all 40 groups of its tile alone left the SMs a third full.
 template <int M>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_w4a8_mma_kernel(const GemvW4Params p) {
     constexpr int GC = 4;                         // groups fetched per step: 2 x GC x 16 bytes in flight per lane
+    constexpr int TPC = kWarps / 2;               // tiles per CTA
     extern __shared__ __align__(16) uint32_t smem[];
     const int KD = p.K >> 3, NG = p.K >> 7;
     uint32_t* s_e = smem;
     uint32_t* s_o = s_e + M * KD;
     float* s_sc = reinterpret_cast<float*>(s_o + M * KD);
     int* s_su = reinterpret_cast<int*>(s_sc + M * NG);
+    // [TPC][32][4] partial sums of the upper half, on a 16-byte boundary
+    float* s_red = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(s_su + M * NG) + 15) & ~uintptr_t(15));
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int gwarp = blockIdx.x * kWarps + (threadIdx.x >> 5), nwarp = gridDim.x * kWarps;
+    const int warp = threadIdx.x >> 5, half = warp & 1, slot = warp >> 1;
+    const int tile = blockIdx.x * TPC + slot;
     const int ntiles = (p.rows + 15) >> 4;
-    const int nchunks = (NG + GC - 1) / GC;
-    const long long total = (long long)((ntiles - gwarp + nwarp - 1) / nwarp) * nchunks;   // (tile, chunk) steps of this warp
+    const bool live = tile < ntiles;
+    const int ngh = (((NG + 1) >> 1) + GC - 1) / GC * GC;            // groups of the lower half (a multiple of GC)
+    const int g_lo = half ? min(ngh, NG) : 0, g_hi = half ? NG : min(ngh, NG);
+    const int nchunks = (g_hi - g_lo + GC - 1) / GC;
     const int tk = g < M ? g : M - 1;             // token whose codes this lane feeds as column g (columns >= M are unused)
     const int t0 = 2 * t, t1 = 2 * t + 1;         // tokens of this lane's accumulator columns
+    const int ra = min(tile * 16 + g, p.rows - 1), rb = min(tile * 16 + g + 8, p.rows - 1);
 
     uint4 na[GC], nb[GC];                         // next step's words of rows g, g + 8
     uint32_t nsa[GC], nsb[GC];                    // and their f16 scales
-    int ftile = gwarp, fchunk = 0;                // position of the fetch
-    auto fetch = [&]() {
-        const int ra = min(ftile * 16 + g, p.rows - 1), rb = min(ftile * 16 + g + 8, p.rows - 1);
-        const bool live = ftile < ntiles;
+    auto fetch = [&](int chunk) {
 #pragma unroll
         for (int j = 0; j < GC; j++) {
-            const int gg = fchunk * GC + j;
-            const bool ok = live && gg < NG;
+            const int gg = g_lo + chunk * GC + j;
+            const bool ok = live && gg < g_hi;
             na[j] = ok ? ld_stream_v4(p.wq + (size_t)ra * KD + gg * 16 + t * 4) : make_uint4(0, 0, 0, 0);
             nb[j] = ok ? ld_stream_v4(p.wq + (size_t)rb * KD + gg * 16 + t * 4) : make_uint4(0, 0, 0, 0);
             nsa[j] = ok ? ld_stream_u16(p.ws + (size_t)ra * NG + gg) : 0u;
             nsb[j] = ok ? ld_stream_u16(p.ws + (size_t)rb * NG + gg) : 0u;
         }
-        if (++fchunk == nchunks) {
-            fchunk = 0;
-            ftile += nwarp;
-        }
     };
-    if (total > 0) fetch();                       // weights do not depend on the preceding kernel
+    if (nchunks > 0) fetch(0);                    // weights do not depend on the preceding kernel
     pdl_wait();
     stage_activations<false>(p, M, s_e, s_o, s_sc, s_su);
 
-    int tile = gwarp, chunk = 0;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};          // (row g, token 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
-    for (long long it = 0; it < total; it++) {
+    for (int chunk = 0; chunk < nchunks; chunk++) {
         uint4 ca[GC], cb[GC];
         float swa[GC], swb[GC];
 #pragma unroll
@@ -332,11 +333,11 @@ gemv_w4a8_mma_kernel(const GemvW4Params p) {
             swa[j] = __half2float(__ushort_as_half((unsigned short)nsa[j]));
             swb[j] = __half2float(__ushort_as_half((unsigned short)nsb[j]));
         }
-        if (it + 1 < total) fetch();
+        if (chunk + 1 < nchunks) fetch(chunk + 1);
 #pragma unroll
         for (int j = 0; j < GC; j++) {
-            const int gg = chunk * GC + j;
-            if (gg >= NG) break;
+            const int gg = g_lo + chunk * GC + j;
+            if (gg >= g_hi) break;
             const uint4 be = *reinterpret_cast<const uint4*>(s_e + tk * KD + gg * 16 + t * 4);
             const uint4 bo = *reinterpret_cast<const uint4*>(s_o + tk * KD + gg * 16 + t * 4);
             int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
@@ -358,19 +359,20 @@ gemv_w4a8_mma_kernel(const GemvW4Params p) {
                 acc[3] += (swb[j] * sa) * (float)(lo[3] + (hi[3] >> 4) - su8);
             }
         }
-        if (++chunk == nchunks) {                 // tile finished
-            const int ra = tile * 16 + g, rb = ra + 8;
-            if (t0 < M) {
-                if (ra < p.rows) p.y[(size_t)t0 * p.N + ra] = acc[0];
-                if (rb < p.rows) p.y[(size_t)t0 * p.N + rb] = acc[2];
-            }
-            if (t1 < M) {
-                if (ra < p.rows) p.y[(size_t)t1 * p.N + ra] = acc[1];
-                if (rb < p.rows) p.y[(size_t)t1 * p.N + rb] = acc[3];
-            }
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-            chunk = 0;
-            tile += nwarp;
+    }
+    // lower half + upper half, then store
+    if (half) *reinterpret_cast<float4*>(s_red + (slot * 32 + lane) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    if (!half && live) {
+        const float4 u = *reinterpret_cast<const float4*>(s_red + (slot * 32 + lane) * 4);
+        const int rra = tile * 16 + g, rrb = rra + 8;
+        if (t0 < M) {
+            if (rra < p.rows) p.y[(size_t)t0 * p.N + rra] = acc[0] + u.x;
+            if (rrb < p.rows) p.y[(size_t)t0 * p.N + rrb] = acc[2] + u.z;
+        }
+        if (t1 < M) {
+            if (rra < p.rows) p.y[(size_t)t1 * p.N + rra] = acc[1] + u.y;
+            if (rrb < p.rows) p.y[(size_t)t1 * p.N + rrb] = acc[3] + u.w;
         }
     }
     pdl_launch_dependents();
@@ -379,19 +381,14 @@ gemv_w4a8_mma_kernel(const GemvW4Params p) {
 template <int M>
 int run_mma(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
     auto kern = gemv_w4a8_mma_kernel<M>;
-    const size_t smem = (size_t)M * (2 * (p.K / 8) * 4 + (p.K / 128) * 8);
+    const size_t smem = (size_t)M * (2 * (p.K / 8) * 4 + (p.K / 128) * 8) + 16 + (kWarps / 2) * 32 * 16;
     FM_REQUIRE(smem <= 200 * 1024, kn, "K=%d needs %zu bytes of shared memory for %d tokens (limit 200 KiB)", p.K, smem, M);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(kn, e);
     }
-    int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
-    if (e != cudaSuccess) return cuda_fail(kn, e);
-    const int blocks_needed = ((p.rows + 15) / 16 + kWarps - 1) / kWarps;
-    int grid = c.sm_count * (per_sm < 1 ? 1 : per_sm);
-    if (grid > blocks_needed) grid = blocks_needed;
-    e = launch_kernel(kern, dim3(grid), dim3(kThreads), smem, c.stream, pdl_enabled(), p);
+    const int grid = ((p.rows + 15) / 16 + kWarps / 2 - 1) / (kWarps / 2);      // four 16-row tiles per CTA
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kThreads), smem, c.stream, pdl_enabled(), p);
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
