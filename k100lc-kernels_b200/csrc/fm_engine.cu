@@ -62,6 +62,7 @@ struct Engine {
     std::map<uintptr_t, size_t> pinned;          // fm_host_alloc buffers (device-addressable host memory)
     void* scratch = nullptr;                     // kernel-internal workspace (grows on demand)
     size_t scratch_bytes = 0;
+    std::vector<void*> retired_scratch;          // outgrown workspaces, still referenced by captured graphs
     std::vector<cudaEvent_t> events;
     std::vector<Graph> graphs;
     std::unordered_map<uint64_t, int> plan_graphs;   // plan hash -> graph id
@@ -305,8 +306,9 @@ void* engine_scratch(size_t bytes) {
     Engine& e = E();
     if (bytes <= e.scratch_bytes) return e.scratch;
     if (e.capturing) return nullptr;
-    cudaStreamSynchronize(e.stream);
-    if (e.scratch) cudaFree(e.scratch);
+    // the old buffer is kept until the engine goes away: graphs captured earlier may hold kernel nodes
+    // that point into it
+    if (e.scratch) e.retired_scratch.push_back(e.scratch);
     e.scratch = nullptr;
     e.scratch_bytes = 0;
     const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
