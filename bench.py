@@ -362,6 +362,22 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
         rt.graph_free(g)
         out[name] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
+    # four tokens per layer through the multi-token stream kernel (tokens = columns of the MMA)
+    mt, nlm = 4, min(nl, st.layers // 4)
+    if nlm > 0:
+        tab_m = rt.stream_table([(st.wq_l(l), st.ws_l(l), st.x + l * mt * K * 4, st.y + l * mt * N * 4) for l in range(nlm)],
+                                rows, K, (mt - 1) * N)
+        aem, aom = rt.alloc(nlm * mt * K // 2), rt.alloc(nlm * mt * K // 2)
+        scm, sum_ = rt.alloc(nlm * mt * NG * 4), rt.alloc(nlm * mt * NG * 4)
+        rt.graph_begin()
+        rt.launch2d("quant_act", NG, nlm * mt, 32, 1, [st.x, aem, aom, scm, sum_, nlm * mt, K])
+        rt.launch("w4a8_decode_stream_m", 1, 1, [tab_m, nlm, rows, K, 0, 0, 0, status, aem, aom, scm, sum_, mt, N])
+        g = rt.graph_end()
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nlm
+        rt.graph_free(g)
+        out["w4a8_m4_stream"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
+        for ptr in (tab_m, aem, aom, scm, sum_):
+            rt.free(ptr)
     if int(rt.download(status, 1, np.int32)[0]) != 0:
         raise RuntimeError("a bounded wait ran out in a stream kernel")
     for p in (aq, asc4, qa, qb, sc16, nvs, table, status, ae, ao, sc8, su8, aq4, sc4):

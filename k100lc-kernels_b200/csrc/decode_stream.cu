@@ -56,6 +56,7 @@ struct StreamParams {
     int npeers;                        // additional GPUs that receive y (0 on one GPU)
     const long long* peer_delta;       // [npeers] byte offset from a local y address to the peer's copy
     int* status;                       // 0 ok, else first failure code
+    int M, ystride;                    // tokens per layer and floats between their outputs (multi-token kernel only)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -520,6 +521,258 @@ w4a8_stream_mma_kernel(const StreamParams p) {
     if (p.npeers) __threadfence_system();
 }
 
+// ------------------------------------------------------------------------------------
+// Several tokens per layer (W4A8, M = 2..4): the tensor-core consumer with the tokens as the
+// columns of the MMA, so a small decode batch streams the weights once.  Same ring, barriers and
+// roles as w4a8_stream_mma_kernel; what differs: the code tile of a layer holds M tokens
+// ([M][K/2] even codes, [M][K/2] odd codes, [M][NG] scales, [M][NG] sums — the layout one 2-D
+// quant_act launch with grid y = layer * M + token leaves behind), lane (g, t) feeds token
+// min(g, M-1) as column g and owns the sums of rows g, g + 8 for tokens 2t and 2t + 1, and y of
+// a layer is token-major: y[token * ystride + row].
+__device__ __forceinline__ void write_out_m(const StreamParams& p, const float* tile, float* y, int n, int lane, int M) {
+    for (int i = lane; i < n * M; i += 32) {
+        const int tok = i / n, row = i - tok * n;            // token-major walk: coalesced global stores
+        const float v = tile[row * M + tok];
+        float* dst = y + (size_t)tok * p.ystride + row;
+        *dst = v;
+        for (int q = 0; q < p.npeers; q++)
+            *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = v;
+    }
+}
+
+template <int STAGES, int M>
+__global__ void __launch_bounds__(10 * 32, 1)
+w4a8_stream_mma_m_kernel(const StreamParams p) {
+    constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
+    constexpr int ROWB = K / 2, SCB = NG * 2;
+    constexpr int STAGE_W = ROWS * ROWB, STAGE = STAGE_W + ROWS * SCB;
+    constexpr int ACT = M * (K + NG * 8);
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + STAGES;
+    uint64_t* act_ready = empty + STAGES;     // [2]
+    uint64_t* act_free = act_ready + 2;       // [2]
+    uint64_t* red_full = act_free + 2;        // [2]
+    uint64_t* red_free = red_full + 2;        // [2]
+    uint64_t* ydone = red_free + 2;           // [2]
+    uint64_t* yfree = ydone + 2;              // [2]
+    uint8_t* ring = smem + 256;
+    uint8_t* act = ring + (size_t)STAGES * STAGE;
+    float* red = reinterpret_cast<float*>(act + 2 * ACT);             // [2][CW][ROWS][M]
+    float* ytile = red + 2 * CW * ROWS * M;                           // [2][kOutCap]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CW);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&act_ready[b], 1);
+            mbar_init(&act_free[b], CW);
+            mbar_init(&red_full[b], CW);
+            mbar_init(&red_free[b], 1);
+            mbar_init(&ydone[b], CW);
+            mbar_init(&yfree[b], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();
+
+    const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const int nst = (r1 - r0 + ROWS - 1) / ROWS;
+    const bool tiled = (r1 - r0) * M <= kOutCap;
+
+    if (warp == CW) {
+        if (lane == 0) {                                   // producer
+            auto copy_codes = [&](int l) -> bool {
+                const int b = l & 1;
+                if (l >= 2 && !mbar_wait(&act_free[b], ((l >> 1) & 1) ^ 1, p.status, 4)) return false;
+                uint8_t* ab = act + (size_t)b * ACT;
+                mbar_expect_tx(&act_ready[b], ACT);
+                bulk_g2s(ab, p.ae + (size_t)l * M * (K / 2), M * (K / 2), &act_ready[b]);
+                bulk_g2s(ab + M * (K / 2), p.ao + (size_t)l * M * (K / 2), M * (K / 2), &act_ready[b]);
+                bulk_g2s(ab + M * K, p.asc + (size_t)l * M * (NG * 4), M * NG * 4, &act_ready[b]);
+                bulk_g2s(ab + M * K + M * NG * 4, p.asu + (size_t)l * M * (NG * 4), M * NG * 4, &act_ready[b]);
+                return true;
+            };
+            int c = 0;
+            const uint8_t* wq = p.layers[0].wq;
+            const uint8_t* ws = p.layers[0].ws;
+            if (!copy_codes(0)) return;
+            for (int l = 0; l < p.nlayers; l++) {
+                const int ln = min(l + 1, p.nlayers - 1);
+                const uint8_t* wq_n = p.layers[ln].wq;
+                const uint8_t* ws_n = p.layers[ln].ws;
+                for (int j = 0; j < nst; j++, c++) {
+                    const int s = c % STAGES;
+                    if (c >= STAGES && !mbar_wait(&empty[s], ((c / STAGES) & 1) ^ 1, p.status, 1)) return;
+                    const int row = r0 + j * ROWS;
+                    const int nr = min(ROWS, r1 - row);
+                    uint8_t* dst = ring + (size_t)s * STAGE;
+                    mbar_expect_tx(&full[s], (uint32_t)(nr * (ROWB + SCB)));
+                    bulk_g2s(dst, wq + (size_t)row * ROWB, (uint32_t)(nr * ROWB), &full[s]);
+                    bulk_g2s(dst + STAGE_W, ws + (size_t)row * SCB, (uint32_t)(nr * SCB), &full[s]);
+                    if (j == 0 && l + 1 < p.nlayers && !copy_codes(l + 1)) return;
+                }
+                wq = wq_n;
+                ws = ws_n;
+            }
+        }
+        return;
+    }
+
+    if (warp == CW + 1) {                                    // writer
+        if (!tiled) return;
+        for (int l = 0; l < p.nlayers; l++) {
+            if (!mbar_wait(&ydone[l & 1], (l >> 1) & 1, p.status, 8)) return;
+            write_out_m(p, ytile + (l & 1) * kOutCap, p.layers[l].y + p.row_base + r0, r1 - r0, lane, M);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&yfree[l & 1]);
+        }
+        if (p.npeers) __threadfence_system();
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    const int tk = g < M ? g : M - 1;                      // token fed as column g (columns >= M are never read)
+    const int t0 = 2 * t, t1 = 2 * t + 1;                  // tokens whose sums this lane owns
+    int c = 0;
+    for (int l = 0; l < p.nlayers; l++) {
+        const uint8_t* ab = act + (size_t)(l & 1) * ACT;
+        float* yt = ytile + (l & 1) * kOutCap;
+        if (tiled && l >= 2 && !mbar_wait(&yfree[l & 1], ((l >> 1) & 1) ^ 1, p.status, 7)) return;
+        if (!mbar_wait(&act_ready[l & 1], (l >> 1) & 1, p.status, 2)) return;
+        uint4 be[GPW], bo[GPW];
+        float sa0[GPW], sa1[GPW];
+        int su0[GPW], su1[GPW];
+#pragma unroll
+        for (int j = 0; j < GPW; j++) {
+            const int gg = j * CW + warp;
+            be[j] = *reinterpret_cast<const uint4*>(ab + tk * (K / 2) + (gg * 16 + 4 * t) * 4);
+            bo[j] = *reinterpret_cast<const uint4*>(ab + M * (K / 2) + tk * (K / 2) + (gg * 16 + 4 * t) * 4);
+            const float* scp = reinterpret_cast<const float*>(ab + M * K);
+            const int* sup = reinterpret_cast<const int*>(ab + M * K + M * NG * 4);
+            sa0[j] = t0 < M ? scp[t0 * NG + gg] : 0.f;
+            sa1[j] = t1 < M ? scp[t1 * NG + gg] : 0.f;
+            su0[j] = t0 < M ? 8 * sup[t0 * NG + gg] : 0;
+            su1[j] = t1 < M ? 8 * sup[t1 * NG + gg] : 0;
+        }
+        float* y = p.layers[l].y + p.row_base;
+
+        for (int jst = 0; jst < nst; jst++, c++) {
+            const int s = c % STAGES;
+            if (!mbar_wait(&full[s], (c / STAGES) & 1, p.status, 3)) return;
+            const uint8_t* st = ring + (size_t)s * STAGE;
+            uint4 xa[GPW], xb[GPW];
+            float swa[GPW], swb[GPW];
+#pragma unroll
+            for (int j = 0; j < GPW; j++) {
+                const int gg = j * CW + warp;
+                xa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * ROWB + gg * 64 + t * 16);
+                xb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * ROWB + gg * 64 + t * 16);
+                swa[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + g * SCB + gg * 2));
+                swb[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + (g + 8) * SCB + gg * 2));
+            }
+            float fa0 = 0.f, fa1 = 0.f, fb0 = 0.f, fb1 = 0.f;   // rows g, g+8 x tokens t0, t1 over this warp's groups
+#pragma unroll
+            for (int j = 0; j < GPW; j++) {
+                int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+                const uint32_t m_lo = 0x0F0F0F0Fu, x_lo = 0x08080808u, m_hi = 0xF0F0F0F0u, x_hi = 0x80808080u;
+                mma_s8(lo, (xa[j].x & m_lo) ^ x_lo, (xb[j].x & m_lo) ^ x_lo, (xa[j].y & m_lo) ^ x_lo, (xb[j].y & m_lo) ^ x_lo,
+                       be[j].x, be[j].y);
+                mma_s8(lo, (xa[j].z & m_lo) ^ x_lo, (xb[j].z & m_lo) ^ x_lo, (xa[j].w & m_lo) ^ x_lo, (xb[j].w & m_lo) ^ x_lo,
+                       be[j].z, be[j].w);
+                mma_u8(hi, (xa[j].x & m_hi) ^ x_hi, (xb[j].x & m_hi) ^ x_hi, (xa[j].y & m_hi) ^ x_hi, (xb[j].y & m_hi) ^ x_hi,
+                       bo[j].x, bo[j].y);
+                mma_u8(hi, (xa[j].z & m_hi) ^ x_hi, (xb[j].z & m_hi) ^ x_hi, (xa[j].w & m_hi) ^ x_hi, (xb[j].w & m_hi) ^ x_hi,
+                       bo[j].z, bo[j].w);
+                // accumulator columns 2t and 2t+1 of this lane are tokens t0 and t1
+                fa0 += (swa[j] * sa0[j]) * (float)(lo[0] + (hi[0] >> 4) - su0[j]);
+                fa1 += (swa[j] * sa1[j]) * (float)(lo[1] + (hi[1] >> 4) - su1[j]);
+                fb0 += (swb[j] * sa0[j]) * (float)(lo[2] + (hi[2] >> 4) - su0[j]);
+                fb1 += (swb[j] * sa1[j]) * (float)(lo[3] + (hi[3] >> 4) - su1[j]);
+            }
+            // release only after the loaded registers have been consumed (see the one-token kernel)
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&empty[s]);
+                if (jst == 0) mbar_arrive(&act_free[l & 1]);
+            }
+            const int rb = c & 1;
+            if (c >= 2 && !mbar_wait(&red_free[rb], ((c >> 1) & 1) ^ 1, p.status, 5)) return;
+            float* rw = red + (size_t)(rb * CW + warp) * ROWS * M;
+            if (t0 < M) {
+                rw[g * M + t0] = fa0;
+                rw[(g + 8) * M + t0] = fb0;
+            }
+            if (t1 < M) {
+                rw[g * M + t1] = fa1;
+                rw[(g + 8) * M + t1] = fb1;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_full[rb]);
+            if (warp == (c % CW)) {                         // this stage's reducer: fixed order over the warps
+                if (!mbar_wait(&red_full[rb], (c >> 1) & 1, p.status, 6)) return;
+                float acc[(ROWS * M + 31) / 32];
+#pragma unroll
+                for (int k = 0; k < (ROWS * M + 31) / 32; k++) {
+                    const int i = k * 32 + lane;
+                    acc[k] = 0.f;
+                    if (i < ROWS * M) {
+                        const float* pr = red + (size_t)rb * CW * ROWS * M + i;
+                        constexpr int W = ROWS * M;
+                        acc[k] = ((pr[0 * W] + pr[4 * W]) + (pr[2 * W] + pr[6 * W])) + ((pr[1 * W] + pr[5 * W]) + (pr[3 * W] + pr[7 * W]));
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_free[rb]);
+#pragma unroll
+                for (int k = 0; k < (ROWS * M + 31) / 32; k++) {
+                    const int i = k * 32 + lane;
+                    const int rr = i / M, tok = i - rr * M, row = r0 + jst * ROWS + rr;
+                    if (i < ROWS * M && row < r1) {
+                        if (tiled) {
+                            yt[(row - r0) * M + tok] = acc[k];
+                        } else {
+                            float* dst = y + (size_t)tok * p.ystride + row;
+                            *dst = acc[k];
+                            for (int q = 0; q < p.npeers; q++)
+                                *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = acc[k];
+                        }
+                    }
+                }
+            }
+        }
+        if (tiled) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ydone[l & 1]);
+        }
+    }
+    if (p.npeers) __threadfence_system();
+}
+
+template <int STAGES, int M>
+int run_stream_mma_m(const char* kn, const LaunchCtx& c, const StreamParams& p) {
+    constexpr int K = 5120;
+    constexpr size_t smem = 256 + (size_t)STAGES * 16 * (K / 2 + 80) + 2 * M * (K + 320) + 2 * 8 * 16 * M * 4 + 2 * kOutCap * 4;
+    static_assert(smem <= 227 * 1024, "shared memory");
+    auto kern = w4a8_stream_mma_m_kernel<STAGES, M>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        configured = true;
+    }
+    int grid = c.sm_count;
+    if (grid > p.rows) grid = p.rows;
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(10 * 32), smem, c.stream, pdl_enabled(), p);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
 template <int STAGES>
 int run_stream_mma(const char* kn, const LaunchCtx& c, const StreamParams& p) {
     constexpr int K = 5120;
@@ -620,9 +873,62 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
     return run_stream<A4, 5, 16, 5>(kn, c, p);
 }
 
+// w4a8_decode_stream_m(layers, nlayers, rows, K, row_base, npeers, peer_delta, status, ae, ao, asc, asu, M, ystride):
+// M = 2..4 tokens per layer.  The code arrays hold [nlayers * M] tokens (one 2-D quant_act launch with grid
+// y = nlayers * M over x[nlayers][M][K]); y of a layer is token-major, y[token * ystride + row_base + row].  The
+// layer table must have been validated by fm_stream_table with row_base + (M - 1) * ystride as its row_base
+// argument, which is what makes every token's rows lie inside the checked footprint of y.
+int launch_w4a8_stream_m(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = "w4a8_decode_stream_m";
+    StreamParams p = {};
+    p.layers = arg_ptr<const StreamLayer>(a[0]);
+    p.nlayers = arg_i32(a[1]);
+    p.rows = arg_i32(a[2]);
+    p.K = arg_i32(a[3]);
+    p.row_base = arg_i32(a[4]);
+    p.npeers = arg_i32(a[5]);
+    p.peer_delta = arg_ptr<const long long>(a[6]);
+    p.status = arg_ptr<int>(a[7]);
+    p.ae = arg_ptr<const uint8_t>(a[8]);
+    p.ao = arg_ptr<const uint8_t>(a[9]);
+    p.asc = arg_ptr<const uint8_t>(a[10]);
+    p.asu = arg_ptr<const uint8_t>(a[11]);
+    p.M = arg_i32(a[12]);
+    p.ystride = arg_i32(a[13]);
+    FM_REQUIRE(p.K == 5120, kn, "K=%d: the fused stream is built for K = 5120 only; launch the per-layer kernels", p.K);
+    FM_REQUIRE(p.M >= 2 && p.M <= 4, kn, "M=%d: this kernel takes 2..4 tokens (w4a8_decode_stream takes one)", p.M);
+    FM_REQUIRE(p.nlayers >= 0 && p.rows > 0 && p.row_base >= 0 && p.npeers >= 0 && p.npeers <= 8, kn,
+               "bad nlayers/rows/row_base/npeers");
+    FM_REQUIRE(p.ystride >= p.row_base + p.rows && (long long)(p.M - 1) * p.ystride + p.row_base < (1LL << 31), kn,
+               "ystride=%d must be at least row_base + rows = %d", p.ystride, p.row_base + p.rows);
+    if (p.nlayers == 0) return FM_OK;
+    FM_REQUIRE(aligned(p.layers, 8) && aligned(p.status, 4), kn, "misaligned layer table or status");
+    FM_RANGE(p.layers, (size_t)p.nlayers * sizeof(StreamLayer), kn, "layers");
+    const int vbase = p.row_base + (p.M - 1) * p.ystride;
+    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, vbase, p.peer_delta, p.npeers, true), kn,
+               "the layer table at %p was not filled by fm_stream_table for nlayers=%d rows=%d K=%d and the row_base "
+               "argument row_base + (M - 1) * ystride = %d (or was overwritten since), or the peer offsets do not come "
+               "from fm_stream_peers for its outputs", (const void*)p.layers, p.nlayers, p.rows, p.K, vbase);
+    FM_RANGE(p.status, 4, kn, "status");
+    if (p.npeers) FM_RANGE(p.peer_delta, (size_t)p.npeers * 8, kn, "peer_delta");
+    FM_REQUIRE(aligned(p.ae, 16) && aligned(p.asc, 16) && aligned(p.ao, 16) && aligned(p.asu, 16), kn,
+               "the activation code arrays must be 16-byte aligned");
+    const size_t tokens = (size_t)p.nlayers * p.M;
+    FM_RANGE(p.ae, tokens * (p.K / 2), kn, "ae");
+    FM_RANGE(p.ao, tokens * (p.K / 2), kn, "ao");
+    FM_RANGE(p.asc, tokens * (p.K / 128) * 4, kn, "asc");
+    FM_RANGE(p.asu, tokens * (p.K / 128) * 4, kn, "asu");
+    switch (p.M) {
+        case 2: return run_stream_mma_m<4, 2>(kn, c, p);
+        case 3: return run_stream_mma_m<4, 3>(kn, c, p);
+        default: return run_stream_mma_m<4, 4>(kn, c, p);
+    }
+}
+
 const KernelEntry kStream[] = {
     {"w4a8_decode_stream", 12, launch_w4_stream<false>, "piiiiipppppp"},
     {"w4a4_decode_stream", 10, launch_w4_stream<true>, "piiiiipppp"},
+    {"w4a8_decode_stream_m", 14, launch_w4a8_stream_m, "piiiiippppppii"},
 };
 
 }  // namespace

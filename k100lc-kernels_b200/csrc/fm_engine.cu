@@ -54,7 +54,7 @@ struct Engine {
     std::vector<KernelEntry> kernels;
     std::unordered_map<std::string, int> by_name;
     std::map<uintptr_t, size_t> allocs;          // base -> bytes
-    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi; };
+    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; };
     std::map<uintptr_t, Table> tables;           // validated stream layer tables
     struct Peers { int npeers; uintptr_t lo, hi; };
     std::map<uintptr_t, Peers> peers;            // validated peer-offset arrays (device address -> window)
@@ -322,7 +322,7 @@ void* engine_scratch(size_t bytes) {
 }
 
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
-                     int npeers) {
+                     int npeers, bool whole_y) {
     Engine& e = E();
     if (!e.check_bounds) return true;
     auto it = e.tables.find(reinterpret_cast<uintptr_t>(table));
@@ -333,7 +333,7 @@ bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_ba
     // every y of the table must lie inside the window the peer offsets were validated for
     auto ip = e.peers.find(reinterpret_cast<uintptr_t>(peer_delta));
     if (ip == e.peers.end() || ip->second.npeers != npeers) return false;
-    return t.y_lo >= ip->second.lo && t.y_hi <= ip->second.hi;
+    return (whole_y ? t.y_ptr_lo : t.y_lo) >= ip->second.lo && t.y_hi <= ip->second.hi;
 }
 
 }  // namespace fm
@@ -605,7 +605,7 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
     if (!range_ok(dev_table, bytes)) { set_errorf("fm_stream_table: the table does not fit its allocation"); return -1; }
     const size_t need[4] = {(size_t)rows * (K / 2), (size_t)rows * (K / 128) * 2, (size_t)K * 4,
                             ((size_t)row_base + rows) * 4};
-    uintptr_t y_lo = ~(uintptr_t)0, y_hi = 0;
+    uintptr_t y_lo = ~(uintptr_t)0, y_hi = 0, y_ptr_lo = ~(uintptr_t)0;
     const size_t align[4] = {16, 16, 16, 4};
     const char* what[4] = {"wq", "ws", "x", "y"};
     for (int l = 0; l < nlayers; l++)
@@ -621,11 +621,12 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
                 const uintptr_t y = static_cast<uintptr_t>(host_layers[4 * l + j]);
                 if (y + (size_t)row_base * 4 < y_lo) y_lo = y + (size_t)row_base * 4;
                 if (y + need[3] > y_hi) y_hi = y + need[3];
+                if (y < y_ptr_lo) y_ptr_lo = y;
             }
         }
     if (copy_sync(dev_table, host_layers, bytes, cudaMemcpyHostToDevice, "fm_stream_table") != 0) return -1;
     touch(dev_table, bytes);
-    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi};
+    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo};
     return 0;
 }
 

@@ -38,8 +38,10 @@ void* engine_scratch(size_t bytes);
 // true when `table` was filled by fm_stream_table with exactly these shapes and has not been
 // overwritten since (or checks are off): every pointer inside it was range-checked then; with
 // npeers > 0 the offset array must come from fm_stream_peers and cover every y of the table
+// (`whole_y`: the kernel writes below row_base too — the multi-token layout — so the peer window must reach
+// down to the lowest y pointer of the table)
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
-                     int npeers);
+                     int npeers, bool whole_y = false);
 
 // Registries of the kernel files -------------------------------------------
 const KernelEntry* quant_kernels(int* n);

@@ -185,3 +185,36 @@ def test_stream_many_rows_per_cta(rt):
     for sl in (slice(0, 1024), slice(rows - 1024, rows)):
         ref = O.gemv_w4(L["wq"][sl], L["ws"][sl], q["q"], q["scale"], 128)["y"][0]
         assert O.rel_err(got[0][sl], ref) < REL
+
+
+@pytest.mark.parametrize("m,rows,row_base", [(2, 1000, 0), (3, 148, 0), (4, 17408, 0), (4, 700, 300)])
+def test_stream_several_tokens_matches_oracle(rt, m, rows, row_base):
+    """w4a8_decode_stream_m: M tokens per layer as the columns of the MMA; y of a layer is token-major."""
+    nl = 3
+    ystride = row_base + rows + 24
+    layers = [synth.rt4_layer(rows, K, m, seed=900 + 10 * m + i) for i in range(nl)]
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"] for L in layers]))                       # [nl][m][K]
+        ae, ao = b.zeros(nl * m * K // 2, np.int8), b.zeros(nl * m * K // 2, np.int8)
+        asc, asu = b.zeros(nl * m * K // 128), b.zeros(nl * m * K // 128, np.int32)
+        y = b.zeros(nl * m * ystride, np.float32, np.nan)
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), x + i * m * K * 4, y + i * m * ystride * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, row_base + (m - 1) * ystride)   # footprint of all m tokens
+        status = b.zeros(1, np.int32)
+        rt.launch2d("quant_act", K // 128, nl * m, 32, 1, [x, ae, ao, asc, asu, nl * m, K])
+        argv = [table, nl, rows, K, row_base, 0, 0, status, ae, ao, asc, asu, m, ystride]
+        rt.launch("w4a8_decode_stream_m", 1, 1, argv)
+        got = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        with pytest.raises(RuntimeError, match="rc=-4"):                    # a table validated for one token is refused
+            t1 = rt.stream_table(ptrs, rows, K, row_base)
+            try:
+                rt.launch("w4a8_decode_stream_m", 1, 1, [t1] + argv[1:])
+            finally:
+                rt.free(t1)
+        rt.free(table)
+    for i, L in enumerate(layers):
+        q = O.quant_act(L["x"])
+        ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"]          # [m][rows]
+        assert O.rel_err(got[i, :, row_base:row_base + rows], ref) < REL
+        assert np.isnan(got[i, :, :row_base]).all() and np.isnan(got[i, :, row_base + rows:]).all()
