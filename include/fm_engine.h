@@ -95,6 +95,8 @@ int   fm_download_async(void* pinned_host, const void* dev, size_t n);
  * allocations for the footprint that (rows, K, row_base) implies — wq rows*K/2 bytes,
  * ws rows*(K/128)*2, x K*4, y (row_base+rows)*4 — then the table is copied to dev_table
  * (nlayers*32 bytes) and remembered as validated until something overwrites it.
+ * For "w4a8_decode_stream_m" (M tokens per layer, y token-major with `ystride` floats between tokens)
+ * pass row_base + (M-1)*ystride as row_base here: the checked footprint of y then covers every token.
  * 0 ok, -4 a pointer fails the check, -1 other errors. */
 int   fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, int rows, int K, int row_base);
 

@@ -218,3 +218,31 @@ def test_stream_several_tokens_matches_oracle(rt, m, rows, row_base):
         ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"]          # [m][rows]
         assert O.rel_err(got[i, :, row_base:row_base + rows], ref) < REL
         assert np.isnan(got[i, :, :row_base]).all() and np.isnan(got[i, :, row_base + rows:]).all()
+
+
+def test_stream_several_tokens_delivers_to_host(rt):
+    """The multi-token kernel stores to every additional receiver too (here: pinned host memory)."""
+    m, rows, nl = 2, 900, 4
+    ystride = rows + 8
+    layers = [synth.rt4_layer(rows, K, m, seed=950 + i) for i in range(nl)]
+    host = rt.pinned((nl, m, ystride), np.float32)
+    host[:] = np.nan
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"] for L in layers]))
+        ae, ao = b.zeros(nl * m * K // 2, np.int8), b.zeros(nl * m * K // 2, np.int8)
+        asc, asu = b.zeros(nl * m * K // 128), b.zeros(nl * m * K // 128, np.int32)
+        y = b.zeros(nl * m * ystride, np.float32, np.nan)
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), x + i * m * K * 4, y + i * m * ystride * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, (m - 1) * ystride)
+        deltas = rt.stream_peers([host.ctypes.data], y, nl * m * ystride * 4)
+        status = b.zeros(1, np.int32)
+        rt.launch2d("quant_act", K // 128, nl * m, 32, 1, [x, ae, ao, asc, asu, nl * m, K])
+        rt.launch("w4a8_decode_stream_m", 1, 1, [table, nl, rows, K, 0, 1, deltas, status, ae, ao, asc, asu, m, ystride])
+        dev = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+        rt.free(deltas)
+    assert np.array_equal(host.view(np.uint32), dev.view(np.uint32))
+    for i, L in enumerate(layers):
+        q = O.quant_act(L["x"])
+        assert O.rel_err(host[i, :, :rows], O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"]) < REL
