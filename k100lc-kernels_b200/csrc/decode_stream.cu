@@ -82,6 +82,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* sta
     atomicCAS(status, 0, code);
     return false;
 }
+// Pins a value in program order: volatile statements are not reordered with each other, so an
+// mbarrier.arrive that follows cannot be scheduled ahead of the arithmetic that produced `v`
+// (and with it ahead of the shared-memory loads that arithmetic consumed).
+__device__ __forceinline__ void consumed(float v) { asm volatile("" ::"f"(v) : "memory"); }
 // 1-D bulk async copy global -> this CTA's shared memory
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -278,6 +282,7 @@ w4_stream_kernel(const StreamParams p) {
             // Release only now: the arithmetic above has consumed every register loaded from the stage
             // (and, in a layer's first stage, from the code tile), so those loads have completed.  An
             // arrive issued right behind the loads can overtake them, and the refill would race with them.
+            consumed(acc);
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(&empty[s]);
@@ -478,6 +483,7 @@ w4a8_stream_mma_kernel(const StreamParams p) {
             // Release only now: the MMAs and multiplies above have consumed every register loaded from
             // the stage (and, in a layer's first stage, from the code tile), so those loads have
             // completed.  An arrive issued right behind the loads can overtake them.
+            consumed(fa + fb);
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(&empty[s]);
@@ -500,6 +506,7 @@ w4a8_stream_mma_kernel(const StreamParams p) {
                     acc = ((pr[0 * ROWS] + pr[4 * ROWS]) + (pr[2 * ROWS] + pr[6 * ROWS])) +
                           ((pr[1 * ROWS] + pr[5 * ROWS]) + (pr[3 * ROWS] + pr[7 * ROWS]));
                 }
+                consumed(acc);                              // the partial sums are read before the tile is released
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_free[rb]);
                 if (lane < ROWS && row < r1) {
@@ -697,6 +704,7 @@ w4a8_stream_mma_m_kernel(const StreamParams p) {
                 fb1 += (swb[j] * sa1[j]) * (float)(lo[3] + (hi[3] >> 4) - su1[j]);
             }
             // release only after the loaded registers have been consumed (see the one-token kernel)
+            consumed((fa0 + fa1) + (fb0 + fb1));
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(&empty[s]);
@@ -727,6 +735,7 @@ w4a8_stream_mma_m_kernel(const StreamParams p) {
                         constexpr int W = ROWS * M;
                         acc[k] = ((pr[0 * W] + pr[4 * W]) + (pr[2 * W] + pr[6 * W])) + ((pr[1 * W] + pr[5 * W]) + (pr[3 * W] + pr[7 * W]));
                     }
+                    consumed(acc[k]);                       // read before the tile is released
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_free[rb]);
