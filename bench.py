@@ -325,6 +325,22 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         rt.graph_free(g)
         out[name] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
     runner.close()
+    if st.layers >= 4:                                  # NVFP4, four tokens (one quantiser launch per token, as the reference does)
+        qa4, qb4, sc4n = rt.alloc(4 * K // 2), rt.alloc(4 * K // 2), rt.alloc(4 * (K // 16) * 4)
+
+        def nvfp4_m4(l):
+            lx = min(l, st.layers - 4)
+            for r in range(4):
+                rt.launch("nvfp4_quant_act", K // 16, 64, [st.x + (lx + r) * K * 4, qa4 + r * K // 2, qb4 + r * K // 2,
+                                                          sc4n + r * (K // 16) * 4, 1, K])
+            rt.launch("nvfp4_gemv<4,1>", rows // 4, 256,
+                      [st.wq_l(l), nvs + (l % nv_layers) * rows * (K // 16), qa4, qb4, sc4n, st.y + lx * N * 4, rows, K, 0.05])
+        g = graph_of(nvfp4_m4, nl)
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
+        rt.graph_free(g)
+        out["nvfp4_m4"] = {"us_per_layer": round(us, 3), "gb_per_s": round(NVFP4_LAYER_BYTES * frac / us / 1e3, 1)}
+        for ptr in (qa4, qb4, sc4n):
+            rt.free(ptr)
     # W4A16: compressed-tensors bytes (offset-binary nibbles, bf16 group scales), fp32 activations
     from k100lc_kernels import DotLinear, Workspace
     nd = min(nl, 8)
@@ -362,6 +378,20 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
         rt.graph_free(g)
         out[name] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
+    # NVFP4 through its stream kernel (one 2-D nvfp4_quant_act launch over the x of all layers in front)
+    nvl = min(nl, nv_layers)
+    tab_n = rt.stream_table([(st.wq_l(l), nvs + l * rows * (K // 16), st.x + l * K * 4, st.y + l * N * 4) for l in range(nvl)], rows, K, 0)
+    qan, qbn, scn = rt.alloc(nvl * K // 2), rt.alloc(nvl * K // 2), rt.alloc(nvl * (K // 16) * 4)
+    rt.graph_begin()
+    rt.launch2d("nvfp4_quant_act", K // 16, nvl, 64, 1, [st.x, qan, qbn, scn, nvl, K])
+    rt.launch("nvfp4_decode_stream", 1, 1, [tab_n, nvl, rows, K, 0, 0, 0, status, qan, qbn, scn, 0.05])
+    g = rt.graph_end()
+    us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nvl
+    rt.graph_free(g)
+    out["nvfp4_m1_stream"] = {"us_per_layer": round(us, 3), "gb_per_s": round(NVFP4_LAYER_BYTES * frac / us / 1e3, 1),
+                              "note": f"{nvl} layers per launch"}
+    for ptr in (tab_n, qan, qbn, scn):
+        rt.free(ptr)
     # four tokens per layer through the multi-token stream kernel (tokens = columns of the MMA)
     mt, nlm = 4, min(nl, st.layers // 4)
     if nlm > 0:

@@ -882,6 +882,236 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
     return run_stream<A4, 5, 16, 5>(kn, c, p);
 }
 
+// ------------------------------------------------------------------------------------
+// NVFP4 (E2M1 weights, E4M3 scale per 16 weights, f32 global scale, int8 activations per 16-block;
+// reference kernels/asm/k_nvfp4/011_*.s): the same ring with the arithmetic of nvfp4_gemv<1,1> —
+// identical integers per block, identical fp32 association — so both give the same bits.
+// A stage is 12 rows of 2560 packed bytes + 320 scale bytes; the code tile of a layer holds the
+// even / odd int8 streams and the 320 block scales of the token (nvfp4_quant_act's outputs),
+// re-interleaved into natural k order in registers once per layer.
+struct Nvfp4StreamParams {
+    StreamParams s;                    // layers[].ws are E4M3 bytes [rows][K/16]; s.ae = even codes, s.ao = odd codes, s.asc = scales
+    float gscale;
+};
+
+template <int CW, int STAGES>
+__global__ void __launch_bounds__((CW + 2) * 32, 1)
+nvfp4_stream_kernel(const Nvfp4StreamParams pp) {
+    const StreamParams& p = pp.s;
+    constexpr int K = 5120, KITER = 5, NB = K / 16;
+    constexpr int ROWB = K / 2, SCB = NB;
+    constexpr int STAGE_W = CW * ROWB, STAGE = STAGE_W + CW * SCB;
+    constexpr int ACT = K + NB * 4;                      // even codes, odd codes, block scales
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + STAGES;
+    uint64_t* act_ready = empty + STAGES;
+    uint64_t* act_free = act_ready + 2;
+    uint64_t* ydone = act_free + 2;
+    uint64_t* yfree = ydone + 2;
+    uint8_t* ring = smem + 256;
+    uint8_t* act = ring + (size_t)STAGES * STAGE;
+    float* ytile = reinterpret_cast<float*>(act + 2 * ACT);   // [2][kOutCap]
+    float* s_lut = ytile + 2 * kOutCap;                       // [256] 0.5 * gscale * E4M3(byte)
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CW);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&act_ready[b], 1);
+            mbar_init(&act_free[b], CW);
+            mbar_init(&ydone[b], CW);
+            mbar_init(&yfree[b], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_lut[i] = (0.5f * pp.gscale) * e4m3_to_f32(i);
+    __syncthreads();
+    pdl_wait();
+
+    const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const int nst = (r1 - r0 + CW - 1) / CW;
+    const bool tiled = (r1 - r0) <= kOutCap;
+
+    if (warp == CW) {
+        if (lane == 0) {                                   // producer
+            auto copy_codes = [&](int l) -> bool {
+                const int b = l & 1;
+                if (l >= 2 && !mbar_wait(&act_free[b], ((l >> 1) & 1) ^ 1, p.status, 4)) return false;
+                uint8_t* ab = act + (size_t)b * ACT;
+                mbar_expect_tx(&act_ready[b], ACT);
+                bulk_g2s(ab, p.ae + (size_t)l * (K / 2), K / 2, &act_ready[b]);
+                bulk_g2s(ab + K / 2, p.ao + (size_t)l * (K / 2), K / 2, &act_ready[b]);
+                bulk_g2s(ab + K, p.asc + (size_t)l * (NB * 4), NB * 4, &act_ready[b]);
+                return true;
+            };
+            int c = 0;
+            const uint8_t* wq = p.layers[0].wq;
+            const uint8_t* ws = p.layers[0].ws;
+            if (!copy_codes(0)) return;
+            for (int l = 0; l < p.nlayers; l++) {
+                const int ln = min(l + 1, p.nlayers - 1);
+                const uint8_t* wq_n = p.layers[ln].wq;
+                const uint8_t* ws_n = p.layers[ln].ws;
+                for (int j = 0; j < nst; j++, c++) {
+                    const int s = c % STAGES;
+                    if (c >= STAGES && !mbar_wait(&empty[s], ((c / STAGES) & 1) ^ 1, p.status, 1)) return;
+                    const int row = r0 + j * CW;
+                    const int nr = min(CW, r1 - row);
+                    uint8_t* dst = ring + (size_t)s * STAGE;
+                    mbar_expect_tx(&full[s], (uint32_t)(nr * (ROWB + SCB)));
+                    bulk_g2s(dst, wq + (size_t)row * ROWB, (uint32_t)(nr * ROWB), &full[s]);
+                    bulk_g2s(dst + STAGE_W, ws + (size_t)row * SCB, (uint32_t)(nr * SCB), &full[s]);
+                    if (j == 0 && l + 1 < p.nlayers && !copy_codes(l + 1)) return;
+                }
+                wq = wq_n;
+                ws = ws_n;
+            }
+        }
+        return;
+    }
+
+    if (warp == CW + 1) {                                    // writer
+        if (!tiled) return;
+        for (int l = 0; l < p.nlayers; l++) {
+            if (!mbar_wait(&ydone[l & 1], (l >> 1) & 1, p.status, 8)) return;
+            write_out(p, ytile + (l & 1) * kOutCap, p.layers[l].y + p.row_base + r0, r1 - r0, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&yfree[l & 1]);
+        }
+        if (p.npeers) __threadfence_system();
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers: warp w takes row w of a stage
+    int c = 0;
+    for (int l = 0; l < p.nlayers; l++) {
+        const uint8_t* ab = act + (size_t)(l & 1) * ACT;
+        float* yt = ytile + (l & 1) * kOutCap;
+        if (tiled && l >= 2 && !mbar_wait(&yfree[l & 1], ((l >> 1) & 1) ^ 1, p.status, 7)) return;
+        if (!mbar_wait(&act_ready[l & 1], (l >> 1) & 1, p.status, 2)) return;
+        uint4 a0[KITER], a1[KITER];                        // the token's codes of this lane's 32 k per step, natural order
+        float2 asc[KITER];                                 // and the scales of its two 16-blocks
+#pragma unroll
+        for (int it = 0; it < KITER; it++) {
+            const int d0 = it * 128 + lane * 4;
+            const uint4 e = *reinterpret_cast<const uint4*>(ab + d0 * 4), o = *reinterpret_cast<const uint4*>(ab + K / 2 + d0 * 4);
+            a0[it] = make_uint4(prmt(e.x, o.x, 0x5140u), prmt(e.x, o.x, 0x7362u), prmt(e.y, o.y, 0x5140u), prmt(e.y, o.y, 0x7362u));
+            a1[it] = make_uint4(prmt(e.z, o.z, 0x5140u), prmt(e.z, o.z, 0x7362u), prmt(e.w, o.w, 0x5140u), prmt(e.w, o.w, 0x7362u));
+            asc[it] = *reinterpret_cast<const float2*>(ab + K + (d0 >> 1) * 4);
+        }
+        float* y = p.layers[l].y + p.row_base;
+
+        for (int j = 0; j < nst; j++, c++) {
+            const int s = c % STAGES;
+            if (!mbar_wait(&full[s], (c / STAGES) & 1, p.status, 3)) return;
+            const int row = r0 + j * CW + warp;
+            const bool live = row < r1;
+            const uint8_t* st = ring + (size_t)s * STAGE;
+            float acc = 0.f;
+            if (live) {
+                const uint4* wrow = reinterpret_cast<const uint4*>(st + (size_t)warp * ROWB);
+                const uint8_t* srow = st + STAGE_W + (size_t)warp * SCB;
+                uint4 w[KITER];
+                uint32_t sb[KITER];
+#pragma unroll
+                for (int it = 0; it < KITER; it++) {
+                    w[it] = wrow[it * 32 + lane];
+                    sb[it] = *reinterpret_cast<const unsigned short*>(srow + ((it * 128 + lane * 4) >> 1));
+                }
+#pragma unroll
+                for (int it = 0; it < KITER; it++) {
+                    int i0 = dot8_e2m1(w[it].x, a0[it].x, a0[it].y, 0);
+                    i0 = dot8_e2m1(w[it].y, a0[it].z, a0[it].w, i0);
+                    int i1 = dot8_e2m1(w[it].z, a1[it].x, a1[it].y, 0);
+                    i1 = dot8_e2m1(w[it].w, a1[it].z, a1[it].w, i1);
+                    acc = fmaf((float)i0, s_lut[sb[it] & 0xFFu] * asc[it].x, acc);
+                    acc = fmaf((float)i1, s_lut[(sb[it] >> 8) & 0xFFu] * asc[it].y, acc);
+                }
+            }
+            consumed(acc);                                  // release only after the loaded data has been used
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&empty[s]);
+                if (j == 0) mbar_arrive(&act_free[l & 1]);
+            }
+            if (!live) continue;
+            acc = warp_sum(acc);
+            if (lane == 0) {
+                if (tiled) {
+                    yt[row - r0] = acc;
+                } else {
+                    y[row] = acc;
+                    for (int q = 0; q < p.npeers; q++)
+                        *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
+                }
+            }
+        }
+        if (tiled) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ydone[l & 1]);
+        }
+    }
+    if (p.npeers) __threadfence_system();
+}
+
+// nvfp4_decode_stream(layers, nlayers, rows, K, row_base, npeers, peer_delta, status, qa, qb, sc, gscale):
+// the layer table's ws entries are the E4M3 block scales [rows][K/16] (the table must have been validated
+// with room for them: fm_stream_table records how many bytes follow every ws pointer inside its allocation);
+// qa / qb / sc are nvfp4_quant_act's outputs for all layers: [nlayers][K/2], [nlayers][K/2], [nlayers][K/16].
+int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = "nvfp4_decode_stream";
+    Nvfp4StreamParams pp = {};
+    StreamParams& p = pp.s;
+    p.layers = arg_ptr<const StreamLayer>(a[0]);
+    p.nlayers = arg_i32(a[1]);
+    p.rows = arg_i32(a[2]);
+    p.K = arg_i32(a[3]);
+    p.row_base = arg_i32(a[4]);
+    p.npeers = arg_i32(a[5]);
+    p.peer_delta = arg_ptr<const long long>(a[6]);
+    p.status = arg_ptr<int>(a[7]);
+    p.ae = arg_ptr<const uint8_t>(a[8]);
+    p.ao = arg_ptr<const uint8_t>(a[9]);
+    p.asc = arg_ptr<const uint8_t>(a[10]);
+    pp.gscale = arg_f32(a[11]);
+    FM_REQUIRE(p.K == 5120, kn, "K=%d: the fused stream is built for K = 5120 only; launch the per-layer kernels", p.K);
+    FM_REQUIRE(p.nlayers >= 0 && p.rows > 0 && p.row_base >= 0 && p.npeers >= 0 && p.npeers <= 8, kn,
+               "bad nlayers/rows/row_base/npeers");
+    if (p.nlayers == 0) return FM_OK;
+    FM_REQUIRE(aligned(p.layers, 8) && aligned(p.status, 4), kn, "misaligned layer table or status");
+    FM_RANGE(p.layers, (size_t)p.nlayers * sizeof(StreamLayer), kn, "layers");
+    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, p.row_base, p.peer_delta, p.npeers, false,
+                               (size_t)p.rows * (p.K / 16)), kn,
+               "the layer table at %p was not filled by fm_stream_table for nlayers=%d rows=%d K=%d row_base=%d (or was "
+               "overwritten since), a ws entry has fewer than rows*K/16 bytes behind it, or the peer offsets do not come "
+               "from fm_stream_peers for its outputs", (const void*)p.layers, p.nlayers, p.rows, p.K, p.row_base);
+    FM_RANGE(p.status, 4, kn, "status");
+    if (p.npeers) FM_RANGE(p.peer_delta, (size_t)p.npeers * 8, kn, "peer_delta");
+    FM_REQUIRE(aligned(p.ae, 16) && aligned(p.ao, 16) && aligned(p.asc, 16), kn, "the activation code arrays must be 16-byte aligned");
+    FM_RANGE(p.ae, (size_t)p.nlayers * (p.K / 2), kn, "qa");
+    FM_RANGE(p.ao, (size_t)p.nlayers * (p.K / 2), kn, "qb");
+    FM_RANGE(p.asc, (size_t)p.nlayers * (p.K / 16) * 4, kn, "sc");
+    constexpr int CW = 12, STAGES = 5, K = 5120;
+    constexpr size_t smem = 256 + (size_t)STAGES * CW * (K / 2 + K / 16) + 2 * (K + (K / 16) * 4) + 2 * kOutCap * 4 + 1024;
+    static_assert(smem <= 227 * 1024, "shared memory");
+    auto kern = nvfp4_stream_kernel<CW, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        configured = true;
+    }
+    int grid = c.sm_count;
+    if (grid > p.rows) grid = p.rows;
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3((CW + 2) * 32), smem, c.stream, pdl_enabled(), pp);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
 // w4a8_decode_stream_m(layers, nlayers, rows, K, row_base, npeers, peer_delta, status, ae, ao, asc, asu, M, ystride):
 // M = 2..4 tokens per layer.  The code arrays hold [nlayers * M] tokens (one 2-D quant_act launch with grid
 // y = nlayers * M over x[nlayers][M][K]); y of a layer is token-major, y[token * ystride + row_base + row].  The
@@ -938,6 +1168,7 @@ const KernelEntry kStream[] = {
     {"w4a8_decode_stream", 12, launch_w4_stream<false>, "piiiiipppppp"},
     {"w4a4_decode_stream", 10, launch_w4_stream<true>, "piiiiipppp"},
     {"w4a8_decode_stream_m", 14, launch_w4a8_stream_m, "piiiiippppppii"},
+    {"nvfp4_decode_stream", 12, launch_nvfp4_stream, "piiiiipppppf"},
 };
 
 }  // namespace

@@ -56,6 +56,26 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     return d;
 }
 
+// ---- NVFP4: E2M1 weights (2 * magnitude in an 8-byte table, the packed word is the PRMT selector)
+// and E4M3 block scales
+constexpr uint32_t kTabLo = 0x03020100u;     // 2*E2M1 magnitude of index 0..3
+constexpr uint32_t kTabHi = 0x0C080604u;     // index 4..7
+__device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
+    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    const float mag = e == 0 ? ldexpf((float)m, -9) : ldexpf((float)(8u + m), (int)e - 10);
+    return (b & 0x80u) ? -mag : mag;
+}
+
+// integer dot of 8 E2M1 codes (one packed word) with 8 int8 activations in natural order
+__device__ __forceinline__ int dot8_e2m1(uint32_t w, uint32_t a_lo, uint32_t a_hi, int acc) {
+    const uint32_t n = w ^ 0x88888888u;
+    acc = dot4(prmt(kTabLo, kTabHi, w), a_lo, acc);
+    acc = dot4(prmt(kTabLo, kTabHi, w >> 16), a_hi, acc);
+    int neg = dot4(prmt(kTabLo, kTabHi, n), a_lo, 0);
+    neg = dot4(prmt(kTabLo, kTabHi, n >> 16), a_hi, neg);
+    return acc - neg;
+}
+
 // Programmatic dependent launch: wait until the preceding kernel on the stream
 // has completed and its writes are visible / allow the next kernel to start.
 // Both are no-ops when the kernel was launched without the attribute.

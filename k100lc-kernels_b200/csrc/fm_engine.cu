@@ -54,7 +54,7 @@ struct Engine {
     std::vector<KernelEntry> kernels;
     std::unordered_map<std::string, int> by_name;
     std::map<uintptr_t, size_t> allocs;          // base -> bytes
-    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; };
+    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; size_t ws_avail; };
     std::map<uintptr_t, Table> tables;           // validated stream layer tables
     struct Peers { int npeers; uintptr_t lo, hi; };
     std::map<uintptr_t, Peers> peers;            // validated peer-offset arrays (device address -> window)
@@ -322,13 +322,14 @@ void* engine_scratch(size_t bytes) {
 }
 
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
-                     int npeers, bool whole_y) {
+                     int npeers, bool whole_y, size_t ws_bytes) {
     Engine& e = E();
     if (!e.check_bounds) return true;
     auto it = e.tables.find(reinterpret_cast<uintptr_t>(table));
     if (it == e.tables.end()) return false;
     const Engine::Table& t = it->second;
     if (!(t.nlayers >= nlayers && t.rows == rows && t.K == K && t.row_base == row_base)) return false;
+    if (ws_bytes > t.ws_avail) return false;
     if (npeers == 0) return true;
     // every y of the table must lie inside the window the peer offsets were validated for
     auto ip = e.peers.find(reinterpret_cast<uintptr_t>(peer_delta));
@@ -606,6 +607,7 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
     const size_t need[4] = {(size_t)rows * (K / 2), (size_t)rows * (K / 128) * 2, (size_t)K * 4,
                             ((size_t)row_base + rows) * 4};
     uintptr_t y_lo = ~(uintptr_t)0, y_hi = 0, y_ptr_lo = ~(uintptr_t)0;
+    size_t ws_avail = ~(size_t)0;                  // fewest bytes between a ws pointer and the end of its allocation
     const size_t align[4] = {16, 16, 16, 4};
     const char* what[4] = {"wq", "ws", "x", "y"};
     for (int l = 0; l < nlayers; l++)
@@ -617,6 +619,17 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
                            l, what[j], need[j], ptr);
                 return FM_EREJECT;
             }
+            if (j == 1) {
+                const uintptr_t w = static_cast<uintptr_t>(host_layers[4 * l + j]);
+                auto ia = e.allocs.upper_bound(w);
+                if (ia != e.allocs.begin()) {
+                    --ia;
+                    const size_t avail = w < ia->first + ia->second ? ia->first + ia->second - w : 0;
+                    if (avail < ws_avail) ws_avail = avail;
+                } else {
+                    ws_avail = 0;
+                }
+            }
             if (j == 3) {
                 const uintptr_t y = static_cast<uintptr_t>(host_layers[4 * l + j]);
                 if (y + (size_t)row_base * 4 < y_lo) y_lo = y + (size_t)row_base * 4;
@@ -626,7 +639,7 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
         }
     if (copy_sync(dev_table, host_layers, bytes, cudaMemcpyHostToDevice, "fm_stream_table") != 0) return -1;
     touch(dev_table, bytes);
-    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo};
+    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo, ws_avail};
     return 0;
 }
 

@@ -27,9 +27,6 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr uint32_t kTabLo = 0x03020100u;     // 2*E2M1 magnitude of index 0..3
-constexpr uint32_t kTabHi = 0x0C080604u;     // index 4..7
-
 struct Nvfp4Params {
     const uint32_t* wq;     // [N][K/8] E2M1 codes, low nibble = lower k
     const uint8_t* ws;      // [N][K/16] E4M3 block scales
@@ -41,22 +38,6 @@ struct Nvfp4Params {
     int N, K, rows;
     float gscale;
 };
-
-__device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
-    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
-    const float mag = e == 0 ? ldexpf((float)m, -9) : ldexpf((float)(8u + m), (int)e - 10);
-    return (b & 0x80u) ? -mag : mag;
-}
-
-// integer dot of 8 E2M1 codes (one packed word) with 8 int8 activations in natural order
-__device__ __forceinline__ int dot8_e2m1(uint32_t w, uint32_t a_lo, uint32_t a_hi, int acc) {
-    const uint32_t n = w ^ 0x88888888u;
-    acc = dot4(prmt(kTabLo, kTabHi, w), a_lo, acc);
-    acc = dot4(prmt(kTabLo, kTabHi, w >> 16), a_hi, acc);
-    int neg = dot4(prmt(kTabLo, kTabHi, n), a_lo, 0);
-    neg = dot4(prmt(kTabLo, kTabHi, n >> 16), a_hi, neg);
-    return acc - neg;
-}
 
 template <int M, int R, int KITER, bool DUMP>
 __global__ void __launch_bounds__(kThreads)

@@ -246,3 +246,41 @@ def test_stream_several_tokens_delivers_to_host(rt):
     for i, L in enumerate(layers):
         q = O.quant_act(L["x"])
         assert O.rel_err(host[i, :, :rows], O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"]) < REL
+
+
+@pytest.mark.parametrize("rows,nlayers", [(1000, 4), (17408, 2)])
+def test_nvfp4_stream_matches_per_layer_and_oracle(rt, rows, nlayers):
+    """nvfp4_decode_stream: one 2-D nvfp4_quant_act launch over all layers, then the stream kernel; same bits as
+    nvfp4_gemv<1,1> layer by layer, and within tolerance of the oracle."""
+    layers = [synth.nvfp4_layer(rows, K, 1, seed=970 + i) for i in range(nlayers)]
+    gscale = float(layers[0]["gscale"])
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"][0] for L in layers]))
+        qa, qb = b.zeros(nlayers * K // 2, np.int8), b.zeros(nlayers * K // 2, np.int8)
+        sc = b.zeros(nlayers * K // 16)
+        ys, ptrs = [], []
+        for i, L in enumerate(layers):
+            py = b.zeros(rows, np.float32, np.nan)
+            ys.append(py)
+            ptrs.append((b.put(L["wq"]), b.put(L["ws"]), x + i * K * 4, py))
+        table = rt.stream_table(ptrs, rows, K, 0)
+        status = b.zeros(1, np.int32)
+        rt.launch2d("nvfp4_quant_act", K // 16, nlayers, 64, 1, [x, qa, qb, sc, nlayers, K])   # grid y = layer
+        rt.launch("nvfp4_decode_stream", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status, qa, qb, sc, gscale])
+        got = [b.get(py, rows) for py in ys]
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        for i, (L, yv) in enumerate(zip(layers, got)):
+            q = O.nvfp4_quant_act(L["x"])
+            ref = O.nvfp4_gemv(L["wq"], L["ws"], q["q"], q["scale"], gscale)["y"][0]
+            assert O.rel_err(yv, ref) < REL
+            py2 = b.zeros(rows, np.float32, np.nan)
+            rt.launch("nvfp4_gemv<1,1>", -(-rows // 4), 256, [ptrs[i][0], ptrs[i][1], qa + i * K // 2, qb + i * K // 2,
+                                                             sc + i * (K // 16) * 4, py2, rows, K, gscale])
+            assert np.array_equal(b.get(py2, rows).view(np.uint32), yv.view(np.uint32))
+        # a table whose scale buffers are too short for NVFP4 (rows * K/16 bytes) is refused
+        short = b.zeros(rows * (K // 128) * 2 // 4 + 4, np.float32)
+        t2 = rt.stream_table([(ptrs[0][0], short, ptrs[0][2], ys[0])], rows, K, 0)
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("nvfp4_decode_stream", 1, 1, [t2, 1, rows, K, 0, 0, 0, status, qa, qb, sc, gscale])
+        rt.free(t2)
+        rt.free(table)
