@@ -1,4 +1,5 @@
-// w4a8_decode_stream / w4a4_decode_stream / w4a8_decode_stream_m: one launch for the GEMVs of a whole stack of independent W4A8
+// w4a8_decode_stream / w4a4_decode_stream / w4a8_decode_stream_m / nvfp4_decode_stream: one launch for the
+// GEMVs of a whole stack of independent W4A8 (W4A4, NVFP4)
 // decode layers (M = 1), software-pipelined across layers so that HBM never idles at a
 // layer boundary.  The activation codes of all layers come from one 2-D launch of the
 // ordinary quant_act kernel (grid y = layer) that precedes it.
