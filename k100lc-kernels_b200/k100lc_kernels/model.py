@@ -275,9 +275,8 @@ class NVFP4Linear:
         qa = self.ws.buffer(self.tag + ".qa", 4 * half)
         qb = self.ws.buffer(self.tag + ".qb", 4 * half)
         sc = self.ws.buffer(self.tag + ".sc", 4 * nb4)
-        for r in range(m):
-            self.rt.launch("nvfp4_quant_act", k // 16, 64,
-                           [int(x_dev) + r * k * 4, qa + r * half, qb + r * half, sc + r * nb4, 1, k])
+        # one 2-D launch, grid y = token row
+        self.rt.launch2d("nvfp4_quant_act", k // 16, m, 64, 1, [int(x_dev), qa, qb, sc, m, k])
         self.rt.launch(f"nvfp4_gemv<{m},1>", cdiv(self.n, 4), 256,
                        [self.wq, self.wsb, qa, qb, sc, y, self.n, k, self.gscale])
 
