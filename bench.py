@@ -603,7 +603,7 @@ def run_ours(args) -> int:
     achieved = bytes_per_launch / us_kernel / 1e3             # GB/s of one GPU's kernel
     line = None
     if rank == 0:
-        paths = path_timings(rt, st, 5) if args.paths else None
+        paths = path_timings(rt, st, 5) if (args.paths and world == 1) else None   # single-GPU diagnostics
         gemm = gemm_timings(rt, st) if (args.paths and world == 1) else None
         cpu = cpu_baseline(args.cpu_layers) if (world == 1 and args.cpu_layers > 0) else None
         line = {
