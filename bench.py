@@ -341,7 +341,7 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
             rt.free(ptr)
     # W4A16: compressed-tensors bytes (offset-binary nibbles, bf16 group scales), fp32 activations
     from k100lc_kernels import DotLinear, Workspace
-    nd = min(nl, 8)
+    nd = min(nl, 16)
     bf16_bits = lambda a: (a.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
     with Workspace(rt) as dws:
         dots = [DotLinear(rt, rows, K, "int4", rng.integers(0, 256, size=(rows, K // 2), dtype=np.uint8),
@@ -354,6 +354,21 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
         rt.graph_free(g)
         out["w4a16_m1"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
+        # the same layers through the W4A16 stream kernel (activation split + stream, two launches)
+        tab16 = rt.stream_table([(d.w, d.tables[0], st.x + i * K * 4, st.y + i * N * 4) for i, d in enumerate(dots)], rows, K, 0)
+        st16 = rt.alloc(4)
+        rt.memset(st16, 0, 4)
+        rt.graph_begin()
+        rt.launch("w4a16_decode_stream", 1, 1, [tab16, nd, rows, K, 0, 0, 0, st16])
+        g = rt.graph_end()
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nd
+        rt.graph_free(g)
+        if int(rt.download(st16, 1, np.int32)[0]) != 0:
+            raise RuntimeError("a bounded wait ran out in the W4A16 stream kernel")
+        out["w4a16_m1_stream"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1),
+                                  "note": f"{nd} layers per launch"}
+        rt.free(tab16)
+        rt.free(st16)
     # the same layers through the multi-layer stream kernels (two launches for all nl layers)
     table = rt.stream_table([(st.wq_l(l), st.ws_l(l), st.x + l * K * 4, st.y + l * N * 4) for l in range(nl)], rows, K, 0)
     status = rt.alloc(4)

@@ -1,5 +1,5 @@
-// w4a8_decode_stream / w4a4_decode_stream / w4a8_decode_stream_m / nvfp4_decode_stream: one launch for the
-// GEMVs of a whole stack of independent W4A8 (W4A4, NVFP4)
+// w4a8_decode_stream / w4a4_decode_stream / w4a8_decode_stream_m / nvfp4_decode_stream / w4a16_decode_stream:
+// one launch for the GEMVs of a whole stack of independent W4A8 (W4A4, NVFP4, W4A16)
 // decode layers (M = 1), software-pipelined across layers so that HBM never idles at a
 // layer boundary.  The activation codes of all layers come from one 2-D launch of the
 // ordinary quant_act kernel (grid y = layer) that precedes it.
@@ -1113,6 +1113,275 @@ int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
+// ------------------------------------------------------------------------------------
+// W4A16 (compressed-tensors INT4: offset-binary codes, bf16 scale per 128 weights, fp32 activations;
+// reference tools/gen_int4_dot.py:88-147): the ring with the tensor-core arithmetic of int4_dot_k.
+// The fp32 activations of every layer are split once, by a small kernel in front, into three bf16
+// terms laid out as the B fragments of mma.sync m16n8k16 (30 720 bytes per layer); the code tile of
+// a layer is that fragment array.  8 consumer warps take 5 of the 40 blocks each: two codes per PRMT
+// into 0x43xx halves (128 + code), one packed subtract of 136, eight MMAs per block; columns 0..2
+// of the accumulator are the three terms, their sum times the block's bf16 scale is the block's
+// contribution, and the per-warp sums meet in the shared tile as in the int8 kernel.
+__global__ void __launch_bounds__(256)
+w4a16_split_layers_kernel(const StreamLayer* __restrict__ layers, uint32_t* __restrict__ out, uint32_t nbpr) {
+    pdl_wait();
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < nbpr * 192) {
+        const uint32_t e = idx & 15, t = (idx >> 4) & 3, term = (idx >> 6) % 3, b = idx / 192;
+        const uint32_t q = e >> 2, h = (e >> 1) & 1, i = e & 1;
+        const float* xs = layers[blockIdx.y].x + (size_t)b * 128 + t * 32 + 8 * q + 4 * i + h;
+        out[(size_t)blockIdx.y * nbpr * 192 + idx] = bf16_term(xs[0], (int)term) | (bf16_term(xs[2], (int)term) << 16);
+    }
+}
+
+struct W4a16StreamParams {
+    StreamParams s;                    // layers[].wq offset-binary codes, layers[].ws bf16 scales [rows][K/128]
+    const uint32_t* frags;             // [nlayers][40 * 192] B fragments of the activations
+};
+
+template <int STAGES>
+__global__ void __launch_bounds__(10 * 32, 1)
+w4a16_stream_kernel(const W4a16StreamParams pp) {
+    const StreamParams& p = pp.s;
+    constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
+    constexpr int ROWB = K / 2, SCB = NG * 2;
+    constexpr int STAGE_W = ROWS * ROWB, STAGE = STAGE_W + ROWS * SCB;
+    constexpr int ACT = NG * 192 * 4;                    // fragment array of one layer
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + STAGES;
+    uint64_t* act_ready = empty + STAGES;
+    uint64_t* act_free = act_ready + 2;
+    uint64_t* red_full = act_free + 2;
+    uint64_t* red_free = red_full + 2;
+    uint64_t* ydone = red_free + 2;
+    uint64_t* yfree = ydone + 2;
+    uint8_t* ring = smem + 256;
+    uint8_t* act = ring + (size_t)STAGES * STAGE;
+    float* red = reinterpret_cast<float*>(act + 2 * ACT);             // [2][CW][ROWS]
+    float* ytile = red + 2 * CW * ROWS;                               // [2][kOutCap]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CW);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&act_ready[b], 1);
+            mbar_init(&act_free[b], CW);
+            mbar_init(&red_full[b], CW);
+            mbar_init(&red_free[b], 1);
+            mbar_init(&ydone[b], CW);
+            mbar_init(&yfree[b], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();
+
+    const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const int nst = (r1 - r0 + ROWS - 1) / ROWS;
+    const bool tiled = (r1 - r0) <= kOutCap;
+
+    if (warp == CW) {
+        if (lane == 0) {                                   // producer
+            auto copy_frags = [&](int l) -> bool {
+                const int b = l & 1;
+                if (l >= 2 && !mbar_wait(&act_free[b], ((l >> 1) & 1) ^ 1, p.status, 4)) return false;
+                mbar_expect_tx(&act_ready[b], ACT);
+                bulk_g2s(act + (size_t)b * ACT, pp.frags + (size_t)l * (NG * 192), ACT, &act_ready[b]);
+                return true;
+            };
+            int c = 0;
+            const uint8_t* wq = p.layers[0].wq;
+            const uint8_t* ws = p.layers[0].ws;
+            if (!copy_frags(0)) return;
+            for (int l = 0; l < p.nlayers; l++) {
+                const int ln = min(l + 1, p.nlayers - 1);
+                const uint8_t* wq_n = p.layers[ln].wq;
+                const uint8_t* ws_n = p.layers[ln].ws;
+                for (int j = 0; j < nst; j++, c++) {
+                    const int s = c % STAGES;
+                    if (c >= STAGES && !mbar_wait(&empty[s], ((c / STAGES) & 1) ^ 1, p.status, 1)) return;
+                    const int row = r0 + j * ROWS;
+                    const int nr = min(ROWS, r1 - row);
+                    uint8_t* dst = ring + (size_t)s * STAGE;
+                    mbar_expect_tx(&full[s], (uint32_t)(nr * (ROWB + SCB)));
+                    bulk_g2s(dst, wq + (size_t)row * ROWB, (uint32_t)(nr * ROWB), &full[s]);
+                    bulk_g2s(dst + STAGE_W, ws + (size_t)row * SCB, (uint32_t)(nr * SCB), &full[s]);
+                    if (j == 0 && l + 1 < p.nlayers && !copy_frags(l + 1)) return;
+                }
+                wq = wq_n;
+                ws = ws_n;
+            }
+        }
+        return;
+    }
+
+    if (warp == CW + 1) {                                    // writer
+        if (!tiled) return;
+        for (int l = 0; l < p.nlayers; l++) {
+            if (!mbar_wait(&ydone[l & 1], (l >> 1) & 1, p.status, 8)) return;
+            write_out(p, ytile + (l & 1) * kOutCap, p.layers[l].y + p.row_base + r0, r1 - r0, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&yfree[l & 1]);
+        }
+        if (p.npeers) __threadfence_system();
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    int c = 0;
+    for (int l = 0; l < p.nlayers; l++) {
+        const uint32_t* ft = reinterpret_cast<const uint32_t*>(act + (size_t)(l & 1) * ACT);
+        float* yt = ytile + (l & 1) * kOutCap;
+        if (tiled && l >= 2 && !mbar_wait(&yfree[l & 1], ((l >> 1) & 1) ^ 1, p.status, 7)) return;
+        if (!mbar_wait(&act_ready[l & 1], (l >> 1) & 1, p.status, 2)) return;
+        uint4 bf[GPW][4];                                  // B fragments of this warp's blocks: {b0,b1 of (q,0), b0,b1 of (q,1)}
+#pragma unroll
+        for (int j = 0; j < GPW; j++) {
+            const int b = j * CW + warp;
+            const uint4* fp = reinterpret_cast<const uint4*>(ft + ((size_t)(b * 3 + (g < 3 ? g : 0)) * 4 + t) * 16);
+#pragma unroll
+            for (int q = 0; q < 4; q++) bf[j][q] = g < 3 ? fp[q] : make_uint4(0, 0, 0, 0);
+        }
+        float* y = p.layers[l].y + p.row_base;
+
+        for (int jst = 0; jst < nst; jst++, c++) {
+            const int s = c % STAGES;
+            if (!mbar_wait(&full[s], (c / STAGES) & 1, p.status, 3)) return;
+            const uint8_t* st = ring + (size_t)s * STAGE;
+            uint4 xa[GPW], xb[GPW];
+            float swa[GPW], swb[GPW];
+#pragma unroll
+            for (int j = 0; j < GPW; j++) {
+                const int b = j * CW + warp;
+                xa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * ROWB + b * 64 + t * 16);
+                xb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * ROWB + b * 64 + t * 16);
+                swa[j] = __uint_as_float((uint32_t)*reinterpret_cast<const unsigned short*>(st + STAGE_W + g * SCB + b * 2) << 16);
+                swb[j] = __uint_as_float((uint32_t)*reinterpret_cast<const unsigned short*>(st + STAGE_W + (g + 8) * SCB + b * 2) << 16);
+            }
+            float fa = 0.f, fb = 0.f;
+#pragma unroll
+            for (int j = 0; j < GPW; j++) {
+                const uint32_t wav[4] = {xa[j].x, xa[j].y, xa[j].z, xa[j].w}, wbv[4] = {xb[j].x, xb[j].y, xb[j].z, xb[j].w};
+                float cc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const uint32_t la = wav[q] & 0x0F0F0F0Fu, ha = (wav[q] >> 4) & 0x0F0F0F0Fu;
+                    const uint32_t lb = wbv[q] & 0x0F0F0F0Fu, hb = (wbv[q] >> 4) & 0x0F0F0F0Fu;
+                    const uint32_t m = 0x43434343u;
+                    mma_bf16(cc, bf16x2_sub136(prmt(la, m, 0x5140u)), bf16x2_sub136(prmt(lb, m, 0x5140u)),
+                             bf16x2_sub136(prmt(la, m, 0x5342u)), bf16x2_sub136(prmt(lb, m, 0x5342u)), bf[j][q].x, bf[j][q].y);
+                    mma_bf16(cc, bf16x2_sub136(prmt(ha, m, 0x5140u)), bf16x2_sub136(prmt(hb, m, 0x5140u)),
+                             bf16x2_sub136(prmt(ha, m, 0x5342u)), bf16x2_sub136(prmt(hb, m, 0x5342u)), bf[j][q].z, bf[j][q].w);
+                }
+                // columns 0, 1 (lane t = 0) and 2 (lane t = 1) hold the three terms: smallest first
+                const float va = __shfl_down_sync(0xffffffffu, cc[0], 1), vb = __shfl_down_sync(0xffffffffu, cc[2], 1);
+                fa += swa[j] * ((va + cc[1]) + cc[0]);
+                fb += swb[j] * ((vb + cc[3]) + cc[2]);
+            }
+            consumed(fa + fb);                              // release only after the loaded data has been used
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&empty[s]);
+                if (jst == 0) mbar_arrive(&act_free[l & 1]);
+            }
+            const int rb = c & 1;
+            if (c >= 2 && !mbar_wait(&red_free[rb], ((c >> 1) & 1) ^ 1, p.status, 5)) return;
+            if (t == 0) {
+                red[(rb * CW + warp) * ROWS + g] = fa;
+                red[(rb * CW + warp) * ROWS + g + 8] = fb;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_full[rb]);
+            if (warp == (c % CW)) {
+                if (!mbar_wait(&red_full[rb], (c >> 1) & 1, p.status, 6)) return;
+                const int row = r0 + jst * ROWS + lane;
+                float acc = 0.f;
+                if (lane < ROWS) {
+                    const float* pr = red + rb * CW * ROWS + lane;
+                    acc = ((pr[0 * ROWS] + pr[4 * ROWS]) + (pr[2 * ROWS] + pr[6 * ROWS])) +
+                          ((pr[1 * ROWS] + pr[5 * ROWS]) + (pr[3 * ROWS] + pr[7 * ROWS]));
+                }
+                consumed(acc);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_free[rb]);
+                if (lane < ROWS && row < r1) {
+                    if (tiled) {
+                        yt[row - r0] = acc;
+                    } else {
+                        y[row] = acc;
+                        for (int q = 0; q < p.npeers; q++)
+                            *reinterpret_cast<float*>(reinterpret_cast<char*>(y + row) + p.peer_delta[q]) = acc;
+                    }
+                }
+            }
+        }
+        if (tiled) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ydone[l & 1]);
+        }
+    }
+    if (p.npeers) __threadfence_system();
+}
+
+// w4a16_decode_stream(layers, nlayers, rows, K, row_base, npeers, peer_delta, status): the table's x entries
+// (fp32 activations [K] per layer) are read here — fm_stream_table must have seen a valid x for every layer —,
+// wq are compressed-tensors codes, ws bf16 scales.  Launches the split kernel (grid y = layer) into the engine
+// workspace (30 720 bytes per layer), then the stream kernel.
+int launch_w4a16_stream(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = "w4a16_decode_stream";
+    W4a16StreamParams pp = {};
+    StreamParams& p = pp.s;
+    p.layers = arg_ptr<const StreamLayer>(a[0]);
+    p.nlayers = arg_i32(a[1]);
+    p.rows = arg_i32(a[2]);
+    p.K = arg_i32(a[3]);
+    p.row_base = arg_i32(a[4]);
+    p.npeers = arg_i32(a[5]);
+    p.peer_delta = arg_ptr<const long long>(a[6]);
+    p.status = arg_ptr<int>(a[7]);
+    FM_REQUIRE(p.K == 5120, kn, "K=%d: the fused stream is built for K = 5120 only; launch the per-layer kernels", p.K);
+    FM_REQUIRE(p.nlayers >= 0 && p.rows > 0 && p.row_base >= 0 && p.npeers >= 0 && p.npeers <= 8, kn,
+               "bad nlayers/rows/row_base/npeers");
+    if (p.nlayers == 0) return FM_OK;
+    FM_REQUIRE(aligned(p.layers, 8) && aligned(p.status, 4), kn, "misaligned layer table or status");
+    FM_RANGE(p.layers, (size_t)p.nlayers * sizeof(StreamLayer), kn, "layers");
+    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, p.row_base, p.peer_delta, p.npeers, false, 0, true), kn,
+               "the layer table at %p was not filled by fm_stream_table for nlayers=%d rows=%d K=%d row_base=%d (or was "
+               "overwritten since), an x entry is missing, or the peer offsets do not come from fm_stream_peers for its "
+               "outputs", (const void*)p.layers, p.nlayers, p.rows, p.K, p.row_base);
+    FM_RANGE(p.status, 4, kn, "status");
+    if (p.npeers) FM_RANGE(p.peer_delta, (size_t)p.npeers * 8, kn, "peer_delta");
+    constexpr int NG = 40;
+    uint32_t* frags = static_cast<uint32_t*>(engine_scratch((size_t)p.nlayers * NG * 192 * 4));
+    FM_REQUIRE(frags != nullptr, kn, "the engine workspace cannot hold %d x 30720 bytes here (FM_SCRATCH_MB, or a first use "
+               "inside a graph capture)", p.nlayers);
+    pp.frags = frags;
+    cudaError_t e = launch_kernel(w4a16_split_layers_kernel, dim3((NG * 192 + 255) / 256, p.nlayers), dim3(256), 0, c.stream,
+                                  pdl_enabled(), p.layers, frags, (uint32_t)NG);
+    if (e != cudaSuccess) return cuda_fail(kn, e);
+    after_launch(kn);
+    constexpr int STAGES = 3, K = 5120;
+    constexpr size_t smem = 256 + (size_t)STAGES * 16 * (K / 2 + 80) + 2 * (NG * 192 * 4) + 2 * 8 * 16 * 4 + 2 * kOutCap * 4;
+    static_assert(smem <= 227 * 1024, "shared memory");
+    auto kern = w4a16_stream_kernel<STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        configured = true;
+    }
+    int grid = c.sm_count;
+    if (grid > p.rows) grid = p.rows;
+    e = launch_kernel(kern, dim3(grid), dim3(10 * 32), smem, c.stream, pdl_enabled(), pp);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
 // w4a8_decode_stream_m(layers, nlayers, rows, K, row_base, npeers, peer_delta, status, ae, ao, asc, asu, M, ystride):
 // M = 2..4 tokens per layer.  The code arrays hold [nlayers * M] tokens (one 2-D quant_act launch with grid
 // y = nlayers * M over x[nlayers][M][K]); y of a layer is token-major, y[token * ystride + row_base + row].  The
@@ -1170,6 +1439,7 @@ const KernelEntry kStream[] = {
     {"w4a4_decode_stream", 10, launch_w4_stream<true>, "piiiiipppp"},
     {"w4a8_decode_stream_m", 14, launch_w4a8_stream_m, "piiiiippppppii"},
     {"nvfp4_decode_stream", 12, launch_nvfp4_stream, "piiiiipppppf"},
+    {"w4a16_decode_stream", 8, launch_w4a16_stream, "piiiiipp"},
 };
 
 }  // namespace

@@ -1,5 +1,6 @@
 // Small device-side building blocks shared by the kernel files (sm_100a).
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -75,6 +76,32 @@ __device__ __forceinline__ int dot8_e2m1(uint32_t w, uint32_t a_lo, uint32_t a_h
     neg = dot4(prmt(kTabLo, kTabHi, n >> 16), a_hi, neg);
     return acc - neg;
 }
+
+// ---- W4A16 on the tensor cores: offset-binary int4 codes as bf16 pairs, fp32 activations as three bf16 terms
+__device__ __forceinline__ uint32_t bf16x2_sub136(uint32_t v) {
+    uint32_t d;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(v), "r"(0x43084308u));     // 136.0 twice
+    return d;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// term `which` (0, 1, 2) of the three-way bf16 split of x, as the upper 16 bits of a float
+__device__ __forceinline__ uint32_t bf16_term(float x, int which) {
+    float r = x;
+    uint32_t t = 0;
+    for (int i = 0; i <= which; i++) {
+        t = __float_as_uint(__bfloat162float(__float2bfloat16_rn(r))) >> 16;
+        r -= __uint_as_float(t << 16);
+    }
+    return t;
+}
+
+// A CTA has one warp per block index of a group of eight adjacent blocks (512 contiguous bytes of
+// every row) and walks 16-row units; the loads of the next two units are in flight while the
+// current two are multiplied (HBM latency under load is several microseconds — a warp that
+// loads, waits and then computes leaves the memory system idle half of the time).
 
 // Programmatic dependent launch: wait until the preceding kernel on the stream
 // has completed and its writes are visible / allow the next kernel to start.

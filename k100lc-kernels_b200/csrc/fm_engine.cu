@@ -54,7 +54,7 @@ struct Engine {
     std::vector<KernelEntry> kernels;
     std::unordered_map<std::string, int> by_name;
     std::map<uintptr_t, size_t> allocs;          // base -> bytes
-    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; size_t ws_avail; };
+    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; size_t ws_avail; bool x_all; };
     std::map<uintptr_t, Table> tables;           // validated stream layer tables
     struct Peers { int npeers; uintptr_t lo, hi; };
     std::map<uintptr_t, Peers> peers;            // validated peer-offset arrays (device address -> window)
@@ -322,7 +322,7 @@ void* engine_scratch(size_t bytes) {
 }
 
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
-                     int npeers, bool whole_y, size_t ws_bytes) {
+                     int npeers, bool whole_y, size_t ws_bytes, bool need_x) {
     Engine& e = E();
     if (!e.check_bounds) return true;
     auto it = e.tables.find(reinterpret_cast<uintptr_t>(table));
@@ -330,6 +330,7 @@ bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_ba
     const Engine::Table& t = it->second;
     if (!(t.nlayers >= nlayers && t.rows == rows && t.K == K && t.row_base == row_base)) return false;
     if (ws_bytes > t.ws_avail) return false;
+    if (need_x && !t.x_all) return false;
     if (npeers == 0) return true;
     // every y of the table must lie inside the window the peer offsets were validated for
     auto ip = e.peers.find(reinterpret_cast<uintptr_t>(peer_delta));
@@ -608,12 +609,13 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
                             ((size_t)row_base + rows) * 4};
     uintptr_t y_lo = ~(uintptr_t)0, y_hi = 0, y_ptr_lo = ~(uintptr_t)0;
     size_t ws_avail = ~(size_t)0;                  // fewest bytes between a ws pointer and the end of its allocation
+    bool x_all = true;                             // every layer has a (validated) x
     const size_t align[4] = {16, 16, 16, 4};
     const char* what[4] = {"wq", "ws", "x", "y"};
     for (int l = 0; l < nlayers; l++)
         for (int j = 0; j < 4; j++) {
             const void* ptr = reinterpret_cast<const void*>(static_cast<uintptr_t>(host_layers[4 * l + j]));
-            if (j == 2 && ptr == nullptr) continue;      // x is informational: the kernel reads the codes
+            if (j == 2 && ptr == nullptr) { x_all = false; continue; }   // x is optional: most kernels read the codes
             if (!range_ok(ptr, need[j]) || !aligned(ptr, align[j])) {
                 set_errorf("fm_stream_table: layer %d: %s (%zu bytes at %p) is misaligned or outside its allocation",
                            l, what[j], need[j], ptr);
@@ -639,7 +641,7 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
         }
     if (copy_sync(dev_table, host_layers, bytes, cudaMemcpyHostToDevice, "fm_stream_table") != 0) return -1;
     touch(dev_table, bytes);
-    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo, ws_avail};
+    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo, ws_avail, x_all};
     return 0;
 }
 

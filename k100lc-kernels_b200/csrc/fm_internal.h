@@ -41,9 +41,9 @@ void* engine_scratch(size_t bytes);
 // (`whole_y`: the kernel writes below row_base too — the multi-token layout — so the peer window must reach
 // down to the lowest y pointer of the table)
 // (`ws_bytes`: a kernel whose scale rows are longer than rows*(K/128)*2 bytes — NVFP4 — asks for that many
-// bytes behind every ws pointer of the table)
+// bytes behind every ws pointer of the table; `need_x`: the kernel reads the x entries, none may be null)
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
-                     int npeers, bool whole_y = false, size_t ws_bytes = 0);
+                     int npeers, bool whole_y = false, size_t ws_bytes = 0, bool need_x = false);
 
 // Registries of the kernel files -------------------------------------------
 const KernelEntry* quant_kernels(int* n);

@@ -192,30 +192,6 @@ int4_dot_kernel(const DotParams p) {
 // a block for rows g and g + 8 (one 16-byte load each) and converts nibbles to bf16 two at a time:
 // PRMT drops two codes into the low bytes of two 0x43xx halves (128 + code), one packed
 // subtract of 136 gives code - 8.  6 instructions per 8 weights instead of 19.
-__device__ __forceinline__ uint32_t bf16x2_sub136(uint32_t v) {
-    uint32_t d;
-    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(v), "r"(0x43084308u));     // 136.0 twice
-    return d;
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// term `which` (0, 1, 2) of the three-way bf16 split of x, as the upper 16 bits of a float
-__device__ __forceinline__ uint32_t bf16_term(float x, int which) {
-    float r = x;
-    uint32_t t = 0;
-    for (int i = 0; i <= which; i++) {
-        t = __float_as_uint(__bfloat162float(__float2bfloat16_rn(r))) >> 16;
-        r -= __uint_as_float(t << 16);
-    }
-    return t;
-}
-
-// A CTA has one warp per block index of a group of eight adjacent blocks (512 contiguous bytes of
-// every row) and walks 16-row units; the loads of the next two units are in flight while the
-// current two are multiplied (HBM latency under load is several microseconds — a warp that
-// loads, waits and then computes leaves the memory system idle half of the time).
 constexpr int kDotWarps = 8;
 
 // B fragments of int4_dot_mma_kernel, computed once per launch instead of once per warp:

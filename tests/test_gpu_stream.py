@@ -284,3 +284,29 @@ def test_nvfp4_stream_matches_per_layer_and_oracle(rt, rows, nlayers):
             rt.launch("nvfp4_decode_stream", 1, 1, [t2, 1, rows, K, 0, 0, 0, status, qa, qb, sc, gscale])
         rt.free(t2)
         rt.free(table)
+
+
+@pytest.mark.parametrize("rows,nlayers", [(1000, 4), (17408, 2)])
+def test_w4a16_stream_matches_oracle(rt, rows, nlayers):
+    """w4a16_decode_stream: compressed-tensors INT4 layers with fp32 activations through the ring; the
+    activations are read from the table's x entries and split on the device."""
+    layers = [synth.w4a16_layer(rows, K, seed=990 + i) for i in range(nlayers)]
+    with Bufs(rt) as b:
+        ys, ptrs = [], []
+        for L in layers:
+            py = b.zeros(rows, np.float32, np.nan)
+            ys.append(py)
+            ptrs.append((b.put(L["packed"]), b.put(L["scale_bf16"]), b.put(L["x"]), py))
+        table = rt.stream_table(ptrs, rows, K, 0)
+        status = b.zeros(1, np.int32)
+        rt.launch("w4a16_decode_stream", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status])
+        got = [b.get(py, rows) for py in ys]
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        # a table without x entries is refused by this kernel
+        t2 = rt.stream_table([(w, s, 0, y) for (w, s, _x, y) in ptrs], rows, K, 0)
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("w4a16_decode_stream", 1, 1, [t2, nlayers, rows, K, 0, 0, 0, status])
+        rt.free(t2)
+        rt.free(table)
+    for L, yv in zip(layers, got):
+        assert O.rel_err(yv, O.w4a16_gemv(L["packed"], L["scale_bf16"], L["x"])[0]) < REL
