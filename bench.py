@@ -66,7 +66,7 @@ def peaks() -> dict:
     if p.is_file():
         d = json.loads(p.read_text())
         return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured (MEASURED_PEAKS.json)"}
-    return {"hbm_gbs": 6650.0, "source": "fallback (6.65 TB/s, earlier measurement on this pool)"}
+    return {"hbm_gbs": 6650.0, "source": "fallback (6.65 TB/s, no MEASURED_PEAKS.json beside bench.py)"}
 
 
 class ClockSampler:
@@ -465,14 +465,26 @@ def gemm_timings(rt, st: "Stream", reps: int = 5) -> dict:
                      "gemm_tops": round(ops / ms_g / 1e9, 1),
                      "frac_of_int8_peak": round(ops / ms_g / 1e9 / pk_int8, 4)}
     out["int8_peak_tops_assumed"] = pk_int8
-    # tcgen05.mma.kind::i8 M128 N128 K32 issued back to back from shared memory completes one MMA per 64.2
-    # clocks on these B200s (8172 MAC per clock per SM, measured once with a stand-alone loop)
-    issue_tops = 2 * 8172.0 * rt.device_attr("sm_count") * rt.device_attr("clock_khz") * 1e3 / 1e12
-    out["int8_mma_issue_rate_tops"] = round(issue_tops, 1)
+    # the tensor cores' own int8 rate, measured here: `mma_i8_peak` issues tcgen05.mma.kind::i8 (M128 N128 K32, the
+    # GEMM's shape) back to back from shared memory on every SM; ops / device time of the launch
+    iters = 8000
+    cyc = rt.alloc(8 * rt.device_attr("sm_count"))
+    rt.graph_begin()
+    rt.launch("mma_i8_peak", 1, 128, [cyc, iters])
+    g = rt.graph_end()
+    ms_pk = time_graph(rt, g, 5, 3, lambda: None)
+    rt.graph_free(g)
+    sms = rt.device_attr("sm_count")
+    issue_tops = 2.0 * 128 * 128 * 32 * iters * sms / ms_pk / 1e9
+    cycles = rt.download(cyc, sms, np.int64)
+    rt.free(cyc)
+    out["int8_mma_peak_measured"] = {"tops": round(issue_tops, 1), "clocks_per_mma": round(float(np.median(cycles)) / iters, 2),
+                                     "mac_per_clock_per_sm": round(128 * 128 * 32 / (float(np.median(cycles)) / iters), 1),
+                                     "how": f"mma_i8_peak: {iters} tcgen05.mma.kind::i8 M128 N128 K32 per SM, operands in shared memory"}
     for name in ("w4a4", "w4a8"):
-        out[name]["frac_of_mma_issue_rate"] = round(out[name]["gemm_tops"] / issue_tops, 4)
-    out["note"] = ("no int8 peak is measured on this pool: frac_of_int8_peak uses 2 x the measured dense bf16 figure, "
-                   "frac_of_mma_issue_rate the tensor core's own int8 rate at the maximum SM clock")
+        out[name]["frac_of_measured_mma_peak"] = round(out[name]["gemm_tops"] / issue_tops, 4)
+    out["note"] = ("frac_of_measured_mma_peak divides by the int8 tensor-core rate measured in this run; "
+                   "frac_of_int8_peak uses 2 x the dense bf16 figure of MEASURED_PEAKS.json")
     if rt.gemm_status() != 0:
         raise RuntimeError("a bounded wait ran out in the GEMM kernel")
     for ptr in (x, wsc, aq4, aq8, asc, c):
@@ -480,25 +492,48 @@ def gemm_timings(rt, st: "Stream", reps: int = 5) -> dict:
     return out
 
 
-def cpu_baseline(sample_layers: int) -> dict:
-    """The reference's CPU arithmetic (NumPy restatement in oracle/) on the host cores, on the
-    first `sample_layers` layers of the same stream."""
+CPU_SAMPLE_LAYERS = 4      # layers of the stream that the CPU legs time per step (0.9 s per layer on 16 cores)
+
+
+def cpu_sample(nl: int):
+    """The first `nl` layers of the stream as the oracle takes them, and one pass over them
+    (quant_act + W4A8 GEMV per layer in NumPy).  Both CPU legs — `cpu_baseline` inside the GPU arm and
+    `--impl reference` — time this same function on this same sample, so they report one number."""
     sys.path.insert(0, str(ROOT / "oracle"))
     import w4_oracle as O
     from k100lc_kernels import synth
     lay = []
-    for l in range(sample_layers):
+    for l in range(nl):
         blks = [synth.stream_layer_block(l, b) for b in range(synth.STREAM_ROW_BLOCKS)]
         lay.append((np.concatenate([b["wq"] for b in blks]).view(np.uint32), np.concatenate([b["ws"] for b in blks]),
                     synth.stream_layer_x(l)[None, :]))
+
+    def step():
+        for wq, ws, x in lay:
+            q = O.quant_act(x)
+            O.gemv_w4(wq, ws, q["q"], q["scale"], 128)
+    return step
+
+
+def time_cpu_sample(nl: int, steps: int, warmup: int) -> tuple[float, str]:
+    """seconds per step of `cpu_sample(nl)` and the description of the sample."""
+    step = cpu_sample(nl)
+    for _ in range(warmup):
+        step()
     t0 = time.perf_counter()
-    for wq, ws, x in lay:
-        q = O.quant_act(x)
-        O.gemv_w4(wq, ws, q["q"], q["scale"], 128)
-    dt = time.perf_counter() - t0
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return dt, (f"first {nl} of the 400 layers per step (quant_act + W4A8 GEMV in NumPy, all host BLAS threads); "
+                f"{steps} timed steps, {warmup} warm-up")
+
+
+def cpu_baseline(sample_layers: int) -> dict:
+    """The reference's CPU arithmetic (NumPy restatement in oracle/) on the host cores, on the
+    first `sample_layers` layers of the same stream."""
+    dt, sample = time_cpu_sample(sample_layers, 3, 1)
     return {"value": round(sample_layers * LAYER_BYTES / dt / 1e9, 4), "unit": "GB/s", "cores": os.cpu_count(),
-            "kind": "port", "seconds_per_layer": round(dt / sample_layers, 3),
-            "sample": f"first {sample_layers} of the 400 layers (quant_act + W4A8 GEMV in NumPy; BLAS uses all host threads)"}
+            "kind": "port", "seconds_per_layer": round(dt / sample_layers, 3), "sample": sample}
 
 
 def run_ours(args) -> int:
@@ -549,6 +584,15 @@ def run_ours(args) -> int:
     gpu_launches = counted[0]                       # kernels of this library inside the timed region
 
     log(f"timed region done: {ms_step:.3f} ms/step")
+    # the same graph back to back for at least a second: long enough for the board to settle at its power
+    # limit, which a 20-step region (tens of milliseconds) is not
+    sustained = None
+    if args.sustain_s > 0:
+        n_sus = max(args.steps, int(args.sustain_s * 1e3 / ms_step) + 1)
+        with ClockSampler(rt.device_attr("device")) as clocks_sus:
+            ms_sus = time_graph(rt, graph, n_sus, 3, barrier, None, clocks_sus)
+        sustained = (ms_sus, n_sus, clocks_sus.summary())
+        log(f"sustained region done: {ms_sus:.3f} ms/step over {n_sus} steps")
     # end to end through the C ABI with host buffers: x of all layers up, y of all layers back, every step
     # (fused: the kernel itself delivers this rank's rows of y to the pinned host array; per-layer
     # mode copies the gathered y back after the graph)
@@ -607,9 +651,11 @@ def run_ours(args) -> int:
     log("reducing timings over ranks")
     if dist is not None:
         import torch
-        t = torch.tensor([ms_step, ms_e2e, ms_kern], dtype=torch.float64)
+        t = torch.tensor([ms_step, ms_e2e, ms_kern, sustained[0] if sustained else 0.0], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, ms_e2e, ms_kern = (float(v) for v in t)
+        ms_step, ms_e2e, ms_kern = (float(v) for v in t[:3])
+        if sustained:
+            sustained = (float(t[3]),) + sustained[1:]
 
     total_bytes = args.layers * LAYER_BYTES         # whole job, all ranks
     pk = peaks()
@@ -652,12 +698,19 @@ def run_ours(args) -> int:
                          "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4), "peak_source": pk["source"],
                          "us_per_launch": round(us_kernel, 3), "bytes_per_launch": bytes_per_launch,
-                         # DRAM bytes of one launch, from the ncu capture of the same kernel on 24 layers
-                         # (1 103 145 000 B read + 5 141 000 B written), scaled by the layer count: every
-                         # weight byte is read once, so traffic is proportional to the layers
+                         "sustained": None if (sustained is None or not fused) else {
+                             "ms_per_token": round(sustained[0], 4), "steps": sustained[1],
+                             "achieved": round(bytes_per_launch / sustained[0] / 1e6, 1),
+                             "frac": round(bytes_per_launch / sustained[0] / 1e6 / pk["hbm_gbs"], 4),
+                             "frac_of_nominal_8000": round(bytes_per_launch / sustained[0] / 1e6 / 8000.0, 4),
+                             "clocks": sustained[2],
+                             "what": "the same graph launched back to back for at least --sustain-s seconds"},
+                         # DRAM bytes of one launch: an ncu capture of the same kernel on 24 layers read
+                         # 1 103 145 000 B and wrote 5 141 000 B; every weight byte is read once, so the traffic
+                         # of a launch is that figure scaled by its layer count
                          "traffic": int(round((1103145000 + 5141000) / 24 * bytes_per_launch / LAYER_BYTES)) if fused else None,
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 24-layer launch, scaled "
-                                           "(profiles/w4a8_decode_stream_24layers_ncu.md)" if fused else None},
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 24-layer launch of the "
+                                           "same kernel, scaled by the layer count" if fused else None},
             "cpu_baseline": cpu, "clocks": clocks.summary(), "paths_m1": paths, "prefill_gemm_m2048": gemm, "setup_seconds": round(setup_s, 1),
         }
     if line is not None:
@@ -678,31 +731,10 @@ def run_reference(args) -> int:
     if rank != 0:
         return 0
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    sys.path.insert(0, str(ROOT / "oracle"))
-    import w4_oracle as O
-    from k100lc_kernels import synth
-    nl = max(1, min(args.cpu_layers, 4))
-    lay = []
-    for l in range(nl):
-        blks = [synth.stream_layer_block(l, b) for b in range(synth.STREAM_ROW_BLOCKS)]
-        lay.append((np.concatenate([b["wq"] for b in blks]).view(np.uint32), np.concatenate([b["ws"] for b in blks]),
-                    synth.stream_layer_x(l)[None, :]))
-
-    def step():
-        for wq, ws, x in lay:
-            q = O.quant_act(x)
-            O.gemv_w4(wq, ws, q["q"], q["scale"], 128)
-
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
-    for _ in range(warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    dt = (time.perf_counter() - t0) / steps
+    nl = max(1, min(args.cpu_layers, CPU_SAMPLE_LAYERS))
+    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
+    dt, sample = time_cpu_sample(nl, steps, warmup)
     val = round(nl * LAYER_BYTES / dt / 1e9, 4)
-    sample = (f"{nl} of the 400 layers per step (quant_act + W4A8 GEMV in NumPy, all host BLAS threads); "
-              f"{steps} timed steps, {warmup} warm-up")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": round(dt * 1e3 * 400 / nl, 1), "higher_is_better": True, "scaling": "strong",
@@ -724,9 +756,11 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=400)
     ap.add_argument("--mode", default="fused", choices=["fused", "graph"],
                     help="fused: one multi-layer kernel per token; graph: 2 by-name launches per layer")
-    ap.add_argument("--cpu-layers", type=int, default=6, help="layers of the stream timed on the CPU (0 = skip)")
+    ap.add_argument("--cpu-layers", type=int, default=CPU_SAMPLE_LAYERS, help="layers of the stream timed on the CPU (0 = skip)")
     ap.add_argument("--no-paths", dest="paths", action="store_false", help="skip the per-path M=1 timings")
     ap.add_argument("--watchdog", type=int, default=600, help="give up after this many seconds")
+    ap.add_argument("--sustain-s", type=float, default=1.0,
+                    help="also time the step back to back for this many seconds (0 = skip)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     return run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -21,6 +21,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <iterator>
 #include <map>
 #include <mutex>
 #include <string>
@@ -45,7 +46,6 @@ struct Engine {
     int sm_count = 0;
     cudaStream_t stream = nullptr;
     std::string image;
-    std::string last_error;
     bool check_bounds = true;
     bool pdl = false;
     bool capturing = false;
@@ -54,10 +54,15 @@ struct Engine {
     std::vector<KernelEntry> kernels;
     std::unordered_map<std::string, int> by_name;
     std::map<uintptr_t, size_t> allocs;          // base -> bytes
-    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; size_t ws_avail; bool x_all; };
+    // A validated record names every allocation (device, imported or pinned) that its pointers lie in:
+    // freeing one of them drops the record, so a launch that still names it is rejected (-4) until
+    // fm_stream_table / fm_stream_peers is called again.
+    struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; size_t ws_avail; bool x_all;
+                   std::vector<uintptr_t> deps; };
     std::map<uintptr_t, Table> tables;           // validated stream layer tables
-    struct Peers { int npeers; uintptr_t lo, hi; };
+    struct Peers { int npeers; uintptr_t lo, hi; std::vector<uintptr_t> deps; };
     std::map<uintptr_t, Peers> peers;            // validated peer-offset arrays (device address -> window)
+    unsigned long long epoch = 0;                // bumped whenever an allocation is freed or a validated record is dropped
     std::map<uintptr_t, size_t> imported;        // peer allocations opened through CUDA IPC
     std::map<uintptr_t, size_t> pinned;          // fm_host_alloc buffers (device-addressable host memory)
     void* scratch = nullptr;                     // kernel-internal workspace (grows on demand)
@@ -65,7 +70,8 @@ struct Engine {
     std::vector<void*> retired_scratch;          // outgrown workspaces, still referenced by captured graphs
     std::vector<cudaEvent_t> events;
     std::vector<Graph> graphs;
-    std::unordered_map<uint64_t, int> plan_graphs;   // plan hash -> graph id
+    struct PlanGraph { int gid; unsigned long long epoch; std::vector<uint64_t> words; };
+    std::unordered_map<uint64_t, PlanGraph> plan_graphs;   // plan hash -> captured graph, the epoch it was checked in, its words
     // NCCL (resolved with dlopen when a communicator is first asked for)
     void* nccl_lib = nullptr;
     void* comm = nullptr;
@@ -77,10 +83,18 @@ Engine& E() {
     return e;
 }
 
+// The text of the last failure is kept per host thread: entry points that do not take the engine
+// lock (fm_w4a8_linear_static) may fail concurrently with engine calls on other threads, and a
+// caller reads the message on the thread that saw the error code.
+std::string& last_error() {
+    static thread_local std::string s;
+    return s;
+}
+
 void set_error(const char* fmt, va_list ap) {
     char buf[512];
     vsnprintf(buf, sizeof buf, fmt, ap);
-    E().last_error = buf;
+    last_error() = buf;
     if (getenv("FM_DEBUG")) fprintf(stderr, "fm_engine: %s\n", buf);
 }
 
@@ -182,13 +196,46 @@ void touch(const void* p, size_t n) {
     Engine& e = E();
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
     for (auto it = e.tables.begin(); it != e.tables.end();) {
-        if (a < it->first + it->second.bytes && it->first < a + n) it = e.tables.erase(it);
+        if (a < it->first + it->second.bytes && it->first < a + n) { it = e.tables.erase(it); e.epoch++; }
         else ++it;
     }
     for (auto it = e.peers.begin(); it != e.peers.end();) {
-        if (a < it->first + (size_t)it->second.npeers * 8 && it->first < a + n) it = e.peers.erase(it);
+        if (a < it->first + (size_t)it->second.npeers * 8 && it->first < a + n) { it = e.peers.erase(it); e.epoch++; }
         else ++it;
     }
+}
+
+// base address of the device, imported or pinned allocation that contains `a` (0 when none does)
+uintptr_t owner_of(uintptr_t a) {
+    Engine& e = E();
+    for (const auto* m : {&e.allocs, &e.pinned}) {
+        auto it = m->upper_bound(a);
+        if (it == m->begin()) continue;
+        --it;
+        if (a >= it->first && a < it->first + it->second) return it->first;
+    }
+    return 0;
+}
+
+void add_dep(std::vector<uintptr_t>& deps, uintptr_t a) {
+    const uintptr_t b = owner_of(a);
+    if (b == 0) return;
+    for (uintptr_t d : deps) if (d == b) return;
+    deps.push_back(b);
+}
+
+// The allocation at `base` is going away: every validated table or peer-offset array that points
+// into it (or lives in it) is dropped, and the epoch moves on so that cached plan graphs, which may
+// hold kernel nodes with pointers into it, are captured afresh through the checks.
+void release_dependents(uintptr_t base) {
+    Engine& e = E();
+    e.epoch++;
+    auto uses = [&](const std::vector<uintptr_t>& deps) {
+        for (uintptr_t d : deps) if (d == base) return true;
+        return false;
+    };
+    for (auto it = e.tables.begin(); it != e.tables.end();) it = uses(it->second.deps) ? e.tables.erase(it) : std::next(it);
+    for (auto it = e.peers.begin(); it != e.peers.end();) it = uses(it->second.deps) ? e.peers.erase(it) : std::next(it);
 }
 
 int do_launch(int kid, uint32_t gx, uint32_t gy, uint32_t wx, uint32_t wy, const uint64_t* argv, int nargs) {
@@ -306,9 +353,18 @@ void* engine_scratch(size_t bytes) {
     Engine& e = E();
     if (bytes <= e.scratch_bytes) return e.scratch;
     if (e.capturing) return nullptr;
-    // the old buffer is kept until the engine goes away: graphs captured earlier may hold kernel nodes
-    // that point into it
-    if (e.scratch) e.retired_scratch.push_back(e.scratch);
+    // graphs captured earlier may hold kernel nodes that point into the old buffer: while any graph is
+    // alive it is only retired (and freed with the last graph); without graphs it is freed at once
+    if (e.scratch) {
+        bool graphs_alive = false;
+        for (const Graph& g : e.graphs) graphs_alive = graphs_alive || g.exec != nullptr;
+        if (graphs_alive) {
+            e.retired_scratch.push_back(e.scratch);
+        } else {
+            cudaStreamSynchronize(e.stream);
+            cudaFree(e.scratch);
+        }
+    }
     e.scratch = nullptr;
     e.scratch_bytes = 0;
     const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
@@ -374,6 +430,7 @@ void fm_free(void* p) {
     auto it = E().allocs.find(reinterpret_cast<uintptr_t>(p));
     if (it != E().allocs.end()) {
         touch(p, it->second);
+        release_dependents(it->first);
         E().allocs.erase(it);
     }
     auto im = E().imported.find(reinterpret_cast<uintptr_t>(p));
@@ -492,11 +549,22 @@ int fm_launch_batch(const uint64_t* plan, int nrec) {
     const size_t words = plan_words(plan, nrec);
     const uint64_t h = fnv1a(plan, words) ^ ((uint64_t)nrec << 48);
     auto it = e.plan_graphs.find(h);
+    // A cached graph is replayed only while nothing it was checked against has changed: same words
+    // (a hash collision must not replay another plan), and no allocation freed or validated table
+    // dropped since the capture (the epoch).  Otherwise it is captured afresh, which runs every
+    // record through the launchers' range and table checks again.
+    if (it != e.plan_graphs.end() &&
+        (it->second.epoch != e.epoch || it->second.words.size() != words ||
+         memcmp(it->second.words.data(), plan, words * 8) != 0)) {
+        fm_graph_free(it->second.gid);
+        e.plan_graphs.erase(it);
+        it = e.plan_graphs.end();
+    }
     if (it == e.plan_graphs.end()) {
         // first sight of this exact plan: capture it (a patched plan hashes differently
         // and is captured afresh, so LaunchPlan.set_arg/set_grid are honoured)
         if (e.plan_graphs.size() >= 64) {          // bound the cache
-            for (auto& kv : e.plan_graphs) fm_graph_free(kv.second);
+            for (auto& kv : e.plan_graphs) fm_graph_free(kv.second.gid);
             e.plan_graphs.clear();
         }
         if (fm_graph_begin() != 0) return run_plan(plan, nrec);
@@ -504,16 +572,18 @@ int fm_launch_batch(const uint64_t* plan, int nrec) {
         const int gid = fm_graph_end();
         if (done != nrec || gid < 0) {
             if (gid >= 0) fm_graph_free(gid);
-            return done == nrec ? run_plan(plan, nrec) : done;   // report the failing record count
+            // nothing of the capture has run: enqueue the records in front of the rejected one for
+            // real, so that the count returned is the count enqueued (as with the reference's batch)
+            return run_plan(plan, done);
         }
-        it = e.plan_graphs.emplace(h, gid).first;
+        it = e.plan_graphs.emplace(h, Engine::PlanGraph{gid, e.epoch, std::vector<uint64_t>(plan, plan + words)}).first;
     }
-    return fm_graph_launch(it->second) == 0 ? nrec : 0;
+    return fm_graph_launch(it->second.gid) == 0 ? nrec : 0;
 }
 
 // ---- extensions -----------------------------------------------------------
 
-const char* fm_last_error(void) { return E().last_error.c_str(); }
+const char* fm_last_error(void) { return last_error().c_str(); }
 
 int fm_device_count(void) {
     int n = 0;
@@ -572,6 +642,8 @@ void fm_host_free(void* p) {
     if (!p) return;
     {
         LOCK;
+        if (E().ready) cudaStreamSynchronize(E().stream);      // a kernel in flight may still be storing into it
+        if (E().pinned.count(reinterpret_cast<uintptr_t>(p))) release_dependents(reinterpret_cast<uintptr_t>(p));
         E().pinned.erase(reinterpret_cast<uintptr_t>(p));
     }
     cudaFreeHost(p);
@@ -608,6 +680,8 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
     const size_t need[4] = {(size_t)rows * (K / 2), (size_t)rows * (K / 128) * 2, (size_t)K * 4,
                             ((size_t)row_base + rows) * 4};
     uintptr_t y_lo = ~(uintptr_t)0, y_hi = 0, y_ptr_lo = ~(uintptr_t)0;
+    std::vector<uintptr_t> deps;                   // allocations the table points into (and the one it lives in)
+    add_dep(deps, reinterpret_cast<uintptr_t>(dev_table));
     size_t ws_avail = ~(size_t)0;                  // fewest bytes between a ws pointer and the end of its allocation
     bool x_all = true;                             // every layer has a (validated) x
     const size_t align[4] = {16, 16, 16, 4};
@@ -621,6 +695,7 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
                            l, what[j], need[j], ptr);
                 return FM_EREJECT;
             }
+            add_dep(deps, static_cast<uintptr_t>(host_layers[4 * l + j]));
             if (j == 1) {
                 const uintptr_t w = static_cast<uintptr_t>(host_layers[4 * l + j]);
                 auto ia = e.allocs.upper_bound(w);
@@ -641,7 +716,7 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
         }
     if (copy_sync(dev_table, host_layers, bytes, cudaMemcpyHostToDevice, "fm_stream_table") != 0) return -1;
     touch(dev_table, bytes);
-    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo, ws_avail, x_all};
+    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo, ws_avail, x_all, deps};
     return 0;
 }
 
@@ -691,8 +766,12 @@ int fm_stream_peers(void* dev_deltas, const uint64_t* peer_bases, int npeers, co
         return FM_EREJECT;
     }
     long long delta[8];
+    std::vector<uintptr_t> deps;
+    add_dep(deps, reinterpret_cast<uintptr_t>(dev_deltas));
+    add_dep(deps, reinterpret_cast<uintptr_t>(local_base));
     for (int q = 0; q < npeers; q++) {
         const uintptr_t pb = static_cast<uintptr_t>(peer_bases[q]);
+        add_dep(deps, pb);
         bool ok = false;                             // a peer GPU's imported allocation, or a pinned host buffer
         for (const auto* m : {&e.imported, &e.pinned}) {
             auto it = m->upper_bound(pb);
@@ -710,7 +789,7 @@ int fm_stream_peers(void* dev_deltas, const uint64_t* peer_bases, int npeers, co
     if (copy_sync(dev_deltas, delta, (size_t)npeers * 8, cudaMemcpyHostToDevice, "fm_stream_peers") != 0) return -1;
     touch(dev_deltas, (size_t)npeers * 8);
     const uintptr_t lo = reinterpret_cast<uintptr_t>(local_base);
-    e.peers[reinterpret_cast<uintptr_t>(dev_deltas)] = Engine::Peers{npeers, lo, lo + (uintptr_t)span};
+    e.peers[reinterpret_cast<uintptr_t>(dev_deltas)] = Engine::Peers{npeers, lo, lo + (uintptr_t)span, deps};
     return 0;
 }
 
@@ -788,6 +867,12 @@ int fm_graph_free(int id) {
     cudaGraphExecDestroy(e.graphs[id].exec);
     cudaGraphDestroy(e.graphs[id].graph);
     e.graphs[id] = Graph();
+    bool graphs_alive = false;
+    for (const Graph& g : e.graphs) graphs_alive = graphs_alive || g.exec != nullptr;
+    if (!graphs_alive) {                       // no graph can point into an outgrown workspace any more
+        for (void* q : e.retired_scratch) cudaFree(q);
+        e.retired_scratch.clear();
+    }
     return 0;
 }
 

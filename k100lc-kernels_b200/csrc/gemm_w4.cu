@@ -74,7 +74,8 @@ struct GemmParams {
     const float* sa;        // [K/128][M]
     const float* sb;        // [K/128][N]
     float* C;               // [M][N]
-    int* dump;              // optional [M][N][K/128]
+    int* dump;              // optional [wm1-wm0][wn1-wn0][K/128]: the integers of the window rows [wm0,wm1) x columns [wn0,wn1)
+    int wm0, wm1, wn0, wn1;
     int M, N, K;
     float inv;              // 1/16 (int8 activations) or 1/256 (int4 activations widened to 16*v)
     int shift;              // log2 of the same factor, for the integer dump
@@ -480,10 +481,15 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 fma2(facc[j], facc[j + 1], f0, f1, s0, s1);
                 fma2(facc[j + 2], facc[j + 3], f2, f3, s2, s3);
                 if (DUMP) {
-                    int* d = p.dump + ((size_t)(m0 + mrow) * p.N + n0 + j) * G + g;
+                    const int mm = m0 + mrow;
+                    if (mm >= p.wm0 && mm < p.wm1) {
 #pragma unroll
-                    for (int u = 0; u < 4; u++)
-                        if (n0 + j + u < p.N) d[u * G] = (int)r[j + u] >> p.shift;
+                        for (int u = 0; u < 4; u++) {
+                            const int nn = n0 + j + u;
+                            if (nn >= p.wn0 && nn < p.wn1)
+                                p.dump[((size_t)(mm - p.wm0) * (p.wn1 - p.wn0) + (nn - p.wn0)) * G + g] = (int)r[j + u] >> p.shift;
+                        }
+                    }
                 }
             }
             tc_fence_before();
@@ -509,6 +515,67 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     if (warp == MMA_WARP) tmem_dealloc(tmem_base, NACC * BN);
     pdl_launch_dependents();
+}
+
+// mma_i8_peak: the rate at which the tensor cores complete tcgen05.mma.kind::i8 (M=128, N=128, K=32, the shape the
+// GEMM issues) when nothing else limits them — operands already in shared memory (zeros), one thread per CTA issuing
+// `iters` MMAs back to back into two alternating accumulators, one commit, one bounded wait.  The denominator of the
+// GEMM's tensor roofline, measured on the device the GEMM runs on.
+__global__ void __launch_bounds__(128, 1)
+mma_i8_peak_kernel(int iters, long long* cycles, int* status) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tbase;
+    for (int i = threadIdx.x; i < 2 * BX_BYTES / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < 32) tmem_alloc(&tbase, 2 * BN);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = instr_desc();
+        const uint64_t ad = smem_desc(smem_u32(smem)), bd = smem_desc(smem_u32(smem) + BX_BYTES);
+        const long long t0 = clock64();
+        for (int i = 0; i < iters; i++) tc_mma_i8(tbase + (i & 1) * BN, ad, bd, idesc, 1);
+        tc_commit(&bar);
+        bool ok = false;
+        for (int i = 0; i < (1 << 24) && !ok; i++) ok = mbar_try_wait(&bar, 0);
+        const long long t1 = clock64();
+        if (!ok) atomicCAS(status, 0, 9);
+        if (cycles) cycles[blockIdx.x] = t1 - t0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) tmem_dealloc(tbase, 2 * BN);
+}
+
+// mma_i8_peak(cycles, iters): one CTA per SM; cycles = device int64 [SM count] (or 0): clocks from the first issue to
+// the completion of the last MMA on each SM.  2 * 128 * 128 * 32 * iters integer operations per CTA.
+int launch_mma_peak(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = "mma_i8_peak";
+    long long* cycles = arg_ptr<long long>(a[0]);
+    const int iters = arg_i32(a[1]);
+    FM_REQUIRE(iters > 0 && iters <= (1 << 20), kn, "iters=%d must be 1..1048576", iters);
+    if (cycles) {
+        FM_REQUIRE(aligned(cycles, 8), kn, "misaligned cycle array");
+        FM_RANGE(cycles, (size_t)c.sm_count * 8, kn, "cycles");
+    }
+    constexpr size_t smem = 2 * BX_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(mma_i8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        configured = true;
+    }
+    int* status = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_gemm_status) != cudaSuccess) return cuda_fail(kn, cudaGetLastError());
+    cudaError_t e = launch_kernel(mma_i8_peak_kernel, dim3(c.sm_count), dim3(128), smem, c.stream, false, iters, cycles, status);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
 // ------------------------------------------------------------------------- host side
@@ -606,7 +673,9 @@ int check_gemm(const char* kn, const LaunchCtx& c, GemmArgs& ga, long long group
     FM_RANGE(p.C, (size_t)p.M * p.N * 4, kn, "C");
     if (dump) {
         FM_REQUIRE(aligned(p.dump, 4), kn, "misaligned accumulator dump");
-        FM_RANGE(p.dump, (size_t)p.M * p.N * G * 4, kn, "iacc");
+        FM_REQUIRE(0 <= p.wm0 && p.wm0 < p.wm1 && p.wm1 <= p.M && 0 <= p.wn0 && p.wn0 < p.wn1 && p.wn1 <= p.N, kn,
+                   "dump window rows [%d,%d) x columns [%d,%d) is empty or outside M=%d N=%d", p.wm0, p.wm1, p.wn0, p.wn1, p.M, p.N);
+        FM_RANGE(p.dump, (size_t)(p.wm1 - p.wm0) * (p.wn1 - p.wn0) * G * 4, kn, "iacc");
     }
     return FM_OK;
 }
@@ -660,13 +729,20 @@ int launch_gemm_a8(const LaunchCtx& c, const uint64_t* a) {
 }
 
 // gemm_w4a4_iacc / gemm_w4a8_iacc (aq, wq, asc, wsc, C, M, N, K, iacc): iacc int32 [M][N][K/128]
-template <bool A8>
+// gemm_w4a4_iacc_win / gemm_w4a8_iacc_win (..., iacc, m0, m1, n0, n1): the whole GEMM runs, the integers of the
+// window rows [m0,m1) x columns [n0,n1) go to iacc int32 [m1-m0][n1-n0][K/128] (the full dump of the
+// M=2048 x N=17408 shape would be 5.7 GB)
+template <bool A8, bool WIN>
 int launch_gemm_iacc(const LaunchCtx& c, const uint64_t* a) {
-    const char* kn = A8 ? "gemm_w4a8_iacc" : "gemm_w4a4_iacc";
+    const char* kn = A8 ? (WIN ? "gemm_w4a8_iacc_win" : "gemm_w4a8_iacc") : (WIN ? "gemm_w4a4_iacc_win" : "gemm_w4a4_iacc");
     GemmArgs ga = {};
     GemmParams& p = ga.p;
     fill(ga, a);
     p.dump = arg_ptr<int>(a[8]);
+    p.wm0 = WIN ? arg_i32(a[9]) : 0;
+    p.wm1 = WIN ? arg_i32(a[10]) : p.M;
+    p.wn0 = WIN ? arg_i32(a[11]) : 0;
+    p.wn1 = WIN ? arg_i32(a[12]) : p.N;
     const int rc = check_gemm<A8>(kn, c, ga, 1LL << 40, true);
     return rc ? rc : run_gemm<A8, true>(kn, c, p, ga.aq, ga.wq);
 }
@@ -675,8 +751,11 @@ const KernelEntry kGemm[] = {
     {"gemm_w4a4_flat", 10, launch_gemm_flat, "pppppiiiii"},
     {"gemm_w4a4", 8, launch_gemm_2d, "pppppiii"},
     {"gemm_w4a8", 8, launch_gemm_a8, "pppppiii"},
-    {"gemm_w4a4_iacc", 9, launch_gemm_iacc<false>, "pppppiiip"},
-    {"gemm_w4a8_iacc", 9, launch_gemm_iacc<true>, "pppppiiip"},
+    {"gemm_w4a4_iacc", 9, launch_gemm_iacc<false, false>, "pppppiiip"},
+    {"gemm_w4a8_iacc", 9, launch_gemm_iacc<true, false>, "pppppiiip"},
+    {"mma_i8_peak", 2, launch_mma_peak, "pi"},
+    {"gemm_w4a4_iacc_win", 13, launch_gemm_iacc<false, true>, "pppppiiipiiii"},
+    {"gemm_w4a8_iacc_win", 13, launch_gemm_iacc<true, true>, "pppppiiipiiii"},
 };
 
 }  // namespace

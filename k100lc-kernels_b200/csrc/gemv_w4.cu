@@ -280,7 +280,8 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
 
 // One warp = one 16-row tile x one half of K (two warps per tile, four tiles per CTA): 17408 rows are
 // only 1088 tiles, and a warp that walked all 40 groups of its tile alone left the SMs a third full.
-template <int M>
+// DUMP: also store the integer accumulators I[m][n][g] (the parity tests compare them bit for bit).
+template <int M, bool DUMP>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_w4a8_mma_kernel(const GemvW4Params p) {
     constexpr int GC = 4;                         // groups fetched per step: 2 x GC x 16 bytes in flight per lane
@@ -349,14 +350,24 @@ gemv_w4a8_mma_kernel(const GemvW4Params p) {
             if (t0 < M) {
                 const float sa = s_sc[t0 * NG + gg];
                 const int su8 = 8 * s_su[t0 * NG + gg];
-                acc[0] += (swa[j] * sa) * (float)(lo[0] + (hi[0] >> 4) - su8);
-                acc[2] += (swb[j] * sa) * (float)(lo[2] + (hi[2] >> 4) - su8);
+                const int ia = lo[0] + (hi[0] >> 4) - su8, ib = lo[2] + (hi[2] >> 4) - su8;
+                acc[0] += (swa[j] * sa) * (float)ia;
+                acc[2] += (swb[j] * sa) * (float)ib;
+                if (DUMP && live) {
+                    if (tile * 16 + g < p.rows) p.iacc[((size_t)t0 * p.N + tile * 16 + g) * NG + gg] = ia;
+                    if (tile * 16 + g + 8 < p.rows) p.iacc[((size_t)t0 * p.N + tile * 16 + g + 8) * NG + gg] = ib;
+                }
             }
             if (t1 < M) {
                 const float sa = s_sc[t1 * NG + gg];
                 const int su8 = 8 * s_su[t1 * NG + gg];
-                acc[1] += (swa[j] * sa) * (float)(lo[1] + (hi[1] >> 4) - su8);
-                acc[3] += (swb[j] * sa) * (float)(lo[3] + (hi[3] >> 4) - su8);
+                const int ia = lo[1] + (hi[1] >> 4) - su8, ib = lo[3] + (hi[3] >> 4) - su8;
+                acc[1] += (swa[j] * sa) * (float)ia;
+                acc[3] += (swb[j] * sa) * (float)ib;
+                if (DUMP && live) {
+                    if (tile * 16 + g < p.rows) p.iacc[((size_t)t1 * p.N + tile * 16 + g) * NG + gg] = ia;
+                    if (tile * 16 + g + 8 < p.rows) p.iacc[((size_t)t1 * p.N + tile * 16 + g + 8) * NG + gg] = ib;
+                }
             }
         }
     }
@@ -378,9 +389,9 @@ gemv_w4a8_mma_kernel(const GemvW4Params p) {
     pdl_launch_dependents();
 }
 
-template <int M>
+template <int M, bool DUMP>
 int run_mma(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
-    auto kern = gemv_w4a8_mma_kernel<M>;
+    auto kern = gemv_w4a8_mma_kernel<M, DUMP>;
     const size_t smem = (size_t)M * (2 * (p.K / 8) * 4 + (p.K / 128) * 8) + 16 + (kWarps / 2) * 32 * 16;
     FM_REQUIRE(smem <= 200 * 1024, kn, "K=%d needs %zu bytes of shared memory for %d tokens (limit 200 KiB)", p.K, smem, M);
     if (smem > 48 * 1024) {
@@ -423,14 +434,19 @@ int run_variant(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
 template <bool A4, int M, bool DUMP>
 int dispatch(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
     const int kiter = (p.K % 1024 == 0) ? p.K / 1024 : 0;
-    if (DUMP) return run_variant<A4, M, 1, 0, false, true>(kn, c, p);
+    if (DUMP) {
+        // the dump comes from the kernel that the by-name entry of this M runs: the tensor-core one for
+        // int8 activations and 2..4 tokens, the dp4a one otherwise
+        if (!A4 && M > 1) return run_mma<M, true>(kn, c, p);
+        return run_variant<A4, M, 1, 0, false, true>(kn, c, p);
+    }
     if (M == 1) {
         if (kiter == 5) return run_variant<A4, 1, 1, 5, true, false>(kn, c, p);
         return run_variant<A4, 1, 1, 0, false, false>(kn, c, p);
     }
     // several tokens with int8 activations: the tensor-core kernel ($FM_GEMV_CFG=1 keeps the dp4a one)
     static const int cfg = getenv("FM_GEMV_CFG") ? atoi(getenv("FM_GEMV_CFG")) : 0;
-    if (!A4 && cfg != 1) return run_mma<M>(kn, c, p);
+    if (!A4 && cfg != 1) return run_mma<M, false>(kn, c, p);
     if (kiter == 5) return run_variant<A4, M, 2, 5, false, false>(kn, c, p);
     return run_variant<A4, M, 2, 0, false, false>(kn, c, p);
 }

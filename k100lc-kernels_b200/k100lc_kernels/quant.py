@@ -28,9 +28,12 @@ def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
 
 def pack_nibbles(values: np.ndarray) -> np.ndarray:
     """``[R, K]`` integers -> ``[R, K/8]`` u32, nibble j of word w = element 8w+j (mod 16)."""
-    v = (np.asarray(values).astype(np.int64) & 0xF).astype(np.uint32)
-    r, k = v.shape
-    return np.bitwise_or.reduce(v.reshape(r, k // 8, 8) << _SHIFTS, axis=2).astype(np.uint32)
+    a = np.asarray(values)
+    r, k = a.shape
+    # bytes first (two nibbles each, low nibble = even k), then four bytes per little-endian word
+    v = (a.astype(np.uint8) if a.dtype.itemsize == 1 else (a.astype(np.int64) & 0xF).astype(np.uint8)) & np.uint8(0xF)
+    b = v[:, 0::2] | (v[:, 1::2] << np.uint8(4))
+    return np.ascontiguousarray(b).view("<u4").reshape(r, k // 8)
 
 
 def unpack_nibbles(words: np.ndarray) -> np.ndarray:

@@ -347,8 +347,8 @@ class Runtime:
         return ms
 
     def pinned(self, shape, dtype) -> np.ndarray:
-        """A NumPy array backed by page-locked host memory (never freed explicitly; it
-        lives as long as the process)."""
+        """A NumPy array backed by page-locked host memory; it lives as long as the process
+        unless it is handed to ``free_pinned``."""
         dt = np.dtype(dtype)
         n = int(np.prod(shape)) * dt.itemsize
         p = self._lib.fm_host_alloc(max(n, 1))
@@ -356,6 +356,11 @@ class Runtime:
             raise MemoryError(f"fm_host_alloc({n}) failed")
         raw = (ctypes.c_char * max(n, 1)).from_address(p)
         return np.frombuffer(raw, dtype=dt, count=int(np.prod(shape))).reshape(shape)
+
+    def free_pinned(self, arr: np.ndarray) -> None:
+        """Release a ``pinned`` array (the array must not be used afterwards).  Peer-offset arrays
+        that name it as a receiver stop being valid."""
+        self._lib.fm_host_free(ctypes.c_void_p(int(arr.ctypes.data)))
 
     def upload_async(self, ptr: int, arr: np.ndarray) -> None:
         if self._lib.fm_upload_async(ctypes.c_void_p(int(ptr)), arr.ctypes.data_as(ctypes.c_void_p),

@@ -128,3 +128,31 @@ def run_gemm_sampled(rt, L, a8):
     ref = O.gemm_w4(qa["q"][mi], L["wq"][ni], qa["scale_gf"][:, mi], L["wsc_gf"][:, ni])["c"]
     assert O.rel_err(c[np.ix_(mi, ni)], ref) < REL
     return c, None, None
+
+
+@pytest.mark.parametrize("a8", [False, True])
+def test_gemm_full_size_accumulators(rt, a8):
+    """M=2048, N=17408, K=5120 (seed 3): the int32 accumulators of every 128-group, bit for bit, on three
+    windows of the full-size run — the last row tile x last column tile, all row tiles across a column-tile
+    boundary, and all column tiles across a row-tile boundary (so every CTA's first and last tile, every
+    accumulator rotation and every ring wrap-around is sampled).  The whole GEMM runs for each window."""
+    L = synth.gemm_layer(seed=3)
+    m, n, k = L["m"], L["n"], L["k"]
+    g = k // 128
+    qa = O.quant_rows_a8(L["x"]) if a8 else O.quant_rows(L["x"])
+    windows = [(m - 128, m, n - 128, n), (0, m, n // 2 - 8, n // 2 + 8), (m // 2 - 8, m // 2 + 8, 0, n)]
+    with Bufs(rt) as b:
+        paq = b.put(_perm8(qa["q"]) if a8 else qa["words"])
+        pwq, pasc, pwsc = b.put(L["wq"]), b.put(qa["scale_gf"]), b.put(L["wsc_gf"])
+        pc = b.zeros(m * n, np.float32, np.nan)
+        for (m0, m1, n0, n1) in windows:
+            cnt = (m1 - m0) * (n1 - n0) * g
+            pi = b.zeros(cnt, np.int32, -7)
+            rt.launch("gemm_w4a8_iacc_win" if a8 else "gemm_w4a4_iacc_win", 1, 256,
+                      [paq, pwq, pasc, pwsc, pc, m, n, k, pi, m0, m1, n0, n1])
+            acc = b.get(pi, cnt, np.int32).reshape(m1 - m0, n1 - n0, g)
+            assert rt.gemm_status() == 0
+            ref = O.gemm_w4(qa["q"][m0:m1], L["wq"][n0:n1], qa["scale_gf"][:, m0:m1], L["wsc_gf"][:, n0:n1])
+            assert np.array_equal(acc, ref["acc"]), f"int32 accumulators differ in window {(m0, m1, n0, n1)}"
+            c = b.get(pc, m * n).reshape(m, n)[m0:m1, n0:n1]
+            assert O.rel_err(c, ref["c"]) < REL

@@ -186,3 +186,47 @@ def test_nvfp4_full_size(rt):
     assert np.array_equal(acc, ref["acc"])
     y2, _, _ = nvfp4_device(rt, L, L["x"], "nvfp4_gemv<1,1>")
     assert O.rel_err(y, ref["y"]) < REL and O.rel_err(y2, ref["y"]) < REL
+
+
+@pytest.mark.parametrize("m", [2, 3, 4])
+def test_w4a8_full_size_several_tokens(rt, m):
+    """17408 x 5120 at M = 2, 3, 4 (seed 1): gemv_w4a8<M,false,2> — the tensor-core kernel — with its own
+    integer accumulators (the dump entry runs the same kernel source) and y."""
+    L = synth.rt4_layer(m=m, seed=1)
+    y, acc, q = w4a8_device(rt, L["wq"], L["ws"], L["x"], dump=True)
+    ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)
+    assert np.array_equal(acc, ref["acc"])
+    y2, _, _ = w4a8_device(rt, L["wq"], L["ws"], L["x"])
+    assert O.rel_err(y, ref["y"]) < REL and O.rel_err(y2, ref["y"]) < REL
+
+
+@pytest.mark.parametrize("m,name", [(2, "gemv_w4a4<2>"), (3, "gemv_w4a4<3>"), (4, "gemv_w4a4<4>"), (4, "gemv_w4a4_r2_k"),
+                                    (3, "gemv_w4a4_r2_m3_k")])
+def test_w4a4_full_size_several_tokens(rt, m, name):
+    L = synth.rt4_layer(m=m, seed=1)
+    y, acc, q = w4a4_device(rt, L["wq"], L["ws"], L["x"], dump=True)
+    ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 32)
+    assert np.array_equal(acc, ref["acc"])
+    y2, _, _ = w4a4_device(rt, L["wq"], L["ws"], L["x"], name=name)
+    assert O.rel_err(y, ref["y"]) < REL and O.rel_err(y2, ref["y"]) < REL
+
+
+@pytest.mark.parametrize("m,bw", [(2, 1), (3, 1), (4, 1), (2, 2), (4, 2)])
+def test_nvfp4_full_size_several_tokens(rt, m, bw):
+    """17408 x 5120 at M = 2..4 (seed 2): nvfp4_gemv<M,1> and the <M,2> variants, accumulators and y."""
+    L = synth.nvfp4_layer(m=m, seed=2)
+    y, acc, q = nvfp4_device(rt, L, L["x"], None, dump=True)
+    ref = O.nvfp4_gemv(L["wq"], L["ws"], q["q"], q["scale"], L["gscale"])
+    assert np.array_equal(acc, ref["acc"])
+    y2, _, _ = nvfp4_device(rt, L, L["x"], f"nvfp4_gemv<{m},{bw}>")
+    assert O.rel_err(y, ref["y"]) < REL and O.rel_err(y2, ref["y"]) < REL
+
+
+def test_w4a8_mma_accumulators_small_and_ragged(rt):
+    """The tensor-core GEMV's own accumulator dump on ragged shapes (N not a multiple of 16, K = 128 .. 2176)."""
+    for m in (2, 3, 4):
+        for n, k in ((37, 1024), (130, 2176), (9, 128), (256, 5120)):
+            L = synth.rt4_layer(n, k, m, seed=640 + m)
+            y, acc, q = w4a8_device(rt, L["wq"], L["ws"], L["x"], dump=True)
+            ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)
+            assert np.array_equal(acc, ref["acc"]) and O.rel_err(y, ref["y"]) < REL

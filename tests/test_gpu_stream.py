@@ -310,3 +310,50 @@ def test_w4a16_stream_matches_oracle(rt, rows, nlayers):
         rt.free(table)
     for L, yv in zip(layers, got):
         assert O.rel_err(yv, O.w4a16_gemv(L["packed"], L["scale_bf16"], L["x"])[0]) < REL
+
+
+def test_freed_buffers_unvalidate_tables_peers_and_cached_plans(rt):
+    """Freeing an allocation that a validated layer table, a peer-offset array or a cached launch plan
+    points into makes the next launch come back with -4 (nothing is launched on the rejected paths);
+    unrelated frees leave them valid."""
+    from k100lc_kernels import LaunchPlan
+    rows, nl = 200, 2
+    layers = [synth.rt4_layer(rows, K, 1, seed=990 + i) for i in range(nl)]
+    host = rt.pinned((nl, rows), np.float32)
+    with Bufs(rt) as b:
+        codes = Codes(rt, b, layers)
+        y = b.zeros(nl * rows, np.float32, np.nan)
+        wq1 = rt.alloc(layers[1]["wq"].nbytes)                 # freed by hand below
+        rt.upload(wq1, layers[1]["wq"])
+        ptrs = [(b.put(layers[0]["wq"]), b.put(layers[0]["ws"]), codes.x, y),
+                (wq1, b.put(layers[1]["ws"]), codes.x + K * 4, y + rows * 4)]
+        table = rt.stream_table(ptrs, rows, K, 0)
+        status = b.zeros(1, np.int32)
+        deltas = rt.stream_peers([host.ctypes.data], y, nl * rows * 4)
+        argv = [table, nl, rows, K, 0, 0, 0, status] + codes.args
+        argv_host = [table, nl, rows, K, 0, 1, deltas, status] + codes.args
+        codes.quantise(rt)
+        rt.launch("w4a8_decode_stream", 1, 1, argv_host)
+        plan = LaunchPlan(rt, [("w4a8_decode_stream", 1, 1, argv)])
+        plan.run()
+        plan.run()                                             # replayed from the cached graph
+        first = b.get(y, nl * rows).copy()
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        assert np.array_equal(host.reshape(-1).view(np.uint32), first.view(np.uint32))
+        scratch = rt.alloc(4096)
+        rt.free(scratch)                                       # an unrelated free: the table stays valid
+        rt.launch("w4a8_decode_stream", 1, 1, argv)
+        plan.run()
+        assert np.array_equal(b.get(y, nl * rows).view(np.uint32), first.view(np.uint32))
+        rt.free_pinned(host)                                   # the receiver goes away: its offsets are dropped
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("w4a8_decode_stream", 1, 1, argv_host)
+        rt.launch("w4a8_decode_stream", 1, 1, argv)            # the table itself is still fine
+        rt.free(wq1)                                           # a layer's weights go away: the table is dropped
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("w4a8_decode_stream", 1, 1, argv)
+        with pytest.raises(RuntimeError):                      # the cached graph is not replayed either
+            plan.run()
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+        rt.free(deltas)

@@ -48,6 +48,43 @@ def test_static_scratch_linear_matches_regular_path(rt):
         runner.close()
 
 
+def _cudart():
+    for name in ("libcudart.so.12", "/usr/local/cuda/lib64/libcudart.so.12", "libcudart.so"):
+        try:
+            return ctypes.CDLL(name)
+        except OSError:
+            continue
+    return None
+
+
+def test_static_scratch_linear_largest_shape_decode_shape_and_caller_stream(rt):
+    """The shapes at the edges of the entry point: four tokens at K = 16384 fill the built-in array and take
+    the large shared-memory configuration of the GEMV; one token at K = 5120 is the decode default (codes
+    held in registers).  The last call runs on a stream made by the caller, without waiting inside the call."""
+    rt_lib = _cudart()
+    stream = ctypes.c_void_p()
+    if rt_lib is not None and rt_lib.cudaStreamCreate(ctypes.byref(stream)) != 0:
+        stream = ctypes.c_void_p()
+    for n, k, m, seed, own_stream in [(96, 16384, 4, 23, False), (700, 5120, 1, 24, False), (300, 5120, 2, 25, True)]:
+        L = synth.rt4_layer(n, k, m, seed=seed)
+        with Bufs(rt) as b:
+            pwq, pws, px = b.put(L["wq"]), b.put(L["ws"]), b.put(L["x"])
+            py = b.zeros(m * n, np.float32, np.nan)
+            rt.sync()
+            if own_stream and stream.value:
+                rc = rt._lib.fm_w4a8_linear_static(ctypes.c_void_p(pwq), ctypes.c_void_p(pws), ctypes.c_void_p(px),
+                                                   ctypes.c_void_p(py), m, n, k, stream, 0)
+                assert rc == 0, rt.last_error()
+                assert rt_lib.cudaStreamSynchronize(stream) == 0
+            else:
+                assert _static(rt, pwq, pws, px, py, m, n, k) == 0, rt.last_error()
+            got = rt.download(py, m * n, np.float32).reshape(m, n)
+        q = O.quant_act(L["x"])
+        assert O.rel_err(got, O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"]) < REL, (n, k, m)
+    if stream.value:
+        rt_lib.cudaStreamDestroy(stream)
+
+
 def test_static_scratch_linear_refuses_oversize(rt):
     with Bufs(rt) as b:
         p = b.zeros(1024)
