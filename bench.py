@@ -193,7 +193,7 @@ class Stream:
         self.enqueue_token(**kw)
         return self.rt.graph_end()
 
-    def capture_fused(self, host_mirror: bool = False) -> int:
+    def capture_fused(self, host_mirror: bool = False, x: int | None = None) -> int:
         """One decoded token as TWO launches: quant_act over the x of all layers (grid y =
         layer), then the multi-layer stream kernel (bulk-copy ring over all layers' weights).
         With several GPUs the kernel's epilogue stores every y row into the y buffer of every
@@ -223,10 +223,10 @@ class Stream:
                 self.deltas_host = rt.stream_peers(self.bases + [self.y_host.ctypes.data], self.y, nl * N * 4)
             npeers, deltas = self.npeers + 1, self.deltas_host
         rt.graph_begin()
-        rt.launch2d("quant_act", NG, nl, 32, 1, [self.x, self.ae_all, self.ao_all, self.asc_all, self.asu_all, nl, K])
+        rt.launch2d("quant_act", NG, nl, 32, 1, [self.x if x is None else x, self.ae_all, self.ao_all, self.asc_all, self.asu_all, nl, K])
         rt.launch("w4a8_decode_stream", 1, 1, [self.table, nl, self.rows, K, self.rank * self.rows, npeers,
                                                deltas, self.status,
-                                               self.ae_all, self.ao_all, self.asc_all, self.asu_all])
+                                               self.ae_all, self.ao_all, self.asc_all, self.asu_all, 0])
         return rt.graph_end()
 
     def y_digest(self) -> str:
@@ -359,7 +359,7 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         st16 = rt.alloc(4)
         rt.memset(st16, 0, 4)
         rt.graph_begin()
-        rt.launch("w4a16_decode_stream", 1, 1, [tab16, nd, rows, K, 0, 0, 0, st16])
+        rt.launch("w4a16_decode_stream", 1, 1, [tab16, nd, rows, K, 0, 0, 0, st16, 0])
         g = rt.graph_end()
         us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nd
         rt.graph_free(g)
@@ -378,11 +378,11 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
 
     def s8():
         rt.launch2d("quant_act", NG, nl, 32, 1, [st.x, ae, ao, sc8, su8, nl, K])
-        rt.launch("w4a8_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, ae, ao, sc8, su8])
+        rt.launch("w4a8_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, ae, ao, sc8, su8, 0])
 
     def s4():
         rt.launch2d("quant_act4", K // 32, nl, 32, 1, [st.x, aq4, sc4, nl, K])
-        rt.launch("w4a4_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, aq4, sc4])
+        rt.launch("w4a4_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, aq4, sc4, 0])
 
     for name, fn in (("w4a8_m1_stream", s8), ("w4a4_m1_stream", s4)):
         rt.graph_begin()
@@ -397,7 +397,7 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
     qan, qbn, scn = rt.alloc(nvl * K // 2), rt.alloc(nvl * K // 2), rt.alloc(nvl * (K // 16) * 4)
     rt.graph_begin()
     rt.launch2d("nvfp4_quant_act", K // 16, nvl, 64, 1, [st.x, qan, qbn, scn, nvl, K])
-    rt.launch("nvfp4_decode_stream", 1, 1, [tab_n, nvl, rows, K, 0, 0, 0, status, qan, qbn, scn, 0.05])
+    rt.launch("nvfp4_decode_stream", 1, 1, [tab_n, nvl, rows, K, 0, 0, 0, status, qan, qbn, scn, 0.05, 0])
     g = rt.graph_end()
     us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nvl
     rt.graph_free(g)
@@ -414,7 +414,7 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         scm, sum_ = rt.alloc(nlm * mt * NG * 4), rt.alloc(nlm * mt * NG * 4)
         rt.graph_begin()
         rt.launch2d("quant_act", NG, nlm * mt, 32, 1, [st.x, aem, aom, scm, sum_, nlm * mt, K])
-        rt.launch("w4a8_decode_stream_m", 1, 1, [tab_m, nlm, rows, K, 0, 0, 0, status, aem, aom, scm, sum_, mt, N])
+        rt.launch("w4a8_decode_stream_m", 1, 1, [tab_m, nlm, rows, K, 0, 0, 0, status, aem, aom, scm, sum_, mt, N, 0])
         g = rt.graph_end()
         us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nlm
         rt.graph_free(g)
@@ -596,12 +596,27 @@ def run_ours(args) -> int:
     # end to end through the C ABI with host buffers: x of all layers up, y of all layers back, every step
     # (fused: the kernel itself delivers this rank's rows of y to the pinned host array; per-layer
     # mode copies the gathered y back after the graph)
-    graph_e2e = st.capture_fused(host_mirror=True) if fused else graph
+    # Inputs are double-buffered on the device: while step t runs on x[t % 2], the x of step t + 1 is uploaded into
+    # the other buffer on the engine's second queue (the upload waits for step t - 1, the last reader of that buffer,
+    # and step t + 1 waits for the upload).  Every step still uploads its own inputs inside the timed region.
     st.y_host[:] = np.nan
-    def e2e_step():
-        rt.upload_async(st.x, st.x_host)
-        rt.graph_launch(graph_e2e)
-        if not fused:
+    if fused:
+        x2 = rt.alloc(args.layers * K * 4)
+        xbuf = (st.x, x2)
+        graphs = (st.capture_fused(host_mirror=True, x=st.x), st.capture_fused(host_mirror=True, x=x2))
+        step_no = [0]
+        rt.upload(st.x, st.x_host)                  # the very first step's inputs (outside the timed steps)
+
+        def e2e_step():
+            t = step_no[0]
+            rt.upload_beside(xbuf[(t + 1) % 2], st.x_host)     # inputs of the next step, beside this one
+            rt.graph_launch(graphs[t % 2])
+            rt.upload_join()
+            step_no[0] = t + 1
+    else:
+        def e2e_step():
+            rt.upload_async(st.x, st.x_host)
+            rt.graph_launch(graph)
             rt.download_async(st.y_host, st.y)
     for _ in range(max(1, args.warmup)):
         e2e_step()
@@ -684,9 +699,9 @@ def run_ours(args) -> int:
             "ms_per_token": round(ms_step, 4), "us_per_layer": round(ms_step * 1e3 / args.layers, 3),
             "e2e": {"value": round(total_bytes / ms_e2e / 1e6, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e, 4),
                     "h2d_bytes_per_step": world * args.layers * K * 4, "d2h_bytes_per_step": args.layers * N * 4,
-                    "api": ("fm_upload_async(x of all layers, every rank) + fm_graph_launch; the stream kernel stores each "
-                            "rank's rows of y into a pinned host array (fm_host_alloc, registered through fm_stream_peers) "
-                            "while it runs; fm_sync ends the step") if fused else
+                    "api": ("per step: fm_upload_beside(x of all layers for the next step, every rank, second device buffer) + "
+                            "fm_graph_launch + fm_upload_join; the stream kernel stores each rank's rows of y into a pinned "
+                            "host array (fm_host_alloc, registered through fm_stream_peers) while it runs; fm_sync ends the run") if fused else
                            "fm_upload_async(x) + fm_graph_launch + fm_download_async(y), pinned host buffers"},
             "gpu_launches": int(gpu_launches),
             "per_layer_launches": None if ms_alt is None else {

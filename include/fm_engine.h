@@ -90,6 +90,13 @@ void  fm_host_free(void* p);
 int   fm_upload_async(void* dev, const void* pinned_host, size_t n);
 int   fm_download_async(void* pinned_host, const void* dev, size_t n);
 
+/* Upload on a second queue, for double-buffered inputs.  The copy starts when everything enqueued on the engine
+ * stream before the call has finished and runs beside what is enqueued after it; fm_upload_join makes the
+ * engine stream wait for it.  Per step t:  fm_upload_beside(x[(t+1)%2]); launch step t (reads x[t%2]);
+ * fm_upload_join().  Not available inside a graph capture.  fm_sync also waits for the second queue. */
+int   fm_upload_beside(void* dev, const void* pinned_host, size_t n);
+int   fm_upload_join(void);
+
 /* Layer table of the fused decode stream ("w4a8_decode_stream"): host_layers holds
  * nlayers x {wq, ws, x, y} device addresses.  Every address is checked against the live
  * allocations for the footprint that (rows, K, row_base) implies — wq rows*K/2 bytes,

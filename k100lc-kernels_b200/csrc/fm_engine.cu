@@ -45,6 +45,9 @@ struct Engine {
     int device = -1;            // -1: choose at init
     int sm_count = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;       // second queue for uploads that run beside the kernels (fm_upload_beside)
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool copy_pending = false;
     std::string image;
     bool check_bounds = true;
     bool pdl = false;
@@ -394,6 +397,15 @@ bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_ba
     return (whole_y ? t.y_ptr_lo : t.y_lo) >= ip->second.lo && t.y_hi <= ip->second.hi;
 }
 
+bool peer_window_ok(const void* peer_delta, int npeers, const void* ptr, size_t bytes) {
+    Engine& e = E();
+    if (!e.check_bounds) return true;
+    auto ip = e.peers.find(reinterpret_cast<uintptr_t>(peer_delta));
+    if (ip == e.peers.end() || ip->second.npeers != npeers) return false;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(ptr);
+    return a >= ip->second.lo && a + bytes <= ip->second.hi;
+}
+
 }  // namespace fm
 
 using namespace fm;
@@ -427,6 +439,7 @@ void fm_free(void* p) {
     LOCK;
     if (!p || !E().ready) return;
     cudaStreamSynchronize(E().stream);        // nothing in flight may still use it
+    if (E().copy_stream) cudaStreamSynchronize(E().copy_stream);
     auto it = E().allocs.find(reinterpret_cast<uintptr_t>(p));
     if (it != E().allocs.end()) {
         touch(p, it->second);
@@ -495,6 +508,7 @@ int fm_sync(void) {
     LOCK;
     NEED_INIT(-1);
     cudaError_t err = cudaStreamSynchronize(E().stream);
+    if (err == cudaSuccess && E().copy_stream) err = cudaStreamSynchronize(E().copy_stream);
     if (err != cudaSuccess) { cuda_fail("fm_sync", err); return -1; }
     return 0;
 }
@@ -658,6 +672,44 @@ int fm_upload_async(void* dev, const void* host, size_t n) {
     if (err != cudaSuccess) { cuda_fail("fm_upload_async", err); return -1; }
     return 0;
 }
+// Upload on a second queue.  The copy starts once everything enqueued on the engine stream BEFORE this call has
+// finished (so it may overwrite a buffer whose last reader is already enqueued), and runs beside whatever is
+// enqueued AFTER it; fm_upload_join makes the engine stream wait for it.  Pattern for double-buffered inputs:
+//   fm_upload_beside(x[(t+1)%2], ...); fm_graph_launch(step t, reading x[t%2]); fm_upload_join();
+int fm_upload_beside(void* dev, const void* host, size_t n) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (e.capturing) { set_errorf("fm_upload_beside: not inside a graph capture"); return -1; }
+    if (!range_ok(dev, n)) { set_errorf("fm_upload_beside: range exceeds the allocation"); return -1; }
+    if (!e.copy_stream) {
+        if (cudaStreamCreateWithFlags(&e.copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&e.ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&e.ev_join, cudaEventDisableTiming) != cudaSuccess) {
+            cuda_fail("fm_upload_beside", cudaGetLastError());
+            return -1;
+        }
+    }
+    touch(dev, n);
+    cudaError_t err = cudaEventRecord(e.ev_fork, e.stream);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(e.copy_stream, e.ev_fork, 0);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(dev, host, n, cudaMemcpyHostToDevice, e.copy_stream);
+    if (err == cudaSuccess) err = cudaEventRecord(e.ev_join, e.copy_stream);
+    if (err != cudaSuccess) { cuda_fail("fm_upload_beside", err); return -1; }
+    e.copy_pending = true;
+    return 0;
+}
+int fm_upload_join(void) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (!e.copy_pending) return 0;
+    cudaError_t err = cudaStreamWaitEvent(e.stream, e.ev_join, 0);
+    if (err != cudaSuccess) { cuda_fail("fm_upload_join", err); return -1; }
+    e.copy_pending = false;
+    return 0;
+}
+
 int fm_download_async(void* host, const void* dev, size_t n) {
     LOCK;
     NEED_INIT(-1);

@@ -45,6 +45,10 @@ void* engine_scratch(size_t bytes);
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
                      int npeers, bool whole_y = false, size_t ws_bytes = 0, bool need_x = false);
 
+// true when [ptr, ptr+bytes) lies inside the local window that fm_stream_peers validated for the offset array
+// `peer_delta` (so every receiver has the same bytes at the same offset), or checks are off
+bool peer_window_ok(const void* peer_delta, int npeers, const void* ptr, size_t bytes);
+
 // Registries of the kernel files -------------------------------------------
 const KernelEntry* quant_kernels(int* n);
 const KernelEntry* gemv_w4_kernels(int* n);

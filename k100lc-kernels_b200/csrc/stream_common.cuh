@@ -1,0 +1,324 @@
+// Shared skeleton of the multi-layer decode stream kernels (decode_stream.cu): one persistent launch
+// walks a stack of independent layers, CTA c owning the same contiguous row range of every layer.
+//
+//   producer warp (one lane)   issues 1-D bulk async copies (cp.async.bulk, never multicast) of ROWS weight
+//                              rows + their scales into a ring of shared-memory stages, completion counted
+//                              on an mbarrier per stage, and the token's activation codes of each layer
+//                              either into a small ring of tiles of their own or into every stage;
+//   consumer warps             one or two groups that take the stages in turn; what a group does with a
+//                              stage is the policy (dp4a or mma.sync arithmetic of one quantisation format);
+//   writer warp                collects nothing itself: the consumers put a CTA's y values of a layer into a
+//                              shared-memory tile and the writer stores it once per layer, coalesced, to the
+//                              local y and to every additional receiver (other GPUs' y over NVLink peer
+//                              mappings, a pinned host buffer), then bumps the layer's completion counter
+//                              on every receiver.
+//
+// Every wait on an mbarrier is bounded.  A wait that runs out records its code in *status, raises a
+// CTA-wide abort flag that every other wait polls, and all roles fall through to a common exit: the
+// producer first waits (bounded again) for the copies it has already issued, so that no bulk copy is
+// still landing in this CTA's shared memory when the CTA gives it up.
+#pragma once
+#include <stdint.h>
+
+#include "device_utils.cuh"
+
+namespace fm {
+namespace stream {
+
+constexpr int kSpinLimit = 1 << 20;    // try_wait rounds (each may sleep up to the suspend hint) before a wait gives up
+constexpr int kOutCap = 512;           // y values of one layer that a CTA collects in shared memory (else stored one by one)
+constexpr int kMaxStages = 8;
+constexpr int kHeader = 512;           // bytes reserved for the barriers at the start of the dynamic shared memory
+
+struct StreamLayer {                   // one entry of the device-side layer table (32 bytes)
+    const uint8_t* wq;                 // [rows][K/2] packed 4-bit codes
+    const uint8_t* ws;                 // [rows][..] weight scales (f16 / bf16 per 128, or E4M3 per 16)
+    const float* x;                    // [K] fp32 activations of this layer (read by the W4A16 kernel only)
+    float* y;                          // [>= row_base + rows] fp32 output of this layer
+};
+
+struct StreamParams {
+    const StreamLayer* layers;         // device table, or nullptr: the single layer `one`
+    const uint8_t *ae, *ao, *asc, *asu;   // activation-quantiser outputs of all layers (meaning depends on the format)
+    int nlayers, rows, K, row_base;
+    int npeers;                        // additional receivers of y (0 on one GPU)
+    const long long* peer_delta;       // [npeers] byte offset from a local y address to the receiver's copy
+    int* status;                       // 0 ok, else the code of the first wait that ran out
+    int M, ystride;                    // tokens per layer and floats between their outputs (token-major y)
+    int* iacc;                         // accumulator dump (parity tests): [nlayers][M][rows][units per row]
+    unsigned* flags;                   // optional [nlayers] completion counters, +1 per CTA and layer on every receiver
+    uint32_t wait_hint_ns;             // suspend-time hint of the barrier waits (0: none)
+    StreamLayer one;
+};
+
+__device__ __forceinline__ StreamLayer get_layer(const StreamParams& p, int l) { return p.layers ? p.layers[l] : p.one; }
+
+struct Bars {
+    uint64_t full[kMaxStages];         // a stage's bytes have landed
+    uint64_t empty[kMaxStages];        // its consumers have used them
+    uint64_t act_ready[kMaxStages];    // a layer's activation tile has landed (tiles of their own only)
+    uint64_t act_free[kMaxStages];     // every consumer warp is done with it
+    uint64_t red_full[4], red_free[4]; // partial-sum tiles of the tensor-core consumers (two per group)
+    uint64_t ydone[2], yfree[2];       // output tile complete / written out
+    volatile int abort;
+};
+static_assert(sizeof(Bars) <= kHeader, "barrier block");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+// one round of waiting: with a hint the thread may sleep up to that many nanoseconds inside the instruction
+// instead of spinning through the issue slots
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    if (hint_ns)
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(smem_u32(b)), "r"(parity), "r"(hint_ns) : "memory");
+    else
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Pins a value in program order: volatile statements are not reordered with each other, so an
+// mbarrier.arrive that follows cannot be scheduled ahead of the arithmetic that produced `v`
+// (and with it ahead of the shared-memory loads that arithmetic consumed).
+__device__ __forceinline__ void consumed(float v) { asm volatile("" ::"f"(v) : "memory"); }
+// 1-D bulk async copy global -> this CTA's shared memory
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// What every role of a CTA needs.
+struct Cta {
+    const StreamParams* p;
+    Bars* bars;
+    uint8_t* ring;
+    uint8_t* act;
+    float* red;
+    float* ytile;
+    uint8_t* extra;
+    int warp, lane;
+    int r0, r1, nst;                   // this CTA's rows [r0, r1) of every layer = nst stages
+    bool tiled;                        // its y values of a layer fit the output tile
+    uint32_t hint;
+};
+
+// bounded wait that also gives up when another role has raised the abort flag
+__device__ __forceinline__ bool cta_wait(const Cta& c, uint64_t* bar, uint32_t parity, int code) {
+    for (int i = 0; i < kSpinLimit; i++) {
+        if (mbar_try_wait(bar, parity, c.hint)) return true;
+        if ((i & 7) == 7 && c.bars->abort) return false;
+    }
+    c.bars->abort = 1;
+    atomicCAS(c.p->status, 0, code);
+    return false;
+}
+// the same without a report: used on the way out, for copies that are still in flight
+__device__ __forceinline__ void quiet_wait(uint64_t* bar, uint32_t parity) {
+    for (int i = 0; i < kSpinLimit && !mbar_try_wait(bar, parity, 1000u); i++) {}
+}
+
+// Status codes: 1 ring slot not freed (producer), 2 activation tile not landed, 3 stage not landed,
+// 4 activation tile not freed, 5 / 6 partial-sum tile, 7 output tile not written, 8 output tile not complete.
+
+// ---- producer ------------------------------------------------------------------------------
+// P supplies: ROWS, STAGES, PITCH, ROWB, SCB, STAGE_W, STAGE, ACT, NACT, ACT_IN_STAGE, OFF_ACT and
+// copy_act(pp, layer, dst, bar), which issues bulk copies of exactly ACT bytes.
+template <class P>
+__device__ __forceinline__ void run_producer(const Cta& c, const typename P::Params& pp) {
+    const StreamParams& p = *c.p;
+    Bars* B = c.bars;
+    int issued = 0, acts = 0;          // stages / activation tiles armed so far
+    bool ok = true;
+    auto copy_tile = [&](int l) -> bool {          // layer l's codes -> tile l % NACT
+        const int b = l % P::NACT;
+        if (l >= P::NACT && !cta_wait(c, &B->act_free[b], ((l / P::NACT) & 1) ^ 1, 4)) return false;
+        mbar_expect_tx(&B->act_ready[b], P::ACT);
+        P::copy_act(pp, l, c.act + (size_t)b * P::ACT, &B->act_ready[b]);
+        acts = l + 1;
+        return true;
+    };
+    // A layer's codes are copied right before its first stage, into tile l % NACT: that tile was last used
+    // by layer l - NACT, and the ring keeps the consumers at most STAGES stages behind, so with
+    // NACT > STAGES / (stages per layer) + 1 tiles the copy never waits for them (the launcher picks NACT).
+    int cc = 0;
+    for (int l = 0; ok && l < p.nlayers; l++) {
+        const StreamLayer lay = get_layer(p, l);
+        if (!P::ACT_IN_STAGE && !copy_tile(l)) { ok = false; break; }
+        for (int j = 0; j < c.nst; j++, cc++) {
+            const int s = cc % P::STAGES;
+            if (cc >= P::STAGES && !cta_wait(c, &B->empty[s], ((cc / P::STAGES) & 1) ^ 1, 1)) { ok = false; break; }
+            const int row = c.r0 + j * P::ROWS;
+            const int nr = min(P::ROWS, c.r1 - row);
+            uint8_t* dst = c.ring + (size_t)s * P::STAGE;
+            mbar_expect_tx(&B->full[s], (uint32_t)(nr * (P::ROWB + P::SCB)) + (P::ACT_IN_STAGE ? P::ACT : 0));
+            if (P::PITCH == P::ROWB) {
+                bulk_g2s(dst, lay.wq + (size_t)row * P::ROWB, (uint32_t)(nr * P::ROWB), &B->full[s]);
+            } else {                                   // padded pitch: one copy per row
+                for (int r = 0; r < nr; r++)
+                    bulk_g2s(dst + (size_t)r * P::PITCH, lay.wq + (size_t)(row + r) * P::ROWB, P::ROWB, &B->full[s]);
+            }
+            bulk_g2s(dst + P::STAGE_W, lay.ws + (size_t)row * P::SCB, (uint32_t)(nr * P::SCB), &B->full[s]);
+            if (P::ACT_IN_STAGE) P::copy_act(pp, l, dst + P::OFF_ACT, &B->full[s]);
+            issued = cc + 1;
+        }
+    }
+    if (!ok) {
+        // leaving early: what was issued must have landed before the CTA's shared memory is given up
+        for (int j = issued > P::STAGES ? issued - P::STAGES : 0; j < issued; j++)
+            quiet_wait(&B->full[j % P::STAGES], (j / P::STAGES) & 1);
+        if (!P::ACT_IN_STAGE)
+            for (int l = acts > P::NACT ? acts - P::NACT : 0; l < acts; l++)
+                quiet_wait(&B->act_ready[l % P::NACT], (l / P::NACT) & 1);
+    }
+}
+
+// ---- writer --------------------------------------------------------------------------------
+// tile layout [row][token]; y of a layer is token-major: y[token * ystride + row]
+template <int M>
+__device__ __forceinline__ void write_out(const StreamParams& p, const float* tile, float* y, int n, int lane) {
+    for (int i = lane; i < n * M; i += 32) {
+        const int tok = M == 1 ? 0 : i / n, row = M == 1 ? i : i - tok * n;      // token-major walk: coalesced stores
+        const float v = tile[row * M + tok];
+        float* dst = y + (size_t)tok * p.ystride + row;
+        *dst = v;
+        for (int q = 0; q < p.npeers; q++)
+            *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = v;
+    }
+}
+
+template <class P>
+__device__ __forceinline__ void run_writer(const Cta& c) {
+    const StreamParams& p = *c.p;
+    if (!c.tiled) return;
+    for (int l = 0; l < p.nlayers; l++) {
+        if (!cta_wait(c, &c.bars->ydone[l & 1], (l >> 1) & 1, 8)) return;
+        write_out<P::M>(p, c.ytile + (l & 1) * kOutCap, get_layer(p, l).y + p.row_base + c.r0, c.r1 - c.r0, c.lane);
+        __syncwarp();
+        if (c.lane == 0) mbar_arrive(&c.bars->yfree[l & 1]);
+        if (p.flags) {
+            // the rows are visible everywhere before the counter of the layer moves: receiver 0 is
+            // this GPU, receiver q > 0 the q-th additional copy
+            __threadfence_system();
+            __syncwarp();
+            if (c.lane <= p.npeers) {
+                unsigned* f = p.flags + l;
+                if (c.lane > 0) f = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(f) + p.peer_delta[c.lane - 1]);
+                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(f) : "memory");
+            }
+        }
+    }
+    if (p.npeers) __threadfence_system();
+}
+
+// ---- consumer side of the layer protocol -----------------------------------------------------
+// before the first stage of layer l that a warp works on
+template <class P>
+__device__ __forceinline__ bool layer_enter(const Cta& c, int l) {
+    if (c.tiled && l >= 2 && !cta_wait(c, &c.bars->yfree[l & 1], ((l >> 1) & 1) ^ 1, 7)) return false;
+    if (!P::ACT_IN_STAGE && !cta_wait(c, &c.bars->act_ready[l % P::NACT], (l / P::NACT) & 1, 2)) return false;
+    return true;
+}
+// the activation tile of layer l is no longer needed by this warp
+template <class P>
+__device__ __forceinline__ void act_release(const Cta& c, int l) {
+    if (!P::ACT_IN_STAGE && c.lane == 0) mbar_arrive(&c.bars->act_free[l % P::NACT]);
+}
+// this warp has put its last y value of layer l into the tile
+__device__ __forceinline__ void layer_done(const Cta& c, int l) {
+    if (c.tiled) {
+        __syncwarp();
+        if (c.lane == 0) mbar_arrive(&c.bars->ydone[l & 1]);
+    }
+}
+// one y value: into the layer's tile `yt`, or (too many rows per CTA for the tile) straight to every receiver
+template <int M>
+__device__ __forceinline__ void emit(const Cta& c, float* yt, float* y, int row, int tok, float v) {
+    const StreamParams& p = *c.p;
+    if (c.tiled) {
+        yt[(row - c.r0) * M + tok] = v;
+    } else {
+        float* dst = y + (size_t)tok * p.ystride + row;
+        *dst = v;
+        for (int q = 0; q < p.npeers; q++)
+            *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = v;
+    }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------
+// P supplies the geometry constants, Params (with a StreamParams member `s`), init_extra() and
+// consume(cta, params, group, warp_in_group).
+template <class P>
+__global__ void __launch_bounds__(P::kThreads, 1)
+stream_kernel(const typename P::Params pp) {
+    const StreamParams& p = pp.s;
+    extern __shared__ __align__(128) uint8_t smem[];
+    Cta c;
+    c.p = &p;
+    c.bars = reinterpret_cast<Bars*>(smem);
+    c.ring = smem + kHeader;
+    c.act = c.ring + (size_t)P::STAGES * P::STAGE;
+    c.red = reinterpret_cast<float*>(c.act + (P::ACT_IN_STAGE ? 0 : P::NACT * P::ACT));
+    c.ytile = c.red + P::NGROUPS * 2 * P::RED;
+    c.extra = reinterpret_cast<uint8_t*>(c.ytile + 2 * kOutCap);
+    c.warp = threadIdx.x >> 5;
+    c.lane = threadIdx.x & 31;
+    c.hint = p.wait_hint_ns;
+    constexpr int CW = P::CW, NCW = P::NGROUPS * CW;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P::STAGES; s++) {
+            mbar_init(&c.bars->full[s], 1);
+            mbar_init(&c.bars->empty[s], CW);
+        }
+        for (int b = 0; b < P::NACT; b++) {
+            mbar_init(&c.bars->act_ready[b], 1);
+            mbar_init(&c.bars->act_free[b], NCW);
+        }
+        for (int b = 0; b < 4; b++) {
+            mbar_init(&c.bars->red_full[b], CW);
+            mbar_init(&c.bars->red_free[b], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&c.bars->ydone[b], NCW);
+            mbar_init(&c.bars->yfree[b], 1);
+        }
+        c.bars->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    P::init_extra(pp, c.extra);
+    __syncthreads();
+    pdl_wait();                                          // the codes come from the preceding quantiser launch
+
+    c.r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+    c.r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
+    c.tiled = (c.r1 - c.r0) * P::M <= kOutCap;
+
+    if (c.warp == NCW) {
+        if (c.lane == 0) run_producer<P>(c, pp);
+    } else if (c.warp == NCW + 1) {
+        run_writer<P>(c);
+    } else {
+        P::consume(c, pp, c.warp / CW, c.warp % CW);
+        if (p.npeers && !c.tiled) __threadfence_system();    // direct peer stores are visible before the kernel ends
+    }
+    // common exit: nobody leaves while a copy issued by the producer may still be landing
+    __syncthreads();
+}
+
+template <class P>
+constexpr size_t smem_bytes() {
+    return (size_t)kHeader + (size_t)P::STAGES * P::STAGE + (P::ACT_IN_STAGE ? 0 : (size_t)P::NACT * P::ACT) +
+           (size_t)P::NGROUPS * 2 * P::RED * 4 + 2 * kOutCap * 4 + P::EXTRA;
+}
+
+}  // namespace stream
+}  // namespace fm

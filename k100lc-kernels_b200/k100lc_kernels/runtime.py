@@ -81,6 +81,8 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_host_free": (None, [c.c_void_p]),
         "fm_upload_async": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_download_async": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
+        "fm_upload_beside": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
+        "fm_upload_join": (c.c_int, []),
         "fm_event_create": (c.c_int, []),
         "fm_event_record": (c.c_int, [c.c_int]),
         "fm_event_elapsed_ms": (c.c_float, [c.c_int, c.c_int]),
@@ -366,6 +368,16 @@ class Runtime:
         if self._lib.fm_upload_async(ctypes.c_void_p(int(ptr)), arr.ctypes.data_as(ctypes.c_void_p),
                                      arr.nbytes) != 0:
             self._fail("fm_upload_async")
+
+    def upload_beside(self, ptr: int, arr: np.ndarray) -> None:
+        """Upload on the engine's second queue: starts when the work enqueued so far has finished, runs
+        beside what is enqueued next; ``upload_join`` makes later launches wait for it."""
+        if self._lib.fm_upload_beside(ctypes.c_void_p(int(ptr)), arr.ctypes.data_as(ctypes.c_void_p), arr.nbytes) != 0:
+            self._fail("fm_upload_beside")
+
+    def upload_join(self) -> None:
+        if self._lib.fm_upload_join() != 0:
+            self._fail("fm_upload_join")
 
     def download_async(self, arr: np.ndarray, ptr: int) -> None:
         if self._lib.fm_download_async(arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(int(ptr)),

@@ -47,7 +47,7 @@ def main() -> int:
     rt.sync()
     dist.barrier()                     # every rank has initialised its y before anyone stores into it
     rt.launch2d("quant_act", k // 128, layers, 32, 1, [x_all, ae, ao, asc, asu, layers, k])
-    rt.launch("w4a8_decode_stream", 1, 1, [table, layers, rows, k, r0, world - 1, deltas, status, ae, ao, asc, asu])
+    rt.launch("w4a8_decode_stream", 1, 1, [table, layers, rows, k, r0, world - 1, deltas, status, ae, ao, asc, asu, 0])
     rt.sync()
     dist.barrier()                     # every rank's stores have landed
     got = rt.download(y, layers * n, np.float32).reshape(layers, n)

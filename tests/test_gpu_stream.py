@@ -41,7 +41,7 @@ def _run_stream(rt, b, layers, rows, row_base=0, n_out=None):
     table = rt.stream_table(ptrs, rows, K, row_base)
     status = b.zeros(1, np.int32)
     codes.quantise(rt)
-    rt.launch("w4a8_decode_stream", 1, 1, [table, len(layers), rows, K, row_base, 0, 0, status] + codes.args)
+    rt.launch("w4a8_decode_stream", 1, 1, [table, len(layers), rows, K, row_base, 0, 0, status] + codes.args + [0])
     out = [b.get(py, n_out) for py in ys]
     assert int(b.get(status, 1, np.int32)[0]) == 0
     rt.free(table)
@@ -77,7 +77,7 @@ def test_stream_row_base_and_repeat(rt):
             ptrs.append((b.put(L["wq"]), b.put(L["ws"]), codes.x + i * K * 4, py))
         table = rt.stream_table(ptrs, rows, K, base)
         status = b.zeros(1, np.int32)
-        argv = [table, 4, rows, K, base, 0, 0, status] + codes.args
+        argv = [table, 4, rows, K, base, 0, 0, status] + codes.args + [0]
         codes.quantise(rt)
         rt.launch("w4a8_decode_stream", 1, 1, argv)
         first = [b.get(py, n_out) for py in ys]
@@ -91,7 +91,7 @@ def test_stream_row_base_and_repeat(rt):
             assert np.array_equal(y1[base:base + rows], y2[base:base + rows])
         # the table is only accepted as validated, with the shapes it was validated for
         with pytest.raises(RuntimeError, match="rc=-4"):
-            rt.launch("w4a8_decode_stream", 1, 1, [table, 4, rows + 8, K, base, 0, 0, status] + codes.args)
+            rt.launch("w4a8_decode_stream", 1, 1, [table, 4, rows + 8, K, base, 0, 0, status] + codes.args + [0])
         rt.memset(table, 0, 32)                         # overwriting it un-validates it
         with pytest.raises(RuntimeError, match="rc=-4"):
             rt.launch("w4a8_decode_stream", 1, 1, argv)
@@ -117,7 +117,7 @@ def test_w4a4_stream_matches_oracle(rt):
         table = rt.stream_table(ptrs, rows, K, 0)
         status = b.zeros(1, np.int32)
         rt.launch2d("quant_act4", K // 32, nl, 32, 1, [x, aq, asc, nl, K])
-        rt.launch("w4a4_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, aq, asc])
+        rt.launch("w4a4_decode_stream", 1, 1, [table, nl, rows, K, 0, 0, 0, status, aq, asc, 0])
         got = [b.get(py, rows) for py in ys]
         assert int(b.get(status, 1, np.int32)[0]) == 0
         rt.free(table)
@@ -148,12 +148,12 @@ def test_stream_delivers_y_to_pinned_host_memory(rt, kernel):
         if a4:
             aq, asc = b.zeros(nl * K // 2, np.uint8), b.zeros(nl * K // 32)
             rt.launch2d("quant_act4", K // 32, nl, 32, 1, [x, aq, asc, nl, K])
-            rt.launch(kernel, 1, 1, [table, nl, rows, K, base, 1, deltas, status, aq, asc])
+            rt.launch(kernel, 1, 1, [table, nl, rows, K, base, 1, deltas, status, aq, asc, 0])
         else:
             ae, ao = b.zeros(nl * K // 2, np.int8), b.zeros(nl * K // 2, np.int8)
             asc, asu = b.zeros(nl * K // 128), b.zeros(nl * K // 128, np.int32)
             rt.launch2d("quant_act", K // 128, nl, 32, 1, [x, ae, ao, asc, asu, nl, K])
-            rt.launch(kernel, 1, 1, [table, nl, rows, K, base, 1, deltas, status, ae, ao, asc, asu])
+            rt.launch(kernel, 1, 1, [table, nl, rows, K, base, 1, deltas, status, ae, ao, asc, asu, 0])
         dev = b.get(y, nl * n_out).reshape(nl, n_out)          # drains the stream
         assert int(b.get(status, 1, np.int32)[0]) == 0
         rt.free(table)
@@ -202,7 +202,7 @@ def test_stream_several_tokens_matches_oracle(rt, m, rows, row_base):
         table = rt.stream_table(ptrs, rows, K, row_base + (m - 1) * ystride)   # footprint of all m tokens
         status = b.zeros(1, np.int32)
         rt.launch2d("quant_act", K // 128, nl * m, 32, 1, [x, ae, ao, asc, asu, nl * m, K])
-        argv = [table, nl, rows, K, row_base, 0, 0, status, ae, ao, asc, asu, m, ystride]
+        argv = [table, nl, rows, K, row_base, 0, 0, status, ae, ao, asc, asu, m, ystride, 0]
         rt.launch("w4a8_decode_stream_m", 1, 1, argv)
         got = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
         assert int(b.get(status, 1, np.int32)[0]) == 0
@@ -237,7 +237,7 @@ def test_stream_several_tokens_delivers_to_host(rt):
         deltas = rt.stream_peers([host.ctypes.data], y, nl * m * ystride * 4)
         status = b.zeros(1, np.int32)
         rt.launch2d("quant_act", K // 128, nl * m, 32, 1, [x, ae, ao, asc, asu, nl * m, K])
-        rt.launch("w4a8_decode_stream_m", 1, 1, [table, nl, rows, K, 0, 1, deltas, status, ae, ao, asc, asu, m, ystride])
+        rt.launch("w4a8_decode_stream_m", 1, 1, [table, nl, rows, K, 0, 1, deltas, status, ae, ao, asc, asu, m, ystride, 0])
         dev = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
         assert int(b.get(status, 1, np.int32)[0]) == 0
         rt.free(table)
@@ -250,8 +250,8 @@ def test_stream_several_tokens_delivers_to_host(rt):
 
 @pytest.mark.parametrize("rows,nlayers", [(1000, 4), (17408, 2)])
 def test_nvfp4_stream_matches_per_layer_and_oracle(rt, rows, nlayers):
-    """nvfp4_decode_stream: one 2-D nvfp4_quant_act launch over all layers, then the stream kernel; same bits as
-    nvfp4_gemv<1,1> layer by layer, and within tolerance of the oracle."""
+    """nvfp4_decode_stream: one 2-D nvfp4_quant_act launch over all layers, then the stream kernel; agrees with
+    nvfp4_gemv<1,1> layer by layer (another association of the fp32 sums, so 1e-6 and not bits) and with the oracle."""
     layers = [synth.nvfp4_layer(rows, K, 1, seed=970 + i) for i in range(nlayers)]
     gscale = float(layers[0]["gscale"])
     with Bufs(rt) as b:
@@ -266,7 +266,7 @@ def test_nvfp4_stream_matches_per_layer_and_oracle(rt, rows, nlayers):
         table = rt.stream_table(ptrs, rows, K, 0)
         status = b.zeros(1, np.int32)
         rt.launch2d("nvfp4_quant_act", K // 16, nlayers, 64, 1, [x, qa, qb, sc, nlayers, K])   # grid y = layer
-        rt.launch("nvfp4_decode_stream", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status, qa, qb, sc, gscale])
+        rt.launch("nvfp4_decode_stream", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status, qa, qb, sc, gscale, 0])
         got = [b.get(py, rows) for py in ys]
         assert int(b.get(status, 1, np.int32)[0]) == 0
         for i, (L, yv) in enumerate(zip(layers, got)):
@@ -276,12 +276,12 @@ def test_nvfp4_stream_matches_per_layer_and_oracle(rt, rows, nlayers):
             py2 = b.zeros(rows, np.float32, np.nan)
             rt.launch("nvfp4_gemv<1,1>", -(-rows // 4), 256, [ptrs[i][0], ptrs[i][1], qa + i * K // 2, qb + i * K // 2,
                                                              sc + i * (K // 16) * 4, py2, rows, K, gscale])
-            assert np.array_equal(b.get(py2, rows).view(np.uint32), yv.view(np.uint32))
+            assert O.rel_err(b.get(py2, rows), yv) < 1e-6
         # a table whose scale buffers are too short for NVFP4 (rows * K/16 bytes) is refused
         short = b.zeros(rows * (K // 128) * 2 // 4 + 4, np.float32)
         t2 = rt.stream_table([(ptrs[0][0], short, ptrs[0][2], ys[0])], rows, K, 0)
         with pytest.raises(RuntimeError, match="rc=-4"):
-            rt.launch("nvfp4_decode_stream", 1, 1, [t2, 1, rows, K, 0, 0, 0, status, qa, qb, sc, gscale])
+            rt.launch("nvfp4_decode_stream", 1, 1, [t2, 1, rows, K, 0, 0, 0, status, qa, qb, sc, gscale, 0])
         rt.free(t2)
         rt.free(table)
 
@@ -299,13 +299,13 @@ def test_w4a16_stream_matches_oracle(rt, rows, nlayers):
             ptrs.append((b.put(L["packed"]), b.put(L["scale_bf16"]), b.put(L["x"]), py))
         table = rt.stream_table(ptrs, rows, K, 0)
         status = b.zeros(1, np.int32)
-        rt.launch("w4a16_decode_stream", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status])
+        rt.launch("w4a16_decode_stream", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status, 0])
         got = [b.get(py, rows) for py in ys]
         assert int(b.get(status, 1, np.int32)[0]) == 0
         # a table without x entries is refused by this kernel
         t2 = rt.stream_table([(w, s, 0, y) for (w, s, _x, y) in ptrs], rows, K, 0)
         with pytest.raises(RuntimeError, match="rc=-4"):
-            rt.launch("w4a16_decode_stream", 1, 1, [t2, nlayers, rows, K, 0, 0, 0, status])
+            rt.launch("w4a16_decode_stream", 1, 1, [t2, nlayers, rows, K, 0, 0, 0, status, 0])
         rt.free(t2)
         rt.free(table)
     for L, yv in zip(layers, got):
@@ -330,8 +330,8 @@ def test_freed_buffers_unvalidate_tables_peers_and_cached_plans(rt):
         table = rt.stream_table(ptrs, rows, K, 0)
         status = b.zeros(1, np.int32)
         deltas = rt.stream_peers([host.ctypes.data], y, nl * rows * 4)
-        argv = [table, nl, rows, K, 0, 0, 0, status] + codes.args
-        argv_host = [table, nl, rows, K, 0, 1, deltas, status] + codes.args
+        argv = [table, nl, rows, K, 0, 0, 0, status] + codes.args + [0]
+        argv_host = [table, nl, rows, K, 0, 1, deltas, status] + codes.args + [0]
         codes.quantise(rt)
         rt.launch("w4a8_decode_stream", 1, 1, argv_host)
         plan = LaunchPlan(rt, [("w4a8_decode_stream", 1, 1, argv)])
@@ -357,3 +357,168 @@ def test_freed_buffers_unvalidate_tables_peers_and_cached_plans(rt):
         assert int(b.get(status, 1, np.int32)[0]) == 0
         rt.free(table)
         rt.free(deltas)
+
+
+@pytest.mark.parametrize("rows,nlayers", [(17408, 2), (2176, 3), (300, 2)])
+def test_stream_accumulators_w4a8_and_w4a4(rt, rows, nlayers):
+    """The integer accumulators of the stream kernels themselves (tensor-core consumer for W4A8 — both the
+    schedule for many stages per layer and the one for a single stage per layer, which 2176 rows on 148 CTAs
+    select — and the dp4a consumer for W4A4), bit for bit against the oracle."""
+    layers = [synth.rt4_layer(rows, K, 1, seed=1200 + i) for i in range(nlayers)]
+    with Bufs(rt) as b:
+        codes = Codes(rt, b, layers)
+        ys, ptrs = [], []
+        for i, L in enumerate(layers):
+            py = b.zeros(rows, np.float32, np.nan)
+            ys.append(py)
+            ptrs.append((b.put(L["wq"]), b.put(L["ws"]), codes.x + i * K * 4, py))
+        table = rt.stream_table(ptrs, rows, K, 0)
+        status = b.zeros(1, np.int32)
+        codes.quantise(rt)
+        pi = b.zeros(nlayers * rows * (K // 128), np.int32, -7)
+        rt.launch("w4a8_decode_stream_iacc", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status] + codes.args + [0, pi])
+        acc8 = b.get(pi, nlayers * rows * (K // 128), np.int32).reshape(nlayers, rows, -1)
+        y8 = [b.get(py, rows) for py in ys]
+        aq, asc4 = b.zeros(nlayers * K // 2, np.uint8), b.zeros(nlayers * K // 32)
+        rt.launch2d("quant_act4", K // 32, nlayers, 32, 1, [codes.x, aq, asc4, nlayers, K])
+        pi4 = b.zeros(nlayers * rows * (K // 32), np.int32, -7)
+        rt.launch("w4a4_decode_stream_iacc", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status, aq, asc4, 0, pi4])
+        acc4 = b.get(pi4, nlayers * rows * (K // 32), np.int32).reshape(nlayers, rows, -1)
+        y4 = [b.get(py, rows) for py in ys]
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+    for i, L in enumerate(layers):
+        q = O.quant_act(L["x"])
+        ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)
+        assert np.array_equal(acc8[i], ref["acc"][0]), "W4A8 stream accumulators differ"
+        assert O.rel_err(y8[i], ref["y"][0]) < REL
+        q4 = O.quant_act4(L["x"])
+        ref4 = O.gemv_w4(L["wq"], L["ws"], q4["q"], q4["scale"], 32)
+        assert np.array_equal(acc4[i], ref4["acc"][0]), "W4A4 stream accumulators differ"
+        assert O.rel_err(y4[i], ref4["y"][0]) < REL
+
+
+@pytest.mark.parametrize("m,rows", [(2, 600), (4, 17408)])
+def test_stream_accumulators_several_tokens(rt, m, rows):
+    nl = 2
+    ystride = rows + 8
+    layers = [synth.rt4_layer(rows, K, m, seed=1300 + 10 * m + i) for i in range(nl)]
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"] for L in layers]))
+        ae, ao = b.zeros(nl * m * K // 2, np.int8), b.zeros(nl * m * K // 2, np.int8)
+        asc, asu = b.zeros(nl * m * K // 128), b.zeros(nl * m * K // 128, np.int32)
+        y = b.zeros(nl * m * ystride, np.float32, np.nan)
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), x + i * m * K * 4, y + i * m * ystride * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, (m - 1) * ystride)
+        status = b.zeros(1, np.int32)
+        rt.launch2d("quant_act", K // 128, nl * m, 32, 1, [x, ae, ao, asc, asu, nl * m, K])
+        pi = b.zeros(nl * m * rows * (K // 128), np.int32, -7)
+        rt.launch("w4a8_decode_stream_m_iacc", 1, 1, [table, nl, rows, K, 0, 0, 0, status, ae, ao, asc, asu, m, ystride, 0, pi])
+        acc = b.get(pi, nl * m * rows * (K // 128), np.int32).reshape(nl, m, rows, -1)
+        got = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+    for i, L in enumerate(layers):
+        q = O.quant_act(L["x"])
+        ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)
+        assert np.array_equal(acc[i], ref["acc"])
+        assert O.rel_err(got[i, :, :rows], ref["y"]) < REL
+
+
+@pytest.mark.parametrize("rows,nlayers", [(17408, 2), (520, 3)])
+def test_stream_accumulators_nvfp4(rt, rows, nlayers):
+    """nvfp4_decode_stream's tensor-core consumer: the int32 of every (row, 16-block), bit for bit."""
+    layers = [synth.nvfp4_layer(rows, K, 1, seed=1400 + i) for i in range(nlayers)]
+    gscale = float(layers[0]["gscale"])
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"][0] for L in layers]))
+        qa, qb = b.zeros(nlayers * K // 2, np.int8), b.zeros(nlayers * K // 2, np.int8)
+        sc = b.zeros(nlayers * K // 16)
+        ys, ptrs = [], []
+        for i, L in enumerate(layers):
+            py = b.zeros(rows, np.float32, np.nan)
+            ys.append(py)
+            ptrs.append((b.put(L["wq"]), b.put(L["ws"]), x + i * K * 4, py))
+        table = rt.stream_table(ptrs, rows, K, 0)
+        status = b.zeros(1, np.int32)
+        rt.launch2d("nvfp4_quant_act", K // 16, nlayers, 64, 1, [x, qa, qb, sc, nlayers, K])
+        pi = b.zeros(nlayers * rows * (K // 16), np.int32, -7)
+        rt.launch("nvfp4_decode_stream_iacc", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status, qa, qb, sc, gscale, 0, pi])
+        acc = b.get(pi, nlayers * rows * (K // 16), np.int32).reshape(nlayers, rows, -1)
+        got = [b.get(py, rows) for py in ys]
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+    for i, L in enumerate(layers):
+        q = O.nvfp4_quant_act(L["x"])
+        ref = O.nvfp4_gemv(L["wq"], L["ws"], q["q"], q["scale"], gscale)
+        assert np.array_equal(acc[i], ref["acc"][0])
+        assert O.rel_err(got[i], ref["y"][0]) < REL
+
+
+def test_stream_schedules_give_identical_bits(rt, monkeypatch):
+    """Every schedule of the W4A8 stream kernel ($FM_STREAM_CFG 0..8, with and without a suspend hint on the
+    barrier waits) leaves the bits of gemv_w4a8<1,false,1> in y, on a shape with many stages per CTA and
+    layer and on one with a single (partial) stage; the NVFP4 consumers agree with each other to 1e-6."""
+    runner = W4Runner(rt)
+    for rows, nl in ((17408, 2), (2176, 6), (100, 9)):
+        layers = [synth.rt4_layer(rows, K, 1, seed=1500 + i) for i in range(nl)]
+        with Bufs(rt) as b:
+            want = None
+            for cfg in (None, 0, 1, 2, 3, 4, 5, 6, 7, 8):
+                for hint in ((0, 2000) if cfg in (None, 3) else (0,)):
+                    if cfg is None:
+                        monkeypatch.delenv("FM_STREAM_CFG", raising=False)
+                    else:
+                        monkeypatch.setenv("FM_STREAM_CFG", str(cfg))
+                    monkeypatch.setenv("FM_STREAM_HINT_NS", str(hint))
+                    got, ptrs = _run_stream(rt, b, layers, rows)
+                    if want is None:
+                        want = [runner.gemv("w4a8", pwq, pws, L["x"], rows, K)[0] for L, (pwq, pws, _x, _y) in zip(layers, ptrs)]
+                    for i in range(nl):
+                        assert np.array_equal(got[i].view(np.uint32), want[i].view(np.uint32)), (rows, cfg, hint, i)
+        monkeypatch.delenv("FM_STREAM_CFG", raising=False)
+        monkeypatch.delenv("FM_STREAM_HINT_NS", raising=False)
+    runner.close()
+
+
+def test_stream_completion_counters_and_bounded_acquire(rt):
+    """flags[layer] ends at the number of CTAs on every receiver (local and pinned host); stream_flag_wait
+    returns at once when the target is met and, for a target that no producer will reach, gives up after
+    its bounded number of polls with status 9 (the context stays usable)."""
+    rows, nl = 1200, 5
+    sms = rt.device_attr("sm_count")
+    layers = [synth.rt4_layer(rows, K, 1, seed=1600 + i) for i in range(nl)]
+    with Bufs(rt) as b:
+        codes = Codes(rt, b, layers)
+        # y of all layers and the counters live in one allocation, mirrored in one pinned host buffer
+        ybytes = nl * rows * 4
+        buf = b.zeros((ybytes + nl * 4) // 4, np.float32, 0)
+        host = rt.pinned(((ybytes + nl * 4) // 4,), np.float32)
+        host[:] = 0
+        flags = buf + ybytes
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), codes.x + i * K * 4, buf + i * rows * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, 0)
+        deltas = rt.stream_peers([host.ctypes.data], buf, ybytes + nl * 4)
+        status = b.zeros(1, np.int32)
+        codes.quantise(rt)
+        rt.launch("w4a8_decode_stream", 1, 1, [table, nl, rows, K, 0, 1, deltas, status] + codes.args + [flags])
+        wstat = b.zeros(1, np.int32)
+        rt.launch("stream_flag_wait", 1, 128, [flags, nl, sms, wstat, 1000])
+        dev = b.get(buf, (ybytes + nl * 4) // 4)
+        assert int(b.get(status, 1, np.int32)[0]) == 0 and int(b.get(wstat, 1, np.int32)[0]) == 0
+        cnt_dev = dev[ybytes // 4:].view(np.uint32)
+        cnt_host = host[ybytes // 4:].view(np.uint32)
+        assert (cnt_dev == sms).all() and (cnt_host == sms).all()
+        assert np.array_equal(host[:ybytes // 4].view(np.uint32), dev[:ybytes // 4].view(np.uint32))
+        # a producer that never comes: the target is one more than anyone will add
+        rt.launch("stream_flag_wait", 1, 128, [flags, nl, sms + 1, wstat, 200])
+        assert int(b.get(wstat, 1, np.int32)[0]) == 9
+        # flags outside the validated window are refused
+        other = b.zeros(nl, np.int32)
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("w4a8_decode_stream", 1, 1, [table, nl, rows, K, 0, 1, deltas, status] + codes.args + [other])
+        rt.free(table)
+        rt.free(deltas)
+    for i, L in enumerate(layers):
+        q = O.quant_act(L["x"])
+        assert O.rel_err(host[i * rows:(i + 1) * rows], O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"][0]) < REL
