@@ -787,9 +787,7 @@ int parse_common(const char* kn, const LaunchCtx& c, const uint64_t* a, uint64_t
 // w4a8_decode_stream_iacc / w4a4_decode_stream_iacc(..., flags, iacc): the same kernels with the integer
 //   accumulators stored as well, iacc int32 [nlayers][rows][K/128 or K/32].
 // grid and work-group arguments are ignored (persistent: one CTA per SM).
-// $FM_STREAM_CFG selects the consumer of w4a8_decode_stream (0 tensor cores, 1 dp4a; higher numbers are
-// schedules of the tensor-core consumer kept for comparison); unset, the launcher chooses by the number of
-// stages a CTA has per layer.
+// $FM_STREAM_CFG selects another schedule of w4a8_decode_stream than the default (see the switch below).
 template <bool A4, bool DUMP>
 int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = A4 ? (DUMP ? "w4a4_decode_stream_iacc" : "w4a4_decode_stream") : (DUMP ? "w4a8_decode_stream_iacc" : "w4a8_decode_stream");
@@ -826,24 +824,22 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
         FM_REQUIRE(aligned(p.iacc, 4), kn, "misaligned accumulator dump");
         FM_RANGE(p.iacc, (size_t)p.nlayers * p.rows * (p.K / (A4 ? 32 : 128)) * 4, kn, "iacc");
         if (A4) return run_policy<W4Dp4a<true, 5, 2, true>>(kn, c, pp);
-        return nst >= 3 ? run_policy<W4A8Mma<1, 5, 1, false, 2, true, 0, true>>(kn, c, pp)
-                        : run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, true>>(kn, c, pp);
+        return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, true>>(kn, c, pp);
     }
     if (A4) return nst >= 3 ? run_policy<W4Dp4a<true, 5, 2, false>>(kn, c, pp) : run_policy<W4Dp4a<true, 4, 5, false>>(kn, c, pp);
-    switch (env_or("FM_STREAM_CFG", -1)) {
+    // Default: the token's codes travel inside every stage and two groups of eight warps take the stages in turn.
+    // Measured on one B200 (400 layers, ms per token, 20-step burst / one-second run): 17408 rows 2.62 / 3.07 against
+    // 3.04 / 3.35 for one group with the fragments in registers (0); 2176 rows — the shard of eight GPUs, one stage per
+    // CTA and layer — 0.384 / 0.442 against 0.496 / 0.507.  The other numbers are kept for comparison.
+    switch (env_or("FM_STREAM_CFG", 3)) {
         case 0: return run_policy<W4A8Mma<1, 5, 1, false, 2, true, 0, false>>(kn, c, pp);    // one group, fragments in registers
-        case 1: return run_policy<W4Dp4a<false, 5, 2, false>>(kn, c, pp);
+        case 1: return run_policy<W4Dp4a<false, 5, 2, false>>(kn, c, pp);                    // dp4a
         case 2: return run_policy<W4A8Mma<1, 4, 1, false, 5, true, 0, false>>(kn, c, pp);    // deeper ring of code tiles
-        case 3: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);    // codes inside every stage, two groups
         case 4: return run_policy<W4A8Mma<1, 4, 1, true, 1, false, 0, false>>(kn, c, pp);    // codes inside every stage, one group
-        case 5: return run_policy<W4A8Mma<1, 5, 2, false, 2, false, 0, false>>(kn, c, pp);   // two groups, fragments from the tile
-        case 6: return run_policy<W4A8Mma<1, 5, 2, false, 2, true, 0, false>>(kn, c, pp);    // two groups, fragments in registers
-        case 7: return run_policy<W4A8Mma<1, 4, 1, false, 2, true, 64, false>>(kn, c, pp);   // padded row pitch (no bank conflicts)
-        case 8: return run_policy<W4A8Mma<1, 4, 1, false, 2, true, 0, false>>(kn, c, pp);    // its control
-        default: break;
+        case 5: return run_policy<W4A8Mma<1, 5, 2, false, 2, false, 0, false>>(kn, c, pp);   // two groups, fragments from a tile of their own
+        case 7: return run_policy<W4A8Mma<1, 4, 1, false, 2, true, 64, false>>(kn, c, pp);   // padded row pitch (no bank conflicts): slower
+        default: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);
     }
-    return nst >= 3 ? run_policy<W4A8Mma<1, 5, 1, false, 2, true, 0, false>>(kn, c, pp)
-                    : run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);
 }
 
 // w4a8_decode_stream_m(common..., ae, ao, asc, asu, M, ystride, flags): M = 2..4 tokens per layer.  The code arrays
@@ -884,6 +880,13 @@ int launch_w4a8_stream_m(const LaunchCtx& c, const uint64_t* a) {
         p.iacc = arg_ptr<int>(a[15]);
         FM_REQUIRE(aligned(p.iacc, 4), kn, "misaligned accumulator dump");
         FM_RANGE(p.iacc, tokens * p.rows * (p.K / 128) * 4, kn, "iacc");
+    }
+    if (!DUMP && env_or("FM_STREAM_M_CFG", 0) == 1) {      // two groups, fragments from the tile
+        switch (p.M) {
+            case 2: return run_policy<W4A8Mma<2, 4, 2, false, 2, false, 0, false>>(kn, c, pp);
+            case 3: return run_policy<W4A8Mma<3, 4, 2, false, 2, false, 0, false>>(kn, c, pp);
+            default: return run_policy<W4A8Mma<4, 4, 2, false, 2, false, 0, false>>(kn, c, pp);
+        }
     }
     switch (p.M) {
         case 2: return run_policy<W4A8Mma<2, 4, 1, false, 2, true, 0, DUMP>>(kn, c, pp);

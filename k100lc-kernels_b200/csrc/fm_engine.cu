@@ -175,6 +175,7 @@ int ensure_init() {
         k = int4_dot_kernels(&n); add_kernels(k, n);
         k = gemm_w4_kernels(&n); add_kernels(k, n);
         k = stream_kernels(&n); add_kernels(k, n);
+        k = norm_act_kernels(&n); add_kernels(k, n);
     }
     e.ready = true;
     return 0;
@@ -192,6 +193,7 @@ void ensure_table() {
     k = int4_dot_kernels(&n); add_kernels(k, n);
     k = gemm_w4_kernels(&n); add_kernels(k, n);
     k = stream_kernels(&n); add_kernels(k, n);
+    k = norm_act_kernels(&n); add_kernels(k, n);
 }
 
 // a write into [p, p+n) makes any validated layer table it touches unvalidated

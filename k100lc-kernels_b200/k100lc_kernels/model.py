@@ -173,6 +173,19 @@ class DotLinear:
         return self.rt.download(out, x.shape[0] * self.n, np.float32).reshape(x.shape[0], self.n)
 
 
+def _gemv_w4a8_codes(rt, runner, tag, wq, ws_f16, codes, rows, n, k, out_dev, sync):
+    from .rt4 import W4A8_KERNEL
+    if rows not in (1, 2, 3, 4):
+        raise ValueError(f"the W4A8 GEMV takes 1..4 rows of codes (got {rows})")
+    ae, ao, asc, asu = (int(c) for c in codes)
+    y = int(out_dev) if out_dev is not None else runner._buf(tag + ".ycodes", rows * n * 4)
+    rows_per_wg = 4 * (1 if rows == 1 else 2)
+    rt.launch(W4A8_KERNEL[rows], cdiv(n, rows_per_wg), 256, [wq, ws_f16, ae, ao, asc, asu, y, n, k])
+    if sync:
+        rt.sync()
+    return y
+
+
 class RT4Linear:
     """RT4 INT4 layer already on the device (``wq``, ``ws_scale`` pointers); W4A8 or W4A4
     decode for M = 1..4 (reference model.py:358-383)."""
@@ -188,6 +201,12 @@ class RT4Linear:
     def forward_device(self, x_dev: int, rows: int, sync: bool = False, out_dev=None) -> int:
         return self.runner.gemv_device(self.path, self.wq, self.ws_scale, None, self.n, self.k,
                                        x_dev=x_dev, m=rows, y_dev=out_dev, sync=sync)
+
+    def forward_codes_device(self, codes, rows: int, out_dev=None, sync: bool = False) -> int:
+        """W4A8 GEMV on activations that are already quantised: ``codes`` = (ae, ao, asc, asu) device
+        pointers as ``quant_act`` / ``rmsnorm_quant_k`` / ``silu_mul_quant_k`` leave them (rows = 1..4)."""
+        return _gemv_w4a8_codes(self.rt, self.runner, self.tag, self.wq, self.ws_scale, codes, rows, self.n, self.k,
+                                out_dev, sync)
 
     def forward(self, x: np.ndarray) -> np.ndarray:
         return self.runner.gemv(self.path, self.wq, self.ws_scale, _as_rows(x), self.n, self.k)
@@ -245,6 +264,13 @@ class Int4Linear:
             self.rt.sync()
         return y
 
+    def forward_codes_device(self, codes, rows: int, out_dev=None, sync: bool = False) -> int:
+        """W4A8 GEMV on activations that are already quantised (see ``RT4Linear.forward_codes_device``)."""
+        if self.path != "w4a8":
+            raise ValueError("pre-quantised int8 codes feed the W4A8 path only")
+        return _gemv_w4a8_codes(self.rt, self._runner, self.tag, self.wq, self.ws_f16, codes, rows, self.n, self.k,
+                                out_dev, sync)
+
     def forward(self, x: np.ndarray) -> np.ndarray:
         x = _as_rows(x)
         px = self.ws.upload(self.tag + ".x", x)
@@ -295,15 +321,117 @@ class NVFP4Linear:
         return self.rt.download(out, x.shape[0] * self.n, np.float32).reshape(x.shape[0], self.n)
 
 
+class RMSNorm:
+    """``y = x * rsqrt(mean(x^2) + eps) * w`` (reference model.py:480-524).  ``forward_device`` returns the
+    normalised fp32 rows; ``forward_quant_device`` runs the norm and the W4A8 activation quantiser as one
+    kernel (``rmsnorm_quant_k``, reference tools/gen_rmsnorm_quant.py) and returns the four ``quant_act``
+    outputs, so the layer that follows needs no quantiser launch and the normalised row never reaches memory."""
+
+    def __init__(self, rt: Runtime, dim: int, weight, eps: float = 1e-6, ws: Workspace | None = None,
+                 tag: str | None = None):
+        if dim % 64:
+            raise ValueError(f"RMSNorm dim={dim} must be a multiple of 64")
+        self.rt, self.dim, self.eps = rt, int(dim), float(eps)
+        self.tag = tag or f"rms_{id(self):x}"
+        self._own_ws = ws is None
+        self.ws = ws or Workspace(rt)
+        self.w = self.ws.upload(self.tag + ".w", np.ascontiguousarray(weight, dtype=np.float32))
+
+    def forward_device(self, x_dev: int, rows: int, sync: bool = False) -> int:
+        out = self.ws.buffer(self.tag + ".out", rows * self.dim * 4)
+        self.rt.launch("rmsnorm_fast_k", rows, 64, [out, int(x_dev), self.w, self.dim, self.eps])
+        if sync:
+            self.rt.sync()
+        return out
+
+    def forward_quant_device(self, x_dev: int, rows: int, sync: bool = False):
+        """-> (ae, ao, asc, asu) device pointers: what ``quant_act`` would leave for the normalised rows."""
+        if self.dim % 128:
+            raise ValueError("the fused norm + quantiser needs dim to be a multiple of 128")
+        half, ng4 = rows * self.dim // 2, rows * (self.dim // 128) * 4
+        bufs = [self.ws.buffer(f"{self.tag}.q{i}", n) for i, n in enumerate((half, half, ng4, ng4))]
+        self.rt.launch("rmsnorm_quant_k", rows, 64, bufs + [int(x_dev), self.w, self.dim, self.eps])
+        if sync:
+            self.rt.sync()
+        return tuple(bufs)
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = _as_rows(x)
+        px = self.ws.upload(self.tag + ".x", x)
+        out = self.forward_device(px, x.shape[0], sync=True)
+        return self.rt.download(out, x.shape[0] * self.dim, np.float32).reshape(x.shape[0], self.dim)
+
+
+class SwiGLU:
+    """``y = silu(gate) * up`` (``silu_mul_k``, reference model.py:527-544)."""
+
+    def __init__(self, rt: Runtime, ws: Workspace | None = None, tag: str = "swiglu"):
+        self.rt, self.tag = rt, tag
+        self._own_ws = ws is None
+        self.ws = ws or Workspace(rt)
+
+    def forward_device(self, gate_dev: int, up_dev: int, n: int, out_dev: int | None = None, sync: bool = False) -> int:
+        out = int(out_dev) if out_dev is not None else self.ws.buffer(self.tag + ".out", n * 4)
+        self.rt.launch("silu_mul_k", cdiv(n, 64), 64, [out, int(gate_dev), int(up_dev), n])
+        if sync:
+            self.rt.sync()
+        return out
+
+
+class MLP:
+    """Gated MLP ``down(silu(gate(x)) * up(x))``, every kernel queued back to back (reference
+    model.py:547-579).  When ``down`` is a W4A8 ``Int4Linear`` / ``RT4Linear`` and at most four rows are in
+    flight, the gate and the quantiser of the down projection run as one kernel (``silu_mul_quant_k``): the
+    reference fuses the gate into its f32 GEMV (model.py:1262-1266); with int8 activations the place to fuse
+    it is the quantiser."""
+
+    def __init__(self, rt: Runtime, gate, up, down, ws: Workspace | None = None, tag: str = "mlp", act: str = "silu"):
+        if act != "silu":
+            raise ValueError("MLP wraps the silu gate only")
+        self.rt, self.tag = rt, tag
+        self.gate, self.up, self.down = gate, up, down
+        self.act = SwiGLU(rt, ws, tag + ".act")
+
+    def _fused_down(self, rows: int) -> bool:
+        return rows <= 4 and getattr(self.down, "path", None) == "w4a8" and hasattr(self.down, "forward_codes_device")
+
+    def forward_device(self, x_dev: int, rows: int, sync: bool = False) -> int:
+        h1 = self.gate.forward_device(x_dev, rows, sync=False)
+        h2 = self.up.forward_device(x_dev, rows, sync=False)
+        ffn = self.gate.n
+        if self._fused_down(rows) and ffn % 128 == 0:
+            ws = self.act.ws
+            half, ng4 = rows * ffn // 2, rows * (ffn // 128) * 4
+            codes = [ws.buffer(f"{self.tag}.q{i}", n) for i, n in enumerate((half, half, ng4, ng4))]
+            self.rt.launch2d("silu_mul_quant_k", 1, rows, 64, 1, codes + [h1, h2, ffn])
+            out = self.down.forward_codes_device(codes, rows)
+        else:
+            act = self.act.forward_device(h1, h2, rows * ffn, sync=False)
+            out = self.down.forward_device(act, rows, sync=False)
+        if sync:
+            self.rt.sync()
+        return out
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = _as_rows(x)
+        ws = self.gate.ws
+        px = ws.upload(self.tag + ".in.x", x)
+        out = self.forward_device(px, x.shape[0], sync=True)
+        return self.rt.download(out, x.shape[0] * self.down.n, np.float32).reshape(x.shape[0], self.down.n)
+
+
+__all__ += ["RMSNorm", "SwiGLU", "MLP"]
+
+
 def _out_of_scope(name: str):
     def __init__(self, *a, **kw):
         raise NotImplementedError(
-            f"{name} belongs to the reference's norm/attention/MoE operators, which are outside the "
+            f"{name} belongs to the reference's attention / sampling operators, which are outside the "
             "weight-streaming quantized linear-layer path built here")
     return type(name, (), {"__init__": __init__, "__doc__": f"Not built (outside the linear-layer path): {name}."})
 
 
-for _n in ("F32Linear", "RMSNorm", "SwiGLU", "MLP", "MoECombine", "MoEExperts", "RoPE", "KVCache", "Sampler",
+for _n in ("F32Linear", "MoECombine", "MoEExperts", "RoPE", "KVCache", "Sampler",
            "Attention", "FlashAttention", "TransformerLayer"):
     globals()[_n] = _out_of_scope(_n)
     __all__.append(_n)

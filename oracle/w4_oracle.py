@@ -305,3 +305,28 @@ def rel_err(got: np.ndarray, ref: np.ndarray) -> float:
     ref = np.asarray(ref, dtype=np.float64)
     den = float(np.abs(ref).max()) or 1.0
     return float(np.abs(np.asarray(got, dtype=np.float64) - ref).max()) / den
+
+
+# --------------------------------------------------------------------------
+# the operators either side of the layer
+# --------------------------------------------------------------------------
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """``y = (x * rs) * w`` with ``rs = float32(1 / sqrt(mean(x^2) + eps))``, the mean taken in
+    float64 — the arithmetic of the reference's host check of its fused kernel
+    (tools/gen_rmsnorm_quant.py:288-296); python/k100lc_kernels/model.py:480-481 states the operator."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    ms = (x.astype(np.float64) ** 2).mean(axis=1, keepdims=True)
+    rs = (1.0 / np.sqrt(ms + eps)).astype(np.float32)
+    return (x * rs).astype(np.float32) * w[None, :]
+
+
+def rmsnorm_quant(x: np.ndarray, w: np.ndarray, eps: float) -> dict:
+    """``quant_act(rmsnorm(x))``: reference tools/gen_rmsnorm_quant.py:16-33, 288-306."""
+    return quant_act(rmsnorm(x, w, eps))
+
+
+def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """``gate / (1 + exp(-gate)) * up`` in float32 (reference tools/selftest_all.py:205-223)."""
+    g = np.ascontiguousarray(gate, dtype=np.float32)
+    return (g / (np.float32(1.0) + np.exp(-g)) * np.ascontiguousarray(up, dtype=np.float32)).astype(np.float32)

@@ -85,3 +85,21 @@ def gemm_case(seed: int = 3, n: int = 128, k: int = 512, m: int = 256):
     b = rng.integers(-8, 8, size=(n, k), dtype=np.int32)
     x = rng.standard_normal((m, k)).astype(np.float32)
     return b, x
+
+
+RMSNORM_QUANT_SHAPES = ((1, 128), (2, 256), (1, 512), (3, 1280), (1, 5120))
+
+
+def rmsnorm_case(rows: int, dim: int, seed: int | None = None, gain: float = 2.0, plain_w: bool = False):
+    """x [rows,dim] ~ gain * N(0,1) and a weight vector: uniform [0.5,1.5) as in
+    tools/gen_rmsnorm_quant.py:311-317, or N(0,1) as in tools/selftest_all.py:268-271."""
+    rng = np.random.default_rng(20261012 + 1000 * rows + dim if seed is None else seed)
+    x = rng.standard_normal((rows, dim)).astype(np.float32) * np.float32(gain)
+    w = rng.standard_normal(dim).astype(np.float32) if plain_w else (rng.random(dim).astype(np.float32) + np.float32(0.5))
+    return x, w
+
+
+def silu_case(seed: int = 4, n: int = 1000):
+    """tools/selftest_all.py:214-219."""
+    rng = np.random.default_rng(seed)
+    return rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)

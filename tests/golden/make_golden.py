@@ -7,7 +7,7 @@ Run where the reference checkout is mounted:
     python tests/golden/make_golden.py --reference /path/to/K100LC-kernels
 
 The script imports the reference's ``tools/selftest_all.py``,
-``tools/gen_int4_dot.py`` and ``python/k100lc_kernels/quant.py`` (no device is
+``tools/gen_int4_dot.py``, ``tools/gen_rmsnorm_quant.py`` and ``python/k100lc_kernels/quant.py`` (no device is
 touched: the reference only opens its runtime inside ``main()``), feeds them the
 seeded inputs of ``tests/cases.py`` and stores the outputs plus the SHA-256 of
 the inputs.  The tests re-create the inputs from the same seeds, check the
@@ -37,6 +37,7 @@ def main() -> int:
     sys.path.insert(0, str(ref_root / "python"))
     import selftest_all as st          # reference test oracle
     import gen_int4_dot as gid         # reference W4A16 host reference
+    import gen_rmsnorm_quant as grq    # reference host check of the fused norm + quantiser
     from k100lc_kernels import quant as rq   # reference host pack/convert
 
     out: dict[str, np.ndarray] = {}
@@ -132,6 +133,17 @@ def main() -> int:
             s = max(np.abs(blk).max() / 7.0, 1e-30)
             xq[r, g * 128:(g + 1) * 128] = np.clip(np.rint(blk / s), -8, 7) * s
     put("gemm_w4a4", cases.digest(b, x), c=xq @ b.astype(np.float32).T)
+
+    # ---- the operators either side of the layer: RMSNorm (+ quantiser) and the SiLU gate ----
+    # (tools/gen_rmsnorm_quant.py:288-306 with the shapes of its self-test; tools/selftest_all.py:205-223, 266-279)
+    for rows, dim in cases.RMSNORM_QUANT_SHAPES:
+        x, w = cases.rmsnorm_case(rows, dim)
+        q, s, asum = grq._ref(x, w, 1e-6)
+        put(f"rmsnorm_quant_{rows}x{dim}", cases.digest(x, w), q=q.astype(np.int8), s=s, asum=asum)
+    x, w = cases.rmsnorm_case(4, 256, seed=8, gain=1.0, plain_w=True)
+    put("rmsnorm", cases.digest(x, w), y=(x / np.sqrt((x ** 2).mean(axis=1, keepdims=True) + 1e-5) * w).astype(np.float32))
+    gate, up = cases.silu_case()
+    put("silu_mul", cases.digest(gate, up), y=(st._silu(gate) * up).astype(np.float32))
 
     np.savez_compressed(HERE / "reference_vectors.npz", **out)
     (HERE / "reference_vectors.json").write_text(json.dumps(

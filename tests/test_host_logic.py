@@ -163,7 +163,7 @@ def test_rt4_file_roundtrip(tmp_path):
 
 def test_out_of_scope_operators_say_so():
     import k100lc_kernels as kk
-    for name in ("RMSNorm", "Attention", "MoEExperts", "Sampler"):
+    for name in ("Attention", "FlashAttention", "KVCache", "Sampler"):
         with pytest.raises(NotImplementedError):
             getattr(kk, name)()
 

@@ -142,3 +142,26 @@ def test_quant_edge_cases():
     t[0, :4] = [7.0, 0.5, 1.5, 2.5]
     q4 = O.quant_act4(t)["q"][0, :4]
     assert list(q4) == [7, 0, 2, 2]
+
+
+@pytest.mark.parametrize("rows,dim", cases.RMSNORM_QUANT_SHAPES)
+def test_rmsnorm_quant_oracle_matches_reference(golden, rows, dim):
+    """oracle.rmsnorm_quant against the reference's host check of rmsnorm_quant_k (tools/gen_rmsnorm_quant.py:288-306)."""
+    arr, meta = golden
+    x, w = cases.rmsnorm_case(rows, dim)
+    name = f"rmsnorm_quant_{rows}x{dim}"
+    assert cases.digest(x, w) == meta[name]["inputs_sha256"]
+    q = O.rmsnorm_quant(x, w, 1e-6)
+    assert np.array_equal(q["q"], arr[name + ".q"])
+    assert np.array_equal(q["scale"], arr[name + ".s"]) and np.array_equal(q["gsum"], arr[name + ".asum"])
+
+
+def test_rmsnorm_and_silu_oracle_match_reference(golden):
+    arr, meta = golden
+    x, w = cases.rmsnorm_case(4, 256, seed=8, gain=1.0, plain_w=True)
+    assert cases.digest(x, w) == meta["rmsnorm"]["inputs_sha256"]
+    ref = arr["rmsnorm.y"]
+    assert np.abs(O.rmsnorm(x, w, 1e-5) - ref).max() <= 1e-4 + 1e-5 * max(1.0, float(np.abs(ref).max()))
+    gate, up = cases.silu_case()
+    assert cases.digest(gate, up) == meta["silu_mul"]["inputs_sha256"]
+    assert np.array_equal(O.silu_mul(gate, up), arr["silu_mul.y"])
