@@ -487,7 +487,19 @@ def gemm_timings(rt, st: "Stream", reps: int = 5) -> dict:
                    "frac_of_int8_peak uses 2 x the dense bf16 figure of MEASURED_PEAKS.json")
     if rt.gemm_status() != 0:
         raise RuntimeError("a bounded wait ran out in the GEMM kernel")
-    for ptr in (x, wsc, aq4, aq8, asc, c):
+    # NVFP4 prefill (nvfp4_quant_act over all rows + nvfp4_gemm_kernel): per-16-block integers on mma.sync m16n8k16
+    from k100lc_kernels.quant import f32_to_e4m3_bits
+    nvs = rt.alloc(N * (K // 16))
+    rt.upload(nvs, f32_to_e4m3_bits(np.exp2(rng.uniform(-4.0, 2.0, size=(N, K // 16))).astype(np.float32)))
+    qa, qb, sc16 = rt.alloc(m * K // 2), rt.alloc(m * K // 2), rt.alloc(m * (K // 16) * 4)
+    qn = lambda l: rt.launch2d("nvfp4_quant_act", K // 16, m, 64, 1, [x, qa, qb, sc16, m, K])
+    gn = lambda l: rt.launch2d("nvfp4_gemm_kernel", N // 64, m // 64, 256, 1, [st.wq_l(l), nvs, qa, qb, sc16, c, m, N, K, 0.05])
+    qn(0)
+    ms_g, ms_all = timed(gn), timed(lambda l: (qn(l), gn(l)))
+    out["nvfp4"] = {"gemm_ms": round(ms_g, 4), "quant_plus_gemm_ms": round(ms_all, 4), "gemm_tmac_per_s": round(ops / 2 / ms_g / 1e9, 1),
+                    "gemm_tops": round(ops / ms_g / 1e9, 1),
+                    "what": "nvfp4_gemm_kernel: one int32 per (token, row, 16-block), scaled in fp32 block by block"}
+    for ptr in (x, wsc, aq4, aq8, asc, c, nvs, qa, qb, sc16):
         rt.free(ptr)
     return out
 

@@ -176,6 +176,7 @@ int ensure_init() {
         k = gemm_w4_kernels(&n); add_kernels(k, n);
         k = stream_kernels(&n); add_kernels(k, n);
         k = norm_act_kernels(&n); add_kernels(k, n);
+        k = nvfp4_gemm_kernels(&n); add_kernels(k, n);
     }
     e.ready = true;
     return 0;
@@ -194,6 +195,7 @@ void ensure_table() {
     k = gemm_w4_kernels(&n); add_kernels(k, n);
     k = stream_kernels(&n); add_kernels(k, n);
     k = norm_act_kernels(&n); add_kernels(k, n);
+    k = nvfp4_gemm_kernels(&n); add_kernels(k, n);
 }
 
 // a write into [p, p+n) makes any validated layer table it touches unvalidated

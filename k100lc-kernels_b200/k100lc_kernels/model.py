@@ -283,7 +283,7 @@ class NVFP4Linear:
     f32 global scale; activations are quantised to int8 per 16-block by
     ``nvfp4_quant_act`` and multiplied by ``nvfp4_gemv<M,1>``.  The reference offers this
     path only as raw launches (docs/KERNEL_CALLING.md:637-646); the class follows the
-    contract of ``Int4Linear``.  Row counts above 4 run in chunks of 4."""
+    contract of ``Int4Linear``.  Row counts above 4 go to the prefill GEMM (``nvfp4_gemm_kernel``)."""
 
     def __init__(self, rt: Runtime, n: int, k: int, codes, block_scales, gscale: float,
                  ws: Workspace | None = None, tag: str | None = None):
@@ -308,6 +308,18 @@ class NVFP4Linear:
 
     def forward_device(self, x_dev: int, rows: int, sync: bool = False, out_dev=None) -> int:
         y = int(out_dev) if out_dev is not None else self.ws.buffer(self.tag + ".y", rows * self.n * 4)
+        if rows > 4 and self.k % 128 == 0:
+            # prefill: one quantiser launch over all rows, then the GEMM (the weights are streamed once)
+            k, half, nb4 = self.k, self.k // 2, (self.k // 16) * 4
+            qa = self.ws.buffer(self.tag + ".gqa", rows * half)
+            qb = self.ws.buffer(self.tag + ".gqb", rows * half)
+            sc = self.ws.buffer(self.tag + ".gsc", rows * nb4)
+            self.rt.launch2d("nvfp4_quant_act", k // 16, rows, 64, 1, [int(x_dev), qa, qb, sc, rows, k])
+            self.rt.launch2d("nvfp4_gemm_kernel", cdiv(self.n, 64), cdiv(rows, 64), 256, 1,
+                             [self.wq, self.wsb, qa, qb, sc, y, rows, self.n, k, self.gscale])
+            if sync:
+                self.rt.sync()
+            return y
         for r0 in range(0, rows, 4):
             self._chunk(int(x_dev) + r0 * self.k * 4, min(4, rows - r0), y + r0 * self.n * 4)
         if sync:

@@ -156,3 +156,65 @@ def test_gemm_full_size_accumulators(rt, a8):
             assert np.array_equal(acc, ref["acc"]), f"int32 accumulators differ in window {(m0, m1, n0, n1)}"
             c = b.get(pc, m * n).reshape(m, n)[m0:m1, n0:n1]
             assert O.rel_err(c, ref["c"]) < REL
+
+
+def _nvfp4_gemm(rt, L, x, name="nvfp4_gemm_kernel", dump=False):
+    n, k, m = L["n"], L["k"], x.shape[0]
+    q = O.nvfp4_quant_act(x)
+    with Bufs(rt) as b:
+        args = [b.put(L["wq"]), b.put(L["ws"]), b.put(q["even"]), b.put(q["odd"]), b.put(q["scale"])]
+        pc = b.zeros(m * n, np.float32, np.nan)
+        args += [pc, m, n, k, float(L["gscale"])]
+        acc = None
+        if dump:
+            pi = b.zeros(m * n * (k // 16), np.int32, -7)
+            rt.launch("nvfp4_gemm_iacc", 1, 256, args + [pi])
+            acc = b.get(pi, m * n * (k // 16), np.int32).reshape(m, n, -1)
+        else:
+            rt.launch2d(name, -(-n // 64), -(-m // 64), 256, 1, args)
+        c = b.get(pc, m * n).reshape(m, n)
+    return c, acc, q
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 128, 128), (200, 72, 512), (128, 384, 1280), (5, 19, 256)])
+def test_nvfp4_gemm_accumulators_and_output(rt, m, n, k):
+    """nvfp4_gemm_kernel (no reference test exists for it: parity unpinned, the oracle is nvfp4_gemv's formula on M rows):
+    the int32 of every (token, row, 16-block) bit for bit, C within 1e-5, ragged M and N included."""
+    L = synth.nvfp4_layer(n, k, m, seed=1700 + m)
+    c, acc, q = _nvfp4_gemm(rt, L, L["x"], dump=True)
+    ref = O.nvfp4_gemv(L["wq"], L["ws"], q["q"], q["scale"], L["gscale"])
+    assert np.array_equal(acc, ref["acc"])
+    assert O.rel_err(c, ref["y"]) < REL
+    for name in ("nvfp4_gemm_kernel", "nvfp4_gemm_kernel_ng"):
+        c2, _, _ = _nvfp4_gemm(rt, L, L["x"], name=name)
+        assert np.array_equal(c2, c)
+    # the GEMM and the GEMV agree row by row
+    if m <= 8:
+        with Bufs(rt) as b:
+            py = b.zeros(m * n, np.float32, np.nan)
+            for r0 in range(0, m, 4):
+                mm = min(4, m - r0)
+                rt.launch(f"nvfp4_gemv<{mm},1>", -(-n // 4), 256,
+                          [b.put(L["wq"]), b.put(L["ws"]), b.put(q["even"][r0:r0 + mm]), b.put(q["odd"][r0:r0 + mm]),
+                           b.put(q["scale"][r0:r0 + mm]), py + r0 * n * 4, n, k, float(L["gscale"])])
+            assert O.rel_err(b.get(py, m * n).reshape(m, n), c) < 1e-6
+
+
+def test_nvfp4_gemm_full_size_sampled_and_linear_prefill(rt):
+    """M=2048, N=17408, K=5120 (seed 2): C on sampled token rows x sampled channels against the oracle on exactly those;
+    NVFP4Linear sends row counts above 4 to the GEMM."""
+    from k100lc_kernels import NVFP4Linear, Workspace
+    L = synth.nvfp4_layer(m=1, seed=2)
+    m = 2048
+    x = np.random.default_rng(21).standard_normal((m, L["k"])).astype(np.float32)
+    c, _, q = _nvfp4_gemm(rt, L, x)
+    assert np.isfinite(c).all()
+    rng = np.random.default_rng(0)
+    mi = np.sort(rng.choice(m, 24, replace=False))
+    ni = np.sort(rng.choice(L["n"], 256, replace=False))
+    ref = O.nvfp4_gemv(L["wq"][ni], L["ws"][ni], q["q"][mi], q["scale"][mi], L["gscale"])["y"]
+    assert O.rel_err(c[np.ix_(mi, ni)], ref) < REL
+    with Workspace(rt) as ws:
+        lin = NVFP4Linear(rt, L["n"], L["k"], L["wq"], L["ws"], L["gscale"], ws, "nvl")
+        y = lin.forward(x[:70])
+    assert np.array_equal(y, c[:70])
