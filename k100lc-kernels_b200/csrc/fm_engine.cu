@@ -177,6 +177,7 @@ int ensure_init() {
         k = stream_kernels(&n); add_kernels(k, n);
         k = norm_act_kernels(&n); add_kernels(k, n);
         k = nvfp4_gemm_kernels(&n); add_kernels(k, n);
+        k = moe_kernels(&n); add_kernels(k, n);
     }
     e.ready = true;
     return 0;
@@ -196,6 +197,7 @@ void ensure_table() {
     k = stream_kernels(&n); add_kernels(k, n);
     k = norm_act_kernels(&n); add_kernels(k, n);
     k = nvfp4_gemm_kernels(&n); add_kernels(k, n);
+    k = moe_kernels(&n); add_kernels(k, n);
 }
 
 // a write into [p, p+n) makes any validated layer table it touches unvalidated

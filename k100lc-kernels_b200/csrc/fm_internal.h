@@ -58,6 +58,7 @@ const KernelEntry* gemm_w4_kernels(int* n);
 const KernelEntry* stream_kernels(int* n);
 const KernelEntry* norm_act_kernels(int* n);
 const KernelEntry* nvfp4_gemm_kernels(int* n);
+const KernelEntry* moe_kernels(int* n);
 
 // Launchers without the engine (no allocation registry, no engine stream): the caller
 // owns every buffer and names the stream.  Same kernels as the by-name entries.

@@ -432,7 +432,116 @@ class MLP:
         return self.rt.download(out, x.shape[0] * self.down.n, np.float32).reshape(x.shape[0], self.down.n)
 
 
-__all__ += ["RMSNorm", "SwiGLU", "MLP"]
+class MoECombine:
+    """``y[r,:] = sum_e weights[r,e] * exp_out[e,r,:]`` (``moe_combine_k``, reference model.py:582-618).
+    ``slot(e)`` is where expert e writes its ``[rows, dim]`` output."""
+
+    def __init__(self, rt: Runtime, rows: int, dim: int, n_exp: int, ws: Workspace | None = None, tag: str = "moe"):
+        self.rt, self.rows, self.dim, self.n_exp, self.tag = rt, int(rows), int(dim), int(n_exp), tag
+        self._own_ws = ws is None
+        self.ws = ws or Workspace(rt)
+        self.exp_out = self.ws.buffer(tag + ".exp", rows * n_exp * dim * 4)
+        self.weights = self.ws.buffer(tag + ".w", rows * n_exp * 4)
+        self.out = self.ws.buffer(tag + ".out", rows * dim * 4)
+
+    def slot(self, e: int) -> int:
+        return self.exp_out + e * self.rows * self.dim * 4
+
+    def forward_device(self, weights_dev: int | None = None, sync: bool = False) -> int:
+        w = int(weights_dev) if weights_dev is not None else self.weights
+        self.rt.launch("moe_combine_k", self.rows, 64, [self.out, self.exp_out, w, self.n_exp, self.rows, self.dim])
+        if sync:
+            self.rt.sync()
+        return self.out
+
+    def forward(self, exp_out: np.ndarray, weights: np.ndarray) -> np.ndarray:
+        self.rt.upload(self.exp_out, np.ascontiguousarray(exp_out, dtype=np.float32))
+        self.rt.upload(self.weights, np.ascontiguousarray(weights, dtype=np.float32))
+        out = self.forward_device(sync=True)
+        return self.rt.download(out, self.rows * self.dim, np.float32).reshape(self.rows, self.dim)
+
+
+class MoEExperts:
+    """Mixture-of-experts forward over token buckets (reference model.py:620-720): the host sorts the
+    (token, expert) pairs of the router by expert, ``gather_rows_k`` copies each pair's input row into its
+    expert's contiguous bucket, every non-empty expert runs its linear layer on its own bucket only — an
+    ``Int4Linear`` / ``RT4Linear`` / ``NVFP4Linear`` / ``DotLinear`` streams its weights once for the whole
+    bucket — and ``moe_combine_gather_k`` adds the weighted expert rows back per token."""
+
+    def __init__(self, rt: Runtime, experts, rows: int, dim: int, out_dim: int, topk: int,
+                 ws: Workspace | None = None, tag: str = "moe_experts"):
+        if dim % 4 or out_dim % 4:
+            raise ValueError(f"dim={dim} and out_dim={out_dim} must be multiples of 4 (128-bit row copies)")
+        self.rt, self.experts = rt, list(experts)
+        self.n_exp = len(self.experts)
+        self.rows, self.dim, self.out_dim, self.topk = int(rows), int(dim), int(out_dim), int(topk)
+        if topk > self.n_exp:
+            raise ValueError(f"topk={topk} exceeds the number of experts {self.n_exp}")
+        self.tag = tag
+        self._own_ws = ws is None
+        self.ws = ws or Workspace(rt)
+        cap = self.rows * self.topk
+        self.x_bucket = self.ws.buffer(tag + ".xb", cap * self.dim * 4)
+        self.exp_bucket = self.ws.buffer(tag + ".eb", cap * self.out_dim * 4)
+        self.idx = self.ws.buffer(tag + ".idx", cap * 4)
+        self.base = self.ws.buffer(tag + ".base", cap * 4)
+        self.weights = self.ws.buffer(tag + ".w", cap * 4)
+        self.y = self.ws.buffer(tag + ".y", self.rows * self.out_dim * 4)
+
+    def route(self, ids, weights):
+        """-> ``(bucket_rows, base, weights, offsets)``: the token row of every bucket slot (buckets laid out
+        expert after expert), the bucket slot of every (token, choice) pair (0 where the pair is unused —
+        expert id out of range or weight 0, whose weight is then 0 as well), the f32 weights with the unused
+        pairs zeroed, and the start of every expert's bucket."""
+        ids = np.asarray(ids)
+        w = np.array(weights, dtype=np.float32)
+        if ids.shape != (self.rows, self.topk) or w.shape != ids.shape:
+            raise ValueError(f"router output {ids.shape} does not match ({self.rows}, {self.topk})")
+        valid = (ids >= 0) & (ids < self.n_exp) & (w != 0.0)
+        w[~valid] = 0.0
+        pair = np.flatnonzero(valid.reshape(-1))
+        ex = ids.reshape(-1)[pair].astype(np.int64)
+        order = np.argsort(ex, kind="stable")                    # bucket order: by expert, then by pair index
+        counts = np.bincount(ex, minlength=self.n_exp)
+        offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+        base = np.zeros(self.rows * self.topk, dtype=np.uint32)
+        base[pair[order]] = np.arange(pair.size, dtype=np.uint32)
+        bucket_rows = (pair[order] // self.topk).astype(np.uint32)
+        return bucket_rows, base.reshape(self.rows, self.topk), w, offsets
+
+    def forward_device(self, x_dev: int, rows: int, ids, weights, sync: bool = False) -> int:
+        if rows != self.rows:
+            raise ValueError(f"built for {self.rows} rows, got {rows}")
+        bucket_rows, base, w, offsets = self.route(ids, weights)
+        total = int(bucket_rows.size)
+        if total:
+            self.rt.upload(self.idx, bucket_rows)
+            self.rt.launch("gather_rows_k", total, 64, [self.x_bucket, int(x_dev), self.idx, total, self.dim])
+            for e, expert in enumerate(self.experts):
+                lo, n = int(offsets[e]), int(offsets[e + 1] - offsets[e])
+                if n:
+                    expert.forward_device(self.x_bucket + lo * self.dim * 4, n,
+                                          out_dev=self.exp_bucket + lo * self.out_dim * 4, sync=False)
+        self.rt.upload(self.base, base)
+        self.rt.upload(self.weights, w)
+        # (with no pair in use every weight is 0 and the combine writes zeros; slot 0 of the bucket is read,
+        # which is inside the buffer whatever it holds)
+        if not total:
+            self.rt.memset(self.exp_bucket, 0, self.out_dim * 4)
+        self.rt.launch("moe_combine_gather_k", rows, 64,
+                       [self.y, self.exp_bucket, self.weights, self.base, self.topk, rows, self.out_dim])
+        if sync:
+            self.rt.sync()
+        return self.y
+
+    def forward(self, x: np.ndarray, ids, weights) -> np.ndarray:
+        x = _as_rows(x)
+        px = self.ws.upload(self.tag + ".x", x)
+        out = self.forward_device(px, x.shape[0], ids, weights, sync=True)
+        return self.rt.download(out, x.shape[0] * self.out_dim, np.float32).reshape(x.shape[0], self.out_dim)
+
+
+__all__ += ["RMSNorm", "SwiGLU", "MLP", "MoECombine", "MoEExperts"]
 
 
 def _out_of_scope(name: str):
@@ -443,7 +552,7 @@ def _out_of_scope(name: str):
     return type(name, (), {"__init__": __init__, "__doc__": f"Not built (outside the linear-layer path): {name}."})
 
 
-for _n in ("F32Linear", "MoECombine", "MoEExperts", "RoPE", "KVCache", "Sampler",
+for _n in ("F32Linear", "RoPE", "KVCache", "Sampler",
            "Attention", "FlashAttention", "TransformerLayer"):
     globals()[_n] = _out_of_scope(_n)
     __all__.append(_n)
