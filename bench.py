@@ -507,6 +507,66 @@ def gemm_timings(rt, st: "Stream", reps: int = 5) -> dict:
 CPU_SAMPLE_LAYERS = 4      # layers of the stream that the CPU legs time per step (0.9 s per layer on 16 cores)
 
 
+# The layer table of the checkpoint the reference measured its INT4 path on (docs/INT4.md:170-181): 400 quantized
+# linear layers of 7 shapes, 12.54 GB of codes and scales.  (N, K, layers)
+SHAPE_TABLE = ((17408, 5120, 128), (5120, 17408, 64), (10240, 5120, 48), (5120, 6144, 64), (6144, 5120, 48),
+               (12288, 5120, 16), (1024, 5120, 32))
+
+
+def shape_table_timings(rt, reps: int = 5) -> dict:
+    """One decoded token over the 400-layer / 7-shape table with synthetic weights, per layer `quant_act` +
+    `gemv_w4a8<1,false,1>` (W4A8) or `int4_dot_k` + `reduce_blocks_k` (W4A16, the path the reference timed it on: 91.9 ms
+    per token there), each as one CUDA graph of by-name launches.  Every layer has its own weights (12.5 GB resident)."""
+    rng = np.random.default_rng(7)
+    from k100lc_kernels import DotLinear, Workspace
+    total_bytes = sum((n * k // 2 + n * (k // 128) * 2) * c for n, k, c in SHAPE_TABLE)
+    kmax, nmax = max(k for _, k, _ in SHAPE_TABLE), max(n for n, _, _ in SHAPE_TABLE)
+    blk = rng.integers(0, 256, size=32 << 20, dtype=np.uint8)                      # 32 MiB of random codes, tiled
+    x = rt.alloc(kmax * 4)
+    rt.upload(x, rng.standard_normal(kmax).astype(np.float32))
+    y = rt.alloc(nmax * 4)
+    ae, ao, asc, asu = rt.alloc(kmax // 2), rt.alloc(kmax // 2), rt.alloc(kmax // 128 * 4), rt.alloc(kmax // 128 * 4)
+    layers = []
+    for n, k, c in SHAPE_TABLE:
+        sc16 = (np.abs(rng.standard_normal((n, k // 128))) * 0.01 + 1e-3).astype(np.float16)
+        for _ in range(c):
+            wq, ws = rt.alloc(n * k // 2), rt.alloc(n * (k // 128) * 2)
+            for off in range(0, n * k // 2, blk.size):
+                rt.upload(wq + off, blk[:min(blk.size, n * k // 2 - off)])
+            rt.upload(ws, sc16)
+            layers.append((n, k, wq, ws))
+    order = rng.permutation(len(layers))                   # shapes interleaved, as in a model
+    out = {"layers": len(layers), "bytes": total_bytes}
+    rt.graph_begin()
+    for i in order:
+        n, k, wq, ws = layers[i]
+        rt.launch("quant_act", k // 128, 32, [x, ae, ao, asc, asu, 1, k])
+        rt.launch("gemv_w4a8<1,false,1>", -(-n // 4), 256, [wq, ws, ae, ao, asc, asu, y, n, k])
+    g = rt.graph_end()
+    ms = time_graph(rt, g, reps, 3, lambda: None)
+    rt.graph_free(g)
+    out["w4a8_by_name"] = {"ms_per_token": round(ms, 4), "gb_per_s": round(total_bytes / ms / 1e6, 1)}
+    per_shape = {}
+    for n, k, c in SHAPE_TABLE:                            # each shape on its own (its layers rotate: > L2 except the smallest)
+        mine = [l for l in layers if l[0] == n and l[1] == k]
+        rt.graph_begin()
+        for _n, _k, wq, ws in mine:
+            rt.launch("quant_act", k // 128, 32, [x, ae, ao, asc, asu, 1, k])
+            rt.launch("gemv_w4a8<1,false,1>", -(-n // 4), 256, [wq, ws, ae, ao, asc, asu, y, n, k])
+        g = rt.graph_end()
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / len(mine)
+        rt.graph_free(g)
+        per_shape[f"{n}x{k}"] = {"layers": c, "us_per_layer": round(us, 3),
+                                 "gb_per_s": round((n * k // 2 + n * (k // 128) * 2) / us / 1e3, 1)}
+    out["w4a8_per_shape"] = per_shape
+    for _n, _k, wq, ws in layers:
+        rt.free(wq)
+        rt.free(ws)
+    for ptr in (x, y, ae, ao, asc, asu):
+        rt.free(ptr)
+    return out
+
+
 def cpu_sample(nl: int):
     """The first `nl` layers of the stream as the oracle takes them, and one pass over them
     (quant_act + W4A8 GEMV per layer in NumPy).  Both CPU legs — `cpu_baseline` inside the GPU arm and
@@ -694,6 +754,12 @@ def run_ours(args) -> int:
         paths = path_timings(rt, st, 5) if (args.paths and world == 1) else None   # single-GPU diagnostics
         gemm = gemm_timings(rt, st) if (args.paths and world == 1) else None
         cpu = cpu_baseline(args.cpu_layers) if (world == 1 and args.cpu_layers > 0) else None
+        shapes = None
+        if args.paths and world == 1 and args.layers >= 400:
+            # the stream's 18.4 GB go first: 12.5 GB more for the second workload's own weights
+            for ptr in (st.wq, st.ws):
+                rt.free(ptr)
+            shapes = shape_table_timings(rt)
         line = {
             "metric": METRIC, "value": round(total_bytes / ms_step / 1e6, 1), "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
@@ -738,7 +804,8 @@ def run_ours(args) -> int:
                          "traffic": int(round((1103145000 + 5141000) / 24 * bytes_per_launch / LAYER_BYTES)) if fused else None,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 24-layer launch of the "
                                            "same kernel, scaled by the layer count" if fused else None},
-            "cpu_baseline": cpu, "clocks": clocks.summary(), "paths_m1": paths, "prefill_gemm_m2048": gemm, "setup_seconds": round(setup_s, 1),
+            "cpu_baseline": cpu, "clocks": clocks.summary(), "paths_m1": paths, "prefill_gemm_m2048": gemm,
+            "shape_table_400_layers": shapes, "setup_seconds": round(setup_s, 1),
         }
     if line is not None:
         print(json.dumps(line), flush=True)

@@ -444,17 +444,26 @@ struct Nvfp4Mma {
                 const uint8_t* st = c.ring + (size_t)s * STAGE;
                 uint4 xa[GPW], xb[GPW];
                 uint32_t sba[GPW], sbb[GPW];             // E4M3 bytes of the lane's two blocks, rows g and g + 8
-#pragma unroll
-                for (int j = 0; j < GPW; j++) {
+                auto load_chunk = [&](int j) {
                     const int gg = j * CW + w;
                     xa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * PITCH + gg * 64 + t * 16);
                     xb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * PITCH + gg * 64 + t * 16);
                     sba[j] = *reinterpret_cast<const unsigned short*>(st + STAGE_W + g * SCB + gg * 8 + 2 * t);
                     sbb[j] = *reinterpret_cast<const unsigned short*>(st + STAGE_W + (g + 8) * SCB + gg * 8 + 2 * t);
+                };
+                if (NGROUPS == 1) {                      // registers to spare: everything in flight at once
+#pragma unroll
+                    for (int j = 0; j < GPW; j++) load_chunk(j);
+                } else {
+                    load_chunk(0);
                 }
                 float fa = 0.f, fb = 0.f;
 #pragma unroll
                 for (int j = 0; j < GPW; j++) {
+                    if (NGROUPS > 1) {                   // one chunk ahead only (96 registers per thread with 18 warps)
+                        if (j + 1 < GPW) load_chunk(j + 1);
+                        asm volatile("" ::: "memory");
+                    }
                     const uint32_t wa[4] = {xa[j].x, xa[j].y, xa[j].z, xa[j].w}, wb[4] = {xb[j].x, xb[j].y, xb[j].z, xb[j].w};
 #pragma unroll
                     for (int blk = 0; blk < 2; blk++) {

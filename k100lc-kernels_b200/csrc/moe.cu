@@ -37,10 +37,10 @@ moe_combine_kernel(float* __restrict__ y, const float* __restrict__ src, const f
             const size_t row = GATHER ? (size_t)base[r * n_sel + e] : (size_t)e * rows + r;
             const float4 v = reinterpret_cast<const float4*>(src + row * dim)[i];
             const float we = w[r * n_sel + e];
-            acc.x += we * v.x;
-            acc.y += we * v.y;
-            acc.z += we * v.z;
-            acc.w += we * v.w;
+            acc.x = __fadd_rn(acc.x, __fmul_rn(we, v.x));       // product rounded first, like the reference's host loop
+            acc.y = __fadd_rn(acc.y, __fmul_rn(we, v.y));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(we, v.z));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(we, v.w));
         }
         reinterpret_cast<float4*>(y + (size_t)r * dim)[i] = acc;
     }

@@ -196,3 +196,41 @@ def test_ct_int4_safetensors_reader(tmp_path):
         CTInt4Layer("missing.layer", tmp_path)
     with pytest.raises(ValueError):
         st.read("other.bias", 20, 20)
+
+
+def test_int4_manifest_round_trip(tmp_path):
+    """The manifest of a synthetic two-file checkpoint names every layer with absolute offsets that read back the
+    layer's bytes, pins the file sizes, and aggregates the per-shape table."""
+    from k100lc_kernels import int4_manifest as im
+    from k100lc_kernels.ct_int4 import write_safetensors
+    rng = np.random.default_rng(5)
+    layers = {"model.layers.0.mlp.gate_proj": (24, 256), "model.layers.0.mlp.down_proj": (16, 384),
+              "model.layers.1.mlp.gate_proj": (24, 256)}
+    blobs = {}
+    for i, (name, (n, k)) in enumerate(layers.items()):
+        packed = rng.integers(0, 2**31, size=(n, k // 8)).astype(np.int32)
+        scale = rng.integers(0, 2**16, size=(n, k // 128)).astype(np.uint16)
+        blobs[name] = (packed, scale)
+        t = {name + ".weight_packed": ("I32", packed), name + ".weight_scale": ("BF16", scale),
+             name + ".weight_shape": ("I64", np.array([n, k], np.int64)), f"pad{i}": ("F32", np.zeros(3 + i, np.float32))}
+        files = tmp_path / ("model-0000%d.safetensors" % (1 + i // 2))
+        if files.exists():                                   # second layer of the same file: rewrite with both
+            prev_name = list(layers)[i - 1]
+            pp, ps = blobs[prev_name]
+            t = {prev_name + ".weight_packed": ("I32", pp), prev_name + ".weight_scale": ("BF16", ps), **t}
+        write_safetensors(files, t)
+    rows = im.write_manifest(tmp_path, tmp_path / "m.tsv")
+    assert [r.name for r in rows] == sorted(layers)
+    back = im.read_manifest(tmp_path / "m.tsv", tmp_path)
+    assert back == rows
+    for r in back:
+        packed, scale = blobs[r.name]
+        p, s = im.read_layer(r, tmp_path)
+        assert p == packed.tobytes() and s == scale.tobytes()
+        p2, s2 = im.read_layer(r, tmp_path, 3, 5)
+        assert p2 == packed[3:8].tobytes() and s2 == scale[3:8].tobytes()
+    assert im.shape_table(rows)[0][:3] == (24, 256, 2)
+    with open(tmp_path / "model-00001.safetensors", "ab") as f:   # a changed file voids the offsets
+        f.write(b"x")
+    with pytest.raises(ValueError, match="regenerate"):
+        im.read_manifest(tmp_path / "m.tsv", tmp_path)
