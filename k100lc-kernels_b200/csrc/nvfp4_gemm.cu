@@ -60,7 +60,7 @@ struct Prefetch {                  // one chunk on its way from global memory to
 };
 
 template <bool DUMP>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, DUMP ? 1 : 2)
 nvfp4_gemm_kernel(const GemmNvParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     Stage* st = reinterpret_cast<Stage*>(smem_raw);

@@ -149,9 +149,13 @@ __device__ __forceinline__ void run_producer(const Cta& c, const typename P::Par
     // A layer's codes are copied right before its first stage, into tile l % NACT: that tile was last used
     // by layer l - NACT, and the ring keeps the consumers at most STAGES stages behind, so with
     // NACT > STAGES / (stages per layer) + 1 tiles the copy never waits for them (the launcher picks NACT).
+    // The table entries of the next two layers are requested ahead of their use: with one stage per layer (a
+    // row shard of eight GPUs) a dependent 32-byte load per layer would otherwise cost this thread a trip to
+    // L2 — most of a stage time — before it can issue anything.
     int cc = 0;
-    for (int l = 0; ok && l < p.nlayers; l++) {
-        const StreamLayer lay = get_layer(p, l);
+    StreamLayer lay = get_layer(p, 0), lay1 = get_layer(p, min(1, p.nlayers - 1)), lay2;
+    for (int l = 0; ok && l < p.nlayers; l++, lay = lay1, lay1 = lay2) {
+        lay2 = get_layer(p, min(l + 2, p.nlayers - 1));
         if (!P::ACT_IN_STAGE && !copy_tile(l)) { ok = false; break; }
         for (int j = 0; j < c.nst; j++, cc++) {
             const int s = cc % P::STAGES;
@@ -199,9 +203,12 @@ template <class P>
 __device__ __forceinline__ void run_writer(const Cta& c) {
     const StreamParams& p = *c.p;
     if (!c.tiled) return;
+    float* y_next = get_layer(p, 0).y;                   // requested a layer ahead (see the producer)
     for (int l = 0; l < p.nlayers; l++) {
+        float* y_l = y_next;
+        y_next = get_layer(p, min(l + 1, p.nlayers - 1)).y;
         if (!cta_wait(c, &c.bars->ydone[l & 1], (l >> 1) & 1, 8)) return;
-        write_out<P::M>(p, c.ytile + (l & 1) * kOutCap, get_layer(p, l).y + p.row_base + c.r0, c.r1 - c.r0, c.lane);
+        write_out<P::M>(p, c.ytile + (l & 1) * kOutCap, y_l + p.row_base + c.r0, c.r1 - c.r0, c.lane);
         __syncwarp();
         if (c.lane == 0) mbar_arrive(&c.bars->yfree[l & 1]);
         if (p.flags) {
