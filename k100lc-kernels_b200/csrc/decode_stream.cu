@@ -35,6 +35,11 @@ __device__ __forceinline__ void mma_u8(int (&c)[4], uint32_t a0, uint32_t a1, ui
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// D = A * B (no accumulator input: the first MMA of a chain needs no zeroed registers)
+__device__ __forceinline__ void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 struct PlainParams {
     StreamParams s;
 };
@@ -467,15 +472,22 @@ struct Nvfp4Mma {
                     const uint32_t wa[4] = {xa[j].x, xa[j].y, xa[j].z, xa[j].w}, wb[4] = {xb[j].x, xb[j].y, xb[j].z, xb[j].w};
 #pragma unroll
                     for (int blk = 0; blk < 2; blk++) {
-                        int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
+                        int cp[4], cn[4];
 #pragma unroll
                         for (int h = 0; h < 2; h++) {
                             const int q = blk * 2 + h;
                             const uint32_t pa = wa[q], pb = wb[q], na = pa ^ 0x88888888u, nb = pb ^ 0x88888888u;
-                            mma_s8(cp, prmt(kTabLo, kTabHi, pa), prmt(kTabLo, kTabHi, pb), prmt(kTabLo, kTabHi, pa >> 16),
-                                   prmt(kTabLo, kTabHi, pb >> 16), b0[j][q], b1[j][q]);
-                            mma_s8(cn, prmt(kTabLo, kTabHi, na), prmt(kTabLo, kTabHi, nb), prmt(kTabLo, kTabHi, na >> 16),
-                                   prmt(kTabLo, kTabHi, nb >> 16), b0[j][q], b1[j][q]);
+                            const uint32_t p0 = prmt(kTabLo, kTabHi, pa), p1 = prmt(kTabLo, kTabHi, pb);
+                            const uint32_t p2 = prmt(kTabLo, kTabHi, pa >> 16), p3 = prmt(kTabLo, kTabHi, pb >> 16);
+                            const uint32_t n0 = prmt(kTabLo, kTabHi, na), n1 = prmt(kTabLo, kTabHi, nb);
+                            const uint32_t n2 = prmt(kTabLo, kTabHi, na >> 16), n3 = prmt(kTabLo, kTabHi, nb >> 16);
+                            if (h == 0) {
+                                mma_s8_first(cp, p0, p1, p2, p3, b0[j][q], b1[j][q]);
+                                mma_s8_first(cn, n0, n1, n2, n3, b0[j][q], b1[j][q]);
+                            } else {
+                                mma_s8(cp, p0, p1, p2, p3, b0[j][q], b1[j][q]);
+                                mma_s8(cn, n0, n1, n2, n3, b0[j][q], b1[j][q]);
+                            }
                         }
                         const int ia = cp[0] - cn[0], ib = cp[2] - cn[2];       // rows g, g + 8, column 2t
                         const float sact = blk ? asc[j].y : asc[j].x;
@@ -511,7 +523,7 @@ struct Nvfp4Mma {
 
 // dp4a consumer of the same format: one warp per row of a stage, the arithmetic of nvfp4_gemv<1,1>
 // (I = dp4a(pos) - dp4a(neg) per packed word, lane l owns the words l, l + 32, ..).
-template <int STAGES_, int NACT_>
+template <int STAGES_, int NACT_, bool DUMP>
 struct Nvfp4Dp4a {
     using Params = Nvfp4Params;
     static constexpr int M = 1, STAGES = STAGES_, NGROUPS = 1, NACT = NACT_;
@@ -571,6 +583,11 @@ struct Nvfp4Dp4a {
                         i1 = dot8_e2m1(wv[it].w, a1[it].z, a1[it].w, i1);
                         acc = fmaf((float)i0, lut[sb[it] & 0xFFu] * asc[it].x, acc);
                         acc = fmaf((float)i1, lut[(sb[it] >> 8) & 0xFFu] * asc[it].y, acc);
+                        if (DUMP) {
+                            int* d = p.iacc + ((size_t)l * p.rows + row) * NB + ((it * 128 + lane * 4) >> 1);
+                            d[0] = i0;
+                            d[1] = i1;
+                        }
                     }
                 }
                 consumed(acc);                                  // release only after the loaded data has been used
@@ -908,7 +925,7 @@ int launch_w4a8_stream_m(const LaunchCtx& c, const uint64_t* a) {
 // [rows][K/16] (the table must have been validated with room for them: fm_stream_table records how many bytes follow
 // every ws pointer inside its allocation); qa / qb / sc are nvfp4_quant_act's outputs for all layers: [nlayers][K/2],
 // [nlayers][K/2], [nlayers][K/16].  nvfp4_decode_stream_iacc(..., flags, iacc): iacc int32 [nlayers][rows][K/16].
-// $FM_NVFP4_CFG=1 keeps the dp4a consumer.
+// $FM_NVFP4_CFG=0 / 2 select the tensor-core consumer (one / two groups) for the run and for the dump.
 template <bool DUMP>
 int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = DUMP ? "nvfp4_decode_stream_iacc" : "nvfp4_decode_stream";
@@ -930,16 +947,19 @@ int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
     FM_RANGE(p.ae, (size_t)p.nlayers * (p.K / 2), kn, "qa");
     FM_RANGE(p.ao, (size_t)p.nlayers * (p.K / 2), kn, "qb");
     FM_RANGE(p.asc, (size_t)p.nlayers * (p.K / 16) * 4, kn, "sc");
+    const int cfg = env_or("FM_NVFP4_CFG", 1);
     if (DUMP) {
         p.iacc = arg_ptr<int>(a[13]);
         FM_REQUIRE(aligned(p.iacc, 4), kn, "misaligned accumulator dump");
         FM_RANGE(p.iacc, (size_t)p.nlayers * p.rows * (p.K / 16) * 4, kn, "iacc");
-        return run_policy<Nvfp4Mma<4, 1, 2, true>>(kn, c, pp);
+        return cfg == 1 ? run_policy<Nvfp4Dp4a<5, 2, true>>(kn, c, pp) : run_policy<Nvfp4Mma<4, 1, 2, true>>(kn, c, pp);
     }
-    switch (env_or("FM_NVFP4_CFG", 0)) {
-        case 1: return run_policy<Nvfp4Dp4a<5, 2>>(kn, c, pp);
-        case 2: return run_policy<Nvfp4Mma<4, 2, 2, false>>(kn, c, pp);      // two consumer groups
-        default: return run_policy<Nvfp4Mma<4, 1, 2, false>>(kn, c, pp);
+    // Default: the dp4a consumer.  Measured per 17408 x 5120 layer (64 layers per launch, burst): dp4a 10.1 us,
+    // tensor-core consumer 10.2 (two groups) - 10.9 us (one group): both are bound by the integer pipe (PRMT decode).
+    switch (cfg) {
+        case 0: return run_policy<Nvfp4Mma<4, 1, 2, false>>(kn, c, pp);      // tensor cores, one consumer group
+        case 2: return run_policy<Nvfp4Mma<4, 2, 2, false>>(kn, c, pp);      // tensor cores, two consumer groups
+        default: return run_policy<Nvfp4Dp4a<5, 2, false>>(kn, c, pp);
     }
 }
 
@@ -998,7 +1018,94 @@ const KernelEntry kStream[] = {
     {"stream_flag_wait", 5, launch_flag_wait, "piipi"},
 };
 
+// Status word of the ring kernels when they are launched by name for a single layer (those entries have
+// no status argument): 0, or the code of the first bounded wait that ran out.  Read and cleared by fm_stream_status().
+__device__ int g_stream_status;
+
+int* byname_status() {
+    static int* ptr = nullptr;
+    if (!ptr && cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_stream_status) != cudaSuccess) {
+        cudaGetLastError();
+        ptr = nullptr;
+    }
+    return ptr;
+}
+
+void one_layer(StreamParams& p, const void* wq, const void* ws, float* y, int rows, int M, int ystride) {
+    p.layers = nullptr;
+    p.one.wq = static_cast<const uint8_t*>(wq);
+    p.one.ws = static_cast<const uint8_t*>(ws);
+    p.one.x = nullptr;
+    p.one.y = y;
+    p.nlayers = 1;
+    p.rows = rows;
+    p.K = 5120;
+    p.row_base = 0;
+    p.npeers = 0;
+    p.M = M;
+    p.ystride = ystride;
+    p.status = byname_status();
+}
+
 }  // namespace
+
+// ---- single-layer launches of the ring kernels for the by-name GEMV entries (K = 5120, 16-byte aligned operands;
+// the callers have range-checked every pointer).  y is token-major with `ystride` floats between tokens.
+int stream_gemv_w4a8(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* ae, const void* ao,
+                     const void* asc, const void* asu, float* y, int M, int ystride, int rows, int* iacc) {
+    PlainParams pp = {};
+    one_layer(pp.s, wq, ws, y, rows, M, ystride);
+    FM_REQUIRE(pp.s.status != nullptr, kn, "the status word of the ring kernels is not addressable");
+    pp.s.ae = static_cast<const uint8_t*>(ae);
+    pp.s.ao = static_cast<const uint8_t*>(ao);
+    pp.s.asc = static_cast<const uint8_t*>(asc);
+    pp.s.asu = static_cast<const uint8_t*>(asu);
+    pp.s.iacc = iacc;
+    if (iacc) {
+        switch (M) {
+            case 1: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, true>>(kn, c, pp);
+            case 2: return run_policy<W4A8Mma<2, 4, 1, false, 2, true, 0, true>>(kn, c, pp);
+            case 3: return run_policy<W4A8Mma<3, 4, 1, false, 2, true, 0, true>>(kn, c, pp);
+            default: return run_policy<W4A8Mma<4, 4, 1, false, 2, true, 0, true>>(kn, c, pp);
+        }
+    }
+    switch (M) {
+        case 1: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);
+        case 2: return run_policy<W4A8Mma<2, 4, 1, false, 2, true, 0, false>>(kn, c, pp);
+        case 3: return run_policy<W4A8Mma<3, 4, 1, false, 2, true, 0, false>>(kn, c, pp);
+        default: return run_policy<W4A8Mma<4, 4, 1, false, 2, true, 0, false>>(kn, c, pp);
+    }
+}
+
+int stream_gemv_w4a4(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* aq, const void* asc,
+                     float* y, int rows) {
+    PlainParams pp = {};
+    one_layer(pp.s, wq, ws, y, rows, 1, 0);
+    FM_REQUIRE(pp.s.status != nullptr, kn, "the status word of the ring kernels is not addressable");
+    pp.s.ae = static_cast<const uint8_t*>(aq);
+    pp.s.asc = static_cast<const uint8_t*>(asc);
+    return run_policy<W4Dp4a<true, 5, 2, false>>(kn, c, pp);
+}
+
+int stream_gemv_nvfp4(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* qa, const void* qb,
+                      const void* sc, float* y, int rows, float gscale) {
+    Nvfp4Params pp = {};
+    one_layer(pp.s, wq, ws, y, rows, 1, 0);
+    FM_REQUIRE(pp.s.status != nullptr, kn, "the status word of the ring kernels is not addressable");
+    pp.s.ae = static_cast<const uint8_t*>(qa);
+    pp.s.ao = static_cast<const uint8_t*>(qb);
+    pp.s.asc = static_cast<const uint8_t*>(sc);
+    pp.gscale = gscale;
+    return run_policy<Nvfp4Dp4a<5, 2, false>>(kn, c, pp);
+}
+
+int stream_read_status(cudaStream_t stream) {
+    int v = 0, zero = 0;
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, g_stream_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int));
+    return v;
+}
 
 const KernelEntry* stream_kernels(int* n) {
     *n = (int)(sizeof(kStream) / sizeof(kStream[0]));

@@ -857,6 +857,12 @@ int fm_gemm_status(void) {
     return gemm_read_status(E().stream);
 }
 
+int fm_stream_status(void) {
+    LOCK;
+    NEED_INIT(-1);
+    return stream_read_status(E().stream);
+}
+
 int fm_event_create(void) {
     LOCK;
     NEED_INIT(-1);

@@ -98,6 +98,7 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_comm_destroy": (c.c_int, []),
         "fm_stream_table": (c.c_int, [c.c_void_p, _u64p, c.c_int, c.c_int, c.c_int, c.c_int]),
         "fm_gemm_status": (c.c_int, []),
+        "fm_stream_status": (c.c_int, []),
         "fm_ipc_export": (c.c_int, [c.c_void_p, c.c_void_p, c.POINTER(c.c_ulonglong), c.POINTER(c.c_ulonglong)]),
         "fm_ipc_import": (c.c_void_p, [c.c_void_p, c.c_ulonglong]),
         "fm_stream_peers": (c.c_int, [c.c_void_p, _u64p, c.c_int, c.c_void_p, c.c_ulonglong]),
@@ -414,6 +415,10 @@ class Runtime:
     def gemm_status(self) -> int:
         """Sync, then 0 or the code of a bounded wait that ran out in a GEMM kernel."""
         return int(self._lib.fm_gemm_status())
+
+    def stream_status(self) -> int:
+        """Sync, then 0 or the code of a bounded wait that ran out in a by-name GEMV that runs on the ring."""
+        return int(self._lib.fm_stream_status())
 
     def ipc_export(self, ptr: int) -> tuple[bytes, int, int]:
         """(64-byte IPC handle, offset of ptr in its allocation, allocation size)."""

@@ -230,3 +230,8 @@ def test_w4a8_mma_accumulators_small_and_ragged(rt):
             y, acc, q = w4a8_device(rt, L["wq"], L["ws"], L["x"], dump=True)
             ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)
             assert np.array_equal(acc, ref["acc"]) and O.rel_err(y, ref["y"]) < REL
+
+
+def test_zz_ring_status_clean(rt):
+    """The by-name GEMVs of this file run on the bulk-copy ring at K = 5120: none of their bounded waits ran out."""
+    assert rt.stream_status() == 0

@@ -425,9 +425,15 @@ def test_stream_accumulators_several_tokens(rt, m, rows):
         assert O.rel_err(got[i, :, :rows], ref["y"]) < REL
 
 
+@pytest.mark.parametrize("cfg", [None, "0", "2"])
 @pytest.mark.parametrize("rows,nlayers", [(17408, 2), (520, 3)])
-def test_stream_accumulators_nvfp4(rt, rows, nlayers):
-    """nvfp4_decode_stream's tensor-core consumer: the int32 of every (row, 16-block), bit for bit."""
+def test_stream_accumulators_nvfp4(rt, monkeypatch, rows, nlayers, cfg):
+    """nvfp4_decode_stream: the int32 of every (row, 16-block), bit for bit, from the default (dp4a) consumer and
+    from the tensor-core consumer ($FM_NVFP4_CFG=0; 2 = two groups runs the same arithmetic)."""
+    if cfg is None:
+        monkeypatch.delenv("FM_NVFP4_CFG", raising=False)
+    else:
+        monkeypatch.setenv("FM_NVFP4_CFG", cfg)
     layers = [synth.nvfp4_layer(rows, K, 1, seed=1400 + i) for i in range(nlayers)]
     gscale = float(layers[0]["gscale"])
     with Bufs(rt) as b:
@@ -446,6 +452,9 @@ def test_stream_accumulators_nvfp4(rt, rows, nlayers):
         rt.launch("nvfp4_decode_stream_iacc", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status, qa, qb, sc, gscale, 0, pi])
         acc = b.get(pi, nlayers * rows * (K // 16), np.int32).reshape(nlayers, rows, -1)
         got = [b.get(py, rows) for py in ys]
+        rt.launch("nvfp4_decode_stream", 1, 1, [table, nlayers, rows, K, 0, 0, 0, status, qa, qb, sc, gscale, 0])
+        got2 = [b.get(py, rows) for py in ys]
+        assert all(np.array_equal(a_, b_) for a_, b_ in zip(got, got2))
         assert int(b.get(status, 1, np.int32)[0]) == 0
         rt.free(table)
     for i, L in enumerate(layers):
