@@ -127,7 +127,7 @@ int   fm_stream_peers(void* dev_deltas, const uint64_t* peer_bases, int npeers, 
 int   fm_gemm_status(void);
 
 /* Drains the stream and returns (then clears) the status word of the decode GEMV entries that run on the bulk-copy
- * ring (gemv_w4a8<M,..>, gemv_w4a4<1>, nvfp4_gemv<1,B> at K = 5120): 0, or the code of the first bounded wait that ran
+ * ring (gemv_w4a8<2..4,..> at K = 5120): 0, or the code of the first bounded wait that ran
  * out (the results are then invalid).  The multi-layer stream entries take a status word as an argument instead. */
 int   fm_stream_status(void);
 

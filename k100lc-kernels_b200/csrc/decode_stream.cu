@@ -1077,28 +1077,6 @@ int stream_gemv_w4a8(const LaunchCtx& c, const char* kn, const void* wq, const v
     }
 }
 
-int stream_gemv_w4a4(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* aq, const void* asc,
-                     float* y, int rows) {
-    PlainParams pp = {};
-    one_layer(pp.s, wq, ws, y, rows, 1, 0);
-    FM_REQUIRE(pp.s.status != nullptr, kn, "the status word of the ring kernels is not addressable");
-    pp.s.ae = static_cast<const uint8_t*>(aq);
-    pp.s.asc = static_cast<const uint8_t*>(asc);
-    return run_policy<W4Dp4a<true, 5, 2, false>>(kn, c, pp);
-}
-
-int stream_gemv_nvfp4(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* qa, const void* qb,
-                      const void* sc, float* y, int rows, float gscale) {
-    Nvfp4Params pp = {};
-    one_layer(pp.s, wq, ws, y, rows, 1, 0);
-    FM_REQUIRE(pp.s.status != nullptr, kn, "the status word of the ring kernels is not addressable");
-    pp.s.ae = static_cast<const uint8_t*>(qa);
-    pp.s.ao = static_cast<const uint8_t*>(qb);
-    pp.s.asc = static_cast<const uint8_t*>(sc);
-    pp.gscale = gscale;
-    return run_policy<Nvfp4Dp4a<5, 2, false>>(kn, c, pp);
-}
-
 int stream_read_status(cudaStream_t stream) {
     int v = 0, zero = 0;
     if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;

@@ -68,15 +68,11 @@ cudaError_t gemv_w4a8_raw(const uint32_t* wq, const void* ws_f16, const int8_t* 
                           const float* asc, const int* asu, float* y, int M, int N, int K, int sm_count,
                           cudaStream_t stream);
 
-// Single-layer launches of the ring kernels (decode_stream.cu) behind the by-name GEMV entries: K = 5120 and every
-// operand 16-byte aligned; the caller has range-checked the pointers.  `iacc` (W4A8 only) != nullptr also stores the
-// integer accumulators [M][rows][K/128].
+// Single-layer launch of the ring kernel (decode_stream.cu) behind gemv_w4a8<2..4,..>: K = 5120 and every operand
+// 16-byte aligned; the caller has range-checked the pointers.  `iacc` != nullptr also stores the integer
+// accumulators [M][rows][K/128].
 int stream_gemv_w4a8(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* ae, const void* ao,
                      const void* asc, const void* asu, float* y, int M, int ystride, int rows, int* iacc);
-int stream_gemv_w4a4(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* aq, const void* asc,
-                     float* y, int rows);
-int stream_gemv_nvfp4(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* qa, const void* qb,
-                      const void* sc, float* y, int rows, float gscale);
 int stream_read_status(cudaStream_t stream);   // 0, or the code of the first bounded wait that ran out in such a launch
 
 int gemm_read_status(cudaStream_t stream);   // 0, or the code of the first bounded wait that ran out

@@ -199,11 +199,6 @@ template <int M, bool DUMP>
 int dispatch(const char* kn, const LaunchCtx& c, const Nvfp4Params& p) {
     const int kiter = (p.K % 1024 == 0) ? p.K / 1024 : 0;
     if (DUMP) return run_variant<M, 1, 0, true>(kn, c, p);
-    if (M == 1 && p.K == 5120 && aligned(p.ws, 16) && aligned(p.qa, 16) && aligned(p.qb, 16) && aligned(p.sc, 16)) {
-        // on the bulk-copy ring of the stream kernels (one layer); $FM_GEMV_CFG=2 keeps the kernel of this file
-        static const int cfg = getenv("FM_GEMV_CFG") ? atoi(getenv("FM_GEMV_CFG")) : 0;
-        if (cfg == 0) return stream_gemv_nvfp4(c, kn, p.wq, p.ws, p.qa, p.qb, p.sc, p.y, p.rows, p.gscale);
-    }
     if (M == 1) {
         // (the register path reads the codes as 16-byte words)
         if (kiter == 5 && aligned(p.qa, 16) && aligned(p.qb, 16)) return run_variant<1, 1, 5, false>(kn, c, p);

@@ -431,9 +431,11 @@ int run_variant(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
-// K = 5120 with 16-byte aligned operands runs on the bulk-copy ring of the stream kernels (one layer): the weights
-// arrive by TMA instead of per-warp loads, and the integer work goes to the tensor cores (W4A8).  $FM_GEMV_CFG=2
-// keeps the kernels of this file for every shape.
+// Two to four tokens of int8 activations at K = 5120 with 16-byte aligned operands run on the bulk-copy ring of the
+// stream kernels (one layer): 15.1 us against 15.8 us for gemv_w4a8_mma_kernel at M = 4.  One token stays here: a ring
+// that is launched for a single layer pays its fill and drain on every launch (11.4 us against 10.3 us for the GEMV
+// alone; likewise W4A4 13.6 / 12.2 and NVFP4 15.9 / 14.4 us with the quantiser).  $FM_GEMV_CFG=2 keeps the kernels of
+// this file for every shape.
 bool ring_ok(const GemvW4Params& p, bool a4) {
     static const int cfg = getenv("FM_GEMV_CFG") ? atoi(getenv("FM_GEMV_CFG")) : 0;
     return cfg == 0 && p.K == 5120 && aligned(p.wq, 16) && aligned(p.ws, 16) && aligned(p.a0, 16) && aligned(p.asc, 16) &&
@@ -443,9 +445,8 @@ bool ring_ok(const GemvW4Params& p, bool a4) {
 template <bool A4, int M, bool DUMP>
 int dispatch(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
     const int kiter = (p.K % 1024 == 0) ? p.K / 1024 : 0;
-    if (!A4 && ring_ok(p, false) && (!DUMP || p.rows == p.N))
+    if (!A4 && M > 1 && ring_ok(p, false) && (!DUMP || p.rows == p.N))
         return stream_gemv_w4a8(c, kn, p.wq, p.ws, p.a0, p.a1, p.asc, p.asu, p.y, M, p.N, p.rows, DUMP ? p.iacc : nullptr);
-    if (A4 && M == 1 && !DUMP && ring_ok(p, true)) return stream_gemv_w4a4(c, kn, p.wq, p.ws, p.a0, p.asc, p.y, p.rows);
     if (DUMP) {
         // the dump comes from the kernel that the by-name entry of this M runs: the tensor-core one for
         // int8 activations and 2..4 tokens, the dp4a one otherwise
