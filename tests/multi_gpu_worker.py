@@ -29,8 +29,10 @@ def main() -> int:
                  x=synth.stream_layer_x(l, k)) for l in range(layers)]
     x_all = rt.alloc(layers * k * 4)
     rt.upload(x_all, np.stack([L["x"] for L in full]))
-    y = rt.alloc(layers * n * 4)
+    y = rt.alloc(layers * n * 4 + layers * 4)          # the gathered outputs, then one completion counter per layer
     rt.memset(y, 0xFF, layers * n * 4)
+    flags = y + layers * n * 4
+    rt.memset(flags, 0, layers * 4)
     ptrs = []
     for l, L in enumerate(full):
         pwq, pws = rt.alloc(rows * k // 2), rt.alloc(rows * (k // 128) * 2)
@@ -39,7 +41,7 @@ def main() -> int:
         ptrs.append((pwq, pws, x_all + l * k * 4, y + l * n * 4))
     table = rt.stream_table(ptrs, rows, k, r0)
     peers = shard.exchange_ipc(rt, dist, y)
-    deltas = rt.stream_peers([peers[r] for r in range(world) if r != rank], y, layers * n * 4)
+    deltas = rt.stream_peers([peers[r] for r in range(world) if r != rank], y, layers * n * 4 + layers * 4)
     ae, ao = rt.alloc(layers * k // 2), rt.alloc(layers * k // 2)
     asc, asu = rt.alloc(layers * (k // 128) * 4), rt.alloc(layers * (k // 128) * 4)
     status = rt.alloc(4)
@@ -47,11 +49,18 @@ def main() -> int:
     rt.sync()
     dist.barrier()                     # every rank has initialised its y before anyone stores into it
     rt.launch2d("quant_act", k // 128, layers, 32, 1, [x_all, ae, ao, asc, asu, layers, k])
-    rt.launch("w4a8_decode_stream", 1, 1, [table, layers, rows, k, r0, world - 1, deltas, status, ae, ao, asc, asu, 0])
-    rt.sync()
-    dist.barrier()                     # every rank's stores have landed
-    got = rt.download(y, layers * n, np.float32).reshape(layers, n)
+    rt.launch("w4a8_decode_stream", 1, 1, [table, layers, rows, k, r0, world - 1, deltas, status, ae, ao, asc, asu, flags])
+    # acquire side of the completion counters: every CTA of every rank adds one per layer on every receiver, so this
+    # GPU's counters reach world x CTAs once all rows of a layer have arrived here — no host barrier in between
+    ctas = min(rt.device_attr("sm_count"), rows)
+    wstat = rt.alloc(4)
+    rt.memset(wstat, 0, 4)
+    rt.launch("stream_flag_wait", 1, 128, [flags, layers, world * ctas, wstat, 1000000])
+    got = rt.download(y, layers * n, np.float32).reshape(layers, n)      # ordered behind the wait kernel on the stream
+    assert int(rt.download(wstat, 1, np.int32)[0]) == 0, "a completion counter did not reach its target in time"
+    assert (rt.download(flags, layers, np.uint32) == world * ctas).all()
     assert int(rt.download(status, 1, np.int32)[0]) == 0
+    dist.barrier()
     for l, L in enumerate(full):
         q = O.quant_act(L["x"][None, :])
         ref = O.gemv_w4(L["wq"].view(np.uint32), L["ws"], q["q"], q["scale"], 128)["y"][0]
