@@ -347,13 +347,25 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         dots = [DotLinear(rt, rows, K, "int4", rng.integers(0, 256, size=(rows, K // 2), dtype=np.uint8),
                           (bf16_bits(np.abs(rng.standard_normal((rows, NG))) * 0.01 + 1e-3),), ws=dws, tag=f"bench_dot{i}")
                 for i in range(nd)]
-        for d in dots:
-            d.forward_device(st.x, 1)                   # output buffers exist before the capture
+        dot_fn = lambda l: dots[l % nd].forward_device(st.x + l * K * 4, 1)
+        for l in range(nl):
+            dot_fn(l)                                   # output buffers and layer tables exist before the capture
         rt.sync()
-        g = graph_of(lambda l: dots[l % nd].forward_device(st.x + l * K * 4, 1), nl)
+        g = graph_of(dot_fn, nl)
         us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
         rt.graph_free(g)
-        out["w4a16_m1"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
+        out["w4a16_m1"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1),
+                           "what": "DotLinear.forward_device: activation split + bulk-copy ring, two launches per layer"}
+        # the reference's launch sequence (int4_dot_k + reduce_blocks_k per token) on the same buffers
+        for d in dots:
+            d.ring = False
+        for l in range(nl):
+            dot_fn(l)
+        rt.sync()
+        g = graph_of(dot_fn, nl)
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nl
+        rt.graph_free(g)
+        out["w4a16_m1_dot_reduce"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
         # the same layers through the W4A16 stream kernel (activation split + stream, two launches)
         tab16 = rt.stream_table([(d.w, d.tables[0], st.x + i * K * 4, st.y + i * N * 4) for i, d in enumerate(dots)], rows, K, 0)
         st16 = rt.alloc(4)

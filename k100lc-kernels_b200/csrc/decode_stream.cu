@@ -243,6 +243,103 @@ struct W4A8Mma {
 };
 
 // ------------------------------------------------------------------------------------
+// W4A4 on the tensor cores (reference arithmetic: kernels/gemv_w4a4_core.h:48-134): the schedule of W4A8Mma
+// with the token's codes inside every stage and, per (row, 32-sub-group), the exact integer
+//   J = sum_{k in sub-group} w[n,k] * q[k]         y += (f16(ws[n, sg / 4]) * asc[sg]) * float(J).
+// A lane's 16-byte word is one sub-group, but an MMA adds over the k slots of all four lanes of a row; the
+// sub-groups are kept apart by the columns of B: column 2t carries the token's codes only in the k slots that
+// lane t feeds (zero elsewhere), so accumulator column 2t — which lane t owns — is lane t's own sub-group.
+// Both operands are formed as 16 x their value with one or two logic instructions per register (a two's-
+// complement nibble in the upper half of a byte is the signed byte 16 * v): J = acc >> 8, exactly, with no
+// correction term.  The four lanes of a row then add their sub-groups with two shuffles.
+template <int STAGES_, int NGROUPS_, bool DUMP>
+struct W4A4Mma {
+    using Params = PlainParams;
+    static constexpr int M = 1, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = 1;
+    static constexpr bool ACT_IN_STAGE = true;
+    static constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
+    static constexpr int ROWB = K / 2, SCB = NG * 2, PITCH = ROWB;
+    static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB;
+    static constexpr int ACT = K / 2 + (K / 32) * 4;            // packed nibbles, sub-group scales
+    static constexpr int STAGE = (OFF_ACT + ACT + 127) & ~127;
+    static constexpr int RED = CW * ROWS, EXTRA = 0;
+    static constexpr int kThreads = (NGROUPS * CW + 2) * 32;
+
+    __device__ static void init_extra(const Params&, uint8_t*) {}
+    __device__ static void copy_act(const Params& pp, int l, uint8_t* dst, uint64_t* bar) {
+        const StreamParams& p = pp.s;
+        bulk_g2s(dst, p.ae + (size_t)l * (K / 2), K / 2, bar);                               // aq
+        bulk_g2s(dst + K / 2, p.asc + (size_t)l * (K / 32 * 4), K / 32 * 4, bar);
+    }
+
+    __device__ static void consume(const Cta& c, const Params& pp, int grp, int w) {
+        const StreamParams& p = pp.s;
+        const int lane = c.lane, g = lane >> 2, t = lane & 3;
+        const uint32_t bmask = g == 2 * t ? 0xF0F0F0F0u : 0u;   // this lane's B registers carry column 2t (or nothing)
+        int cg = 0;
+        for (int l = 0; l < p.nlayers; l++) {
+            const int c0 = l * c.nst;
+            const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;
+            float* yt = c.ytile + (l & 1) * kOutCap;
+            float* y = get_layer(p, l).y + p.row_base;
+            if (!layer_enter<W4A4Mma>(c, l)) return;
+            for (int jst = jf; jst < c.nst; jst += NGROUPS, cg++) {
+                const int cc = c0 + jst, s = cc % STAGES;
+                if (!cta_wait(c, &c.bars->full[s], (cc / STAGES) & 1, 3)) return;
+                const uint8_t* st = c.ring + (size_t)s * STAGE;
+                const uint8_t* ab = st + OFF_ACT;
+                uint4 xa[GPW], xb[GPW];
+                float swa[GPW], swb[GPW];
+#pragma unroll
+                for (int j = 0; j < GPW; j++) {
+                    const int gg = j * CW + w;
+                    xa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * PITCH + gg * 64 + t * 16);
+                    xb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * PITCH + gg * 64 + t * 16);
+                    swa[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + g * SCB + gg * 2));
+                    swb[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + (g + 8) * SCB + gg * 2));
+                }
+                float fa = 0.f, fb = 0.f;
+#pragma unroll
+                for (int j = 0; j < GPW; j++) {
+                    const int gg = j * CW + w;
+                    const uint4 a = *reinterpret_cast<const uint4*>(ab + gg * 64 + t * 16);   // the sub-group's 32 codes
+                    const float sa = *reinterpret_cast<const float*>(ab + K / 2 + (gg * 4 + t) * 4);
+                    const uint32_t m_hi = 0xF0F0F0F0u;
+                    int acc[4] = {0, 0, 0, 0};
+                    // even k: low nibbles moved to the upper half of their bytes; odd k: high nibbles in place
+                    mma_s8(acc, (xa[j].x << 4) & m_hi, (xb[j].x << 4) & m_hi, (xa[j].y << 4) & m_hi, (xb[j].y << 4) & m_hi,
+                           (a.x << 4) & bmask, (a.y << 4) & bmask);
+                    mma_s8(acc, (xa[j].z << 4) & m_hi, (xb[j].z << 4) & m_hi, (xa[j].w << 4) & m_hi, (xb[j].w << 4) & m_hi,
+                           (a.z << 4) & bmask, (a.w << 4) & bmask);
+                    mma_s8(acc, xa[j].x & m_hi, xb[j].x & m_hi, xa[j].y & m_hi, xb[j].y & m_hi, a.x & bmask, a.y & bmask);
+                    mma_s8(acc, xa[j].z & m_hi, xb[j].z & m_hi, xa[j].w & m_hi, xb[j].w & m_hi, a.z & bmask, a.w & bmask);
+                    const int ia = acc[0] >> 8, ib = acc[2] >> 8;      // rows g, g + 8, column 2t: 256 * J exactly
+                    fa += (swa[j] * sa) * (float)ia;
+                    fb += (swb[j] * sa) * (float)ib;
+                    if (DUMP) {
+                        const int ra = c.r0 + jst * ROWS + g, rb = ra + 8, sg = gg * 4 + t;
+                        if (ra < c.r1) p.iacc[((size_t)l * p.rows + ra) * (K / 32) + sg] = ia;
+                        if (rb < c.r1) p.iacc[((size_t)l * p.rows + rb) * (K / 32) + sg] = ib;
+                    }
+                }
+                consumed(fa + fb);                       // release only after the loaded data has been used
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&c.bars->empty[s]);
+                // the four lanes of a row hold the sums over their own sub-groups
+                fa += __shfl_xor_sync(0xffffffffu, fa, 1);
+                fb += __shfl_xor_sync(0xffffffffu, fb, 1);
+                fa += __shfl_xor_sync(0xffffffffu, fa, 2);
+                fb += __shfl_xor_sync(0xffffffffu, fb, 2);
+                const float vals[2] = {fa, fb};
+                const int idx[2] = {t == 0 ? g : -1, t == 0 ? g + 8 : -1};
+                if (!reduce_and_emit<W4A4Mma>(c, grp, w, cg, vals, idx, yt, y, c.r0 + jst * ROWS)) return;
+            }
+            layer_done(c, l);
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------
 // dp4a consumer (W4A4 always; W4A8 as the alternative to the tensor-core consumer): one warp per row of
 // a stage, lane l the 16-byte words l, l + 32, .. of that row (LDS.128) into registers; nibbles -> dp4a
 // against the token's codes held in registers, two shuffles per 128-group (W4A8) or none (W4A4: a
@@ -849,10 +946,15 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
         p.iacc = arg_ptr<int>(a[9 + nact]);
         FM_REQUIRE(aligned(p.iacc, 4), kn, "misaligned accumulator dump");
         FM_RANGE(p.iacc, (size_t)p.nlayers * p.rows * (p.K / (A4 ? 32 : 128)) * 4, kn, "iacc");
-        if (A4) return run_policy<W4Dp4a<true, 5, 2, true>>(kn, c, pp);
+        if (A4) return env_or("FM_STREAM_CFG", 3) != 1 ? run_policy<W4A4Mma<4, 2, true>>(kn, c, pp)
+                                                       : run_policy<W4Dp4a<true, 5, 2, true>>(kn, c, pp);
         return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, true>>(kn, c, pp);
     }
-    if (A4) return nst >= 3 ? run_policy<W4Dp4a<true, 5, 2, false>>(kn, c, pp) : run_policy<W4Dp4a<true, 4, 5, false>>(kn, c, pp);
+    if (A4) {
+        // tensor-core consumer, two groups; $FM_STREAM_CFG=1 keeps the dp4a consumer
+        if (env_or("FM_STREAM_CFG", 3) != 1) return run_policy<W4A4Mma<4, 2, false>>(kn, c, pp);
+        return nst >= 3 ? run_policy<W4Dp4a<true, 5, 2, false>>(kn, c, pp) : run_policy<W4Dp4a<true, 4, 5, false>>(kn, c, pp);
+    }
     // Default: the token's codes travel inside every stage and two groups of eight warps take the stages in turn.
     // Measured on one B200 (400 layers, ms per token, 20-step burst / one-second run): 17408 rows 2.62 / 3.07 against
     // 3.04 / 3.35 for one group with the fragments in registers (0); 2176 rows — the shard of eight GPUs, one stage per

@@ -113,7 +113,7 @@ class DotLinear:
     ``(bf16_scale_bytes,)``.  One kernel pair per token row (reference model.py:260-277)."""
 
     def __init__(self, rt: Runtime, n: int, k: int, kind: str, weight_bytes, tables=(),
-                 ws: Workspace | None = None, tag: str | None = None):
+                 ws: Workspace | None = None, tag: str | None = None, ring: bool = True):
         if kind not in QUANT_SPECS:
             raise ValueError(f"unknown weight format {kind!r}; built here: {sorted(QUANT_SPECS)}")
         spec = QUANT_SPECS[kind]
@@ -133,14 +133,40 @@ class DotLinear:
         self.ids = self.ws.upload(self.tag + ".ids", np.arange(self.n, dtype=np.uint32))
         self.m_nbpr = div_magic(self.nbpr, self.nblocks)
         self.m_rows = div_magic(self.n, self.n)
+        self.ring = ring and rt.has("w4a16_decode_stream")
 
     def _argv(self, x_dev, rows_per_exp, magic_rpe, ids, stride, rows_per_w, magic_rpw):
         return ([self.w, int(x_dev), self.partial, self.nblocks, 64, self.nbpr, self.m_nbpr,
                  rows_per_exp, magic_rpe] + self.tables + [int(ids), stride, rows_per_w, magic_rpw])
 
+    def _ring_table(self, x_dev: int, out: int, rows: int):
+        """One validated layer-table entry per token row (same weights, its own x and y) for
+        ``w4a16_decode_stream``; cached per (x, y, rows) because validating a table is a host round trip."""
+        key = (int(x_dev), int(out), rows)
+        if not hasattr(self, "_tables"):
+            self._tables, self._status = {}, self.ws.buffer(self.tag + ".ring_status", 4)
+            self.rt.memset(self._status, 0, 4)
+        if key not in self._tables:
+            slot = len(self._tables) % 8                     # eight table buffers of the workspace, reused in turn
+            for k_old in [k for k, v in self._tables.items() if v[1] == slot]:
+                del self._tables[k_old]
+            dev = self.ws.buffer(f"{self.tag}.ring_table{slot}", 32 * max(rows, 4))
+            self._tables[key] = (self.rt.stream_table(
+                [(self.w, self.tables[0], int(x_dev) + r * self.k * 4, out + r * self.n * 4) for r in range(rows)],
+                self.n, self.k, 0, dev=dev), slot)
+        return self._tables[key][0]
+
     def forward_device(self, x_dev: int, rows: int, sync: bool = False, out_dev=None) -> int:
         out = int(out_dev) if out_dev is not None else self.ws.buffer(self.tag + ".out", rows * self.n * 4)
         stride = self.nbpr * self.spec["block_bytes"]
+        if self.kind == "int4" and self.k == 5120 and self.ring and int(x_dev) % 16 == 0:
+            # dense layout at K = 5120: the activation split and the bulk-copy ring, two launches for all rows
+            # (the reference's dot + reduce pair per row, with its partial[N * 40] round trip, stays below)
+            self.rt.launch("w4a16_decode_stream", 1, 1,
+                           [self._ring_table(x_dev, out, rows), rows, self.n, self.k, 0, 0, 0, self._status, 0])
+            if sync:
+                self.rt.sync()
+            return out
         for r in range(rows):
             self.rt.launch(self.spec["kernel"], cdiv(self.nblocks, 64), 64,
                            self._argv(int(x_dev) + r * self.k * 4, self.n, self.m_rows, self.ids, stride,

@@ -402,13 +402,16 @@ class Runtime:
     def graph_free(self, graph: int) -> None:
         self._lib.fm_graph_free(graph)
 
-    def stream_table(self, layers, rows: int, k: int, row_base: int = 0) -> int:
+    def stream_table(self, layers, rows: int, k: int, row_base: int = 0, dev: int | None = None) -> int:
         """Validated device table for ``w4a8_decode_stream``: ``layers`` is a list of
-        ``(wq, ws, x, y)`` device pointers; returns the table's device pointer."""
+        ``(wq, ws, x, y)`` device pointers; returns the table's device pointer (a fresh allocation of
+        32 bytes per layer unless ``dev`` names a buffer of that size)."""
         flat = (ctypes.c_uint64 * (4 * len(layers)))(*[int(v) for lay in layers for v in lay])
-        dev = self.alloc(32 * len(layers))
+        own = dev is None
+        dev = self.alloc(32 * len(layers)) if own else int(dev)
         if self._lib.fm_stream_table(ctypes.c_void_p(dev), flat, len(layers), int(rows), int(k), int(row_base)) != 0:
-            self.free(dev)
+            if own:
+                self.free(dev)
             self._fail("fm_stream_table")
         return dev
 
