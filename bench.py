@@ -684,7 +684,51 @@ def run_ours(args) -> int:
     # the other buffer on the engine's second queue (the upload waits for step t - 1, the last reader of that buffer,
     # and step t + 1 waits for the upload).  Every step still uploads its own inputs inside the timed region.
     st.y_host[:] = np.nan
-    if fused:
+    e2e_h2d = world * args.layers * K * 4
+    if fused and world > 1:
+        # Several GPUs: the activations are replicated, but uploading all of x on every rank makes the host
+        # serve N x 8.2 MB per token (at eight GPUs that, not the kernel, set the step time).  Instead every rank
+        # uploads 1/N of x, the copy engines push that slice into every peer's buffer over NVLink (beside the
+        # running kernel, no SM involved), and a step starts behind a bounded acquire on N counters that the pushes
+        # bump.  Four buffers: a peer can be up to two steps behind when a slice for the step after next arrives.
+        from k100lc_kernels.shard import exchange_ipc
+        NB, xb = 4, args.layers * K * 4
+        sl = xb // world                                             # bytes of one rank's slice
+        total_steps = max(1, args.warmup) + args.steps + 2
+        xall = rt.alloc(NB * xb + NB * world * 4)
+        rt.memset(xall, 0, NB * xb + NB * world * 4)
+        fl0 = NB * xb                                                # offset of the counters: [NB][world] u32
+        steps_dev = rt.alloc(4 * (total_steps + 2))
+        rt.upload(steps_dev, np.arange(total_steps + 2, dtype=np.uint32))
+        wstat = rt.alloc(4)
+        rt.memset(wstat, 0, 4)
+        rt.sync()
+        barrier()
+        px = exchange_ipc(rt, dist, xall)
+        x_flat = st.x_host.reshape(-1).view(np.uint8)
+        graphs = [st.capture_fused(host_mirror=True, x=xall + b * xb) for b in range(NB)]
+        step_no = [0]
+        e2e_h2d = args.layers * K * 4
+
+        def distribute(step):                                        # this rank's slice of the inputs of `step`
+            b = step % NB
+            mine = xall + b * xb + rank * sl
+            rt.upload_beside(mine, x_flat[rank * sl:(rank + 1) * sl])
+            for q in range(world):
+                if q != rank:
+                    rt.copy_beside(px[q] + b * xb + rank * sl, mine, sl)
+            for q in range(world):                                   # counter of (buffer, this rank) := step + 1, after the data
+                rt.copy_beside(px[q] + fl0 + (b * world + rank) * 4, steps_dev + 4 * (step + 1), 4)
+
+        distribute(0)
+
+        def e2e_step():
+            t = step_no[0]
+            distribute(t + 1)                                        # beside step t
+            rt.launch("stream_flag_wait", 1, 128, [xall + fl0 + (t % NB) * world * 4, world, t + 1, wstat, 2000000])
+            rt.graph_launch(graphs[t % NB])
+            step_no[0] = t + 1
+    elif fused:
         x2 = rt.alloc(args.layers * K * 4)
         xbuf = (st.x, x2)
         graphs = (st.capture_fused(host_mirror=True, x=st.x), st.capture_fused(host_mirror=True, x=x2))
@@ -714,6 +758,12 @@ def run_ours(args) -> int:
     rt.sync()
     barrier()
     ms_e2e = rt.elapsed_ms(e0, e1) / args.steps
+    if fused and world > 1:
+        if int(rt.download(wstat, 1, np.int32)[0]) != 0:
+            raise RuntimeError("an input slice of a peer did not arrive in time (stream_flag_wait gave up)")
+        got_x = rt.download(xall + ((step_no[0] - 1) % NB) * xb, args.layers * K, np.float32)
+        if not np.array_equal(got_x, st.x_host.reshape(-1)):
+            raise RuntimeError("the gathered inputs of the last step differ from the host's x")
     if fused:                                       # what the host received is what the device holds
         lo = rank * st.rows
         dev_y = rt.download(st.y, args.layers * N, np.float32).reshape(args.layers, N)
@@ -788,10 +838,14 @@ def run_ours(args) -> int:
                        "l2": "inputs (18.4 GB of weights) are larger than L2; no flush needed"},
             "ms_per_token": round(ms_step, 4), "us_per_layer": round(ms_step * 1e3 / args.layers, 3),
             "e2e": {"value": round(total_bytes / ms_e2e / 1e6, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e, 4),
-                    "h2d_bytes_per_step": world * args.layers * K * 4, "d2h_bytes_per_step": args.layers * N * 4,
-                    "api": ("per step: fm_upload_beside(x of all layers for the next step, every rank, second device buffer) + "
-                            "fm_graph_launch + fm_upload_join; the stream kernel stores each rank's rows of y into a pinned "
-                            "host array (fm_host_alloc, registered through fm_stream_peers) while it runs; fm_sync ends the run") if fused else
+                    "h2d_bytes_per_step": e2e_h2d, "d2h_bytes_per_step": args.layers * N * 4,
+                    "api": (("per step: fm_upload_beside(this rank's 1/N of the next step's x) + fm_copy_beside of that slice into every "
+                             "peer's buffer (copy engines over NVLink) + stream_flag_wait on the N arrival counters + fm_graph_launch; "
+                             if world > 1 else
+                             "per step: fm_upload_beside(x of all layers for the next step, second device buffer) + fm_graph_launch + "
+                             "fm_upload_join; ") +
+                            "the stream kernel stores each rank's rows of y into a pinned host array (fm_host_alloc, registered "
+                            "through fm_stream_peers) while it runs; fm_sync ends the run") if fused else
                            "fm_upload_async(x) + fm_graph_launch + fm_download_async(y), pinned host buffers"},
             "gpu_launches": int(gpu_launches),
             "per_layer_launches": None if ms_alt is None else {

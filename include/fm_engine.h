@@ -96,6 +96,9 @@ int   fm_download_async(void* pinned_host, const void* dev, size_t n);
  * fm_upload_join().  Not available inside a graph capture.  fm_sync also waits for the second queue. */
 int   fm_upload_beside(void* dev, const void* pinned_host, size_t n);
 int   fm_upload_join(void);
+/* Device-to-device copy on the second queue, behind what that queue already holds; dst may be a peer's allocation
+ * opened with fm_ipc_import (copy engines, no SM needed: it runs beside the kernels of the engine stream). */
+int   fm_copy_beside(void* dst, const void* src, size_t n);
 
 /* Layer table of the fused decode stream ("w4a8_decode_stream"): host_layers holds
  * nlayers x {wq, ws, x, y} device addresses.  Every address is checked against the live

@@ -156,7 +156,7 @@ struct W4A8Mma {
         for (int l = 0; l < p.nlayers; l++) {
             const int c0 = l * c.nst;
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;     // this group's first stage of the layer
-            float* yt = c.ytile + (l & 1) * kOutCap;
+            float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + p.row_base;
             if (!layer_enter<W4A8Mma>(c, l)) return;
             const uint8_t* tile = c.act + (size_t)(l % NACT) * ACT;
@@ -280,7 +280,7 @@ struct W4A4Mma {
         for (int l = 0; l < p.nlayers; l++) {
             const int c0 = l * c.nst;
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;
-            float* yt = c.ytile + (l & 1) * kOutCap;
+            float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + p.row_base;
             if (!layer_enter<W4A4Mma>(c, l)) return;
             for (int jst = jf; jst < c.nst; jst += NGROUPS, cg++) {
@@ -380,7 +380,7 @@ struct W4Dp4a {
         for (int l = 0; l < p.nlayers; l++) {
             if (!layer_enter<W4Dp4a>(c, l)) return;
             const uint8_t* ab = c.act + (size_t)(l % NACT) * ACT;
-            float* yt = c.ytile + (l & 1) * kOutCap;
+            float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + p.row_base;
             // register copy of the token's codes for this lane's words
             uint4 ae[KITER], ao[KITER];
@@ -516,7 +516,7 @@ struct Nvfp4Mma {
         for (int l = 0; l < p.nlayers; l++) {
             const int c0 = l * c.nst;
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;
-            float* yt = c.ytile + (l & 1) * kOutCap;
+            float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + p.row_base;
             if (!layer_enter<Nvfp4Mma>(c, l)) return;
             const uint8_t* ab = c.act + (size_t)(l % NACT) * ACT;
@@ -643,7 +643,7 @@ struct Nvfp4Dp4a {
         for (int l = 0; l < p.nlayers; l++) {
             if (!layer_enter<Nvfp4Dp4a>(c, l)) return;
             const uint8_t* ab = c.act + (size_t)(l % NACT) * ACT;
-            float* yt = c.ytile + (l & 1) * kOutCap;
+            float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + p.row_base;
             uint4 a0[KITER], a1[KITER];                        // the token's codes of this lane's 32 k per step, natural order
             float2 asc[KITER];                                 // and the scales of its two 16-blocks
@@ -750,7 +750,7 @@ struct W4A16Mma {
         for (int l = 0; l < p.nlayers; l++) {
             if (!layer_enter<W4A16Mma>(c, l)) return;
             const uint32_t* ft = reinterpret_cast<const uint32_t*>(c.act + (size_t)(l % NACT) * ACT);
-            float* yt = c.ytile + (l & 1) * kOutCap;
+            float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + p.row_base;
             uint4 bf[GPW][4];                                  // B fragments of this warp's blocks: {b0,b1 of (q,0), b0,b1 of (q,1)}
 #pragma unroll

@@ -705,6 +705,24 @@ int fm_upload_beside(void* dev, const void* host, size_t n) {
     e.copy_pending = true;
     return 0;
 }
+// Device-to-device copy on the second queue, behind whatever that queue already holds (an fm_upload_beside, say):
+// `dst` may lie in a peer's allocation opened with fm_ipc_import, which makes this the copy-engine way to hand a
+// freshly uploaded slice to the other GPUs while the kernels of the engine stream keep running.
+int fm_copy_beside(void* dst, const void* src, size_t n) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (e.capturing) { set_errorf("fm_copy_beside: not inside a graph capture"); return -1; }
+    if (!range_ok(dst, n) || !range_ok(src, n)) { set_errorf("fm_copy_beside: range exceeds an allocation"); return -1; }
+    if (!e.copy_stream) { set_errorf("fm_copy_beside: call fm_upload_beside first (it opens the second queue)"); return -1; }
+    if (n == 0) return 0;
+    touch(dst, n);
+    cudaError_t err = cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToDevice, e.copy_stream);
+    if (err == cudaSuccess) err = cudaEventRecord(e.ev_join, e.copy_stream);
+    if (err != cudaSuccess) { cuda_fail("fm_copy_beside", err); return -1; }
+    e.copy_pending = true;
+    return 0;
+}
 int fm_upload_join(void) {
     LOCK;
     NEED_INIT(-1);

@@ -28,6 +28,7 @@ namespace stream {
 constexpr int kSpinLimit = 1 << 20;    // try_wait rounds (each may sleep up to the suspend hint) before a wait gives up
 constexpr int kOutCap = 512;           // y values of one layer that a CTA collects in shared memory (else stored one by one)
 constexpr int kMaxStages = 8;
+constexpr int kYBufs = 4;              // output tiles of a CTA: the writer may lag the consumers by up to three layers
 constexpr int kHeader = 512;           // bytes reserved for the barriers at the start of the dynamic shared memory
 
 struct StreamLayer {                   // one entry of the device-side layer table (32 bytes)
@@ -59,7 +60,7 @@ struct Bars {
     uint64_t act_ready[kMaxStages];    // a layer's activation tile has landed (tiles of their own only)
     uint64_t act_free[kMaxStages];     // every consumer warp is done with it
     uint64_t red_full[4], red_free[4]; // partial-sum tiles of the tensor-core consumers (two per group)
-    uint64_t ydone[2], yfree[2];       // output tile complete / written out
+    uint64_t ydone[kYBufs], yfree[kYBufs];   // output tile complete / written out
     volatile int abort;
 };
 static_assert(sizeof(Bars) <= kHeader, "barrier block");
@@ -186,16 +187,20 @@ __device__ __forceinline__ void run_producer(const Cta& c, const typename P::Par
 }
 
 // ---- writer --------------------------------------------------------------------------------
-// tile layout [row][token]; y of a layer is token-major: y[token * ystride + row]
+// tile layout [row][token]; y of a layer is token-major: y[token * ystride + row].  `delta` are the receivers' byte
+// offsets, held in registers: read from global memory inside the loop they cost a dependent load per receiver and
+// layer, which is more than a stage time when a CTA has one stage per layer.
 template <int M>
-__device__ __forceinline__ void write_out(const StreamParams& p, const float* tile, float* y, int n, int lane) {
+__device__ __forceinline__ void write_out(const StreamParams& p, const float* tile, float* y, int n, int lane,
+                                          const long long (&delta)[8]) {
     for (int i = lane; i < n * M; i += 32) {
         const int tok = M == 1 ? 0 : i / n, row = M == 1 ? i : i - tok * n;      // token-major walk: coalesced stores
         const float v = tile[row * M + tok];
         float* dst = y + (size_t)tok * p.ystride + row;
         *dst = v;
-        for (int q = 0; q < p.npeers; q++)
-            *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = v;
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            if (q < p.npeers) *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + delta[q]) = v;
     }
 }
 
@@ -203,14 +208,18 @@ template <class P>
 __device__ __forceinline__ void run_writer(const Cta& c) {
     const StreamParams& p = *c.p;
     if (!c.tiled) return;
+    long long delta[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) delta[q] = q < p.npeers ? p.peer_delta[q] : 0;
     float* y_next = get_layer(p, 0).y;                   // requested a layer ahead (see the producer)
     for (int l = 0; l < p.nlayers; l++) {
         float* y_l = y_next;
         y_next = get_layer(p, min(l + 1, p.nlayers - 1)).y;
-        if (!cta_wait(c, &c.bars->ydone[l & 1], (l >> 1) & 1, 8)) return;
-        write_out<P::M>(p, c.ytile + (l & 1) * kOutCap, y_l + p.row_base + c.r0, c.r1 - c.r0, c.lane);
+        const int b = l % kYBufs;
+        if (!cta_wait(c, &c.bars->ydone[b], (l / kYBufs) & 1, 8)) return;
+        write_out<P::M>(p, c.ytile + b * kOutCap, y_l + p.row_base + c.r0, c.r1 - c.r0, c.lane, delta);
         __syncwarp();
-        if (c.lane == 0) mbar_arrive(&c.bars->yfree[l & 1]);
+        if (c.lane == 0) mbar_arrive(&c.bars->yfree[b]);
         if (p.flags) {
             // the rows are visible everywhere before the counter of the layer moves: receiver 0 is
             // this GPU, receiver q > 0 the q-th additional copy
@@ -230,7 +239,7 @@ __device__ __forceinline__ void run_writer(const Cta& c) {
 // before the first stage of layer l that a warp works on
 template <class P>
 __device__ __forceinline__ bool layer_enter(const Cta& c, int l) {
-    if (c.tiled && l >= 2 && !cta_wait(c, &c.bars->yfree[l & 1], ((l >> 1) & 1) ^ 1, 7)) return false;
+    if (c.tiled && l >= kYBufs && !cta_wait(c, &c.bars->yfree[l % kYBufs], ((l / kYBufs) & 1) ^ 1, 7)) return false;
     if (!P::ACT_IN_STAGE && !cta_wait(c, &c.bars->act_ready[l % P::NACT], (l / P::NACT) & 1, 2)) return false;
     return true;
 }
@@ -243,7 +252,7 @@ __device__ __forceinline__ void act_release(const Cta& c, int l) {
 __device__ __forceinline__ void layer_done(const Cta& c, int l) {
     if (c.tiled) {
         __syncwarp();
-        if (c.lane == 0) mbar_arrive(&c.bars->ydone[l & 1]);
+        if (c.lane == 0) mbar_arrive(&c.bars->ydone[l % kYBufs]);
     }
 }
 // one y value: into the layer's tile `yt`, or (too many rows per CTA for the tile) straight to every receiver
@@ -275,7 +284,7 @@ stream_kernel(const typename P::Params pp) {
     c.act = c.ring + (size_t)P::STAGES * P::STAGE;
     c.red = reinterpret_cast<float*>(c.act + (P::ACT_IN_STAGE ? 0 : P::NACT * P::ACT));
     c.ytile = c.red + P::NGROUPS * 2 * P::RED;
-    c.extra = reinterpret_cast<uint8_t*>(c.ytile + 2 * kOutCap);
+    c.extra = reinterpret_cast<uint8_t*>(c.ytile + kYBufs * kOutCap);
     c.warp = threadIdx.x >> 5;
     c.lane = threadIdx.x & 31;
     c.hint = p.wait_hint_ns;
@@ -293,7 +302,7 @@ stream_kernel(const typename P::Params pp) {
             mbar_init(&c.bars->red_full[b], CW);
             mbar_init(&c.bars->red_free[b], 1);
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < kYBufs; b++) {
             mbar_init(&c.bars->ydone[b], NCW);
             mbar_init(&c.bars->yfree[b], 1);
         }
@@ -324,7 +333,7 @@ stream_kernel(const typename P::Params pp) {
 template <class P>
 constexpr size_t smem_bytes() {
     return (size_t)kHeader + (size_t)P::STAGES * P::STAGE + (P::ACT_IN_STAGE ? 0 : (size_t)P::NACT * P::ACT) +
-           (size_t)P::NGROUPS * 2 * P::RED * 4 + 2 * kOutCap * 4 + P::EXTRA;
+           (size_t)P::NGROUPS * 2 * P::RED * 4 + (size_t)kYBufs * kOutCap * 4 + P::EXTRA;
 }
 
 }  // namespace stream

@@ -83,6 +83,7 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_download_async": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_upload_beside": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_upload_join": (c.c_int, []),
+        "fm_copy_beside": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_event_create": (c.c_int, []),
         "fm_event_record": (c.c_int, [c.c_int]),
         "fm_event_elapsed_ms": (c.c_float, [c.c_int, c.c_int]),
@@ -375,6 +376,11 @@ class Runtime:
         beside what is enqueued next; ``upload_join`` makes later launches wait for it."""
         if self._lib.fm_upload_beside(ctypes.c_void_p(int(ptr)), arr.ctypes.data_as(ctypes.c_void_p), arr.nbytes) != 0:
             self._fail("fm_upload_beside")
+
+    def copy_beside(self, dst: int, src: int, nbytes: int) -> None:
+        """Device-to-device copy on the second queue (``dst`` may be a peer's imported allocation)."""
+        if self._lib.fm_copy_beside(ctypes.c_void_p(int(dst)), ctypes.c_void_p(int(src)), int(nbytes)) != 0:
+            self._fail("fm_copy_beside")
 
     def upload_join(self) -> None:
         if self._lib.fm_upload_join() != 0:
