@@ -964,7 +964,6 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
         case 1: return run_policy<W4Dp4a<false, 5, 2, false>>(kn, c, pp);                    // dp4a
         case 2: return run_policy<W4A8Mma<1, 4, 1, false, 5, true, 0, false>>(kn, c, pp);    // deeper ring of code tiles
         case 4: return run_policy<W4A8Mma<1, 4, 1, true, 1, false, 0, false>>(kn, c, pp);    // codes inside every stage, one group
-        case 5: return run_policy<W4A8Mma<1, 5, 2, false, 2, false, 0, false>>(kn, c, pp);   // two groups, fragments from a tile of their own
         case 7: return run_policy<W4A8Mma<1, 4, 1, false, 2, true, 64, false>>(kn, c, pp);   // padded row pitch (no bank conflicts): slower
         default: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);
     }
