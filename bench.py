@@ -155,7 +155,8 @@ class Stream:
         self.wq = rt.alloc(layers * self.rows * (K // 2))
         self.ws = rt.alloc(layers * self.rows * NG * 2)
         self.x = rt.alloc(layers * K * 4)
-        self.y = rt.alloc(layers * N * 4)                         # gathered outputs [layers][N]
+        self.ysz = layers * N * 4
+        self.y = rt.alloc(2 * self.ysz)                           # gathered outputs [layers][N], two buffers
         self.yloc = rt.alloc(layers * self.rows * 4) if world > 1 else self.y
         self.ae, self.ao = rt.alloc(K // 2), rt.alloc(K // 2)
         self.asc, self.asu = rt.alloc(NG * 4), rt.alloc(NG * 4)
@@ -193,7 +194,7 @@ class Stream:
         self.enqueue_token(**kw)
         return self.rt.graph_end()
 
-    def capture_fused(self, host_mirror: bool = False, x: int | None = None) -> int:
+    def capture_fused(self, host_mirror: bool = False, x: int | None = None, ybuf: int = 0) -> int:
         """One decoded token as TWO launches: quant_act over the x of all layers (grid y =
         layer), then the multi-layer stream kernel (bulk-copy ring over all layers' weights).
         With several GPUs the kernel's epilogue stores every y row into the y buffer of every
@@ -201,10 +202,11 @@ class Stream:
         With `host_mirror` the pinned host array y_host is one more receiver of this rank's
         rows: the result reaches the host while the kernel runs, with no copy afterwards."""
         rt, nl = self.rt, self.layers
-        if not hasattr(self, "table"):
+        if not hasattr(self, "tables"):
             base = self.rank * self.rows
-            self.table = rt.stream_table([(self.wq_l(l), self.ws_l(l), self.x + l * K * 4, self.y + l * N * 4)
-                                          for l in range(nl)], self.rows, K, base)
+            self.tables = [rt.stream_table([(self.wq_l(l), self.ws_l(l), self.x + l * K * 4, self.y + b * self.ysz + l * N * 4)
+                                            for l in range(nl)], self.rows, K, base) for b in range(2)]
+            self.table = self.tables[0]
             self.status = rt.alloc(4)
             rt.memset(self.status, 0, 4)
             self.ae_all, self.ao_all = rt.alloc(nl * K // 2), rt.alloc(nl * K // 2)
@@ -214,17 +216,19 @@ class Stream:
                 from k100lc_kernels.shard import exchange_ipc
                 peers = exchange_ipc(rt, self.dist, self.y)
                 bases = [peers[r] for r in range(self.world) if r != self.rank]
-                self.deltas = rt.stream_peers(bases, self.y, nl * N * 4)
+                self.deltas = rt.stream_peers(bases, self.y, 2 * self.ysz)
                 self.npeers = len(bases)
             self.bases = bases if self.world > 1 else []
         npeers, deltas = self.npeers, self.deltas
         if host_mirror:
+            if ybuf != 0:
+                raise ValueError("the host receiver mirrors the first y buffer")
             if not hasattr(self, "deltas_host"):
-                self.deltas_host = rt.stream_peers(self.bases + [self.y_host.ctypes.data], self.y, nl * N * 4)
+                self.deltas_host = rt.stream_peers(self.bases + [self.y_host.ctypes.data], self.y, self.ysz)
             npeers, deltas = self.npeers + 1, self.deltas_host
         rt.graph_begin()
         rt.launch2d("quant_act", NG, nl, 32, 1, [self.x if x is None else x, self.ae_all, self.ao_all, self.asc_all, self.asu_all, nl, K])
-        rt.launch("w4a8_decode_stream", 1, 1, [self.table, nl, self.rows, K, self.rank * self.rows, npeers,
+        rt.launch("w4a8_decode_stream", 1, 1, [self.tables[ybuf], nl, self.rows, K, self.rank * self.rows, npeers,
                                                deltas, self.status,
                                                self.ae_all, self.ao_all, self.asc_all, self.asu_all, 0])
         return rt.graph_end()
@@ -677,20 +681,31 @@ def run_ours(args) -> int:
             ms_sus = time_graph(rt, graph, n_sus, 3, barrier, None, clocks_sus)
         sustained = (ms_sus, n_sus, clocks_sus.summary())
         log(f"sustained region done: {ms_sus:.3f} ms/step over {n_sus} steps")
-    # end to end through the C ABI with host buffers: x of all layers up, y of all layers back, every step
-    # (fused: the kernel itself delivers this rank's rows of y to the pinned host array; per-layer
-    # mode copies the gathered y back after the graph)
-    # Inputs are double-buffered on the device: while step t runs on x[t % 2], the x of step t + 1 is uploaded into
-    # the other buffer on the engine's second queue (the upload waits for step t - 1, the last reader of that buffer,
-    # and step t + 1 waits for the upload).  Every step still uploads its own inputs inside the timed region.
+    # end to end through the C ABI with host buffers: x of all layers up, y of all layers back, every step.
+    # Inputs and outputs are double-buffered on the device so that the copies of neighbouring steps run on the
+    # copy engines beside the kernel of this step: the x of step t + 1 is uploaded on the engine's second queue
+    # while step t runs (the upload waits for the last reader of its buffer, step t + 1 waits for the upload), and
+    # this rank's rows of the y of step t are downloaded on the third queue while step t + 1 runs (step t + 2, the
+    # next writer of that y buffer, waits for the download).  Every step still moves its own inputs and results
+    # inside the timed region; fm_sync ends it.  --e2e-mirror: the kernel stores its rows into the pinned host array
+    # itself instead (one more receiver of the writer warp, no copy afterwards).
     st.y_host[:] = np.nan
     e2e_h2d = world * args.layers * K * 4
+    lo = rank * st.rows
+    mirror = bool(args.e2e_mirror)
+
+    def fetch_y(t):                                 # this rank's rows of all layers of y buffer t % 2 -> y_host
+        if mirror:
+            return
+        rt.download_beside(st.y_host, st.y + (t % 2) * st.ysz + lo * 4, width=st.rows * 4, height=args.layers,
+                           dpitch=N * 4, hpitch=N * 4, host_offset=lo * 4)
+
     if fused and world > 1:
         # Several GPUs: the activations are replicated, but uploading all of x on every rank makes the host
-        # serve N x 8.2 MB per token (at eight GPUs that, not the kernel, set the step time).  Instead every rank
-        # uploads 1/N of x, the copy engines push that slice into every peer's buffer over NVLink (beside the
-        # running kernel, no SM involved), and a step starts behind a bounded acquire on N counters that the pushes
-        # bump.  Four buffers: a peer can be up to two steps behind when a slice for the step after next arrives.
+        # serve N x 8.2 MB per token.  Instead every rank uploads 1/N of x, the copy engines push that slice into
+        # every peer's buffer over NVLink (beside the running kernel, no SM involved), and a step starts behind a
+        # bounded acquire on N counters that the pushes bump.  Four buffers: a peer can be up to two steps behind
+        # when a slice for the step after next arrives.
         from k100lc_kernels.shard import exchange_ipc
         NB, xb = 4, args.layers * K * 4
         sl = xb // world                                             # bytes of one rank's slice
@@ -706,7 +721,7 @@ def run_ours(args) -> int:
         barrier()
         px = exchange_ipc(rt, dist, xall)
         x_flat = st.x_host.reshape(-1).view(np.uint8)
-        graphs = [st.capture_fused(host_mirror=True, x=xall + b * xb) for b in range(NB)]
+        graphs = [st.capture_fused(host_mirror=mirror, x=xall + b * xb, ybuf=0 if mirror else b % 2) for b in range(NB)]
         step_no = [0]
         e2e_h2d = args.layers * K * 4
 
@@ -726,20 +741,24 @@ def run_ours(args) -> int:
             t = step_no[0]
             distribute(t + 1)                                        # beside step t
             rt.launch("stream_flag_wait", 1, 128, [xall + fl0 + (t % NB) * world * 4, world, t + 1, wstat, 2000000])
+            rt.download_join(1)                                      # y[t % 2] was last read by the download of step t - 2
             rt.graph_launch(graphs[t % NB])
+            fetch_y(t)
             step_no[0] = t + 1
     elif fused:
         x2 = rt.alloc(args.layers * K * 4)
         xbuf = (st.x, x2)
-        graphs = (st.capture_fused(host_mirror=True, x=st.x), st.capture_fused(host_mirror=True, x=x2))
+        graphs = tuple(st.capture_fused(host_mirror=mirror, x=xbuf[b], ybuf=0 if mirror else b) for b in range(2))
         step_no = [0]
         rt.upload(st.x, st.x_host)                  # the very first step's inputs (outside the timed steps)
 
         def e2e_step():
             t = step_no[0]
             rt.upload_beside(xbuf[(t + 1) % 2], st.x_host)     # inputs of the next step, beside this one
+            rt.download_join(1)
             rt.graph_launch(graphs[t % 2])
             rt.upload_join()
+            fetch_y(t)
             step_no[0] = t + 1
     else:
         def e2e_step():
@@ -765,10 +784,10 @@ def run_ours(args) -> int:
         if not np.array_equal(got_x, st.x_host.reshape(-1)):
             raise RuntimeError("the gathered inputs of the last step differ from the host's x")
     if fused:                                       # what the host received is what the device holds
-        lo = rank * st.rows
-        dev_y = rt.download(st.y, args.layers * N, np.float32).reshape(args.layers, N)
+        last = 0 if mirror else (step_no[0] - 1) % 2
+        dev_y = rt.download(st.y + last * st.ysz, args.layers * N, np.float32).reshape(args.layers, N)
         if not np.array_equal(st.y_host[:, lo:lo + st.rows].view(np.uint32), dev_y[:, lo:lo + st.rows].view(np.uint32)):
-            raise RuntimeError("the host copy of y written by the stream kernel differs from the device copy")
+            raise RuntimeError("the host copy of this rank's rows of y differs from the device copy")
 
     # the dominant kernel alone, for the roofline: the fused stream kernel is the whole step;
     # in per-layer mode it is gemv_w4a8<1,false,1> without the quantiser
@@ -844,8 +863,11 @@ def run_ours(args) -> int:
                              if world > 1 else
                              "per step: fm_upload_beside(x of all layers for the next step, second device buffer) + fm_graph_launch + "
                              "fm_upload_join; ") +
-                            "the stream kernel stores each rank's rows of y into a pinned host array (fm_host_alloc, registered "
-                            "through fm_stream_peers) while it runs; fm_sync ends the run") if fused else
+                            ("the stream kernel stores each rank's rows of y into a pinned host array (fm_host_alloc, registered "
+                             "through fm_stream_peers) while it runs; " if mirror else
+                             "fm_download_beside of this rank's rows of the step's y into a pinned host array (third queue, beside "
+                             "the next step; two y buffers, fm_download_join(1) before the next writer); ") +
+                            "fm_sync ends the run") if fused else
                            "fm_upload_async(x) + fm_graph_launch + fm_download_async(y), pinned host buffers"},
             "gpu_launches": int(gpu_launches),
             "per_layer_launches": None if ms_alt is None else {
@@ -919,6 +941,8 @@ def main() -> int:
     ap.add_argument("--cpu-layers", type=int, default=CPU_SAMPLE_LAYERS, help="layers of the stream timed on the CPU (0 = skip)")
     ap.add_argument("--no-paths", dest="paths", action="store_false", help="skip the per-path M=1 timings")
     ap.add_argument("--watchdog", type=int, default=600, help="give up after this many seconds")
+    ap.add_argument("--e2e-mirror", action="store_true",
+                    help="end to end: the kernel stores y into the pinned host array itself instead of a download beside the next step")
     ap.add_argument("--sustain-s", type=float, default=1.0,
                     help="also time the step back to back for this many seconds (0 = skip)")
     args = ap.parse_args()

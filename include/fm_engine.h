@@ -99,6 +99,14 @@ int   fm_upload_join(void);
 /* Device-to-device copy on the second queue, behind what that queue already holds; dst may be a peer's allocation
  * opened with fm_ipc_import (copy engines, no SM needed: it runs beside the kernels of the engine stream). */
 int   fm_copy_beside(void* dst, const void* src, size_t n);
+/* Download on a third queue, for double-buffered outputs: `height` rows of `width` bytes, `dpitch` / `hpitch` bytes
+ * between the starts of rows on the device / the host (height 1: a plain copy of `width` bytes).  The copy starts
+ * when everything enqueued on the engine stream before the call has finished and runs beside what is enqueued after
+ * it.  fm_download_join(lag) makes the engine stream wait for the download issued `lag` calls before the latest
+ * (0..3).  Per step t:  fm_download_join(1); launch step t (writes y[t%2]); fm_download_beside(host, .., y[t%2], ..).
+ * Not available inside a graph capture.  fm_sync also waits for the third queue. */
+int   fm_download_beside(void* pinned_host, size_t hpitch, const void* dev, size_t dpitch, size_t width, size_t height);
+int   fm_download_join(int lag);
 
 /* Layer table of the fused decode stream ("w4a8_decode_stream"): host_layers holds
  * nlayers x {wq, ws, x, y} device addresses.  Every address is checked against the live

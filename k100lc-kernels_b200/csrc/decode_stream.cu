@@ -1026,7 +1026,7 @@ int launch_w4a8_stream_m(const LaunchCtx& c, const uint64_t* a) {
 // [rows][K/16] (the table must have been validated with room for them: fm_stream_table records how many bytes follow
 // every ws pointer inside its allocation); qa / qb / sc are nvfp4_quant_act's outputs for all layers: [nlayers][K/2],
 // [nlayers][K/2], [nlayers][K/16].  nvfp4_decode_stream_iacc(..., flags, iacc): iacc int32 [nlayers][rows][K/16].
-// $FM_NVFP4_CFG=0 / 2 select the tensor-core consumer (one / two groups) for the run and for the dump.
+// $FM_NVFP4_CFG=1 selects the dp4a consumer, 0 / 2 the mma.sync consumer (one / two groups), for the run and for the dump.
 template <bool DUMP>
 int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = DUMP ? "nvfp4_decode_stream_iacc" : "nvfp4_decode_stream";
@@ -1048,18 +1048,24 @@ int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
     FM_RANGE(p.ae, (size_t)p.nlayers * (p.K / 2), kn, "qa");
     FM_RANGE(p.ao, (size_t)p.nlayers * (p.K / 2), kn, "qb");
     FM_RANGE(p.asc, (size_t)p.nlayers * (p.K / 16) * 4, kn, "sc");
-    const int cfg = env_or("FM_NVFP4_CFG", 1);
+    // Default (3): the tcgen05 consumer of nvfp4_tc_stream.cu — the codes go from HBM to the MMA without an instruction.
+    // Measured per 17408 x 5120 layer (64 layers per launch, burst): dp4a (1) 10.1 us, mma.sync consumer 10.2 (two
+    // groups, 2) - 10.9 us (one group, 0): those three are bound by the integer pipe (PRMT decode).
+    int cfg = env_or("FM_NVFP4_CFG", 3);
     if (DUMP) {
         p.iacc = arg_ptr<int>(a[13]);
         FM_REQUIRE(aligned(p.iacc, 4), kn, "misaligned accumulator dump");
         FM_RANGE(p.iacc, (size_t)p.nlayers * p.rows * (p.K / 16) * 4, kn, "iacc");
-        return cfg == 1 ? run_policy<Nvfp4Dp4a<5, 2, true>>(kn, c, pp) : run_policy<Nvfp4Mma<4, 1, 2, true>>(kn, c, pp);
     }
-    // Default: the dp4a consumer.  Measured per 17408 x 5120 layer (64 layers per launch, burst): dp4a 10.1 us,
-    // tensor-core consumer 10.2 (two groups) - 10.9 us (one group): both are bound by the integer pipe (PRMT decode).
+    if (cfg == 3) {
+        const int rc3 = nvfp4_tc_stream(kn, c, p, pp.gscale, DUMP);
+        if (rc3 <= 0) return rc3;
+        cfg = 1;                                             // no tensor maps for this table here: the dp4a consumer
+    }
+    if (DUMP) return cfg == 1 ? run_policy<Nvfp4Dp4a<5, 2, true>>(kn, c, pp) : run_policy<Nvfp4Mma<4, 1, 2, true>>(kn, c, pp);
     switch (cfg) {
-        case 0: return run_policy<Nvfp4Mma<4, 1, 2, false>>(kn, c, pp);      // tensor cores, one consumer group
-        case 2: return run_policy<Nvfp4Mma<4, 2, 2, false>>(kn, c, pp);      // tensor cores, two consumer groups
+        case 0: return run_policy<Nvfp4Mma<4, 1, 2, false>>(kn, c, pp);      // mma.sync, one consumer group
+        case 2: return run_policy<Nvfp4Mma<4, 2, 2, false>>(kn, c, pp);      // mma.sync, two consumer groups
         default: return run_policy<Nvfp4Dp4a<5, 2, false>>(kn, c, pp);
     }
 }

@@ -47,6 +47,9 @@ struct Engine {
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;       // second queue for uploads that run beside the kernels (fm_upload_beside)
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaStream_t down_stream = nullptr;       // third queue for downloads that run beside the kernels (fm_download_beside)
+    cudaEvent_t ev_dfork = nullptr, ev_down[4] = {nullptr, nullptr, nullptr, nullptr};
+    unsigned long long downloads = 0;         // fm_download_beside calls so far (ev_down is a ring over them)
     bool copy_pending = false;
     std::string image;
     bool check_bounds = true;
@@ -61,7 +64,12 @@ struct Engine {
     // freeing one of them drops the record, so a launch that still names it is rejected (-4) until
     // fm_stream_table / fm_stream_peers is called again.
     struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; size_t ws_avail; bool x_all;
-                   std::vector<uintptr_t> deps; };
+                   std::vector<uintptr_t> deps;
+                   unsigned long long serial = 0;        // distinguishes this record from an earlier one at the same address
+                   std::vector<uintptr_t> wq; };         // the wq entry of every layer (for the TMA tensor maps)
+    struct MapSet { void* dev; unsigned long long serial; };
+    std::map<uintptr_t, MapSet> table_maps;      // table address -> device array of tensor maps built for record `serial`
+    unsigned long long table_serial = 0;
     std::map<uintptr_t, Table> tables;           // validated stream layer tables
     struct Peers { int npeers; uintptr_t lo, hi; std::vector<uintptr_t> deps; };
     std::map<uintptr_t, Peers> peers;            // validated peer-offset arrays (device address -> window)
@@ -403,6 +411,36 @@ bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_ba
     return (whole_y ? t.y_ptr_lo : t.y_lo) >= ip->second.lo && t.y_hi <= ip->second.hi;
 }
 
+const void* stream_table_maps(const void* table, int nlayers, int rows, int K) {
+    Engine& e = E();
+    const uintptr_t key = reinterpret_cast<uintptr_t>(table);
+    auto it = e.tables.find(key);
+    if (it == e.tables.end()) return nullptr;
+    const Engine::Table& t = it->second;
+    if (t.nlayers < nlayers || t.rows != rows || t.K != K || (int)t.wq.size() < nlayers) return nullptr;
+    auto im = e.table_maps.find(key);
+    if (im != e.table_maps.end() && im->second.serial == t.serial) return im->second.dev;
+    if (e.capturing) return nullptr;                        // building needs an allocation and a synchronous copy
+    std::vector<unsigned char> host((size_t)t.nlayers * 128);
+    for (int l = 0; l < t.nlayers; l++)
+        if (!encode_u4_rows_map(host.data() + (size_t)l * 128, reinterpret_cast<const void*>(t.wq[l]), (uint64_t)rows, (uint64_t)K))
+            return nullptr;
+    if (im != e.table_maps.end()) {                         // maps of an older record at this address
+        cudaStreamSynchronize(e.stream);
+        cudaFree(im->second.dev);
+        e.table_maps.erase(im);
+    }
+    void* dev = nullptr;
+    if (cudaMalloc(&dev, host.size()) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (cudaMemcpy(dev, host.data(), host.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(dev);
+        return nullptr;
+    }
+    e.table_maps[key] = Engine::MapSet{dev, t.serial};
+    return dev;
+}
+
 bool peer_window_ok(const void* peer_delta, int npeers, const void* ptr, size_t bytes) {
     Engine& e = E();
     if (!e.check_bounds) return true;
@@ -446,6 +484,7 @@ void fm_free(void* p) {
     if (!p || !E().ready) return;
     cudaStreamSynchronize(E().stream);        // nothing in flight may still use it
     if (E().copy_stream) cudaStreamSynchronize(E().copy_stream);
+    if (E().down_stream) cudaStreamSynchronize(E().down_stream);
     auto it = E().allocs.find(reinterpret_cast<uintptr_t>(p));
     if (it != E().allocs.end()) {
         touch(p, it->second);
@@ -515,6 +554,7 @@ int fm_sync(void) {
     NEED_INIT(-1);
     cudaError_t err = cudaStreamSynchronize(E().stream);
     if (err == cudaSuccess && E().copy_stream) err = cudaStreamSynchronize(E().copy_stream);
+    if (err == cudaSuccess && E().down_stream) err = cudaStreamSynchronize(E().down_stream);
     if (err != cudaSuccess) { cuda_fail("fm_sync", err); return -1; }
     return 0;
 }
@@ -734,6 +774,46 @@ int fm_upload_join(void) {
     return 0;
 }
 
+// Download on a third queue: `height` rows of `width` bytes, `dpitch` / `hpitch` bytes between the starts of rows on
+// the device / the host (height 1: a plain copy).  The copy starts once everything enqueued on the engine stream BEFORE
+// this call has finished and runs beside whatever is enqueued after it.  fm_download_join(lag) makes the engine stream
+// wait for the download issued `lag` calls before the latest (0..3).  Pattern for double-buffered outputs:
+//   fm_download_join(1); fm_graph_launch(step t, writing y[t%2]); fm_download_beside(host, ..., y[t%2], ...);
+int fm_download_beside(void* host, size_t hpitch, const void* dev, size_t dpitch, size_t width, size_t height) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (e.capturing) { set_errorf("fm_download_beside: not inside a graph capture"); return -1; }
+    if (width == 0 || height == 0) return 0;
+    if (height > 1 && (dpitch < width || hpitch < width)) { set_errorf("fm_download_beside: a pitch is smaller than the width"); return -1; }
+    if (!range_ok(dev, (height - 1) * dpitch + width)) { set_errorf("fm_download_beside: range exceeds the allocation"); return -1; }
+    if (!e.down_stream) {
+        bool ok = cudaStreamCreateWithFlags(&e.down_stream, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&e.ev_dfork, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; ok && i < 4; i++) ok = cudaEventCreateWithFlags(&e.ev_down[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) { cuda_fail("fm_download_beside", cudaGetLastError()); return -1; }
+    }
+    cudaError_t err = cudaEventRecord(e.ev_dfork, e.stream);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(e.down_stream, e.ev_dfork, 0);
+    if (err == cudaSuccess)
+        err = height == 1 ? cudaMemcpyAsync(host, dev, width, cudaMemcpyDeviceToHost, e.down_stream)
+                          : cudaMemcpy2DAsync(host, hpitch, dev, dpitch, width, height, cudaMemcpyDeviceToHost, e.down_stream);
+    if (err == cudaSuccess) err = cudaEventRecord(e.ev_down[e.downloads % 4], e.down_stream);
+    if (err != cudaSuccess) { cuda_fail("fm_download_beside", err); return -1; }
+    e.downloads++;
+    return 0;
+}
+int fm_download_join(int lag) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (lag < 0 || lag > 3) { set_errorf("fm_download_join: lag=%d must be 0..3", lag); return -1; }
+    if (e.downloads <= (unsigned long long)lag) return 0;       // nothing that old has been issued
+    cudaError_t err = cudaStreamWaitEvent(e.stream, e.ev_down[(e.downloads - 1 - lag) % 4], 0);
+    if (err != cudaSuccess) { cuda_fail("fm_download_join", err); return -1; }
+    return 0;
+}
+
 int fm_download_async(void* host, const void* dev, size_t n) {
     LOCK;
     NEED_INIT(-1);
@@ -757,6 +837,8 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
                             ((size_t)row_base + rows) * 4};
     uintptr_t y_lo = ~(uintptr_t)0, y_hi = 0, y_ptr_lo = ~(uintptr_t)0;
     std::vector<uintptr_t> deps;                   // allocations the table points into (and the one it lives in)
+    std::vector<uintptr_t> wqs((size_t)nlayers);
+    for (int l = 0; l < nlayers; l++) wqs[l] = static_cast<uintptr_t>(host_layers[4 * l]);
     add_dep(deps, reinterpret_cast<uintptr_t>(dev_table));
     size_t ws_avail = ~(size_t)0;                  // fewest bytes between a ws pointer and the end of its allocation
     bool x_all = true;                             // every layer has a (validated) x
@@ -792,7 +874,8 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
         }
     if (copy_sync(dev_table, host_layers, bytes, cudaMemcpyHostToDevice, "fm_stream_table") != 0) return -1;
     touch(dev_table, bytes);
-    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo, ws_avail, x_all, deps};
+    e.tables[reinterpret_cast<uintptr_t>(dev_table)] =
+        Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo, ws_avail, x_all, deps, ++e.table_serial, wqs};
     return 0;
 }
 

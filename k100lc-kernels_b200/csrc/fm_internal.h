@@ -45,6 +45,15 @@ void* engine_scratch(size_t bytes);
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
                      int npeers, bool whole_y = false, size_t ws_bytes = 0, bool need_x = false);
 
+// Device array of `nlayers` TMA tensor maps (128 bytes each) over the wq entries of a validated layer table, each
+// layer's codes seen as [rows][K] 4-bit values with a box of 128 rows x 128 values, 128-byte swizzle, unpacked to one
+// byte of shared memory per value.  Built when first asked for and kept with the table's record; nullptr when the
+// table has no record with these shapes, a wq pointer is not 32-byte aligned, the driver refuses the encoding, or the
+// array would have to be allocated inside a stream capture.
+const void* stream_table_maps(const void* table, int nlayers, int rows, int K);
+// one such map (gemm_w4.cu holds the encoder): false when the driver refuses it
+bool encode_u4_rows_map(void* map128, const void* base, uint64_t rows, uint64_t K);
+
 // true when [ptr, ptr+bytes) lies inside the local window that fm_stream_peers validated for the offset array
 // `peer_delta` (so every receiver has the same bytes at the same offset), or checks are off
 bool peer_window_ok(const void* peer_delta, int npeers, const void* ptr, size_t bytes);
@@ -73,6 +82,10 @@ cudaError_t gemv_w4a8_raw(const uint32_t* wq, const void* ws_f16, const int8_t* 
 // accumulators [M][rows][K/128].
 int stream_gemv_w4a8(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* ae, const void* ao,
                      const void* asc, const void* asu, float* y, int M, int ystride, int rows, int* iacc);
+namespace stream { struct StreamParams; }
+// nvfp4_decode_stream on the tcgen05 path (nvfp4_tc_stream.cu).  FM_OK after enqueueing, negative after a rejection,
+// 1 when this path cannot take the launch and the caller should use another consumer.
+int nvfp4_tc_stream(const char* kn, const LaunchCtx& c, const stream::StreamParams& sp, float gscale, bool dump);
 int stream_read_status(cudaStream_t stream);   // 0, or the code of the first bounded wait that ran out in such a launch
 
 int gemm_read_status(cudaStream_t stream);   // 0, or the code of the first bounded wait that ran out

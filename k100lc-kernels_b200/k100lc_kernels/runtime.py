@@ -84,6 +84,8 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_upload_beside": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_upload_join": (c.c_int, []),
         "fm_copy_beside": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
+        "fm_download_beside": (c.c_int, [c.c_void_p, c.c_size_t, c.c_void_p, c.c_size_t, c.c_size_t, c.c_size_t]),
+        "fm_download_join": (c.c_int, [c.c_int]),
         "fm_event_create": (c.c_int, []),
         "fm_event_record": (c.c_int, [c.c_int]),
         "fm_event_elapsed_ms": (c.c_float, [c.c_int, c.c_int]),
@@ -385,6 +387,24 @@ class Runtime:
     def upload_join(self) -> None:
         if self._lib.fm_upload_join() != 0:
             self._fail("fm_upload_join")
+
+    def download_beside(self, arr: np.ndarray, ptr: int, width: int | None = None, height: int = 1,
+                        dpitch: int = 0, hpitch: int = 0, host_offset: int = 0) -> None:
+        """Download on the engine's third queue: starts when the work enqueued so far has finished, runs beside
+        what is enqueued next.  Plain form: all of ``arr``.  2-D form: ``height`` rows of ``width`` bytes, rows
+        ``dpitch`` / ``hpitch`` bytes apart on the device / in ``arr``, starting ``host_offset`` bytes into ``arr``."""
+        if width is None:
+            width, height = arr.nbytes, 1
+        elif host_offset + (height - 1) * hpitch + width > arr.nbytes:
+            raise ValueError("download_beside: the rows do not fit the host array")
+        if self._lib.fm_download_beside(ctypes.c_void_p(int(arr.ctypes.data) + int(host_offset)), int(hpitch),
+                                        ctypes.c_void_p(int(ptr)), int(dpitch), int(width), int(height)) != 0:
+            self._fail("fm_download_beside")
+
+    def download_join(self, lag: int = 0) -> None:
+        """Later launches wait for the ``download_beside`` issued ``lag`` calls before the latest."""
+        if self._lib.fm_download_join(int(lag)) != 0:
+            self._fail("fm_download_join")
 
     def download_async(self, arr: np.ndarray, ptr: int) -> None:
         if self._lib.fm_download_async(arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(int(ptr)),

@@ -163,3 +163,46 @@ def test_error_codes_and_bounds(rt):
     with pytest.raises(RuntimeError):
         Runtime(hsaco="/tmp/some_other_image.so", lib=rt.hsaco)
     rt.sync()
+
+
+def test_copy_queues_beside_the_engine_stream(rt):
+    """fm_upload_beside / fm_copy_beside / fm_upload_join and fm_download_beside / fm_download_join: a two-buffer
+    pipeline of (upload, kernel, strided download) steps leaves every step's result in pinned host memory, and the
+    argument checks hold."""
+    rows, width = 64, 48                               # download `width` floats of each of `rows` rows of 256
+    n = rows * 256
+    host_in = rt.pinned((4, n), np.float32)
+    host_in[:] = np.random.default_rng(3).standard_normal((4, n)).astype(np.float32)
+    host_out = rt.pinned((4, rows, width), np.float32)
+    host_out[:] = np.nan
+    with Bufs(rt) as b:
+        x = [b.zeros(n), b.zeros(n)]
+        mid = b.zeros(n)
+        y = [b.zeros(n), b.zeros(n)]
+        rt.upload(x[0], host_in[0])
+        for t in range(4):
+            if t + 1 < 4:
+                rt.upload_beside(x[(t + 1) % 2], host_in[t + 1])
+            rt.download_join(1)                        # y[t % 2] was last read by the download of step t - 2
+            rt.copy_dev(mid, x[t % 2], n * 4)          # the "kernel" of the step on the engine stream: two copies
+            rt.copy_dev(y[t % 2], mid, n * 4)
+            rt.upload_join()
+            rt.download_beside(host_out, y[t % 2] + 16 * 4, width=width * 4, height=rows, dpitch=256 * 4,
+                               hpitch=width * 4, host_offset=t * rows * width * 4)
+        rt.sync()
+        for t in range(4):
+            assert np.array_equal(host_out[t], host_in[t].reshape(rows, 256)[:, 16:16 + width])
+        flat = rt.pinned((n,), np.float32)
+        rt.download_beside(flat, y[1])                 # plain form: all of the array
+        rt.download_join(0)
+        rt.sync()
+        assert np.array_equal(flat, host_in[3])
+        with pytest.raises(RuntimeError):
+            rt.download_beside(flat, y[1] + 4)         # runs past the allocation
+        with pytest.raises(RuntimeError):
+            rt.download_join(7)
+        with pytest.raises(ValueError):
+            rt.download_beside(flat, y[1], width=4096, height=rows, dpitch=1024, hpitch=4096)
+        rt.free_pinned(flat)
+    rt.free_pinned(host_in)
+    rt.free_pinned(host_out)

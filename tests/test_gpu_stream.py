@@ -425,11 +425,12 @@ def test_stream_accumulators_several_tokens(rt, m, rows):
         assert O.rel_err(got[i, :, :rows], ref["y"]) < REL
 
 
-@pytest.mark.parametrize("cfg", [None, "0", "2"])
+@pytest.mark.parametrize("cfg", [None, "1", "0", "2"])
 @pytest.mark.parametrize("rows,nlayers", [(17408, 2), (520, 3)])
 def test_stream_accumulators_nvfp4(rt, monkeypatch, rows, nlayers, cfg):
-    """nvfp4_decode_stream: the int32 of every (row, 16-block), bit for bit, from the default (dp4a) consumer and
-    from the tensor-core consumer ($FM_NVFP4_CFG=0; 2 = two groups runs the same arithmetic)."""
+    """nvfp4_decode_stream: the int32 of every (row, 16-block), bit for bit, from the default consumer (tcgen05
+    kind::f8f6f4: the integer is rebuilt from the exact fp32 block sums of the lo / hi halves of the activation
+    codes), the dp4a consumer ($FM_NVFP4_CFG=1) and the mma.sync consumer (0; 2 = two groups, same arithmetic)."""
     if cfg is None:
         monkeypatch.delenv("FM_NVFP4_CFG", raising=False)
     else:
@@ -462,6 +463,57 @@ def test_stream_accumulators_nvfp4(rt, monkeypatch, rows, nlayers, cfg):
         ref = O.nvfp4_gemv(L["wq"], L["ws"], q["q"], q["scale"], gscale)
         assert np.array_equal(acc[i], ref["acc"][0])
         assert O.rel_err(got[i], ref["y"][0]) < REL
+
+
+def test_nvfp4_stream_counters_host_receiver_and_extreme_codes(rt):
+    """The tcgen05 consumer of nvfp4_decode_stream with a pinned host receiver and completion counters: rows that do
+    not fill the last 128-row tile, fewer tiles per layer than CTAs, activation codes over the whole int8 range
+    (-128 and 127 included, written directly instead of through the quantiser) and every finite E4M3 scale code."""
+    rows, nl = 333, 7
+    sms = rt.device_attr("sm_count")
+    layers = [synth.nvfp4_layer(rows, K, 1, seed=1700 + i) for i in range(nl)]
+    rng = np.random.default_rng(5)
+    finite = np.array([c for c in range(256) if (c & 0x7F) != 0x7F], dtype=np.uint8)
+    for i, L in enumerate(layers):
+        ws = np.asarray(L["ws"]).reshape(rows, K // 16).copy()
+        ws[i % rows, :] = finite[rng.integers(0, len(finite), size=K // 16)]
+        ws[(i + 1) % rows, :len(finite)] = finite
+        L["ws"] = ws
+    q = rng.integers(-128, 128, size=(nl, K)).astype(np.int8)
+    q[:, 0:16] = -128
+    q[:, 16:32] = 127
+    q[:, 32:48:2] = -128
+    asc = np.exp2(rng.uniform(-8.0, -2.0, size=(nl, K // 16))).astype(np.float32)
+    gscale = float(layers[0]["gscale"])
+    with Bufs(rt) as b:
+        qa, qb = b.put(np.ascontiguousarray(q[:, 0::2])), b.put(np.ascontiguousarray(q[:, 1::2]))
+        sc = b.put(asc)
+        ybytes = nl * rows * 4
+        buf = b.zeros((ybytes + nl * 4) // 4, np.float32, 0)
+        host = rt.pinned(((ybytes + nl * 4) // 4,), np.float32)
+        host[:] = 0
+        flags = buf + ybytes
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), 0, buf + i * rows * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, 0)
+        deltas = rt.stream_peers([host.ctypes.data], buf, ybytes + nl * 4)
+        status = b.zeros(1, np.int32)
+        rt.launch("nvfp4_decode_stream", 1, 1, [table, nl, rows, K, 0, 1, deltas, status, qa, qb, sc, gscale, flags])
+        wstat = b.zeros(1, np.int32)
+        rt.launch("stream_flag_wait", 1, 128, [flags, nl, sms, wstat, 1000])
+        dev = b.get(buf, (ybytes + nl * 4) // 4)
+        assert int(b.get(status, 1, np.int32)[0]) == 0 and int(b.get(wstat, 1, np.int32)[0]) == 0
+        assert (dev[ybytes // 4:].view(np.uint32) == sms).all() and (host[ybytes // 4:].view(np.uint32) == sms).all()
+        assert np.array_equal(host[:ybytes // 4].view(np.uint32), dev[:ybytes // 4].view(np.uint32))
+        pi = b.zeros(nl * rows * (K // 16), np.int32, -7)
+        rt.launch("nvfp4_decode_stream_iacc", 1, 1, [table, nl, rows, K, 0, 0, 0, status, qa, qb, sc, gscale, 0, pi])
+        acc = b.get(pi, nl * rows * (K // 16), np.int32).reshape(nl, rows, -1)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+        rt.free(deltas)
+    for i, L in enumerate(layers):
+        ref = O.nvfp4_gemv(L["wq"], L["ws"], q[i:i + 1].astype(np.int32), asc[i:i + 1], gscale)
+        assert np.array_equal(acc[i], ref["acc"][0])
+        assert O.rel_err(host[i * rows:(i + 1) * rows], ref["y"][0]) < REL
 
 
 def test_stream_schedules_give_identical_bits(rt, monkeypatch):
