@@ -1051,6 +1051,7 @@ int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
     // Default (3): the tcgen05 consumer of nvfp4_tc_stream.cu — the codes go from HBM to the MMA without an instruction.
     // Measured per 17408 x 5120 layer (64 layers per launch, burst): dp4a (1) 10.1 us, mma.sync consumer 10.2 (two
     // groups, 2) - 10.9 us (one group, 0): those three are bound by the integer pipe (PRMT decode).
+    const bool forced = getenv("FM_NVFP4_CFG") != nullptr;
     int cfg = env_or("FM_NVFP4_CFG", 3);
     if (DUMP) {
         p.iacc = arg_ptr<int>(a[13]);
@@ -1060,7 +1061,9 @@ int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
     if (cfg == 3) {
         const int rc3 = nvfp4_tc_stream(kn, c, p, pp.gscale, DUMP);
         if (rc3 <= 0) return rc3;
-        cfg = 1;                                             // no tensor maps for this table here: the dp4a consumer
+        FM_REQUIRE(!forced, kn, "FM_NVFP4_CFG=3: the tcgen05 consumer cannot take this launch (the table has no tensor maps: the driver "
+                   "refused the encoding; or the workspace is too small)");
+        cfg = 1;                                             // no tensor maps for this table: the dp4a consumer
     }
     if (DUMP) return cfg == 1 ? run_policy<Nvfp4Dp4a<5, 2, true>>(kn, c, pp) : run_policy<Nvfp4Mma<4, 1, 2, true>>(kn, c, pp);
     switch (cfg) {

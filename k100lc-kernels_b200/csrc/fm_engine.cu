@@ -423,7 +423,8 @@ const void* stream_table_maps(const void* table, int nlayers, int rows, int K) {
     if (e.capturing) return nullptr;                        // building needs an allocation and a synchronous copy
     std::vector<unsigned char> host((size_t)t.nlayers * 128);
     for (int l = 0; l < t.nlayers; l++)
-        if (!encode_u4_rows_map(host.data() + (size_t)l * 128, reinterpret_cast<const void*>(t.wq[l]), (uint64_t)rows, (uint64_t)K))
+        if (!encode_bytes_rows_map(host.data() + (size_t)l * 128, reinterpret_cast<const void*>(t.wq[l]), (uint64_t)rows,
+                                   (uint64_t)K / 2, 128))
             return nullptr;
     if (im != e.table_maps.end()) {                         // maps of an older record at this address
         cudaStreamSynchronize(e.stream);
@@ -876,6 +877,9 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
     touch(dev_table, bytes);
     e.tables[reinterpret_cast<uintptr_t>(dev_table)] =
         Engine::Table{bytes, nlayers, rows, K, row_base, y_lo, y_hi, y_ptr_lo, ws_avail, x_all, deps, ++e.table_serial, wqs};
+    // The TMA tensor maps over the wq entries are built now, while allocating is allowed (a launch inside a graph
+    // capture could not).  Best effort: a table the driver refuses to encode simply has none.
+    if (K % 256 == 0) stream_table_maps(dev_table, nlayers, rows, K);
     return 0;
 }
 

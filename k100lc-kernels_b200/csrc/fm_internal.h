@@ -46,13 +46,12 @@ bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_ba
                      int npeers, bool whole_y = false, size_t ws_bytes = 0, bool need_x = false);
 
 // Device array of `nlayers` TMA tensor maps (128 bytes each) over the wq entries of a validated layer table, each
-// layer's codes seen as [rows][K] 4-bit values with a box of 128 rows x 128 values, 128-byte swizzle, unpacked to one
-// byte of shared memory per value.  Built when first asked for and kept with the table's record; nullptr when the
-// table has no record with these shapes, a wq pointer is not 32-byte aligned, the driver refuses the encoding, or the
-// array would have to be allocated inside a stream capture.
+// layer's packed codes seen as [rows][K/2] bytes with a box of 128 bytes x 128 rows and the 128-byte swizzle.  Built by
+// fm_stream_table (or when first asked for) and kept with the table's record; nullptr when the table has no record
+// with these shapes, the driver refuses the encoding, or the array would have to be allocated inside a stream capture.
 const void* stream_table_maps(const void* table, int nlayers, int rows, int K);
 // one such map (gemm_w4.cu holds the encoder): false when the driver refuses it
-bool encode_u4_rows_map(void* map128, const void* base, uint64_t rows, uint64_t K);
+bool encode_bytes_rows_map(void* map128, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes);
 
 // true when [ptr, ptr+bytes) lies inside the local window that fm_stream_peers validated for the offset array
 // `peer_delta` (so every receiver has the same bytes at the same offset), or checks are off

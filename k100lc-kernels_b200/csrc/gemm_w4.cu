@@ -689,18 +689,10 @@ const KernelEntry* gemm_w4_kernels(int* n) {
     return kGemm;
 }
 
-bool encode_u4_rows_map(void* map128, const void* base, uint64_t rows, uint64_t K) {
-    EncodeTiledFn enc = tensor_map_encoder();
-    if (!enc || (reinterpret_cast<uintptr_t>(base) & 31) || K % 128 || (K / 2) % 32) return false;
-    const cuuint64_t dims[2] = {K, rows};
-    const cuuint64_t strides[1] = {K / 2};
-    const cuuint32_t box[2] = {128, 128};
-    const cuuint32_t estr[2] = {1, 1};
-    return enc(static_cast<CUtensorMap*>(map128), CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides,
-               box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+bool encode_bytes_rows_map(void* map128, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes) {
+    return make_map(static_cast<CUtensorMap*>(map128), base, rows, row_bytes, box_bytes,
+                    box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
 }
-
 // status word of the GEMM kernels: drains the stream, reads it and clears it
 int gemm_read_status(cudaStream_t stream) {
     int v = 0, zero = 0;

@@ -56,25 +56,26 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint6
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-// kind::f8f6f4: 8-bit, 6-bit and 4-bit floating-point operands (4-bit ones in shared memory as 16 values in 8 bytes
-// followed by 8 bytes of padding, which is how TMA unpacks the 16U4_ALIGN16B tensor type), fp32 accumulator
-__device__ __forceinline__ void tc_mma_f8f6f4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 32 lanes x 4 columns of 32-bit: thread t of the warp gets lane t, columns c..c+3 (asynchronous, see tmem_ld_fence)
-__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(taddr) : "memory");
-}
+// 32 lanes x 16 columns of 32-bit: thread t of the warp gets lane t, columns c..c+15 (asynchronous, see tmem_ld_wait64)
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr) : "memory");
 }
-// all tcgen05.ld of this thread issued so far have delivered their registers
-__device__ __forceinline__ void tmem_ld_fence() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// all tcgen05.ld of this thread issued so far have delivered their registers; the registers are operands of the
+// wait, so that no use of them can be scheduled ahead of it
+__device__ __forceinline__ void tmem_ld_wait64(uint32_t (&r)[4][16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0][0]), "+r"(r[0][1]), "+r"(r[0][2]), "+r"(r[0][3]), "+r"(r[0][4]), "+r"(r[0][5]), "+r"(r[0][6]), "+r"(r[0][7]),
+                   "+r"(r[0][8]), "+r"(r[0][9]), "+r"(r[0][10]), "+r"(r[0][11]), "+r"(r[1][0]), "+r"(r[1][1]), "+r"(r[1][2]), "+r"(r[1][3]),
+                   "+r"(r[1][4]), "+r"(r[1][5]), "+r"(r[1][6]), "+r"(r[1][7]), "+r"(r[1][8]), "+r"(r[1][9]), "+r"(r[1][10]), "+r"(r[1][11])
+                 :: "memory");
+    asm volatile("" : "+r"(r[2][0]), "+r"(r[2][1]), "+r"(r[2][2]), "+r"(r[2][3]), "+r"(r[2][4]), "+r"(r[2][5]), "+r"(r[2][6]), "+r"(r[2][7]),
+                      "+r"(r[2][8]), "+r"(r[2][9]), "+r"(r[2][10]), "+r"(r[2][11]), "+r"(r[3][0]), "+r"(r[3][1]), "+r"(r[3][2]), "+r"(r[3][3]),
+                      "+r"(r[3][4]), "+r"(r[3][5]), "+r"(r[3][6]), "+r"(r[3][7]), "+r"(r[3][8]), "+r"(r[3][9]), "+r"(r[3][10]), "+r"(r[3][11])
+                 :: "memory");
+}
 // 32 lanes x 32 columns of 32-bit: thread t of the warp gets lane t, columns c..c+31 (asynchronous:
 // the registers are valid after tmem_ld_wait)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {

@@ -425,7 +425,7 @@ def test_stream_accumulators_several_tokens(rt, m, rows):
         assert O.rel_err(got[i, :, :rows], ref["y"]) < REL
 
 
-@pytest.mark.parametrize("cfg", [None, "1", "0", "2"])
+@pytest.mark.parametrize("cfg", [None, "3", "1", "0", "2"])
 @pytest.mark.parametrize("rows,nlayers", [(17408, 2), (520, 3)])
 def test_stream_accumulators_nvfp4(rt, monkeypatch, rows, nlayers, cfg):
     """nvfp4_decode_stream: the int32 of every (row, 16-block), bit for bit, from the default consumer (tcgen05
@@ -465,10 +465,11 @@ def test_stream_accumulators_nvfp4(rt, monkeypatch, rows, nlayers, cfg):
         assert O.rel_err(got[i], ref["y"][0]) < REL
 
 
-def test_nvfp4_stream_counters_host_receiver_and_extreme_codes(rt):
+def test_nvfp4_stream_counters_host_receiver_and_extreme_codes(rt, monkeypatch):
     """The tcgen05 consumer of nvfp4_decode_stream with a pinned host receiver and completion counters: rows that do
     not fill the last 128-row tile, fewer tiles per layer than CTAs, activation codes over the whole int8 range
     (-128 and 127 included, written directly instead of through the quantiser) and every finite E4M3 scale code."""
+    monkeypatch.setenv("FM_NVFP4_CFG", "3")            # the tcgen05 consumer or an error, no other consumer in its place
     rows, nl = 333, 7
     sms = rt.device_attr("sm_count")
     layers = [synth.nvfp4_layer(rows, K, 1, seed=1700 + i) for i in range(nl)]
