@@ -273,7 +273,7 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
     rows = st.rows
     aq, asc4 = rt.alloc(K // 2), rt.alloc((K // 32) * 4)
     qa, qb, sc16 = rt.alloc(K // 2), rt.alloc(K // 2), rt.alloc((K // 16) * 4)
-    nv_layers = min(nl, 16)
+    nv_layers = min(nl, 64)
     nvs = rt.alloc(nv_layers * rows * (K // 16))
     rng = np.random.default_rng(2)
     from k100lc_kernels.quant import f32_to_e4m3_bits
@@ -411,14 +411,21 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
     nvl = min(nl, nv_layers)
     tab_n = rt.stream_table([(st.wq_l(l), nvs + l * rows * (K // 16), st.x + l * K * 4, st.y + l * N * 4) for l in range(nvl)], rows, K, 0)
     qan, qbn, scn = rt.alloc(nvl * K // 2), rt.alloc(nvl * K // 2), rt.alloc(nvl * (K // 16) * 4)
-    rt.graph_begin()
-    rt.launch2d("nvfp4_quant_act", K // 16, nvl, 64, 1, [st.x, qan, qbn, scn, nvl, K])
-    rt.launch("nvfp4_decode_stream", 1, 1, [tab_n, nvl, rows, K, 0, 0, 0, status, qan, qbn, scn, 0.05, 0])
-    g = rt.graph_end()
-    us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nvl
-    rt.graph_free(g)
-    out["nvfp4_m1_stream"] = {"us_per_layer": round(us, 3), "gb_per_s": round(NVFP4_LAYER_BYTES * frac / us / 1e3, 1),
-                              "note": f"{nvl} layers per launch"}
+    for key, cfg, what in (("nvfp4_m1_stream", None, "tcgen05 kind::mxf4 consumer (default)"),
+                           ("nvfp4_m1_stream_dp4a", "1", "dp4a consumer ($FM_NVFP4_CFG=1)")):
+        if cfg is None:
+            os.environ.pop("FM_NVFP4_CFG", None)
+        else:
+            os.environ["FM_NVFP4_CFG"] = cfg
+        rt.graph_begin()
+        rt.launch2d("nvfp4_quant_act", K // 16, nvl, 64, 1, [st.x, qan, qbn, scn, nvl, K])
+        rt.launch("nvfp4_decode_stream", 1, 1, [tab_n, nvl, rows, K, 0, 0, 0, status, qan, qbn, scn, 0.05, 0])
+        g = rt.graph_end()
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nvl
+        rt.graph_free(g)
+        out[key] = {"us_per_layer": round(us, 3), "gb_per_s": round(NVFP4_LAYER_BYTES * frac / us / 1e3, 1),
+                    "note": f"{nvl} layers per launch; {what}"}
+    os.environ.pop("FM_NVFP4_CFG", None)
     for ptr in (tab_n, qan, qbn, scn):
         rt.free(ptr)
     # four tokens per layer through the multi-token stream kernel (tokens = columns of the MMA)
@@ -672,15 +679,6 @@ def run_ours(args) -> int:
     gpu_launches = counted[0]                       # kernels of this library inside the timed region
 
     log(f"timed region done: {ms_step:.3f} ms/step")
-    # the same graph back to back for at least a second: long enough for the board to settle at its power
-    # limit, which a 20-step region (tens of milliseconds) is not
-    sustained = None
-    if args.sustain_s > 0:
-        n_sus = max(args.steps, int(args.sustain_s * 1e3 / ms_step) + 1)
-        with ClockSampler(rt.device_attr("device")) as clocks_sus:
-            ms_sus = time_graph(rt, graph, n_sus, 3, barrier, None, clocks_sus)
-        sustained = (ms_sus, n_sus, clocks_sus.summary())
-        log(f"sustained region done: {ms_sus:.3f} ms/step over {n_sus} steps")
     # end to end through the C ABI with host buffers: x of all layers up, y of all layers back, every step.
     # Inputs and outputs are double-buffered on the device so that the copies of neighbouring steps run on the
     # copy engines beside the kernel of this step: the x of step t + 1 is uploaded on the engine's second queue
@@ -789,6 +787,16 @@ def run_ours(args) -> int:
         if not np.array_equal(st.y_host[:, lo:lo + st.rows].view(np.uint32), dev_y[:, lo:lo + st.rows].view(np.uint32)):
             raise RuntimeError("the host copy of this rank's rows of y differs from the device copy")
 
+    # (after the two 20-step regions, which are then measured in the same state of the board)
+    # the same graph back to back for at least a second: long enough for the board to settle at its power
+    # limit, which a 20-step region (tens of milliseconds) is not
+    sustained = None
+    if args.sustain_s > 0:
+        n_sus = max(args.steps, int(args.sustain_s * 1e3 / ms_step) + 1)
+        with ClockSampler(rt.device_attr("device")) as clocks_sus:
+            ms_sus = time_graph(rt, graph, n_sus, 3, barrier, None, clocks_sus)
+        sustained = (ms_sus, n_sus, clocks_sus.summary())
+        log(f"sustained region done: {ms_sus:.3f} ms/step over {n_sus} steps")
     # the dominant kernel alone, for the roofline: the fused stream kernel is the whole step;
     # in per-layer mode it is gemv_w4a8<1,false,1> without the quantiser
     if fused:
