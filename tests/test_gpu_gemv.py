@@ -72,10 +72,10 @@ def test_w4_golden(rt, golden, name, seed, m, kernel):
 
 
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
-@pytest.mark.parametrize("n,k", [(256, 5120), (37, 1024), (130, 2176), (9, 128)])
+@pytest.mark.parametrize("n,k", [(256, 5120), (37, 1024), (130, 2176), (9, 128), (70, 6144), (45, 17408)])
 def test_w4_accumulators_and_output(rt, m, n, k):
-    """Ragged N, K that is / is not a multiple of 1024, every M: integer accumulators
-    bit-exact, outputs within 1e-5."""
+    """Ragged N, K that is / is not a multiple of 1024 (5120, 6144 and 17408 have unrolled kernels of their own
+    at M = 1), every M: integer accumulators bit-exact, outputs within 1e-5."""
     L = synth.rt4_layer(n, k, m, seed=300 + m)
     for dev, grp in ((w4a8_device, 128), (w4a4_device, 32)):
         y, acc, q = dev(rt, L["wq"], L["ws"], L["x"], dump=True)
