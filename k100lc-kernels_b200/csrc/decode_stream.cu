@@ -726,43 +726,55 @@ struct W4a16Params {
     const uint32_t* frags;             // [nlayers][40 * 192] B fragments of the activations
 };
 
-template <int STAGES_, int NACT_>
+//   NGROUPS consumer groups that take the stages in turn (2: a group has two stage times for its own stage)
+//   BREG    a warp keeps the B fragments of its blocks in registers for the whole layer (80 registers: one group only);
+//           otherwise they are read from the layer's tile with every stage
+template <int STAGES_, int NGROUPS_, int NACT_, bool BREG>
 struct W4A16Mma {
     using Params = W4a16Params;
-    static constexpr int M = 1, STAGES = STAGES_, NGROUPS = 1, NACT = NACT_;
+    static constexpr int M = 1, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = NACT_;
     static constexpr bool ACT_IN_STAGE = false;
     static constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
     static constexpr int ROWB = K / 2, SCB = NG * 2, PITCH = ROWB;
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB, STAGE = OFF_ACT;
     static constexpr int ACT = NG * 192 * 4;             // fragment array of one layer
     static constexpr int RED = CW * ROWS, EXTRA = 0;
-    static constexpr int kThreads = (CW + 2) * 32;
+    static constexpr int kThreads = (NGROUPS * CW + 2) * 32;
+    static_assert(!BREG || NGROUPS == 1, "fragments in registers leave no room for a second group");
 
     __device__ static void init_extra(const Params&, uint8_t*) {}
     __device__ static void copy_act(const Params& pp, int l, uint8_t* dst, uint64_t* bar) {
         bulk_g2s(dst, pp.frags + (size_t)l * (NG * 192), ACT, bar);
     }
+    // B fragments of block b for this lane: {b0,b1 of (q,0), b0,b1 of (q,1)}, q = 0..3
+    __device__ static __forceinline__ uint4 frag(const uint32_t* ft, int b, int g, int t, int q) {
+        if (g >= 3) return make_uint4(0, 0, 0, 0);
+        return reinterpret_cast<const uint4*>(ft + ((size_t)(b * 3 + g) * 4 + t) * 16)[q];
+    }
 
     __device__ static void consume(const Cta& c, const Params& pp, int grp, int w) {
         const StreamParams& p = pp.s;
         const int lane = c.lane, g = lane >> 2, t = lane & 3;
-        int cg = 0;
+        int cg = 0;                                      // stages this group has taken so far
         for (int l = 0; l < p.nlayers; l++) {
+            const int c0 = l * c.nst;
+            const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;     // this group's first stage of the layer
             if (!layer_enter<W4A16Mma>(c, l)) return;
             const uint32_t* ft = reinterpret_cast<const uint32_t*>(c.act + (size_t)(l % NACT) * ACT);
             float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + p.row_base;
-            uint4 bf[GPW][4];                                  // B fragments of this warp's blocks: {b0,b1 of (q,0), b0,b1 of (q,1)}
+            uint4 bf[BREG ? GPW : 1][4];
+            bool held = false;                           // the tile has not been released yet
+            if (BREG) {
 #pragma unroll
-            for (int j = 0; j < GPW; j++) {
-                const int b = j * CW + w;
-                const uint4* fp = reinterpret_cast<const uint4*>(ft + ((size_t)(b * 3 + (g < 3 ? g : 0)) * 4 + t) * 16);
+                for (int j = 0; j < GPW; j++)
 #pragma unroll
-                for (int q = 0; q < 4; q++) bf[j][q] = g < 3 ? fp[q] : make_uint4(0, 0, 0, 0);
+                    for (int q = 0; q < 4; q++) bf[j][q] = frag(ft, j * CW + w, g, t, q);
+                held = true;
             }
-            for (int jst = 0; jst < c.nst; jst++, cg++) {
-                const int s = cg % STAGES;
-                if (!cta_wait(c, &c.bars->full[s], (cg / STAGES) & 1, 3)) return;
+            for (int jst = jf; jst < c.nst; jst += NGROUPS, cg++) {
+                const int cc0 = c0 + jst, s = cc0 % STAGES;
+                if (!cta_wait(c, &c.bars->full[s], (cc0 / STAGES) & 1, 3)) return;
                 const uint8_t* st = c.ring + (size_t)s * STAGE;
                 uint4 xa[GPW], xb[GPW];
                 float swa[GPW], swb[GPW];
@@ -781,13 +793,14 @@ struct W4A16Mma {
                     float cc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
+                        const uint4 f = BREG ? bf[j][q] : frag(ft, j * CW + w, g, t, q);
                         const uint32_t la = wav[q] & 0x0F0F0F0Fu, ha = (wav[q] >> 4) & 0x0F0F0F0Fu;
                         const uint32_t lb = wbv[q] & 0x0F0F0F0Fu, hb = (wbv[q] >> 4) & 0x0F0F0F0Fu;
                         const uint32_t m = 0x43434343u;
                         mma_bf16(cc, bf16x2_sub136(prmt(la, m, 0x5140u)), bf16x2_sub136(prmt(lb, m, 0x5140u)),
-                                 bf16x2_sub136(prmt(la, m, 0x5342u)), bf16x2_sub136(prmt(lb, m, 0x5342u)), bf[j][q].x, bf[j][q].y);
+                                 bf16x2_sub136(prmt(la, m, 0x5342u)), bf16x2_sub136(prmt(lb, m, 0x5342u)), f.x, f.y);
                         mma_bf16(cc, bf16x2_sub136(prmt(ha, m, 0x5140u)), bf16x2_sub136(prmt(hb, m, 0x5140u)),
-                                 bf16x2_sub136(prmt(ha, m, 0x5342u)), bf16x2_sub136(prmt(hb, m, 0x5342u)), bf[j][q].z, bf[j][q].w);
+                                 bf16x2_sub136(prmt(ha, m, 0x5342u)), bf16x2_sub136(prmt(hb, m, 0x5342u)), f.z, f.w);
                     }
                     // columns 0, 1 (lane t = 0) and 2 (lane t = 1) hold the three terms: smallest first
                     const float va = __shfl_down_sync(0xffffffffu, cc[0], 1), vb = __shfl_down_sync(0xffffffffu, cc[2], 1);
@@ -797,11 +810,15 @@ struct W4A16Mma {
                 consumed(fa + fb);                              // release only after the loaded data has been used
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&c.bars->empty[s]);
-                if (jst == 0) act_release<W4A16Mma>(c, l);
+                if (BREG && held) {
+                    act_release<W4A16Mma>(c, l);
+                    held = false;
+                }
                 const float vals[2] = {fa, fb};
                 const int idx[2] = {t == 0 ? g : -1, t == 0 ? g + 8 : -1};
                 if (!reduce_and_emit<W4A16Mma>(c, grp, w, cg, vals, idx, yt, y, c.r0 + jst * ROWS)) return;
             }
+            if (!BREG || held) act_release<W4A16Mma>(c, l);
             layer_done(c, l);
         }
     }
@@ -1095,7 +1112,10 @@ int launch_w4a16_stream(const LaunchCtx& c, const uint64_t* a) {
                                   pdl_enabled(), p.layers, frags, (uint32_t)NG);
     if (e != cudaSuccess) return cuda_fail(kn, e);
     after_launch(kn);
-    return run_policy<W4A16Mma<3, 2>>(kn, c, pp);
+    // Two consumer groups reading the fragments from the layer's tile; $FM_W4A16_CFG=0: one group with the fragments
+    // of the layer in registers.
+    if (env_or("FM_W4A16_CFG", 1) == 0) return run_policy<W4A16Mma<3, 1, 2, true>>(kn, c, pp);
+    return run_policy<W4A16Mma<3, 2, 2, false>>(kn, c, pp);
 }
 
 // stream_flag_wait(flags, nlayers, target, status, spins)

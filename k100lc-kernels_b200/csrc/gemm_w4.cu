@@ -522,7 +522,8 @@ EncodeTiledFn tensor_map_encoder() {
     return fn;
 }
 // bytes [rows][row_bytes], row-major and dense; box = box_bytes x 128 rows
-bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes, CUtensorMapSwizzle sw) {
+bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes, CUtensorMapSwizzle sw,
+              CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
     EncodeTiledFn enc = tensor_map_encoder();
     if (!enc) return false;
     const cuuint64_t dims[2] = {row_bytes, rows};
@@ -530,8 +531,7 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t row_byte
     const cuuint32_t box[2] = {box_bytes, 128};
     const cuuint32_t estr[2] = {1, 1};
     return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+               CU_TENSOR_MAP_INTERLEAVE_NONE, sw, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // aq: packed int4 [M][K/8] words (A8 false) or int8 [M][K] (A8 true)
@@ -690,8 +690,9 @@ const KernelEntry* gemm_w4_kernels(int* n) {
 }
 
 bool encode_bytes_rows_map(void* map128, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes) {
+    // (256-byte L2 promotion: the next stage's 128 bytes of a row come along; 1 % over 128 bytes or none)
     return make_map(static_cast<CUtensorMap*>(map128), base, rows, row_bytes, box_bytes,
-                    box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+                    box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 // status word of the GEMM kernels: drains the stream, reads it and clears it
 int gemm_read_status(cudaStream_t stream) {
