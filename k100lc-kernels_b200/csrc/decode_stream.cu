@@ -106,7 +106,7 @@ __device__ __forceinline__ bool reduce_and_emit(const Cta& c, int grp, int w, in
 //   PAD     bytes added to the pitch of a row inside a stage (64: the two rows of a quarter-warp's 16-byte
 //           loads fall into different banks; the rows are then copied one by one)
 //   DUMP    also store the integer accumulators
-template <int M_, int STAGES_, int NGROUPS_, bool AIS, int NACT_, bool BREG, int PAD, bool DUMP>
+template <int M_, int STAGES_, int NGROUPS_, bool AIS, int NACT_, bool BREG, int PAD, bool DUMP, int NPROD_ = 1>
 struct W4A8Mma {
     using Params = PlainParams;
     static constexpr int M = M_, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = AIS ? 1 : NACT_;
@@ -116,8 +116,8 @@ struct W4A8Mma {
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB;
     static constexpr int ACT = M * (K + NG * 8);
     static constexpr int STAGE = (OFF_ACT + (AIS ? ACT : 0) + 127) & ~127;
-    static constexpr int RED = CW * ROWS * M, EXTRA = 0;
-    static constexpr int kThreads = (NGROUPS * CW + 2) * 32;
+    static constexpr int RED = CW * ROWS * M, EXTRA = 0, NPROD = NPROD_;
+    static constexpr int kThreads = (NGROUPS * CW + 1 + NPROD) * 32;
     static_assert(!(AIS && BREG), "fragments in registers need a tile that outlives the stage");
 
     __device__ static void init_extra(const Params&, uint8_t*) {}
@@ -252,7 +252,7 @@ struct W4A8Mma {
 // Both operands are formed as 16 x their value with one or two logic instructions per register (a two's-
 // complement nibble in the upper half of a byte is the signed byte 16 * v): J = acc >> 8, exactly, with no
 // correction term.  The four lanes of a row then add their sub-groups with two shuffles.
-template <int STAGES_, int NGROUPS_, bool DUMP>
+template <int STAGES_, int NGROUPS_, bool DUMP, int NPROD_ = 1>
 struct W4A4Mma {
     using Params = PlainParams;
     static constexpr int M = 1, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = 1;
@@ -263,7 +263,8 @@ struct W4A4Mma {
     static constexpr int ACT = K / 2 + (K / 32) * 4;            // packed nibbles, sub-group scales
     static constexpr int STAGE = (OFF_ACT + ACT + 127) & ~127;
     static constexpr int RED = CW * ROWS, EXTRA = 0;
-    static constexpr int kThreads = (NGROUPS * CW + 2) * 32;
+    static constexpr int NPROD = NPROD_;
+    static constexpr int kThreads = (NGROUPS * CW + 1 + NPROD) * 32;
 
     __device__ static void init_extra(const Params&, uint8_t*) {}
     __device__ static void copy_act(const Params& pp, int l, uint8_t* dst, uint64_t* bar) {
@@ -357,6 +358,7 @@ struct W4Dp4a {
     static constexpr int ACT = A4 ? K / 2 + (K / 32) * 4      // packed nibbles, sub-group scales
                                   : K + NG * 8;             // even codes, odd codes, scales, sums
     static constexpr int RED = 0, EXTRA = 0;
+    static constexpr int NPROD = 1;
     static constexpr int kThreads = (CW + 2) * 32;
 
     __device__ static void init_extra(const Params&, uint8_t*) {}
@@ -502,6 +504,7 @@ struct Nvfp4Mma {
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB, STAGE = OFF_ACT;
     static constexpr int ACT = K + NB * 4;
     static constexpr int RED = CW * ROWS, EXTRA = 1024;
+    static constexpr int NPROD = 1;
     static constexpr int kThreads = (NGROUPS * CW + 2) * 32;
 
     __device__ static void init_extra(const Params& pp, uint8_t* extra) { nvfp4_init_lut(pp.gscale, extra); }
@@ -630,6 +633,7 @@ struct Nvfp4Dp4a {
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB, STAGE = OFF_ACT;
     static constexpr int ACT = K + NB * 4;
     static constexpr int RED = 0, EXTRA = 1024;
+    static constexpr int NPROD = 1;
     static constexpr int kThreads = (CW + 2) * 32;
 
     __device__ static void init_extra(const Params& pp, uint8_t* extra) { nvfp4_init_lut(pp.gscale, extra); }
@@ -739,6 +743,7 @@ struct W4A16Mma {
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB, STAGE = OFF_ACT;
     static constexpr int ACT = NG * 192 * 4;             // fragment array of one layer
     static constexpr int RED = CW * ROWS, EXTRA = 0;
+    static constexpr int NPROD = 1;
     static constexpr int kThreads = (NGROUPS * CW + 2) * 32;
     static_assert(!BREG || NGROUPS == 1, "fragments in registers leave no room for a second group");
 
@@ -969,20 +974,22 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
     }
     if (A4) {
         // tensor-core consumer, two groups; $FM_STREAM_CFG=1 keeps the dp4a consumer
-        if (env_or("FM_STREAM_CFG", 3) != 1) return run_policy<W4A4Mma<4, 2, false>>(kn, c, pp);
+        if (env_or("FM_STREAM_CFG", 3) != 1) return run_policy<W4A4Mma<4, 2, false, 2>>(kn, c, pp);
         return nst >= 3 ? run_policy<W4Dp4a<true, 5, 2, false>>(kn, c, pp) : run_policy<W4Dp4a<true, 4, 5, false>>(kn, c, pp);
     }
     // Default: the token's codes travel inside every stage and two groups of eight warps take the stages in turn.
     // Measured on one B200 (400 layers, ms per token, 20-step burst / one-second run): 17408 rows 2.62 / 3.07 against
     // 3.04 / 3.35 for one group with the fragments in registers (0); 2176 rows — the shard of eight GPUs, one stage per
-    // CTA and layer — 0.384 / 0.442 against 0.496 / 0.507.  The other numbers are kept for comparison.
-    switch (env_or("FM_STREAM_CFG", 3)) {
+    // CTA and layer — 0.384 / 0.442 against 0.496 / 0.507.  The stages go round two producer lanes (one lane: 1 % slower
+    // on the shard shapes, 1.6 % in the one-second run at 17408 rows).  The other numbers are kept for comparison.
+    switch (env_or("FM_STREAM_CFG", -1)) {
         case 0: return run_policy<W4A8Mma<1, 5, 1, false, 2, true, 0, false>>(kn, c, pp);    // one group, fragments in registers
         case 1: return run_policy<W4Dp4a<false, 5, 2, false>>(kn, c, pp);                    // dp4a
         case 2: return run_policy<W4A8Mma<1, 4, 1, false, 5, true, 0, false>>(kn, c, pp);    // deeper ring of code tiles
         case 4: return run_policy<W4A8Mma<1, 4, 1, true, 1, false, 0, false>>(kn, c, pp);    // codes inside every stage, one group
         case 7: return run_policy<W4A8Mma<1, 4, 1, false, 2, true, 64, false>>(kn, c, pp);   // padded row pitch (no bank conflicts): slower
-        default: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);
+        case 3: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);    // the default with one producer lane
+        default: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false, 2>>(kn, c, pp);
     }
 }
 

@@ -208,12 +208,29 @@ void ensure_table() {
     k = moe_kernels(&n); add_kernels(k, n);
 }
 
+// The tensor maps of a layer table whose record is dropped: captured graphs may still hold kernel nodes that point at
+// them, so while any graph is alive (or a capture is running) they are only retired, and freed with the last graph.
+void drop_table_maps(uintptr_t table) {
+    Engine& e = E();
+    auto im = e.table_maps.find(table);
+    if (im == e.table_maps.end()) return;
+    bool graphs_alive = e.capturing;
+    for (const Graph& g : e.graphs) graphs_alive = graphs_alive || g.exec != nullptr;
+    if (graphs_alive) {
+        e.retired_scratch.push_back(im->second.dev);
+    } else {
+        cudaStreamSynchronize(e.stream);
+        cudaFree(im->second.dev);
+    }
+    e.table_maps.erase(im);
+}
+
 // a write into [p, p+n) makes any validated layer table it touches unvalidated
 void touch(const void* p, size_t n) {
     Engine& e = E();
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
     for (auto it = e.tables.begin(); it != e.tables.end();) {
-        if (a < it->first + it->second.bytes && it->first < a + n) { it = e.tables.erase(it); e.epoch++; }
+        if (a < it->first + it->second.bytes && it->first < a + n) { drop_table_maps(it->first); it = e.tables.erase(it); e.epoch++; }
         else ++it;
     }
     for (auto it = e.peers.begin(); it != e.peers.end();) {
@@ -251,7 +268,10 @@ void release_dependents(uintptr_t base) {
         for (uintptr_t d : deps) if (d == base) return true;
         return false;
     };
-    for (auto it = e.tables.begin(); it != e.tables.end();) it = uses(it->second.deps) ? e.tables.erase(it) : std::next(it);
+    for (auto it = e.tables.begin(); it != e.tables.end();) {
+        if (uses(it->second.deps)) { drop_table_maps(it->first); it = e.tables.erase(it); }
+        else ++it;
+    }
     for (auto it = e.peers.begin(); it != e.peers.end();) it = uses(it->second.deps) ? e.peers.erase(it) : std::next(it);
 }
 
@@ -426,11 +446,7 @@ const void* stream_table_maps(const void* table, int nlayers, int rows, int K) {
         if (!encode_bytes_rows_map(host.data() + (size_t)l * 128, reinterpret_cast<const void*>(t.wq[l]), (uint64_t)rows,
                                    (uint64_t)K / 2, 128))
             return nullptr;
-    if (im != e.table_maps.end()) {                         // maps of an older record at this address
-        cudaStreamSynchronize(e.stream);
-        cudaFree(im->second.dev);
-        e.table_maps.erase(im);
-    }
+    if (im != e.table_maps.end()) drop_table_maps(key);      // maps of an older record at this address
     void* dev = nullptr;
     if (cudaMalloc(&dev, host.size()) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     if (cudaMemcpy(dev, host.data(), host.size(), cudaMemcpyHostToDevice) != cudaSuccess) {

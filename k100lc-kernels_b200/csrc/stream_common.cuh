@@ -133,11 +133,15 @@ __device__ __forceinline__ void quiet_wait(uint64_t* bar, uint32_t parity) {
 // ---- producer ------------------------------------------------------------------------------
 // P supplies: ROWS, STAGES, PITCH, ROWB, SCB, STAGE_W, STAGE, ACT, NACT, ACT_IN_STAGE, OFF_ACT and
 // copy_act(pp, layer, dst, bar), which issues bulk copies of exactly ACT bytes.
+// `pl` of P::NPROD producer lanes: with the codes inside every stage a stage is self-contained, and the stages can go
+// round several lanes (each is a chain of a barrier wait and half a dozen copy instructions per stage, which paces
+// the ring when a CTA has a single small stage per layer).
 template <class P>
-__device__ __forceinline__ void run_producer(const Cta& c, const typename P::Params& pp) {
+__device__ __forceinline__ void run_producer(const Cta& c, const typename P::Params& pp, int pl) {
     const StreamParams& p = *c.p;
     Bars* B = c.bars;
-    int issued = 0, acts = 0;          // stages / activation tiles armed so far
+    static_assert(P::NPROD == 1 || P::ACT_IN_STAGE, "several producer lanes need self-contained stages");
+    int issued = 0, acts = 0;          // stages armed by any lane up to this lane's last one / activation tiles armed
     bool ok = true;
     auto copy_tile = [&](int l) -> bool {          // layer l's codes -> tile l % NACT
         const int b = l % P::NACT;
@@ -159,6 +163,7 @@ __device__ __forceinline__ void run_producer(const Cta& c, const typename P::Par
         lay2 = get_layer(p, min(l + 2, p.nlayers - 1));
         if (!P::ACT_IN_STAGE && !copy_tile(l)) { ok = false; break; }
         for (int j = 0; j < c.nst; j++, cc++) {
+            if (P::NPROD > 1 && cc % P::NPROD != pl) continue;
             const int s = cc % P::STAGES;
             if (cc >= P::STAGES && !cta_wait(c, &B->empty[s], ((cc / P::STAGES) & 1) ^ 1, 1)) { ok = false; break; }
             const int row = c.r0 + j * P::ROWS;
@@ -179,7 +184,7 @@ __device__ __forceinline__ void run_producer(const Cta& c, const typename P::Par
     if (!ok) {
         // leaving early: what was issued must have landed before the CTA's shared memory is given up
         for (int j = issued > P::STAGES ? issued - P::STAGES : 0; j < issued; j++)
-            quiet_wait(&B->full[j % P::STAGES], (j / P::STAGES) & 1);
+            if (j % P::NPROD == pl) quiet_wait(&B->full[j % P::STAGES], (j / P::STAGES) & 1);
         if (!P::ACT_IN_STAGE)
             for (int l = acts > P::NACT ? acts - P::NACT : 0; l < acts; l++)
                 quiet_wait(&B->act_ready[l % P::NACT], (l / P::NACT) & 1);
@@ -318,9 +323,9 @@ stream_kernel(const typename P::Params pp) {
     c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
     c.tiled = (c.r1 - c.r0) * P::M <= kOutCap;
 
-    if (c.warp == NCW) {
-        if (c.lane == 0) run_producer<P>(c, pp);
-    } else if (c.warp == NCW + 1) {
+    if (c.warp >= NCW && c.warp < NCW + P::NPROD) {
+        if (c.lane == 0) run_producer<P>(c, pp, c.warp - NCW);
+    } else if (c.warp == NCW + P::NPROD) {
         run_writer<P>(c);
     } else {
         P::consume(c, pp, c.warp / CW, c.warp % CW);

@@ -526,7 +526,7 @@ def test_stream_schedules_give_identical_bits(rt, monkeypatch):
         layers = [synth.rt4_layer(rows, K, 1, seed=1500 + i) for i in range(nl)]
         with Bufs(rt) as b:
             want = None
-            for cfg in (None, 0, 1, 2, 4, 7):
+            for cfg in (None, 0, 1, 2, 3, 4, 7):
                 for hint in ((0, 2000) if cfg is None else (0,)):
                     if cfg is None:
                         monkeypatch.delenv("FM_STREAM_CFG", raising=False)
