@@ -18,22 +18,22 @@
 // of 1/2 below 2^5 and a block sum stays below 2^9: the fp32 accumulation is exact, I = 2*(D0 + 7*D1 + 49*D2) is the
 // oracle's integer bit for bit (the _iacc entry stores it), and nothing is accumulated across MMAs — each MMA
 // writes 16 fresh columns of tensor memory.
-// (Measured first and dropped: kind::f8f6f4 with TMA's unpacking 16U4_ALIGN16B tensor type and the activations as two
+// (Built first and dropped: kind::f8f6f4 with TMA's unpacking 16U4_ALIGN16B tensor type and the activations as two
 //  E4M3 halves.  Bit-exact too, but the padded shared-memory form — one byte per code — halves the weight bytes a CTA
-//  can have in flight, and with HBM's loaded latency of about 3.5 us that held the stream at 13.5 us per layer.)
+//  can have in flight and doubles the MMAs per byte; the dense form needs neither.)
 //
 // Mapping.  Work unit: a tile of 128 rows of one layer, all of K; tile t goes to CTA t mod grid, so the layers
 // complete in order.  Per tile K/256 stages; per stage
-//   * copy lane: one TMA box copy (128 rows x 128 bytes = 256 codes per row, 128-byte swizzle: the K-major layout the
-//     MMA reads), the stage's B image (prepared once per token by nvfp4_bimg_kernel: 12 columns x 128 bytes) and the
-//     16 products asc[b]*gscale, all counted on one mbarrier; twelve stages = 192 KB of weights in flight per SM;
-//   * MMA lane: four tcgen05.mma (M128 N16 K64) into a 64-column slice of tensor memory, one commit that frees the
-//     stage and one that hands the slice to the epilogue;
+//   * a copy lane (two take the stages in turn): one TMA box copy (128 rows x 128 bytes = 256 codes per row, 128-byte
+//     swizzle: the K-major layout the MMA reads), the stage's B image (prepared once per token by nvfp4_bimg_kernel:
+//     12 columns x 128 bytes) and the 16 products asc[b]*gscale, all counted on one mbarrier; twelve stages = 192 KB
+//     of weights in flight per SM;
+//   * an MMA lane (four take the stages in turn): four tcgen05.mma (M128 N16 K64) into a 64-column slice of tensor
+//     memory, one commit that frees the stage and one that hands the slice to the epilogue;
 //   * eight epilogue warps, two per lane quarter of tensor memory taking the stages in turn: one thread per row;
 //     tcgen05.ld of the 48 digit sums, I/2 = D0 + 7*D1 + 49*D2, the E4M3 block scale of the row (16 bytes per
-//     stage through L1, requested four stages ahead), one multiply
-//     and one fused multiply-add per block; after the last stage the two partial sums of a row meet and y goes to
-//     the local y and every receiver.
+//     stage through L1, requested four stages ahead), one multiply and one fused multiply-add per block; after the
+//     last stage the two partial sums of a row meet and y goes to the local y and every receiver.
 // All waits are bounded (status 11..17); a wait that runs out raises the CTA-wide abort flag, the copy lane waits
 // for the copies it issued, the MMA lane for its MMAs, and tensor memory is released before the CTA returns.
 #include <cuda.h>
