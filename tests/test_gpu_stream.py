@@ -188,8 +188,10 @@ def test_stream_many_rows_per_cta(rt):
 
 
 @pytest.mark.parametrize("m,rows,row_base", [(2, 1000, 0), (3, 148, 0), (4, 17408, 0), (4, 700, 300)])
-def test_stream_several_tokens_matches_oracle(rt, m, rows, row_base):
-    """w4a8_decode_stream_m: M tokens per layer as the columns of the MMA; y of a layer is token-major."""
+def test_stream_several_tokens_matches_oracle(rt, monkeypatch, m, rows, row_base):
+    """w4a8_decode_stream_m: M tokens per layer as the columns of the MMA; y of a layer is token-major.  The default
+    schedule (two consumer groups) and the one-group schedule ($FM_STREAM_M_CFG=0, whose accumulators the _iacc entry
+    dumps) leave identical bits."""
     nl = 3
     ystride = row_base + rows + 24
     layers = [synth.rt4_layer(rows, K, m, seed=900 + 10 * m + i) for i in range(nl)]
@@ -206,6 +208,13 @@ def test_stream_several_tokens_matches_oracle(rt, m, rows, row_base):
         rt.launch("w4a8_decode_stream_m", 1, 1, argv)
         got = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
         assert int(b.get(status, 1, np.int32)[0]) == 0
+        monkeypatch.setenv("FM_STREAM_M_CFG", "0")
+        rt.memset(y, 0xFF, nl * m * ystride * 4)
+        rt.launch("w4a8_decode_stream_m", 1, 1, argv)
+        one_group = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
+        monkeypatch.delenv("FM_STREAM_M_CFG")
+        assert np.array_equal(got[:, :, row_base:row_base + rows].view(np.uint32),
+                              one_group[:, :, row_base:row_base + rows].view(np.uint32))
         with pytest.raises(RuntimeError, match="rc=-4"):                    # a table validated for one token is refused
             t1 = rt.stream_table(ptrs, rows, K, row_base)
             try:
