@@ -526,6 +526,37 @@ def test_nvfp4_stream_counters_host_receiver_and_extreme_codes(rt, monkeypatch):
         assert O.rel_err(host[i * rows:(i + 1) * rows], ref["y"][0]) < REL
 
 
+@pytest.mark.parametrize("rows,nl", [(1, 1), (127, 2), (128, 3), (129, 1), (2176, 5)])
+def test_nvfp4_tcgen05_stream_tile_edges(rt, monkeypatch, rows, nl):
+    """The tcgen05 consumer on row counts around its 128-row tile (one row; one short of, exactly and one past a tile;
+    the 17-tile shard of eight GPUs) with one and several layers: accumulators bit for bit, y within 1e-5, rows
+    outside the layer untouched."""
+    monkeypatch.setenv("FM_NVFP4_CFG", "3")
+    layers = [synth.nvfp4_layer(rows, K, 1, seed=1800 + 7 * rows + i) for i in range(nl)]
+    gscale = float(layers[0]["gscale"])
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"][0] for L in layers]))
+        qa, qb = b.zeros(nl * K // 2, np.int8), b.zeros(nl * K // 2, np.int8)
+        sc = b.zeros(nl * K // 16)
+        y = b.zeros(nl * (rows + 8), np.float32, np.nan)
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), x + i * K * 4, y + i * (rows + 8) * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, 3)                    # rows land at y[3 .. 3 + rows)
+        status = b.zeros(1, np.int32)
+        rt.launch2d("nvfp4_quant_act", K // 16, nl, 64, 1, [x, qa, qb, sc, nl, K])
+        pi = b.zeros(nl * rows * (K // 16), np.int32, -7)
+        rt.launch("nvfp4_decode_stream_iacc", 1, 1, [table, nl, rows, K, 3, 0, 0, status, qa, qb, sc, gscale, 0, pi])
+        acc = b.get(pi, nl * rows * (K // 16), np.int32).reshape(nl, rows, -1)
+        got = b.get(y, nl * (rows + 8)).reshape(nl, rows + 8)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        rt.free(table)
+    for i, L in enumerate(layers):
+        q = O.nvfp4_quant_act(L["x"])
+        ref = O.nvfp4_gemv(L["wq"], L["ws"], q["q"], q["scale"], gscale)
+        assert np.array_equal(acc[i], ref["acc"][0])
+        assert O.rel_err(got[i, 3:3 + rows], ref["y"][0]) < REL
+        assert np.isnan(got[i, :3]).all() and np.isnan(got[i, 3 + rows:]).all()
+
+
 def test_stream_schedules_give_identical_bits(rt, monkeypatch):
     """Every schedule of the W4A8 stream kernel ($FM_STREAM_CFG, with and without a suspend hint on the
     barrier waits) leaves the bits of gemv_w4a8<1,false,1> in y, on a shape with many stages per CTA and
