@@ -797,6 +797,18 @@ def run_ours(args) -> int:
             ms_sus = time_graph(rt, graph, n_sus, 3, barrier, None, clocks_sus)
         sustained = (ms_sus, n_sus, clocks_sus.summary())
         log(f"sustained region done: {ms_sus:.3f} ms/step over {n_sus} steps")
+    # read ceiling: the copies of the stream kernel (same producer, ring and stage geometry) with consumers that only
+    # release the stages — what the memory system allows this access pattern, measured in the same run
+    ms_ceiling = None
+    if fused and rt.has("w4a8_stream_read_ceiling"):
+        rt.graph_begin()
+        rt.launch2d("quant_act", NG, args.layers, 32, 1, [st.x, st.ae_all, st.ao_all, st.asc_all, st.asu_all, args.layers, K])
+        rt.launch("w4a8_stream_read_ceiling", 1, 1, [st.tables[0], args.layers, st.rows, K, rank * st.rows, 0, 0, st.status,
+                                                     st.ae_all, st.ao_all, st.asc_all, st.asu_all, 0])
+        gc = rt.graph_end()
+        ms_ceiling = time_graph(rt, gc, args.steps, 3, barrier)
+        rt.graph_free(gc)
+        log(f"read ceiling: {ms_ceiling:.3f} ms/step")
     # the dominant kernel alone, for the roofline: the fused stream kernel is the whole step;
     # in per-layer mode it is gemv_w4a8<1,false,1> without the quantiser
     if fused:
@@ -827,11 +839,13 @@ def run_ours(args) -> int:
     log("reducing timings over ranks")
     if dist is not None:
         import torch
-        t = torch.tensor([ms_step, ms_e2e, ms_kern, sustained[0] if sustained else 0.0], dtype=torch.float64)
+        t = torch.tensor([ms_step, ms_e2e, ms_kern, sustained[0] if sustained else 0.0, ms_ceiling or 0.0], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, ms_e2e, ms_kern = (float(v) for v in t[:3])
         if sustained:
             sustained = (float(t[3]),) + sustained[1:]
+        if ms_ceiling:
+            ms_ceiling = float(t[4])
 
     total_bytes = args.layers * LAYER_BYTES         # whole job, all ranks
     pk = peaks()
@@ -894,6 +908,11 @@ def run_ours(args) -> int:
                              "frac_of_nominal_8000": round(bytes_per_launch / sustained[0] / 1e6 / 8000.0, 4),
                              "clocks": sustained[2],
                              "what": "the same graph launched back to back for at least --sustain-s seconds"},
+                         "read_ceiling": None if not ms_ceiling else {
+                             "ms_per_token": round(ms_ceiling, 4), "achieved": round(bytes_per_launch / ms_ceiling / 1e6, 1),
+                             "frac_of_ceiling": round(ms_ceiling / ms_kern, 4),
+                             "what": "w4a8_stream_read_ceiling: the stream kernel's copies (same ring and stages) with consumers "
+                                     "that release every stage unread; frac_of_ceiling = its time / the stream kernel's time"},
                          # DRAM bytes of one launch: an ncu capture of the same kernel on 24 layers read
                          # 1 103 145 000 B and wrote 5 141 000 B; every weight byte is read once, so the traffic
                          # of a launch is that figure scaled by its layer count

@@ -243,6 +243,41 @@ struct W4A8Mma {
 };
 
 // ------------------------------------------------------------------------------------
+// Read ceiling of the W4A8 stream: the producer, the ring, the stage geometry and the copies (weights, scales and the
+// token's codes inside every stage) of the default W4A8 schedule, with consumers that release every stage as soon as it
+// has landed — no shared-memory read, no arithmetic, no output.  What this kernel takes per token is what the memory
+// system allows this access pattern; the distance of w4a8_decode_stream from it is what its arithmetic costs.
+template <int STAGES_, int NPROD_>
+struct W4A8ReadCeiling {
+    using Params = PlainParams;
+    using Base = W4A8Mma<1, STAGES_, 2, true, 1, false, 0, false, NPROD_>;
+    static constexpr int M = 1, STAGES = STAGES_, NGROUPS = 2, NACT = 1;
+    static constexpr bool ACT_IN_STAGE = true, NO_OUTPUT = true;
+    static constexpr int K = Base::K, NG = Base::NG, CW = Base::CW, ROWS = Base::ROWS;
+    static constexpr int ROWB = Base::ROWB, SCB = Base::SCB, PITCH = Base::PITCH;
+    static constexpr int STAGE_W = Base::STAGE_W, OFF_ACT = Base::OFF_ACT, ACT = Base::ACT, STAGE = Base::STAGE;
+    static constexpr int RED = Base::RED, EXTRA = 0, NPROD = NPROD_;
+    static constexpr int kThreads = Base::kThreads;
+
+    __device__ static void init_extra(const Params&, uint8_t*) {}
+    __device__ static void copy_act(const Params& pp, int l, uint8_t* dst, uint64_t* bar) { Base::copy_act(pp, l, dst, bar); }
+    __device__ static void consume(const Cta& c, const Params& pp, int grp, int w) {
+        const StreamParams& p = pp.s;
+        for (int l = 0; l < p.nlayers; l++) {
+            const int c0 = l * c.nst;
+            const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;
+            for (int jst = jf; jst < c.nst; jst += NGROUPS) {
+                const int cc = c0 + jst, s = cc % STAGES;
+                if (!cta_wait(c, &c.bars->full[s], (cc / STAGES) & 1, 3)) return;
+                __syncwarp();
+                if (c.lane == 0) mbar_arrive(&c.bars->empty[s]);
+            }
+        }
+        (void)w;
+    }
+};
+
+// ------------------------------------------------------------------------------------
 // W4A4 on the tensor cores (reference arithmetic: kernels/gemv_w4a4_core.h:48-134): the schedule of W4A8Mma
 // with the token's codes inside every stage and, per (row, 32-sub-group), the exact integer
 //   J = sum_{k in sub-group} w[n,k] * q[k]         y += (f16(ws[n, sg / 4]) * asc[sg]) * float(J).
@@ -993,6 +1028,32 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
     }
 }
 
+// w4a8_stream_read_ceiling(common..., ae, ao, asc, asu, flags): the arguments of w4a8_decode_stream; copies what that
+// kernel copies and computes nothing (y is not written, flags are not counted).
+int launch_w4a8_read_ceiling(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = "w4a8_stream_read_ceiling";
+    PlainParams pp = {};
+    StreamParams& p = pp.s;
+    const int rc = parse_common(kn, c, a, a[12], p, 1);
+    if (rc) return rc < 0 ? rc : FM_OK;
+    p.ae = arg_ptr<const uint8_t>(a[8]);
+    p.ao = arg_ptr<const uint8_t>(a[9]);
+    p.asc = arg_ptr<const uint8_t>(a[10]);
+    p.asu = arg_ptr<const uint8_t>(a[11]);
+    p.npeers = 0;
+    p.flags = nullptr;
+    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, p.row_base, nullptr, 0), kn,
+               "the layer table at %p was not filled by fm_stream_table for nlayers=%d rows=%d K=%d row_base=%d (or was "
+               "overwritten, or a buffer it points into was freed since)", (const void*)p.layers, p.nlayers, p.rows, p.K, p.row_base);
+    FM_REQUIRE(aligned(p.ae, 16) && aligned(p.ao, 16) && aligned(p.asc, 16) && aligned(p.asu, 16), kn,
+               "the activation code arrays must be 16-byte aligned");
+    FM_RANGE(p.ae, (size_t)p.nlayers * (p.K / 2), kn, "ae");
+    FM_RANGE(p.ao, (size_t)p.nlayers * (p.K / 2), kn, "ao");
+    FM_RANGE(p.asc, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asc");
+    FM_RANGE(p.asu, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asu");
+    return run_policy<W4A8ReadCeiling<4, 2>>(kn, c, pp);
+}
+
 // w4a8_decode_stream_m(common..., ae, ao, asc, asu, M, ystride, flags): M = 2..4 tokens per layer.  The code arrays
 // hold [nlayers * M] tokens (one 2-D quant_act launch with grid y = nlayers * M over x[nlayers][M][K]); y of a layer is
 // token-major, y[token * ystride + row_base + row].  The layer table must have been validated by fm_stream_table with
@@ -1156,6 +1217,7 @@ const KernelEntry kStream[] = {
     {"w4a8_decode_stream_m_iacc", 16, launch_w4a8_stream_m<true>, "piiiiippppppiipp"},
     {"nvfp4_decode_stream_iacc", 14, launch_nvfp4_stream<true>, "piiiiipppppfpp"},
     {"stream_flag_wait", 5, launch_flag_wait, "piipi"},
+    {"w4a8_stream_read_ceiling", 13, launch_w4a8_read_ceiling, "piiiiippppppp"},
 };
 
 // Status word of the ring kernels when they are launched by name for a single layer (those entries have

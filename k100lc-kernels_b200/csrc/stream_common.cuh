@@ -20,6 +20,8 @@
 #pragma once
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "device_utils.cuh"
 
 namespace fm {
@@ -274,6 +276,11 @@ __device__ __forceinline__ void emit(const Cta& c, float* yt, float* y, int row,
     }
 }
 
+// A policy may declare `static constexpr bool NO_OUTPUT = true`: its consumers produce no y (the read-ceiling probe),
+// so there is no output tile and the writer has nothing to do.
+template <class P, class = void> struct no_output : std::false_type {};
+template <class P> struct no_output<P, std::void_t<decltype(P::NO_OUTPUT)>> : std::bool_constant<P::NO_OUTPUT> {};
+
 // ---- the kernel ------------------------------------------------------------------------------
 // P supplies the geometry constants, Params (with a StreamParams member `s`), init_extra() and
 // consume(cta, params, group, warp_in_group).
@@ -321,7 +328,7 @@ stream_kernel(const typename P::Params pp) {
     c.r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
     c.r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
     c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
-    c.tiled = (c.r1 - c.r0) * P::M <= kOutCap;
+    c.tiled = !no_output<P>::value && (c.r1 - c.r0) * P::M <= kOutCap;
 
     if (c.warp >= NCW && c.warp < NCW + P::NPROD) {
         if (c.lane == 0) run_producer<P>(c, pp, c.warp - NCW);

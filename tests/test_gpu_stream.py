@@ -557,6 +557,26 @@ def test_nvfp4_tcgen05_stream_tile_edges(rt, monkeypatch, rows, nl):
         assert np.isnan(got[i, :3]).all() and np.isnan(got[i, 3 + rows:]).all()
 
 
+def test_read_ceiling_kernel_copies_and_writes_nothing(rt):
+    """w4a8_stream_read_ceiling takes the arguments of w4a8_decode_stream, walks all stages (status 0) and leaves y as
+    it was; a table of another shape is refused."""
+    rows, nl = 2176, 6
+    layers = [synth.rt4_layer(rows, K, 1, seed=1900 + i) for i in range(nl)]
+    with Bufs(rt) as b:
+        codes = Codes(rt, b, layers)
+        y = b.zeros(nl * rows, np.float32, np.nan)
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), codes.x + i * K * 4, y + i * rows * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, 0)
+        status = b.zeros(1, np.int32)
+        codes.quantise(rt)
+        rt.launch("w4a8_stream_read_ceiling", 1, 1, [table, nl, rows, K, 0, 0, 0, status] + codes.args + [0])
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        assert np.isnan(b.get(y, nl * rows)).all()
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("w4a8_stream_read_ceiling", 1, 1, [table, nl, rows + 16, K, 0, 0, 0, status] + codes.args + [0])
+        rt.free(table)
+
+
 def test_stream_schedules_give_identical_bits(rt, monkeypatch):
     """Every schedule of the W4A8 stream kernel ($FM_STREAM_CFG, with and without a suspend hint on the
     barrier waits) leaves the bits of gemv_w4a8<1,false,1> in y, on a shape with many stages per CTA and
