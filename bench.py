@@ -582,6 +582,52 @@ def shape_table_timings(rt, reps: int = 5) -> dict:
         per_shape[f"{n}x{k}"] = {"layers": c, "us_per_layer": round(us, 3),
                                  "gb_per_s": round((n * k // 2 + n * (k // 128) * 2) / us / 1e3, 1)}
     out["w4a8_per_shape"] = per_shape
+    # The same token as ONE launch of w4a8_layers_stream (plus one 2-D quant_act launch per distinct K): every layer has
+    # its own input and its own y; a layer's x is padded with zeros to whole chunks of 5120 k, so that its codes are too.
+    if rt.has("w4a8_layers_stream"):
+        ks = sorted({k for _, k, _ in SHAPE_TABLE})
+        kpad = {k: -(-k // 5120) * 5120 for k in ks}
+        idx_of = {k: [i for i in order if layers[i][1] == k] for k in ks}        # layers of one K, in model order
+        slot = {i: j for k in ks for j, i in enumerate(idx_of[k])}
+        bufs = {}
+        for k in ks:
+            cnt, kp = len(idx_of[k]), kpad[k]
+            xk = rt.alloc(cnt * kp * 4)
+            xh = np.zeros((cnt, kp), dtype=np.float32)
+            xh[:, :k] = rng.standard_normal((cnt, k)).astype(np.float32)
+            rt.upload(xk, xh)
+            bufs[k] = (xk, rt.alloc(cnt * kp // 2), rt.alloc(cnt * kp // 2), rt.alloc(cnt * kp // 128 * 4), rt.alloc(cnt * kp // 128 * 4))
+        yall = rt.alloc(sum(n * c for n, _, c in SHAPE_TABLE) * 4)
+        entries, yo = [], 0
+        for i in order:
+            n, k, wq, ws = layers[i]
+            xk, a0, a1, a2, a3 = bufs[k]
+            j, kp = slot[i], kpad[k]
+            entries += rt.layer_chunks(wq, ws, yall + yo * 4, a0 + j * kp // 2, a1 + j * kp // 2, a2 + j * kp // 128 * 4,
+                                       a3 + j * kp // 128 * 4, n, k)
+            yo += n
+        table, shp = rt.stream_table_var(entries)
+        status = rt.alloc(4)
+        rt.memset(status, 0, 4)
+        rt.graph_begin()
+        for k in ks:
+            xk, a0, a1, a2, a3 = bufs[k]
+            rt.launch2d("quant_act", kpad[k] // 128, len(idx_of[k]), 32, 1, [xk, a0, a1, a2, a3, len(idx_of[k]), kpad[k]])
+        rt.launch("w4a8_layers_stream", 1, 1, [table, shp, len(entries), 0, 0, status, 0])
+        g = rt.graph_end()
+        ms = time_graph(rt, g, reps, 3, lambda: None)
+        rt.graph_free(g)
+        if int(rt.download(status, 1, np.int32)[0]) != 0:
+            raise RuntimeError("w4a8_layers_stream reported a bounded wait that ran out")
+        out["w4a8_layers_stream"] = {"ms_per_token": round(ms, 4), "gb_per_s": round(total_bytes / ms / 1e6, 1),
+                                     "table_entries": len(entries),
+                                     "what": "all 400 layers in one launch (a layer of the table = 5120 k of a weight matrix; "
+                                             "longer rows are consecutive entries that add to y), one quant_act launch per K"}
+        for ptr in (table, shp, status, yall):
+            rt.free(ptr)
+        for k in ks:
+            for ptr in bufs[k]:
+                rt.free(ptr)
     for _n, _k, wq, ws in layers:
         rt.free(wq)
         rt.free(ws)

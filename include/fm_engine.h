@@ -117,6 +117,20 @@ int   fm_download_join(int lag);
  * pass row_base + (M-1)*ystride as row_base here: the checked footprint of y then covers every token.
  * 0 ok, -4 a pointer fails the check, -1 other errors. */
 int   fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, int rows, int K, int row_base);
+/* Layer table of "w4a8_layers_stream": layers of different shapes in one launch.  A layer here is 5120 k of a set of
+ * weight rows; a weight matrix with longer rows (K = 6144, 17408, ...) is ceil(K/5120) consecutive layers over the same
+ * rows and the same y, the second and later ones with accumulate = 1.  host_layers holds nlayers x 16 values:
+ *   wq, ws      first byte of this chunk in the first row (wq + chunk*2560, ws + chunk*80)
+ *   0, y        (no x), output of the weight matrix
+ *   ae, ao, asc, asu   the token's quantised activations of this chunk (quant_act outputs at k = chunk*5120: 2560 + 2560
+ *               bytes of codes, 40 scales, 40 sums); behind the matrix's K they must be zero (pad the arrays to a
+ *               multiple of 5120 k and clear them once)
+ *   rows, wpitch, spitch    weight rows, bytes between rows of wq (K/2) and of ws (K/128*2)
+ *   wbytes, sbytes          valid bytes of a row in this chunk: 2560 / 80, less in the last chunk of a longer row
+ *   accumulate, row_base, 0
+ * Every range is checked against the live allocations; dev_table receives nlayers*32 bytes, dev_shapes nlayers*64.
+ * 0 ok, -4 a pointer or a shape fails the check, -1 other errors. */
+int   fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_layers, int nlayers);
 
 /* Peer memory for the row-sharded stream (one process per GPU).  fm_ipc_export gives the
  * 64-byte CUDA IPC handle of the fm_alloc allocation that contains `dev`, the offset of

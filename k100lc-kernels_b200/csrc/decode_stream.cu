@@ -106,11 +106,13 @@ __device__ __forceinline__ bool reduce_and_emit(const Cta& c, int grp, int w, in
 //   PAD     bytes added to the pitch of a row inside a stage (64: the two rows of a quarter-warp's 16-byte
 //           loads fall into different banks; the rows are then copied one by one)
 //   DUMP    also store the integer accumulators
-template <int M_, int STAGES_, int NGROUPS_, bool AIS, int NACT_, bool BREG, int PAD, bool DUMP, int NPROD_ = 1>
+//   VAR     the layers have shapes of their own (StreamParams::var): rows per layer, row pitch, chunks of longer rows
+template <int M_, int STAGES_, int NGROUPS_, bool AIS, int NACT_, bool BREG, int PAD, bool DUMP, int NPROD_ = 1, bool VAR_ = false>
 struct W4A8Mma {
     using Params = PlainParams;
     static constexpr int M = M_, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = AIS ? 1 : NACT_;
-    static constexpr bool ACT_IN_STAGE = AIS;
+    static constexpr bool ACT_IN_STAGE = AIS, VAR = VAR_;
+    static_assert(!VAR || (AIS && M_ == 1 && !DUMP && PAD == 0), "per-layer shapes: one token, codes inside the stage");
     static constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
     static constexpr int ROWB = K / 2, SCB = NG * 2, PITCH = ROWB + PAD;
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB;
@@ -123,6 +125,14 @@ struct W4A8Mma {
     __device__ static void init_extra(const Params&, uint8_t*) {}
     __device__ static void copy_act(const Params& pp, int l, uint8_t* dst, uint64_t* bar) {
         const StreamParams& p = pp.s;
+        if (VAR) {                                       // the chunk's codes, by the layer's own pointers
+            const VarLayer v = p.var[l];
+            bulk_g2s(dst, v.ae, K / 2, bar);
+            bulk_g2s(dst + K / 2, v.ao, K / 2, bar);
+            bulk_g2s(dst + K, v.asc, NG * 4, bar);
+            bulk_g2s(dst + K + NG * 4, v.asu, NG * 4, bar);
+            return;
+        }
         bulk_g2s(dst, p.ae + (size_t)l * M * (K / 2), M * (K / 2), bar);
         bulk_g2s(dst + M * (K / 2), p.ao + (size_t)l * M * (K / 2), M * (K / 2), bar);
         bulk_g2s(dst + M * K, p.asc + (size_t)l * M * (NG * 4), M * NG * 4, bar);
@@ -148,16 +158,18 @@ struct W4A8Mma {
         return f;
     }
 
-    __device__ static void consume(const Cta& c, const Params& pp, int grp, int w) {
+    __device__ static void consume(const Cta& cta, const Params& pp, int grp, int w) {
+        Cta c = cta;                                     // (rows and stages of the CTA follow the layer when VAR)
         const StreamParams& p = pp.s;
         const int lane = c.lane, g = lane >> 2, t = lane & 3;
         const int t0 = 2 * t, t1 = 2 * t + 1;
         int cg = 0;                                      // stages this group has taken so far
-        for (int l = 0; l < p.nlayers; l++) {
-            const int c0 = l * c.nst;
+        int c0 = 0;                                      // stages of the layers before this one
+        for (int l = 0; l < p.nlayers; c0 += c.nst, l++) {
+            set_geom<W4A8Mma>(c, l);
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;     // this group's first stage of the layer
             float* yt = c.ytile + (l % kYBufs) * kOutCap;
-            float* y = get_layer(p, l).y + p.row_base;
+            float* y = get_layer(p, l).y + (VAR ? 0 : p.row_base);      // (VAR: always through the tile, the writer adds the base)
             if (!layer_enter<W4A8Mma>(c, l)) return;
             const uint8_t* tile = c.act + (size_t)(l % NACT) * ACT;
             Frag fr[BREG ? GPW : 1];
@@ -1054,6 +1066,60 @@ int launch_w4a8_read_ceiling(const LaunchCtx& c, const uint64_t* a) {
     return run_policy<W4A8ReadCeiling<4, 2>>(kn, c, pp);
 }
 
+// w4a8_layers_stream(layers, shapes, nlayers, npeers, peer_delta, status, flags): W4A8, one token, layers of different
+// shapes in one launch.  `layers` / `shapes` are the two device arrays filled by fm_stream_table_var (a layer = 5120 k of
+// a set of rows; longer rows are consecutive layers that add to the same y); npeers, peer_delta, status and flags as for
+// the other stream kernels.  Every CTA takes an equal share of the rows of every layer.
+int launch_w4a8_layers_stream(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = "w4a8_layers_stream";
+    PlainParams pp = {};
+    StreamParams& p = pp.s;
+    p.layers = arg_ptr<const StreamLayer>(a[0]);
+    p.var = arg_ptr<const VarLayer>(a[1]);
+    p.nlayers = arg_i32(a[2]);
+    p.npeers = arg_i32(a[3]);
+    p.peer_delta = arg_ptr<const long long>(a[4]);
+    p.status = arg_ptr<int>(a[5]);
+    p.flags = arg_ptr<unsigned>(a[6]);
+    p.K = 5120;
+    p.M = 1;
+    p.ystride = 0;
+    p.wait_hint_ns = (uint32_t)env_or("FM_STREAM_HINT_NS", 0);
+    FM_REQUIRE(p.nlayers >= 0 && p.npeers >= 0 && p.npeers <= 8, kn, "bad nlayers / npeers");
+    if (p.nlayers == 0) return FM_OK;
+    FM_REQUIRE(aligned(p.status, 4), kn, "misaligned status");
+    FM_RANGE(p.status, 4, kn, "status");
+    if (p.npeers) FM_RANGE(p.peer_delta, (size_t)p.npeers * 8, kn, "peer_delta");
+    int min_rows = 0, max_rows = 0;
+    FM_REQUIRE(stream_var_ok(p.layers, p.var, p.nlayers, p.peer_delta, p.npeers, &min_rows, &max_rows), kn,
+               "the layer table at %p and the shapes at %p were not filled by fm_stream_table_var for at least %d layers (or were "
+               "overwritten, or a buffer they point into was freed since), or the peer offsets do not come from fm_stream_peers "
+               "for its outputs", (const void*)p.layers, (const void*)p.var, p.nlayers);
+    p.rows = max_rows;
+    const int grid = c.sm_count < min_rows ? c.sm_count : min_rows;
+    FM_REQUIRE((max_rows + grid - 1) / grid <= kOutCap, kn,
+               "a CTA would own %d rows of the largest layer (%d rows on %d CTAs); the output tile holds %d", (max_rows + grid - 1) / grid,
+               max_rows, grid, kOutCap);
+    if (p.flags) {
+        FM_REQUIRE(aligned(p.flags, 4), kn, "misaligned flags");
+        FM_RANGE(p.flags, (size_t)p.nlayers * 4, kn, "flags");
+        FM_REQUIRE(p.npeers == 0 || peer_window_ok(p.peer_delta, p.npeers, p.flags, (size_t)p.nlayers * 4), kn,
+                   "the flags array must lie inside the window that fm_stream_peers validated for these offsets");
+    }
+    using P = W4A8Mma<1, 4, 2, true, 1, false, 0, false, 2, true>;
+    constexpr size_t smem = smem_bytes<P>();
+    static_assert(smem <= 227 * 1024, "shared memory");
+    auto kern = stream_kernel<P>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(kn, e);
+        configured = true;
+    }
+    cudaError_t e = launch_kernel(kern, dim3(grid), dim3(P::kThreads), smem, c.stream, pdl_enabled(), pp);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
 // w4a8_decode_stream_m(common..., ae, ao, asc, asu, M, ystride, flags): M = 2..4 tokens per layer.  The code arrays
 // hold [nlayers * M] tokens (one 2-D quant_act launch with grid y = nlayers * M over x[nlayers][M][K]); y of a layer is
 // token-major, y[token * ystride + row_base + row].  The layer table must have been validated by fm_stream_table with
@@ -1218,6 +1284,7 @@ const KernelEntry kStream[] = {
     {"nvfp4_decode_stream_iacc", 14, launch_nvfp4_stream<true>, "piiiiipppppfpp"},
     {"stream_flag_wait", 5, launch_flag_wait, "piipi"},
     {"w4a8_stream_read_ceiling", 13, launch_w4a8_read_ceiling, "piiiiippppppp"},
+    {"w4a8_layers_stream", 7, launch_w4a8_layers_stream, "ppiippp"},
 };
 
 // Status word of the ring kernels when they are launched by name for a single layer (those entries have

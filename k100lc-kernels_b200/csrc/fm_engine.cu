@@ -66,7 +66,9 @@ struct Engine {
     struct Table { size_t bytes; int nlayers, rows, K, row_base; uintptr_t y_lo, y_hi, y_ptr_lo; size_t ws_avail; bool x_all;
                    std::vector<uintptr_t> deps;
                    unsigned long long serial = 0;        // distinguishes this record from an earlier one at the same address
-                   std::vector<uintptr_t> wq; };         // the wq entry of every layer (for the TMA tensor maps)
+                   std::vector<uintptr_t> wq;            // the wq entry of every layer (for the TMA tensor maps)
+                   uintptr_t shapes = 0;                 // fm_stream_table_var: device array of per-layer shapes (64 bytes each)
+                   int min_rows = 0, max_rows = 0; };
     struct MapSet { void* dev; unsigned long long serial; };
     std::map<uintptr_t, MapSet> table_maps;      // table address -> device array of tensor maps built for record `serial`
     unsigned long long table_serial = 0;
@@ -230,7 +232,10 @@ void touch(const void* p, size_t n) {
     Engine& e = E();
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
     for (auto it = e.tables.begin(); it != e.tables.end();) {
-        if (a < it->first + it->second.bytes && it->first < a + n) { drop_table_maps(it->first); it = e.tables.erase(it); e.epoch++; }
+        const Engine::Table& t = it->second;
+        const bool hit = (a < it->first + t.bytes && it->first < a + n) ||
+                         (t.shapes && a < t.shapes + (size_t)t.nlayers * 64 && t.shapes < a + n);
+        if (hit) { drop_table_maps(it->first); it = e.tables.erase(it); e.epoch++; }
         else ++it;
     }
     for (auto it = e.peers.begin(); it != e.peers.end();) {
@@ -429,6 +434,21 @@ bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_ba
     auto ip = e.peers.find(reinterpret_cast<uintptr_t>(peer_delta));
     if (ip == e.peers.end() || ip->second.npeers != npeers) return false;
     return (whole_y ? t.y_ptr_lo : t.y_lo) >= ip->second.lo && t.y_hi <= ip->second.hi;
+}
+
+bool stream_var_ok(const void* table, const void* shapes, int nlayers, const void* peer_delta, int npeers, int* min_rows,
+                   int* max_rows) {
+    Engine& e = E();
+    auto it = e.tables.find(reinterpret_cast<uintptr_t>(table));
+    if (it == e.tables.end()) return false;                 // (the shapes are needed even when the checks are off)
+    const Engine::Table& t = it->second;
+    if (!t.shapes || t.shapes != reinterpret_cast<uintptr_t>(shapes) || t.nlayers < nlayers) return false;
+    *min_rows = t.min_rows;
+    *max_rows = t.max_rows;
+    if (npeers == 0 || !e.check_bounds) return true;
+    auto ip = e.peers.find(reinterpret_cast<uintptr_t>(peer_delta));
+    if (ip == e.peers.end() || ip->second.npeers != npeers) return false;
+    return t.y_lo >= ip->second.lo && t.y_hi <= ip->second.hi;
 }
 
 const void* stream_table_maps(const void* table, int nlayers, int rows, int K) {
@@ -896,6 +916,73 @@ int fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers, i
     // The TMA tensor maps over the wq entries are built now, while allocating is allowed (a launch inside a graph
     // capture could not).  Best effort: a table the driver refuses to encode simply has none.
     if (K % 256 == 0) stream_table_maps(dev_table, nlayers, rows, K);
+    return 0;
+}
+
+int fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_layers, int nlayers) {
+    LOCK;
+    NEED_INIT(-1);
+    Engine& e = E();
+    if (nlayers <= 0) { set_errorf("fm_stream_table_var: nlayers must be positive"); return -1; }
+    const size_t tbytes = (size_t)nlayers * 32, sbytes_all = (size_t)nlayers * 64;
+    if (!range_ok(dev_table, tbytes) || !range_ok(dev_shapes, sbytes_all) || !aligned(dev_table, 8) || !aligned(dev_shapes, 16)) {
+        set_errorf("fm_stream_table_var: the table or the shape array does not fit its allocation (or is misaligned)");
+        return -1;
+    }
+    struct Shape { uint64_t ae, ao, asc, asu; int rows, wpitch, spitch, wbytes, sbytes, accumulate, row_base, pad; };
+    static_assert(sizeof(Shape) == 64, "shape entry");
+    std::vector<uint64_t> tab((size_t)nlayers * 4);
+    std::vector<Shape> shp((size_t)nlayers);
+    std::vector<uintptr_t> deps;
+    add_dep(deps, reinterpret_cast<uintptr_t>(dev_table));
+    add_dep(deps, reinterpret_cast<uintptr_t>(dev_shapes));
+    uintptr_t y_lo = ~(uintptr_t)0, y_hi = 0;
+    int min_rows = 1 << 30, max_rows = 0;
+    for (int l = 0; l < nlayers; l++) {
+        const uint64_t* h = host_layers + (size_t)l * 16;
+        Shape& sh = shp[l];
+        sh = Shape{h[4], h[5], h[6], h[7], (int)h[8], (int)h[9], (int)h[10], (int)h[11], (int)h[12], (int)h[13], (int)h[14], 0};
+        const bool shape_ok = sh.rows > 0 && sh.wbytes > 0 && sh.wbytes <= 2560 && sh.wbytes % 16 == 0 && sh.wpitch >= sh.wbytes &&
+                              sh.wpitch % 16 == 0 && sh.sbytes > 0 && sh.sbytes <= 80 && sh.sbytes % 16 == 0 &&
+                              sh.spitch >= sh.sbytes && sh.spitch % 16 == 0 && sh.sbytes * 32 == sh.wbytes &&
+                              (sh.accumulate == 0 || sh.accumulate == 1) && sh.row_base >= 0;
+        if (!shape_ok) {
+            set_errorf("fm_stream_table_var: layer %d: rows=%d wpitch=%d wbytes=%d spitch=%d sbytes=%d accumulate=%d row_base=%d is "
+                       "not a shape this kernel takes (chunks of at most 5120 k, 16-byte granules, sbytes = wbytes / 32)", l, sh.rows,
+                       sh.wpitch, sh.wbytes, sh.spitch, sh.sbytes, sh.accumulate, sh.row_base);
+            return FM_EREJECT;
+        }
+        const void* ptrs[7] = {(const void*)(uintptr_t)h[0], (const void*)(uintptr_t)h[1], (const void*)(uintptr_t)h[3],
+                               (const void*)(uintptr_t)h[4], (const void*)(uintptr_t)h[5], (const void*)(uintptr_t)h[6],
+                               (const void*)(uintptr_t)h[7]};
+        const size_t need[7] = {(size_t)(sh.rows - 1) * sh.wpitch + sh.wbytes, (size_t)(sh.rows - 1) * sh.spitch + sh.sbytes,
+                                ((size_t)sh.row_base + sh.rows) * 4, 2560, 2560, 160, 160};
+        const size_t algn[7] = {16, 16, 4, 16, 16, 16, 16};
+        const char* what[7] = {"wq", "ws", "y", "ae", "ao", "asc", "asu"};
+        for (int j = 0; j < 7; j++) {
+            if (!range_ok(ptrs[j], need[j]) || !aligned(ptrs[j], algn[j])) {
+                set_errorf("fm_stream_table_var: layer %d: %s (%zu bytes at %p) is misaligned or outside its allocation", l, what[j],
+                           need[j], ptrs[j]);
+                return FM_EREJECT;
+            }
+            add_dep(deps, reinterpret_cast<uintptr_t>(ptrs[j]));
+        }
+        tab[4 * l] = h[0]; tab[4 * l + 1] = h[1]; tab[4 * l + 2] = 0; tab[4 * l + 3] = h[3];
+        const uintptr_t y = (uintptr_t)h[3];
+        if (y + (size_t)sh.row_base * 4 < y_lo) y_lo = y + (size_t)sh.row_base * 4;
+        if (y + need[2] > y_hi) y_hi = y + need[2];
+        if (sh.rows < min_rows) min_rows = sh.rows;
+        if (sh.rows > max_rows) max_rows = sh.rows;
+    }
+    if (copy_sync(dev_table, tab.data(), tbytes, cudaMemcpyHostToDevice, "fm_stream_table_var") != 0) return -1;
+    if (copy_sync(dev_shapes, shp.data(), sbytes_all, cudaMemcpyHostToDevice, "fm_stream_table_var") != 0) return -1;
+    touch(dev_table, tbytes);
+    touch(dev_shapes, sbytes_all);
+    Engine::Table t{tbytes, nlayers, max_rows, 5120, 0, y_lo, y_hi, y_lo, 0, false, deps, ++e.table_serial, {}};
+    t.shapes = reinterpret_cast<uintptr_t>(dev_shapes);
+    t.min_rows = min_rows;
+    t.max_rows = max_rows;
+    e.tables[reinterpret_cast<uintptr_t>(dev_table)] = t;
     return 0;
 }
 

@@ -45,6 +45,12 @@ void* engine_scratch(size_t bytes);
 bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_base, const void* peer_delta,
                      int npeers, bool whole_y = false, size_t ws_bytes = 0, bool need_x = false);
 
+// true when `table` / `shapes` were filled by fm_stream_table_var for at least `nlayers` layers and are still valid (or
+// checks are off); reports the smallest and largest row count of the layers.  With npeers > 0 the peer offsets must
+// cover every y of the table.
+bool stream_var_ok(const void* table, const void* shapes, int nlayers, const void* peer_delta, int npeers, int* min_rows,
+                   int* max_rows);
+
 // Device array of `nlayers` TMA tensor maps (128 bytes each) over the wq entries of a validated layer table, each
 // layer's packed codes seen as [rows][K/2] bytes with a box of 128 bytes x 128 rows and the 128-byte swizzle.  Built by
 // fm_stream_table (or when first asked for) and kept with the table's record; nullptr when the table has no record

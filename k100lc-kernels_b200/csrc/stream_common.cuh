@@ -40,8 +40,22 @@ struct StreamLayer {                   // one entry of the device-side layer tab
     float* y;                          // [>= row_base + rows] fp32 output of this layer
 };
 
+// Per-layer shape of a table whose layers differ (the policies that declare VAR).  A layer here is 5120 k of a set of
+// weight rows: a weight matrix with longer rows is several such layers over the same rows, the second and later ones
+// adding to y (`accumulate`); rows may be `wpitch` bytes apart with `wbytes` valid bytes in this chunk.
+struct VarLayer {                      // 64 bytes
+    const uint8_t *ae, *ao, *asc, *asu;   // the token's codes of this chunk: 2560 + 2560 bytes, 40 scales, 40 sums (zero behind the row's K)
+    int rows;                          // weight rows of this layer
+    int wpitch, spitch;                // bytes between the rows of wq / ws
+    int wbytes, sbytes;                // valid bytes of a row of wq / ws in this chunk (2560 / 80 for a full chunk)
+    int accumulate;                    // 0: y = value; 1: y += value
+    int row_base;                      // first output index of these rows inside the layer's y
+    int pad;
+};
+
 struct StreamParams {
     const StreamLayer* layers;         // device table, or nullptr: the single layer `one`
+    const VarLayer* var;               // per-layer shapes (VAR policies), else nullptr: `rows` and `row_base` below for all
     const uint8_t *ae, *ao, *asc, *asu;   // activation-quantiser outputs of all layers (meaning depends on the format)
     int nlayers, rows, K, row_base;
     int npeers;                        // additional receivers of y (0 on one GPU)
@@ -132,6 +146,21 @@ __device__ __forceinline__ void quiet_wait(uint64_t* bar, uint32_t parity) {
 // Status codes: 1 ring slot not freed (producer), 2 activation tile not landed, 3 stage not landed,
 // 4 activation tile not freed, 5 / 6 partial-sum tile, 7 output tile not written, 8 output tile not complete.
 
+// A policy may declare `static constexpr bool VAR = true`: the layers of its table have shapes of their own
+// (StreamParams::var), and every role recomputes this CTA's rows and stages at the start of each layer.
+template <class P, class = void> struct is_var : std::false_type {};
+template <class P> struct is_var<P, std::void_t<decltype(P::VAR)>> : std::bool_constant<P::VAR> {};
+
+template <class P>
+__device__ __forceinline__ void set_geom(Cta& c, int l) {
+    if constexpr (is_var<P>::value) {
+        const int rows = c.p->var[l].rows;
+        c.r0 = (int)((long long)rows * blockIdx.x / gridDim.x);
+        c.r1 = (int)((long long)rows * (blockIdx.x + 1) / gridDim.x);
+        c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
+    }
+}
+
 // ---- producer ------------------------------------------------------------------------------
 // P supplies: ROWS, STAGES, PITCH, ROWB, SCB, STAGE_W, STAGE, ACT, NACT, ACT_IN_STAGE, OFF_ACT and
 // copy_act(pp, layer, dst, bar), which issues bulk copies of exactly ACT bytes.
@@ -139,7 +168,8 @@ __device__ __forceinline__ void quiet_wait(uint64_t* bar, uint32_t parity) {
 // round several lanes (each is a chain of a barrier wait and half a dozen copy instructions per stage, which paces
 // the ring when a CTA has a single small stage per layer).
 template <class P>
-__device__ __forceinline__ void run_producer(const Cta& c, const typename P::Params& pp, int pl) {
+__device__ __forceinline__ void run_producer(const Cta& cta, const typename P::Params& pp, int pl) {
+    Cta c = cta;                       // rows and stages of this CTA change with the layer when the shapes do
     const StreamParams& p = *c.p;
     Bars* B = c.bars;
     static_assert(P::NPROD == 1 || P::ACT_IN_STAGE, "several producer lanes need self-contained stages");
@@ -160,9 +190,19 @@ __device__ __forceinline__ void run_producer(const Cta& c, const typename P::Par
     // row shard of eight GPUs) a dependent 32-byte load per layer would otherwise cost this thread a trip to
     // L2 — most of a stage time — before it can issue anything.
     int cc = 0;
+    VarLayer vnext = {};
+    if constexpr (is_var<P>::value) vnext = p.var[0];
     StreamLayer lay = get_layer(p, 0), lay1 = get_layer(p, min(1, p.nlayers - 1)), lay2;
     for (int l = 0; ok && l < p.nlayers; l++, lay = lay1, lay1 = lay2) {
         lay2 = get_layer(p, min(l + 2, p.nlayers - 1));
+        VarLayer vl = {};
+        if constexpr (is_var<P>::value) {                  // this layer's shape was requested a layer ago
+            vl = vnext;
+            vnext = p.var[min(l + 1, p.nlayers - 1)];
+            c.r0 = (int)((long long)vl.rows * blockIdx.x / gridDim.x);
+            c.r1 = (int)((long long)vl.rows * (blockIdx.x + 1) / gridDim.x);
+            c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
+        }
         if (!P::ACT_IN_STAGE && !copy_tile(l)) { ok = false; break; }
         for (int j = 0; j < c.nst; j++, cc++) {
             if (P::NPROD > 1 && cc % P::NPROD != pl) continue;
@@ -171,6 +211,27 @@ __device__ __forceinline__ void run_producer(const Cta& c, const typename P::Par
             const int row = c.r0 + j * P::ROWS;
             const int nr = min(P::ROWS, c.r1 - row);
             uint8_t* dst = c.ring + (size_t)s * P::STAGE;
+            if constexpr (is_var<P>::value) {
+                // rows may be further apart than a chunk is wide, and the last chunk of a row may be short: the rest of
+                // the stage keeps what it held (finite numbers: the ring is cleared at the start), and the token's codes
+                // behind the row's K are zero
+                mbar_expect_tx(&B->full[s], (uint32_t)(nr * (vl.wbytes + vl.sbytes)) + P::ACT);
+                if (vl.wpitch == P::ROWB && vl.wbytes == P::ROWB) {
+                    bulk_g2s(dst, lay.wq + (size_t)row * P::ROWB, (uint32_t)(nr * P::ROWB), &B->full[s]);
+                } else {
+                    for (int r = 0; r < nr; r++)
+                        bulk_g2s(dst + (size_t)r * P::PITCH, lay.wq + (size_t)(row + r) * vl.wpitch, (uint32_t)vl.wbytes, &B->full[s]);
+                }
+                if (vl.spitch == P::SCB && vl.sbytes == P::SCB) {
+                    bulk_g2s(dst + P::STAGE_W, lay.ws + (size_t)row * P::SCB, (uint32_t)(nr * P::SCB), &B->full[s]);
+                } else {
+                    for (int r = 0; r < nr; r++)
+                        bulk_g2s(dst + P::STAGE_W + r * P::SCB, lay.ws + (size_t)(row + r) * vl.spitch, (uint32_t)vl.sbytes, &B->full[s]);
+                }
+                P::copy_act(pp, l, dst + P::OFF_ACT, &B->full[s]);
+                issued = cc + 1;
+                continue;
+            }
             mbar_expect_tx(&B->full[s], (uint32_t)(nr * (P::ROWB + P::SCB)) + (P::ACT_IN_STAGE ? P::ACT : 0));
             if (P::PITCH == P::ROWB) {
                 bulk_g2s(dst, lay.wq + (size_t)row * P::ROWB, (uint32_t)(nr * P::ROWB), &B->full[s]);
@@ -197,13 +258,15 @@ __device__ __forceinline__ void run_producer(const Cta& c, const typename P::Par
 // tile layout [row][token]; y of a layer is token-major: y[token * ystride + row].  `delta` are the receivers' byte
 // offsets, held in registers: read from global memory inside the loop they cost a dependent load per receiver and
 // layer, which is more than a stage time when a CTA has one stage per layer.
+// `add`: the tile is added to what y holds (the later chunks of a row that is longer than a layer's 5120 k; the same
+// lane wrote that value, in program order, when it handled the chunk before).
 template <int M>
 __device__ __forceinline__ void write_out(const StreamParams& p, const float* tile, float* y, int n, int lane,
-                                          const long long (&delta)[8]) {
+                                          const long long (&delta)[8], bool add = false) {
     for (int i = lane; i < n * M; i += 32) {
         const int tok = M == 1 ? 0 : i / n, row = M == 1 ? i : i - tok * n;      // token-major walk: coalesced stores
-        const float v = tile[row * M + tok];
         float* dst = y + (size_t)tok * p.ystride + row;
+        const float v = add ? *dst + tile[row * M + tok] : tile[row * M + tok];
         *dst = v;
 #pragma unroll
         for (int q = 0; q < 8; q++)
@@ -212,7 +275,8 @@ __device__ __forceinline__ void write_out(const StreamParams& p, const float* ti
 }
 
 template <class P>
-__device__ __forceinline__ void run_writer(const Cta& c) {
+__device__ __forceinline__ void run_writer(const Cta& cta) {
+    Cta c = cta;
     const StreamParams& p = *c.p;
     if (!c.tiled) return;
     long long delta[8];
@@ -223,8 +287,15 @@ __device__ __forceinline__ void run_writer(const Cta& c) {
         float* y_l = y_next;
         y_next = get_layer(p, min(l + 1, p.nlayers - 1)).y;
         const int b = l % kYBufs;
+        set_geom<P>(c, l);
+        int row_base = p.row_base;
+        bool add = false;
+        if constexpr (is_var<P>::value) {
+            row_base = p.var[l].row_base;
+            add = p.var[l].accumulate != 0;
+        }
         if (!cta_wait(c, &c.bars->ydone[b], (l / kYBufs) & 1, 8)) return;
-        write_out<P::M>(p, c.ytile + b * kOutCap, y_l + p.row_base + c.r0, c.r1 - c.r0, c.lane, delta);
+        write_out<P::M>(p, c.ytile + b * kOutCap, y_l + row_base + c.r0, c.r1 - c.r0, c.lane, delta, add);
         __syncwarp();
         if (c.lane == 0) mbar_arrive(&c.bars->yfree[b]);
         if (p.flags) {
@@ -322,13 +393,20 @@ stream_kernel(const typename P::Params pp) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     P::init_extra(pp, c.extra);
+    if constexpr (is_var<P>::value) {
+        // a short chunk leaves the rest of its rows in the stage as it was: make sure that is never an uninitialised
+        // bit pattern (a NaN scale times a zero activation scale would still be a NaN)
+        for (int i = threadIdx.x; i < P::STAGES * P::STAGE / 16; i += blockDim.x)
+            reinterpret_cast<uint4*>(c.ring)[i] = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
     pdl_wait();                                          // the codes come from the preceding quantiser launch
 
     c.r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
     c.r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
     c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
-    c.tiled = !no_output<P>::value && (c.r1 - c.r0) * P::M <= kOutCap;
+    c.tiled = !no_output<P>::value && (is_var<P>::value || (c.r1 - c.r0) * P::M <= kOutCap);   // (the launcher of a VAR policy checks the tile)
 
     if (c.warp >= NCW && c.warp < NCW + P::NPROD) {
         if (c.lane == 0) run_producer<P>(c, pp, c.warp - NCW);

@@ -86,6 +86,7 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_copy_beside": (c.c_int, [c.c_void_p, c.c_void_p, c.c_size_t]),
         "fm_download_beside": (c.c_int, [c.c_void_p, c.c_size_t, c.c_void_p, c.c_size_t, c.c_size_t, c.c_size_t]),
         "fm_download_join": (c.c_int, [c.c_int]),
+        "fm_stream_table_var": (c.c_int, [c.c_void_p, c.c_void_p, c.POINTER(c.c_uint64), c.c_int]),
         "fm_event_create": (c.c_int, []),
         "fm_event_record": (c.c_int, [c.c_int]),
         "fm_event_elapsed_ms": (c.c_float, [c.c_int, c.c_int]),
@@ -440,6 +441,34 @@ class Runtime:
                 self.free(dev)
             self._fail("fm_stream_table")
         return dev
+
+    @staticmethod
+    def layer_chunks(wq: int, ws: int, y: int, ae: int, ao: int, asc: int, asu: int, rows: int, k: int,
+                     row_base: int = 0) -> list:
+        """The entries of ``stream_table_var`` for one W4A8 weight matrix ``[rows, k]`` (k a multiple of 1024): one
+        entry per 5120 k, the later ones adding to ``y``.  ``ae, ao, asc, asu`` are the outputs of ``quant_act`` for
+        this matrix's input, in arrays padded with zeros to a multiple of 5120 k (2560-byte codes, 40 scales / sums
+        per chunk)."""
+        if k % 1024:
+            raise ValueError("layer_chunks: K must be a multiple of 1024")
+        out = []
+        for c in range(-(-k // 5120)):
+            kc = min(5120, k - 5120 * c)
+            out.append((wq + c * 2560, ws + c * 80, 0, y, ae + c * 2560, ao + c * 2560, asc + c * 160, asu + c * 160,
+                        rows, k // 2, (k // 128) * 2, kc // 2, (kc // 128) * 2, 1 if c else 0, row_base, 0))
+        return out
+
+    def stream_table_var(self, entries) -> tuple[int, int]:
+        """Validated layer table and shape array for ``w4a8_layers_stream``: ``entries`` is a list of 16-tuples as
+        ``layer_chunks`` makes them.  Returns the two device pointers (fresh allocations: 32 and 64 bytes per entry)."""
+        n = len(entries)
+        flat = (ctypes.c_uint64 * (16 * n))(*[int(v) for ent in entries for v in ent])
+        table, shapes = self.alloc(32 * n), self.alloc(64 * n)
+        if self._lib.fm_stream_table_var(ctypes.c_void_p(table), ctypes.c_void_p(shapes), flat, n) != 0:
+            self.free(table)
+            self.free(shapes)
+            self._fail("fm_stream_table_var")
+        return table, shapes
 
     def gemm_status(self) -> int:
         """Sync, then 0 or the code of a bounded wait that ran out in a GEMM kernel."""

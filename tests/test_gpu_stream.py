@@ -557,6 +557,65 @@ def test_nvfp4_tcgen05_stream_tile_edges(rt, monkeypatch, rows, nl):
         assert np.isnan(got[i, :3]).all() and np.isnan(got[i, 3 + rows:]).all()
 
 
+def test_layers_of_different_shapes_in_one_launch(rt):
+    """w4a8_layers_stream: weight matrices of different (rows, K) in one launch — K = 5120, 6144 (a full and a 1024-k
+    chunk) and 17408 (three full chunks and one of 2048 k), row counts from a few to thousands, a pinned host receiver
+    and completion counters.  y within 1e-5 of the oracle over the whole K, and the bits of gemv_w4a8<1,false,1> where
+    the row is a single chunk."""
+    shapes = [(300, 5120), (200, 6144), (2176, 5120), (150, 17408), (1024, 5120), (37, 6144), (5120, 17408)]
+    sms = rt.device_attr("sm_count")
+    layers = [synth.rt4_layer(n, k, 1, seed=2000 + i) for i, (n, k) in enumerate(shapes)]
+    ytot = sum(n for n, _ in shapes)
+    with Bufs(rt) as b:
+        entries, outs, acts = [], [], []
+        nchunks = sum(-(-k // 5120) for _, k in shapes)
+        buf = b.zeros(ytot + nchunks, np.float32, np.nan)            # every y, then one counter per table entry
+        host = rt.pinned((ytot + nchunks,), np.float32)
+        host[:] = 0
+        rt.memset(buf + ytot * 4, 0, nchunks * 4)
+        off = 0
+        for (n, k), L in zip(shapes, layers):
+            kp = -(-k // 5120) * 5120                              # the code arrays are padded with zeros to whole chunks
+            x = b.put(L["x"][0])
+            ae, ao = b.zeros(kp // 2, np.int8), b.zeros(kp // 2, np.int8)
+            asc, asu = b.zeros(kp // 128), b.zeros(kp // 128, np.int32)
+            rt.launch("quant_act", k // 128, 32, [x, ae, ao, asc, asu, 1, k])
+            wq, ws = b.put(L["wq"]), b.put(L["ws"])
+            entries += rt.layer_chunks(wq, ws, buf + off * 4, ae, ao, asc, asu, n, k)
+            outs.append(off)
+            acts.append((wq, ws, ae, ao, asc, asu))
+            off += n
+        table, shp = rt.stream_table_var(entries)
+        deltas = rt.stream_peers([host.ctypes.data], buf, (ytot + nchunks) * 4)
+        status = b.zeros(1, np.int32)
+        flags = buf + ytot * 4
+        rt.launch("w4a8_layers_stream", 1, 1, [table, shp, len(entries), 1, deltas, status, flags])
+        dev = b.get(buf, ytot + nchunks)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        ctas = min(sms, min(n for n, _ in shapes))
+        assert (dev[ytot:].view(np.uint32) == ctas).all() and (host[ytot:].view(np.uint32) == ctas).all()
+        assert np.array_equal(host[:ytot].view(np.uint32), dev[:ytot].view(np.uint32))
+        for (n, k), L, o, (wq, ws, ae, ao, asc, asu) in zip(shapes, layers, outs, acts):
+            q = O.quant_act(L["x"])
+            ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128)["y"][0]
+            assert O.rel_err(dev[o:o + n], ref) < REL, (n, k)
+            if k == 5120:
+                y1 = b.zeros(n, np.float32, np.nan)
+                rt.launch("gemv_w4a8<1,false,1>", -(-n // 4), 256, [wq, ws, ae, ao, asc, asu, y1, n, k])
+                assert np.array_equal(b.get(y1, n).view(np.uint32), dev[o:o + n].view(np.uint32))
+        # a shape the kernel does not take, and a table that was not validated, are refused
+        bad = list(entries[0])
+        bad[11] = 2560 + 16
+        with pytest.raises(RuntimeError, match="not a shape this kernel takes"):
+            rt.stream_table_var([tuple(bad)])
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch("w4a8_layers_stream", 1, 1, [table, shp + 64, len(entries) - 1, 0, 0, status, 0])
+        rt.free(table)
+        rt.free(shp)
+        rt.free(deltas)
+    rt.free_pinned(host)
+
+
 def test_read_ceiling_kernel_copies_and_writes_nothing(rt):
     """w4a8_stream_read_ceiling takes the arguments of w4a8_decode_stream, walks all stages (status 0) and leaves y as
     it was; a table of another shape is refused."""
