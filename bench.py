@@ -623,7 +623,28 @@ def shape_table_timings(rt, reps: int = 5) -> dict:
                                      "table_entries": len(entries),
                                      "what": "all 400 layers in one launch (a layer of the table = 5120 k of a weight matrix; "
                                              "longer rows are consecutive entries that add to y), one quant_act launch per K"}
-        for ptr in (table, shp, status, yall):
+        rt.free(table)
+        rt.free(shp)
+        per_shape_s = {}
+        for n, k, c in SHAPE_TABLE:                        # each shape on its own through the same kernel
+            xk, a0, a1, a2, a3 = bufs[k]
+            kp = kpad[k]
+            ent = []
+            for i in [i for i in order if layers[i][0] == n and layers[i][1] == k]:
+                j = slot[i]
+                ent += rt.layer_chunks(layers[i][2], layers[i][3], yall, a0 + j * kp // 2, a1 + j * kp // 2,
+                                       a2 + j * kp // 128 * 4, a3 + j * kp // 128 * 4, n, k)
+            tb, sh = rt.stream_table_var(ent)
+            rt.graph_begin()
+            rt.launch("w4a8_layers_stream", 1, 1, [tb, sh, len(ent), 0, 0, status, 0])
+            g = rt.graph_end()
+            us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / c
+            rt.graph_free(g)
+            rt.free(tb)
+            rt.free(sh)
+            per_shape_s[f"{n}x{k}"] = {"us_per_layer": round(us, 3), "gb_per_s": round((n * k // 2 + n * (k // 128) * 2) / us / 1e3, 1)}
+        out["w4a8_layers_stream_per_shape"] = per_shape_s
+        for ptr in (status, yall):
             rt.free(ptr)
         for k in ks:
             for ptr in bufs[k]:

@@ -127,7 +127,7 @@ int   fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers,
  *               multiple of 5120 k and clear them once)
  *   rows, wpitch, spitch    weight rows, bytes between rows of wq (K/2) and of ws (K/128*2)
  *   wbytes, sbytes          valid bytes of a row in this chunk: 2560 / 80, less in the last chunk of a longer row
- *   accumulate, row_base, 0
+ *   accumulate, row_base, chunk    chunk = which 5120 k of the row (0, 1, ...)
  * Every range is checked against the live allocations; dev_table receives nlayers*32 bytes, dev_shapes nlayers*64.
  * 0 ok, -4 a pointer or a shape fails the check, -1 other errors. */
 int   fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_layers, int nlayers);

@@ -1091,7 +1091,7 @@ int launch_w4a8_layers_stream(const LaunchCtx& c, const uint64_t* a) {
     FM_RANGE(p.status, 4, kn, "status");
     if (p.npeers) FM_RANGE(p.peer_delta, (size_t)p.npeers * 8, kn, "peer_delta");
     int min_rows = 0, max_rows = 0;
-    FM_REQUIRE(stream_var_ok(p.layers, p.var, p.nlayers, p.peer_delta, p.npeers, &min_rows, &max_rows), kn,
+    FM_REQUIRE(stream_var_ok(p.layers, p.var, p.nlayers, p.peer_delta, p.npeers, &min_rows, &max_rows, &p.chunk_maps), kn,
                "the layer table at %p and the shapes at %p were not filled by fm_stream_table_var for at least %d layers (or were "
                "overwritten, or a buffer they point into was freed since), or the peer offsets do not come from fm_stream_peers "
                "for its outputs", (const void*)p.layers, (const void*)p.var, p.nlayers);

@@ -437,7 +437,7 @@ bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_ba
 }
 
 bool stream_var_ok(const void* table, const void* shapes, int nlayers, const void* peer_delta, int npeers, int* min_rows,
-                   int* max_rows) {
+                   int* max_rows, const void** chunk_maps) {
     Engine& e = E();
     auto it = e.tables.find(reinterpret_cast<uintptr_t>(table));
     if (it == e.tables.end()) return false;                 // (the shapes are needed even when the checks are off)
@@ -445,6 +445,8 @@ bool stream_var_ok(const void* table, const void* shapes, int nlayers, const voi
     if (!t.shapes || t.shapes != reinterpret_cast<uintptr_t>(shapes) || t.nlayers < nlayers) return false;
     *min_rows = t.min_rows;
     *max_rows = t.max_rows;
+    auto im = e.table_maps.find(it->first);
+    *chunk_maps = (im != e.table_maps.end() && im->second.serial == t.serial) ? im->second.dev : nullptr;
     if (npeers == 0 || !e.check_bounds) return true;
     auto ip = e.peers.find(reinterpret_cast<uintptr_t>(peer_delta));
     if (ip == e.peers.end() || ip->second.npeers != npeers) return false;
@@ -929,7 +931,7 @@ int fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_
         set_errorf("fm_stream_table_var: the table or the shape array does not fit its allocation (or is misaligned)");
         return -1;
     }
-    struct Shape { uint64_t ae, ao, asc, asu; int rows, wpitch, spitch, wbytes, sbytes, accumulate, row_base, pad; };
+    struct Shape { uint64_t ae, ao, asc, asu; int rows, wpitch, spitch, wbytes, sbytes, accumulate, row_base, chunk; };
     static_assert(sizeof(Shape) == 64, "shape entry");
     std::vector<uint64_t> tab((size_t)nlayers * 4);
     std::vector<Shape> shp((size_t)nlayers);
@@ -941,11 +943,12 @@ int fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_
     for (int l = 0; l < nlayers; l++) {
         const uint64_t* h = host_layers + (size_t)l * 16;
         Shape& sh = shp[l];
-        sh = Shape{h[4], h[5], h[6], h[7], (int)h[8], (int)h[9], (int)h[10], (int)h[11], (int)h[12], (int)h[13], (int)h[14], 0};
+        sh = Shape{h[4], h[5], h[6], h[7], (int)h[8], (int)h[9], (int)h[10], (int)h[11], (int)h[12], (int)h[13], (int)h[14], (int)h[15]};
         const bool shape_ok = sh.rows > 0 && sh.wbytes > 0 && sh.wbytes <= 2560 && sh.wbytes % 16 == 0 && sh.wpitch >= sh.wbytes &&
                               sh.wpitch % 16 == 0 && sh.sbytes > 0 && sh.sbytes <= 80 && sh.sbytes % 16 == 0 &&
                               sh.spitch >= sh.sbytes && sh.spitch % 16 == 0 && sh.sbytes * 32 == sh.wbytes &&
-                              (sh.accumulate == 0 || sh.accumulate == 1) && sh.row_base >= 0;
+                              (sh.accumulate == 0 || sh.accumulate == 1) && sh.row_base >= 0 && sh.chunk >= 0 &&
+                              (long long)sh.chunk * 2560 + sh.wbytes <= sh.wpitch && (long long)sh.chunk * 80 + sh.sbytes <= sh.spitch;
         if (!shape_ok) {
             set_errorf("fm_stream_table_var: layer %d: rows=%d wpitch=%d wbytes=%d spitch=%d sbytes=%d accumulate=%d row_base=%d is "
                        "not a shape this kernel takes (chunks of at most 5120 k, 16-byte granules, sbytes = wbytes / 32)", l, sh.rows,
@@ -983,6 +986,30 @@ int fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_
     t.min_rows = min_rows;
     t.max_rows = max_rows;
     e.tables[reinterpret_cast<uintptr_t>(dev_table)] = t;
+    // TMA maps for the layers that are chunks of longer rows (a box copy per 16 rows instead of a bulk copy per row);
+    // best effort: without them the kernel copies row by row
+    bool any = false, ok = true;
+    std::vector<unsigned char> maps((size_t)nlayers * 256, 0);
+    for (int l = 0; l < nlayers && ok; l++) {
+        const Shape& sh = shp[l];
+        if (sh.wpitch == 2560 && sh.spitch == 80) continue;
+        any = true;
+        ok = sh.wpitch % 512 == 0 &&
+             encode_chunk_maps(maps.data() + (size_t)l * 256, maps.data() + (size_t)l * 256 + 128,
+                               reinterpret_cast<const void*>((uintptr_t)tab[4 * l] - (size_t)sh.chunk * 2560),
+                               reinterpret_cast<const void*>((uintptr_t)tab[4 * l + 1] - (size_t)sh.chunk * 80), (uint64_t)sh.rows,
+                               (uint64_t)sh.wpitch, (uint64_t)sh.spitch);
+    }
+    if (any && ok && !e.capturing) {
+        void* dev = nullptr;
+        if (cudaMalloc(&dev, maps.size()) == cudaSuccess &&
+            cudaMemcpy(dev, maps.data(), maps.size(), cudaMemcpyHostToDevice) == cudaSuccess) {
+            e.table_maps[reinterpret_cast<uintptr_t>(dev_table)] = Engine::MapSet{dev, t.serial};
+        } else {
+            cudaGetLastError();
+            if (dev) cudaFree(dev);
+        }
+    }
     return 0;
 }
 

@@ -46,10 +46,13 @@ bool stream_table_ok(const void* table, int nlayers, int rows, int K, int row_ba
                      int npeers, bool whole_y = false, size_t ws_bytes = 0, bool need_x = false);
 
 // true when `table` / `shapes` were filled by fm_stream_table_var for at least `nlayers` layers and are still valid (or
-// checks are off); reports the smallest and largest row count of the layers.  With npeers > 0 the peer offsets must
-// cover every y of the table.
+// checks are off); reports the smallest and largest row count of the layers and the device array of TMA maps for the
+// layers that are chunks of longer rows (two maps of 128 bytes per layer: weights, scales; nullptr when the driver
+// refused one).  With npeers > 0 the peer offsets must cover every y of the table.
 bool stream_var_ok(const void* table, const void* shapes, int nlayers, const void* peer_delta, int npeers, int* min_rows,
-                   int* max_rows);
+                   int* max_rows, const void** chunk_maps);
+bool encode_chunk_maps(void* wmap128, void* smap128, const void* wbase, const void* sbase, uint64_t rows, uint64_t wpitch,
+                       uint64_t spitch);
 
 // Device array of `nlayers` TMA tensor maps (128 bytes each) over the wq entries of a validated layer table, each
 // layer's packed codes seen as [rows][K/2] bytes with a box of 128 bytes x 128 rows and the 128-byte swizzle.  Built by

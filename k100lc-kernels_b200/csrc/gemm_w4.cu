@@ -689,6 +689,28 @@ const KernelEntry* gemm_w4_kernels(int* n) {
     return kGemm;
 }
 
+// Maps for a 5120-k chunk of 16 rows of a packed weight matrix whose rows are longer than the chunk (and of their
+// group scales): the weight map sees a row as pieces of 512 bytes, so that a box of (512 bytes, 5 pieces, 16 rows) lands
+// as 16 contiguous rows of 2560 bytes; the scale map is [rows][spitch bytes] with a box of 80 bytes x 16 rows.  Pieces
+// and bytes past the end of a row read as zero.
+bool encode_chunk_maps(void* wmap128, void* smap128, const void* wbase, const void* sbase, uint64_t rows, uint64_t wpitch,
+                       uint64_t spitch) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc || wpitch % 512 || spitch % 16) return false;
+    const cuuint64_t wd[3] = {128, wpitch / 512, rows};
+    const cuuint64_t ws[2] = {512, wpitch};
+    const cuuint32_t wb[3] = {128, 5, 16}, e3[3] = {1, 1, 1};
+    if (enc(static_cast<CUtensorMap*>(wmap128), CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(wbase), wd, ws, wb, e3,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    const cuuint64_t sd[2] = {spitch / 4, rows};
+    const cuuint64_t ss[1] = {spitch};
+    const cuuint32_t sb[2] = {20, 16}, e2[2] = {1, 1};
+    return enc(static_cast<CUtensorMap*>(smap128), CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(sbase), sd, ss, sb, e2,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 bool encode_bytes_rows_map(void* map128, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes) {
     // (256-byte L2 promotion: the next stage's 128 bytes of a row come along; 1 % over 128 bytes or none)
     return make_map(static_cast<CUtensorMap*>(map128), base, rows, row_bytes, box_bytes,

@@ -50,12 +50,13 @@ struct VarLayer {                      // 64 bytes
     int wbytes, sbytes;                // valid bytes of a row of wq / ws in this chunk (2560 / 80 for a full chunk)
     int accumulate;                    // 0: y = value; 1: y += value
     int row_base;                      // first output index of these rows inside the layer's y
-    int pad;
+    int chunk;                         // which 5120 k of the row this layer is (its wq / ws point at that chunk of row 0)
 };
 
 struct StreamParams {
     const StreamLayer* layers;         // device table, or nullptr: the single layer `one`
     const VarLayer* var;               // per-layer shapes (VAR policies), else nullptr: `rows` and `row_base` below for all
+    const void* chunk_maps;            // VAR: two TMA maps (128 bytes each: weights, scales) per layer that is a chunk of longer rows, or nullptr
     const uint8_t *ae, *ao, *asc, *asu;   // activation-quantiser outputs of all layers (meaning depends on the format)
     int nlayers, rows, K, row_base;
     int npeers;                        // additional receivers of y (0 on one GPU)
@@ -107,6 +108,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity, uint
 // mbarrier.arrive that follows cannot be scheduled ahead of the arithmetic that produced `v`
 // (and with it ahead of the shared-memory loads that arithmetic consumed).
 __device__ __forceinline__ void consumed(float v) { asm volatile("" ::"f"(v) : "memory"); }
+// tiled TMA copies (never multicast) global -> this CTA's shared memory
+__device__ __forceinline__ void tma_g2s_3d(void* dst, const void* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_g2s_2d(void* dst, const void* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
 // 1-D bulk async copy global -> this CTA's shared memory
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -215,6 +225,18 @@ __device__ __forceinline__ void run_producer(const Cta& cta, const typename P::P
                 // rows may be further apart than a chunk is wide, and the last chunk of a row may be short: the rest of
                 // the stage keeps what it held (finite numbers: the ring is cleared at the start), and the token's codes
                 // behind the row's K are zero
+                const bool strided = vl.wpitch != P::ROWB || vl.spitch != P::SCB;
+                if (strided && nr == P::ROWS && p.chunk_maps) {
+                    // a chunk of 16 longer rows: one box copy for the weights (pieces of the rows past their end read
+                    // as zero), one for the scales
+                    const uint8_t* maps = static_cast<const uint8_t*>(p.chunk_maps) + (size_t)l * 256;
+                    mbar_expect_tx(&B->full[s], (uint32_t)(P::ROWS * (P::ROWB + P::SCB)) + P::ACT);
+                    tma_g2s_3d(dst, maps, 0, vl.chunk * 5, row, &B->full[s]);
+                    tma_g2s_2d(dst + P::STAGE_W, maps + 128, vl.chunk * 20, row, &B->full[s]);
+                    P::copy_act(pp, l, dst + P::OFF_ACT, &B->full[s]);
+                    issued = cc + 1;
+                    continue;
+                }
                 mbar_expect_tx(&B->full[s], (uint32_t)(nr * (vl.wbytes + vl.sbytes)) + P::ACT);
                 if (vl.wpitch == P::ROWB && vl.wbytes == P::ROWB) {
                     bulk_g2s(dst, lay.wq + (size_t)row * P::ROWB, (uint32_t)(nr * P::ROWB), &B->full[s]);

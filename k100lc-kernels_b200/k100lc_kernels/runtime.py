@@ -455,7 +455,7 @@ class Runtime:
         for c in range(-(-k // 5120)):
             kc = min(5120, k - 5120 * c)
             out.append((wq + c * 2560, ws + c * 80, 0, y, ae + c * 2560, ao + c * 2560, asc + c * 160, asu + c * 160,
-                        rows, k // 2, (k // 128) * 2, kc // 2, (kc // 128) * 2, 1 if c else 0, row_base, 0))
+                        rows, k // 2, (k // 128) * 2, kc // 2, (kc // 128) * 2, 1 if c else 0, row_base, c))
         return out
 
     def stream_table_var(self, entries) -> tuple[int, int]:
