@@ -1069,7 +1069,8 @@ int launch_w4a8_read_ceiling(const LaunchCtx& c, const uint64_t* a) {
 // w4a8_layers_stream(layers, shapes, nlayers, npeers, peer_delta, status, flags): W4A8, one token, layers of different
 // shapes in one launch.  `layers` / `shapes` are the two device arrays filled by fm_stream_table_var (a layer = 5120 k of
 // a set of rows; longer rows are consecutive layers that add to the same y); npeers, peer_delta, status and flags as for
-// the other stream kernels.  Every CTA takes an equal share of the rows of every layer.
+// the other stream kernels (flags: one counter per table entry, each reaching min(SM count, rows of the largest layer)).
+// Every CTA takes an equal share of the rows of every layer.
 int launch_w4a8_layers_stream(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = "w4a8_layers_stream";
     PlainParams pp = {};
@@ -1096,7 +1097,10 @@ int launch_w4a8_layers_stream(const LaunchCtx& c, const uint64_t* a) {
                "overwritten, or a buffer they point into was freed since), or the peer offsets do not come from fm_stream_peers "
                "for its outputs", (const void*)p.layers, (const void*)p.var, p.nlayers);
     p.rows = max_rows;
-    const int grid = c.sm_count < min_rows ? c.sm_count : min_rows;
+    // one CTA per SM unless even the largest layer has fewer rows; a CTA without rows in a small layer still takes part
+    // in the layer's hand-overs (and counts in its completion counter)
+    const int grid = c.sm_count < max_rows ? c.sm_count : max_rows;
+    (void)min_rows;
     FM_REQUIRE((max_rows + grid - 1) / grid <= kOutCap, kn,
                "a CTA would own %d rows of the largest layer (%d rows on %d CTAs); the output tile holds %d", (max_rows + grid - 1) / grid,
                max_rows, grid, kOutCap);

@@ -592,7 +592,7 @@ def test_layers_of_different_shapes_in_one_launch(rt):
         rt.launch("w4a8_layers_stream", 1, 1, [table, shp, len(entries), 1, deltas, status, flags])
         dev = b.get(buf, ytot + nchunks)
         assert int(b.get(status, 1, np.int32)[0]) == 0
-        ctas = min(sms, min(n for n, _ in shapes))
+        ctas = min(sms, max(n for n, _ in shapes))
         assert (dev[ytot:].view(np.uint32) == ctas).all() and (host[ytot:].view(np.uint32) == ctas).all()
         assert np.array_equal(host[:ytot].view(np.uint32), dev[:ytot].view(np.uint32))
         for (n, k), L, o, (wq, ws, ae, ao, asc, asu) in zip(shapes, layers, outs, acts):
