@@ -955,6 +955,15 @@ int fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_
                        sh.wpitch, sh.wbytes, sh.spitch, sh.sbytes, sh.accumulate, sh.row_base);
             return FM_EREJECT;
         }
+        if (sh.accumulate) {                             // a later chunk continues the entry in front of it
+            const Shape* pv = l ? &shp[l - 1] : nullptr;
+            if (!pv || host_layers[(size_t)(l - 1) * 16 + 3] != h[3] || pv->rows != sh.rows || pv->row_base != sh.row_base ||
+                pv->chunk + 1 != sh.chunk) {
+                set_errorf("fm_stream_table_var: layer %d adds to y but the entry in front of it is not the chunk before it of the "
+                           "same rows and the same y", l);
+                return FM_EREJECT;
+            }
+        }
         const void* ptrs[7] = {(const void*)(uintptr_t)h[0], (const void*)(uintptr_t)h[1], (const void*)(uintptr_t)h[3],
                                (const void*)(uintptr_t)h[4], (const void*)(uintptr_t)h[5], (const void*)(uintptr_t)h[6],
                                (const void*)(uintptr_t)h[7]};

@@ -608,6 +608,8 @@ def test_layers_of_different_shapes_in_one_launch(rt):
         bad[11] = 2560 + 16
         with pytest.raises(RuntimeError, match="not a shape this kernel takes"):
             rt.stream_table_var([tuple(bad)])
+        with pytest.raises(RuntimeError, match="adds to y"):            # a later chunk without the chunk before it
+            rt.stream_table_var([entries[2]])
         with pytest.raises(RuntimeError, match="rc=-4"):
             rt.launch("w4a8_layers_stream", 1, 1, [table, shp + 64, len(entries) - 1, 0, 0, status, 0])
         rt.free(table)
