@@ -1231,6 +1231,51 @@ int launch_nvfp4_stream(const LaunchCtx& c, const uint64_t* a) {
     }
 }
 
+// nvfp4_decode_stream_m(common..., qa, qb, sc, gscale, M, ystride, flags): M = 2..4 tokens per layer on the tcgen05
+// consumer (a token is 12 more columns of B; the weights are streamed once).  The code arrays hold [nlayers * M] tokens
+// (one 2-D nvfp4_quant_act launch with grid y = nlayers * M over x[nlayers][M][K]); y of a layer is token-major,
+// y[token * ystride + row_base + row]; the table must have been validated with row_base + (M - 1) * ystride as its
+// row_base argument, as for w4a8_decode_stream_m.  nvfp4_decode_stream_m_iacc(..., flags, iacc): iacc int32
+// [nlayers][M][rows][K/16].  There is no other consumer behind this entry: -4 when the table has no tensor maps.
+template <bool DUMP>
+int launch_nvfp4_stream_m(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = DUMP ? "nvfp4_decode_stream_m_iacc" : "nvfp4_decode_stream_m";
+    Nvfp4Params pp = {};
+    StreamParams& p = pp.s;
+    const int M = arg_i32(a[12]);
+    FM_REQUIRE(M >= 2 && M <= 4, kn, "M=%d: this kernel takes 2..4 tokens (nvfp4_decode_stream takes one)", M);
+    const int rc = parse_common(kn, c, a, a[14], p, M);
+    if (rc) return rc < 0 ? rc : FM_OK;
+    p.ae = arg_ptr<const uint8_t>(a[8]);
+    p.ao = arg_ptr<const uint8_t>(a[9]);
+    p.asc = arg_ptr<const uint8_t>(a[10]);
+    pp.gscale = arg_f32(a[11]);
+    p.ystride = arg_i32(a[13]);
+    FM_REQUIRE(p.ystride >= p.row_base + p.rows && (long long)(p.M - 1) * p.ystride + p.row_base < (1LL << 31), kn,
+               "ystride=%d must be at least row_base + rows = %d", p.ystride, p.row_base + p.rows);
+    const int vbase = p.row_base + (p.M - 1) * p.ystride;
+    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, vbase, p.peer_delta, p.npeers, true,
+                               (size_t)p.rows * (p.K / 16)), kn,
+               "the layer table at %p was not filled by fm_stream_table for nlayers=%d rows=%d K=%d and the row_base argument "
+               "row_base + (M - 1) * ystride = %d (or was overwritten, or a buffer it points into was freed since), a ws entry has "
+               "fewer than rows*K/16 bytes behind it, or the peer offsets do not come from fm_stream_peers for its outputs",
+               (const void*)p.layers, p.nlayers, p.rows, p.K, vbase);
+    FM_REQUIRE(aligned(p.ae, 16) && aligned(p.ao, 16) && aligned(p.asc, 16), kn, "the activation code arrays must be 16-byte aligned");
+    const size_t tokens = (size_t)p.nlayers * p.M;
+    FM_RANGE(p.ae, tokens * (p.K / 2), kn, "qa");
+    FM_RANGE(p.ao, tokens * (p.K / 2), kn, "qb");
+    FM_RANGE(p.asc, tokens * (p.K / 16) * 4, kn, "sc");
+    if (DUMP) {
+        p.iacc = arg_ptr<int>(a[15]);
+        FM_REQUIRE(aligned(p.iacc, 4), kn, "misaligned accumulator dump");
+        FM_RANGE(p.iacc, tokens * p.rows * (p.K / 16) * 4, kn, "iacc");
+    }
+    const int rc3 = nvfp4_tc_stream(kn, c, p, pp.gscale, DUMP);
+    FM_REQUIRE(rc3 <= 0, kn, "the tcgen05 consumer cannot take this launch (the table has no tensor maps, K is not a multiple of "
+               "1024, or the workspace is too small)");
+    return rc3;
+}
+
 // w4a16_decode_stream(common..., flags): the table's x entries (fp32 activations [K] per layer) are read here —
 // fm_stream_table must have seen a valid x for every layer —, wq are compressed-tensors codes, ws bf16 scales.
 // Launches the split kernel (grid y = layer) into the engine workspace (30 720 bytes per layer), then the stream kernel.
@@ -1288,6 +1333,8 @@ const KernelEntry kStream[] = {
     {"nvfp4_decode_stream_iacc", 14, launch_nvfp4_stream<true>, "piiiiipppppfpp"},
     {"stream_flag_wait", 5, launch_flag_wait, "piipi"},
     {"w4a8_stream_read_ceiling", 13, launch_w4a8_read_ceiling, "piiiiippppppp"},
+    {"nvfp4_decode_stream_m", 15, launch_nvfp4_stream_m<false>, "piiiiipppppfiip"},
+    {"nvfp4_decode_stream_m_iacc", 16, launch_nvfp4_stream_m<true>, "piiiiipppppfiipp"},
     {"w4a8_layers_stream", 7, launch_w4a8_layers_stream, "ppiippp"},
 };
 

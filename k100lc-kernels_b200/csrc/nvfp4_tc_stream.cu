@@ -52,16 +52,9 @@ using stream::StreamParams;
 
 constexpr int TM = 128;                       // rows per tile = TMEM lanes
 constexpr int SK = 256;                       // k per stage
-constexpr int NCOL = 16;                      // columns of one MMA: 3 digits x 4 quarters of its K = 64, 4 unused
-constexpr int UCOL = 12;                      // columns of B that carry data
-constexpr int STAGES = 12;
-constexpr int NACC = 6;                       // 64-column slices of tensor memory
-constexpr int ACC_COLS = 4 * NCOL;            // four MMAs per stage
 constexpr int SF_COL = 448;                   // 16 columns of scale factors, all 1
 constexpr int ASG_SLOTS = 24;                 // > STAGES + NACC stages between a slot's write and its reuse
 constexpr int A_BYTES = TM * SK / 2;          // one box of 128 rows x 128 bytes, packed codes
-constexpr int B_BYTES = NCOL * 128;           // 16 columns x 128 bytes
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 // Every role is a chain of barrier waits, and a wait costs a few hundred cycles even when the barrier is ready: one
 // thread per role would hold the stream to its own pace.  So the stages go round NCOPY copy lanes and NMMA MMA lanes
 // (one lane of a warp each), and round two epilogue warps per TMEM lane quarter.
@@ -69,9 +62,31 @@ constexpr int NCOPY = 2, NMMA = 4;
 constexpr int EPI_WARP0 = NCOPY + NMMA;        // a multiple of 2; warp % 4 is the TMEM lane quarter a warp may read
 constexpr int kThreads = (EPI_WARP0 + 8) * 32;
 constexpr int kSpin = 1 << 20;
-constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * STAGE_BYTES + ASG_SLOTS * 64 + 2 * TM * 4 + 1024;
-static_assert(kSmemBytes <= 227 * 1024, "shared memory");
-static_assert(ASG_SLOTS > STAGES + NACC, "slot reuse distance");
+constexpr int kMaxStages = 12, kMaxAcc = 6;
+
+// What depends on the number of tokens M (1..4): a token is 12 columns of B (3 digits x 4 quarters of an MMA's K = 64).
+template <int M>
+struct Geo {
+    static constexpr int UCOL = 12 * M;                       // columns of B that carry data
+    static constexpr int NCOL = (UCOL + 15) / 16 * 16;        // columns of one MMA
+    static constexpr int B_BYTES = NCOL * 128;                // NCOL columns x 128 bytes
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int ACC_COLS = 4 * NCOL;                 // four MMAs per stage
+    static constexpr int NACC = M == 1 ? 6 : 2;               // slices of tensor memory (even: a slice belongs to the even or the odd stages)
+    static constexpr int STAGES = M == 1 ? 12 : M == 2 ? 10 : 8;
+    // MMA lanes in use.  The barrier waits go by phase parity, which is only unambiguous while a waiter is never two
+    // phases behind its barrier: a lane that takes every NMMA-th stage needs NMMA <= NACC (the slice it waits for was
+    // released one phase after the one it saw last) and STAGES a multiple of NMMA and NCOPY (a slot's stages stay
+    // with one lane).
+    static constexpr int NMMA_USED = M == 1 ? NMMA : 2;
+    static_assert(NMMA_USED <= NACC && NMMA_USED <= NMMA && STAGES % NMMA_USED == 0 && STAGES % NCOPY == 0, "lane / ring sizes");
+    static constexpr int ASG = 16 * M;                        // scale products of a stage
+    static constexpr int kImgBytes = UCOL * 128 + ASG * 4;    // B image of a stage, then its scale products
+    static constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * STAGE_BYTES + ASG_SLOTS * ASG * 4 + 2 * M * TM * 4 + 1024;
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory");
+    static_assert(NACC * ACC_COLS <= SF_COL, "tensor memory");
+    static_assert(ASG_SLOTS > STAGES + NACC && STAGES <= kMaxStages && NACC <= kMaxAcc, "rings");
+};
 
 struct TcParams {
     StreamParams s;
@@ -79,11 +94,10 @@ struct TcParams {
     const uint8_t* bimg;                      // [nlayers][K/256][kImgBytes]: B image + scale products of a stage
     int tiles_per_layer, ntiles;
 };
-constexpr int kImgBytes = UCOL * 128 + 64;    // one token: columns 0..11, then 16 floats
 
 struct __align__(16) Control {
-    uint64_t full[STAGES], empty[STAGES];
-    uint64_t acc_full[NACC], acc_empty[NACC];
+    uint64_t full[kMaxStages], empty[kMaxStages];
+    uint64_t acc_full[kMaxAcc], acc_empty[kMaxAcc];
     uint64_t drain[NMMA];
     uint64_t stored;                          // the four storing warps have stored their rows of a tile (completion counters)
     uint64_t ysum[4][2];                      // per lane quarter and buffer: the odd-stage warp has put its partial sums into ytmp
@@ -102,10 +116,10 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* b, uint32_t parity, Cont
     return false;
 }
 
-// kind::mxf4 (block-scaled): A = B = E2M1 (format 1), both K-major, N = 16, scale factors UE8M0 (bit 23),
+// kind::mxf4 (block-scaled): A = B = E2M1 (format 1), both K-major, N = ncol, scale factors UE8M0 (bit 23),
 // M = 128, K = 64 (bit 31 clear), scale-factor byte ids 0
-__device__ __forceinline__ uint32_t instr_desc() {
-    return (1u << 7) | (1u << 10) | ((uint32_t)(NCOL >> 3) << 17) | (1u << 23) | ((uint32_t)(TM >> 4) << 24);
+__device__ __forceinline__ uint32_t instr_desc(int ncol) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(ncol >> 3) << 17) | (1u << 23) | ((uint32_t)(TM >> 4) << 24);
 }
 __device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb) {
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, 0, 0;\n"
@@ -132,25 +146,27 @@ __device__ __forceinline__ uint32_t digit_code(int q, int which) {
     return (a == 3 ? 5u : 2u * a) | (d < 0 ? 8u : 0u);
 }
 
-// B image of every stage of every layer for one token.  grid (K/256, nlayers), 112 threads: thread i < 96 writes one
-// 16-byte piece of the image, threads 96..111 one scale product each.
-//   image [column n = digit*4 + quarter, 0..11][128 bytes = 256 codes, 16-byte pieces XOR-swizzled by n & 7],
-//   then asg[16] = asc * gscale
-__global__ void __launch_bounds__(112)
+// B image of every stage of every layer.  grid (K/256, nlayers), 112 * M threads: thread i < 96 * M writes one 16-byte
+// piece of the image, the next 16 * M one scale product each.
+//   image [column n = token*12 + digit*4 + quarter][128 bytes = 256 codes, 16-byte pieces XOR-swizzled by n & 7],
+//   then asg[token][16] = asc * gscale.  The codes of layer l, token k are rows l*M + k of qe / qo / asc.
+template <int M>
+__global__ void __launch_bounds__(112 * M)
 nvfp4_bimg_kernel(const int8_t* __restrict__ qe, const int8_t* __restrict__ qo, const float* __restrict__ asc, float gscale,
                   uint8_t* __restrict__ bimg, int K) {
+    using G = Geo<M>;
     pdl_wait();
     const int s = blockIdx.x, l = blockIdx.y, nst = K / SK, t = threadIdx.x;
-    uint8_t* img = bimg + ((size_t)l * nst + s) * kImgBytes;
-    if (t < 96) {
+    uint8_t* img = bimg + ((size_t)l * nst + s) * G::kImgBytes;
+    if (t < 8 * G::UCOL) {
         const int n = t >> 3, phys = t & 7;
         const int c16 = phys ^ (n & 7);                    // logical 16-byte piece = 32 consecutive k = two quarters
-        const int dg = n >> 2, qt = n & 3;
+        const int tok = n / 12, dg = (n % 12) >> 2, qt = n & 3;
         uint32_t out[4] = {0u, 0u, 0u, 0u};
         if ((qt >> 1) == (c16 & 1)) {
             const int h = qt & 1;                          // which half of the piece is this column's quarter
             const int k0 = s * SK + c16 * 32 + 16 * h;     // 16 codes from here: bytes 8h..8h+7 of the piece
-            const size_t o = (size_t)l * (K / 2) + k0 / 2;
+            const size_t o = ((size_t)l * M + tok) * (K / 2) + k0 / 2;
             const uint2 e = *reinterpret_cast<const uint2*>(qe + o), od = *reinterpret_cast<const uint2*>(qo + o);
             const uint32_t ew[2] = {e.x, e.y}, ow[2] = {od.x, od.y};
 #pragma unroll
@@ -162,22 +178,25 @@ nvfp4_bimg_kernel(const int8_t* __restrict__ qe, const int8_t* __restrict__ qo, 
         }
         *reinterpret_cast<uint4*>(img + n * 128 + phys * 16) = make_uint4(out[0], out[1], out[2], out[3]);
     } else {
-        const int b = t - 96;
-        reinterpret_cast<float*>(img + UCOL * 128)[b] = asc[(size_t)l * (K / 16) + s * 16 + b] * gscale;
+        const int i = t - 8 * G::UCOL, tok = i >> 4, b = i & 15;
+        reinterpret_cast<float*>(img + G::UCOL * 128)[i] = asc[((size_t)l * M + tok) * (K / 16) + s * 16 + b] * gscale;
     }
     pdl_launch_dependents();
 }
 
-template <bool DUMP>
+template <int M, bool DUMP>
 __global__ void __launch_bounds__(kThreads, 1)
 nvfp4_tc_stream_kernel(const TcParams pp) {
+    using Ge = Geo<M>;
+    constexpr int STAGES = Ge::STAGES, STAGE_BYTES = Ge::STAGE_BYTES, B_BYTES = Ge::B_BYTES, NCOL = Ge::NCOL, UCOL = Ge::UCOL;
+    constexpr int ACC_COLS = Ge::ACC_COLS, NACC = Ge::NACC, ASG = Ge::ASG, kImgBytes = Ge::kImgBytes;
     const StreamParams& p = pp.s;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     Control* ctl = reinterpret_cast<Control*>(smem);
     uint8_t* stages = smem + 1024;
-    float* asg_ring = reinterpret_cast<float*>(stages + STAGES * STAGE_BYTES);     // [ASG_SLOTS][16]
-    float* ytmp = asg_ring + ASG_SLOTS * 16;                                       // [2][128] partial sums of the odd stages
+    float* asg_ring = reinterpret_cast<float*>(stages + STAGES * STAGE_BYTES);     // [ASG_SLOTS][M][16]
+    float* ytmp = asg_ring + ASG_SLOTS * ASG;                                      // [2][M][128] partial sums of the odd stages
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nst = p.K / SK;
     const int G = (int)gridDim.x;
@@ -203,7 +222,7 @@ nvfp4_tc_stream_kernel(const TcParams pp) {
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // columns 12..15 of B are never written by a copy: they stay zero for the whole kernel
+    // the columns of B behind the tokens' 12 each are never written by a copy: they stay zero for the whole kernel
     for (int i = threadIdx.x; i < STAGES * (B_BYTES / 16); i += kThreads) {
         const int s = i / (B_BYTES / 16), o = i % (B_BYTES / 16);
         *reinterpret_cast<uint4*>(stages + s * STAGE_BYTES + A_BYTES + o * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -245,7 +264,7 @@ nvfp4_tc_stream_kernel(const TcParams pp) {
                     tma_2d(st, map, s * (SK / 2), r0, &ctl->full[slot]);
                     const uint8_t* im = img + (size_t)s * kImgBytes;
                     bulk_g2s(st + A_BYTES, im, UCOL * 128, &ctl->full[slot]);
-                    bulk_g2s(asg_ring + (it % ASG_SLOTS) * 16, im + UCOL * 128, 64, &ctl->full[slot]);
+                    bulk_g2s(asg_ring + (it % ASG_SLOTS) * ASG, im + UCOL * 128, ASG * 4, &ctl->full[slot]);
                     issued = it;
                 }
                 if (!ok) break;
@@ -260,10 +279,11 @@ nvfp4_tc_stream_kernel(const TcParams pp) {
         // ================================================================ MMA lanes (stage it belongs to lane it % NMMA)
         if (lane == 0) {
             const int m = warp - NCOPY;
-            const uint32_t idesc = instr_desc();
+            constexpr int NL = Ge::NMMA_USED;              // lanes m >= NL have no stages
+            const uint32_t idesc = instr_desc(NCOL);
             const uint64_t adesc0 = smem_desc_sw128(smem_u32(stages));
             const uint64_t bdesc0 = smem_desc_sw128(smem_u32(stages) + A_BYTES);
-            for (int it = m; it < total; it += NMMA) {
+            for (int it = m; it < total && m < NL; it += NL) {
                 const int slot = it % STAGES, a = it % NACC;
                 if (it >= NACC && !wait_or_abort(&ctl->acc_empty[a], ((it / NACC) & 1) ^ 1, ctl, status, 13)) break;
                 if (!wait_or_abort(&ctl->full[slot], (it / STAGES) & 1, ctl, status, 12)) break;
@@ -315,7 +335,9 @@ nvfp4_tc_stream_kernel(const TcParams pp) {
             const bool live = row < p.rows;
             const StreamLayer L = p.layers[l];
             const uint8_t* wsn = t + G < pp.ntiles ? scale_row(t + G) : wsr;      // the row of the next tile
-            float y = 0.f;
+            float y[M];
+#pragma unroll
+            for (int k = 0; k < M; k++) y[k] = 0.f;
             bool ok = true;
             for (int s0 = ph; s0 < nst && ok; s0 += 2 * PF) {
 #pragma unroll
@@ -326,33 +348,66 @@ nvfp4_tc_stream_kernel(const TcParams pp) {
                     if (!wait_or_abort(&ctl->acc_full[a], (it / NACC) & 1, ctl, status, 14)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t ta = tmem_base + ((uint32_t)(lq * 32) << 16) + a * ACC_COLS;
-                    uint32_t r[4][16];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) tmem_ld16(ta + j * NCOL, r[j]);
-                    const float4* ag = reinterpret_cast<const float4*>(asg_ring + (it % ASG_SLOTS) * 16);
-                    float asg[16];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const float4 v = ag[j];
-                        asg[4 * j] = v.x; asg[4 * j + 1] = v.y; asg[4 * j + 2] = v.z; asg[4 * j + 3] = v.w;
-                    }
-                    tmem_ld_wait64(r);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);        // the slice is in registers
+                    const float* ag = asg_ring + (it % ASG_SLOTS) * ASG;
                     const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
+                    if constexpr (M == 1) {
+                        uint32_t r[4][16];
 #pragma unroll
-                    for (int j = 0; j < 4; j++)
+                        for (int j = 0; j < 4; j++) tmem_ld16(ta + j * NCOL, r[j]);
+                        float asg[16];
 #pragma unroll
-                        for (int qt = 0; qt < 4; qt++) {
-                            const int b = 4 * j + qt;
-                            // block sum: D0 + 7 * D1 + 49 * D2 (= I / 2), exact
-                            const float tsum = fmaf(__uint_as_float(r[j][8 + qt]), 49.f,
-                                                    fmaf(__uint_as_float(r[j][4 + qt]), 7.f, __uint_as_float(r[j][qt])));
-                            const float sw = e4m3_raw(scw[j], qt) * 0x1p120f;
-                            y = fmaf(tsum, sw * asg[b], y);
-                            if (DUMP && live) p.iacc[((size_t)l * p.rows + row) * nb + s * 16 + b] = (int)(2.f * tsum);
+                        for (int j = 0; j < 4; j++) {
+                            const float4 v = reinterpret_cast<const float4*>(ag)[j];
+                            asg[4 * j] = v.x; asg[4 * j + 1] = v.y; asg[4 * j + 2] = v.z; asg[4 * j + 3] = v.w;
                         }
+                        tmem_ld_wait64(r);
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);        // the slice is in registers
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+#pragma unroll
+                            for (int qt = 0; qt < 4; qt++) {
+                                const int b = 4 * j + qt;
+                                // block sum: D0 + 7 * D1 + 49 * D2 (= I / 2), exact
+                                const float tsum = fmaf(__uint_as_float(r[j][8 + qt]), 49.f,
+                                                        fmaf(__uint_as_float(r[j][4 + qt]), 7.f, __uint_as_float(r[j][qt])));
+                                const float sw = e4m3_raw(scw[j], qt) * 0x1p120f;
+                                y[0] = fmaf(tsum, sw * asg[b], y[0]);
+                                if (DUMP && live) p.iacc[((size_t)l * p.rows + row) * nb + s * 16 + b] = (int)(2.f * tsum);
+                            }
+                    } else {
+                        // several tokens: the slice is taken one MMA (64 k, four blocks, NCOL columns) at a time; a token's
+                        // 12 digit sums are registers 12*token .. 12*token + 11 of it
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint32_t r[NCOL];
+#pragma unroll
+                            for (int v = 0; v < NCOL / 16; v++) tmem_ld16(ta + j * NCOL + v * 16, r + v * 16);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int v = 0; v < UCOL; v++) asm volatile("" : "+r"(r[v]) :: "memory");   // no use ahead of the wait
+                            if (j == 3) {
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);    // the last of the slice is in registers
+                            }
+                            float sw[4];
+#pragma unroll
+                            for (int qt = 0; qt < 4; qt++) sw[qt] = e4m3_raw(scw[j], qt) * 0x1p120f;
+#pragma unroll
+                            for (int k = 0; k < M; k++)
+#pragma unroll
+                                for (int qt = 0; qt < 4; qt++) {
+                                    const int b = 4 * j + qt;
+                                    const float tsum = fmaf(__uint_as_float(r[12 * k + 8 + qt]), 49.f,
+                                                            fmaf(__uint_as_float(r[12 * k + 4 + qt]), 7.f, __uint_as_float(r[12 * k + qt])));
+                                    y[k] = fmaf(tsum, sw[qt] * ag[k * 16 + b], y[k]);
+                                    if (DUMP && live)
+                                        p.iacc[(((size_t)l * M + k) * p.rows + row) * nb + s * 16 + b] = (int)(2.f * tsum);
+                                }
+                        }
+                    }
                 }
             }
             wsr = wsn;
@@ -365,22 +420,27 @@ nvfp4_tc_stream_kernel(const TcParams pp) {
             const uint32_t par = (ntile >> 1) & 1;
             if (ph == 1) {
                 if (ntile >= 2 && !wait_or_abort(&ctl->yfree[lq][buf], par ^ 1, ctl, status, 17)) break;
-                ytmp[buf * TM + trow] = y;
+#pragma unroll
+                for (int k = 0; k < M; k++) ytmp[(buf * M + k) * TM + trow] = y[k];
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->ysum[lq][buf]);
                 continue;
             }
             if (!wait_or_abort(&ctl->ysum[lq][buf], par, ctl, status, 16)) break;
-            y += ytmp[buf * TM + trow];
+#pragma unroll
+            for (int k = 0; k < M; k++) y[k] += ytmp[(buf * M + k) * TM + trow];
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->yfree[lq][buf]);
             if (live) {
-                float* dst = L.y + p.row_base + row;
-                *dst = y;
 #pragma unroll
-                for (int q = 0; q < 8; q++)
-                    if (q < p.npeers)
-                        *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = y;
+                for (int k = 0; k < M; k++) {                              // y of a layer is token-major
+                    float* dst = L.y + (size_t)k * p.ystride + p.row_base + row;
+                    *dst = y[k];
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        if (q < p.npeers)
+                            *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = y[k];
+                }
             }
             if (p.flags) {
                 // every epilogue thread has stored its row: counters of the layers this CTA is now done with
@@ -426,15 +486,13 @@ nvfp4_tc_stream_kernel(const TcParams pp) {
 
 }  // namespace
 
-// The launcher behind nvfp4_decode_stream: prepares the B images of all layers in the engine workspace, then the stream
-// kernel.  Returns FM_OK after enqueueing both, a negative code after a rejection, or 1 when this path cannot take the
-// launch (no tensor maps for the table, workspace cannot grow here) and the caller should use another consumer.
-int nvfp4_tc_stream(const char* kn, const LaunchCtx& c, const stream::StreamParams& sp, float gscale, bool dump) {
+namespace {
+template <int M>
+int run_tc(const char* kn, const LaunchCtx& c, const stream::StreamParams& sp, float gscale, bool dump, const void* maps) {
+    using G = Geo<M>;
     const int nst = sp.K / SK;
-    if (sp.K % (4 * SK) || nst <= NACC || sp.M != 1 || !sp.layers) return 1;      // the epilogue unrolls the stages by four
-    const void* maps = stream_table_maps(sp.layers, sp.nlayers, sp.rows, sp.K);
-    if (!maps) return 1;
-    uint8_t* bimg = static_cast<uint8_t*>(engine_scratch((size_t)sp.nlayers * nst * kImgBytes));
+    if (nst <= G::NACC) return 1;
+    uint8_t* bimg = static_cast<uint8_t*>(engine_scratch((size_t)sp.nlayers * nst * G::kImgBytes));
     if (!bimg) return 1;
     TcParams pp = {};
     pp.s = sp;
@@ -442,21 +500,38 @@ int nvfp4_tc_stream(const char* kn, const LaunchCtx& c, const stream::StreamPara
     pp.bimg = bimg;
     pp.tiles_per_layer = (sp.rows + TM - 1) / TM;
     pp.ntiles = pp.tiles_per_layer * sp.nlayers;
-    auto kern = dump ? nvfp4_tc_stream_kernel<true> : nvfp4_tc_stream_kernel<false>;
+    auto kern = dump ? nvfp4_tc_stream_kernel<M, true> : nvfp4_tc_stream_kernel<M, false>;
     static bool configured[2] = {false, false};
     if (!configured[dump]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::kSmemBytes);
         if (e != cudaSuccess) return cuda_fail(kn, e);
         configured[dump] = true;
     }
-    cudaError_t e = launch_kernel(nvfp4_bimg_kernel, dim3(nst, sp.nlayers), dim3(112), 0, c.stream, pdl_enabled(),
+    cudaError_t e = launch_kernel(nvfp4_bimg_kernel<M>, dim3(nst, sp.nlayers), dim3(112 * M), 0, c.stream, pdl_enabled(),
                                   reinterpret_cast<const int8_t*>(sp.ae), reinterpret_cast<const int8_t*>(sp.ao),
                                   reinterpret_cast<const float*>(sp.asc), gscale, bimg, sp.K);
     if (e != cudaSuccess) return cuda_fail(kn, e);
     after_launch(kn);
     const int grid = c.sm_count < sp.rows ? c.sm_count : sp.rows;     // the CTA count the completion counters promise
-    e = launch_kernel(kern, dim3(grid), dim3(kThreads), kSmemBytes, c.stream, pdl_enabled(), pp);
+    e = launch_kernel(kern, dim3(grid), dim3(kThreads), G::kSmemBytes, c.stream, pdl_enabled(), pp);
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+}  // namespace
+
+// The launcher behind nvfp4_decode_stream (sp.M = 1) and nvfp4_decode_stream_m (2..4 tokens per layer): prepares the B
+// images of all layers in the engine workspace, then the stream kernel.  Returns FM_OK after enqueueing both, a negative
+// code after a rejection, or 1 when this path cannot take the launch (no tensor maps for the table, workspace cannot
+// grow here) and the caller should use another consumer.
+int nvfp4_tc_stream(const char* kn, const LaunchCtx& c, const stream::StreamParams& sp, float gscale, bool dump) {
+    if (sp.K % (4 * SK) || sp.M < 1 || sp.M > 4 || !sp.layers) return 1;      // the epilogue unrolls the stages by four
+    const void* maps = stream_table_maps(sp.layers, sp.nlayers, sp.rows, sp.K);
+    if (!maps) return 1;
+    switch (sp.M) {
+        case 1: return run_tc<1>(kn, c, sp, gscale, dump, maps);
+        case 2: return run_tc<2>(kn, c, sp, gscale, dump, maps);
+        case 3: return run_tc<3>(kn, c, sp, gscale, dump, maps);
+        default: return run_tc<4>(kn, c, sp, gscale, dump, maps);
+    }
 }
 
 }  // namespace fm

@@ -557,6 +557,46 @@ def test_nvfp4_tcgen05_stream_tile_edges(rt, monkeypatch, rows, nl):
         assert np.isnan(got[i, :3]).all() and np.isnan(got[i, 3 + rows:]).all()
 
 
+@pytest.mark.parametrize("m,rows,nl,row_base", [(2, 300, 3, 0), (3, 129, 2, 5), (4, 1000, 2, 0), (4, 17408, 2, 0)])
+def test_nvfp4_stream_several_tokens(rt, m, rows, nl, row_base):
+    """nvfp4_decode_stream_m: 2..4 tokens per layer on the tcgen05 consumer (12 columns of B per token).  The int32 of
+    every (token, row, 16-block) bit for bit, y (token-major) within 1e-5, a pinned host receiver with the same bits."""
+    ystride = row_base + rows + 8
+    layers = [synth.nvfp4_layer(rows, K, m, seed=2100 + 10 * m + i) for i in range(nl)]
+    gscale = float(layers[0]["gscale"])
+    host = rt.pinned((nl, m, ystride), np.float32)
+    host[:] = np.nan
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"] for L in layers]))                       # [nl][m][K]
+        qa, qb = b.zeros(nl * m * K // 2, np.int8), b.zeros(nl * m * K // 2, np.int8)
+        sc = b.zeros(nl * m * K // 16)
+        y = b.zeros(nl * m * ystride, np.float32, np.nan)
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), x + i * m * K * 4, y + i * m * ystride * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, row_base + (m - 1) * ystride)
+        deltas = rt.stream_peers([host.ctypes.data], y, nl * m * ystride * 4)
+        status = b.zeros(1, np.int32)
+        rt.launch2d("nvfp4_quant_act", K // 16, nl * m, 64, 1, [x, qa, qb, sc, nl * m, K])
+        pi = b.zeros(nl * m * rows * (K // 16), np.int32, -7)
+        rt.launch("nvfp4_decode_stream_m_iacc", 1, 1, [table, nl, rows, K, row_base, 0, 0, status, qa, qb, sc, gscale, m, ystride, 0, pi])
+        acc = b.get(pi, nl * m * rows * (K // 16), np.int32).reshape(nl, m, rows, -1)
+        rt.memset(y, 0xFF, nl * m * ystride * 4)
+        rt.launch("nvfp4_decode_stream_m", 1, 1, [table, nl, rows, K, row_base, 1, deltas, status, qa, qb, sc, gscale, m, ystride, 0])
+        dev = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        with pytest.raises(RuntimeError, match="rc=-4"):                    # one token belongs to nvfp4_decode_stream
+            rt.launch("nvfp4_decode_stream_m", 1, 1, [table, nl, rows, K, row_base, 0, 0, status, qa, qb, sc, gscale, 1, ystride, 0])
+        rt.free(table)
+        rt.free(deltas)
+    sl = slice(row_base, row_base + rows)
+    assert np.array_equal(host[:, :, sl].view(np.uint32), dev[:, :, sl].view(np.uint32))
+    for i, L in enumerate(layers):
+        q = O.nvfp4_quant_act(L["x"])
+        ref = O.nvfp4_gemv(L["wq"], L["ws"], q["q"], q["scale"], gscale)
+        assert np.array_equal(acc[i], ref["acc"])
+        assert O.rel_err(dev[i, :, sl], ref["y"]) < REL
+    rt.free_pinned(host)
+
+
 def test_layers_of_different_shapes_in_one_launch(rt):
     """w4a8_layers_stream: weight matrices of different (rows, K) in one launch — K = 5120, 6144 (a full and a 1024-k
     chunk) and 17408 (three full chunks and one of 2048 k), row counts from a few to thousands, a pinned host receiver
