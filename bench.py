@@ -444,6 +444,21 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         out["w4a8_m4_stream"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
         for ptr in (tab_m, aem, aom, scm, sum_):
             rt.free(ptr)
+    # the same for NVFP4: four tokens per layer on the tcgen05 consumer (12 columns of B per token)
+    nlm = min(nv_layers, st.layers) // mt
+    if nlm > 0 and rt.has("nvfp4_decode_stream_m"):
+        tab_m = rt.stream_table([(st.wq_l(l), nvs + l * rows * (K // 16), st.x + l * mt * K * 4, st.y + l * mt * N * 4)
+                                 for l in range(nlm)], rows, K, (mt - 1) * N)
+        qam, qbm, scm = rt.alloc(nlm * mt * K // 2), rt.alloc(nlm * mt * K // 2), rt.alloc(nlm * mt * (K // 16) * 4)
+        rt.graph_begin()
+        rt.launch2d("nvfp4_quant_act", K // 16, nlm * mt, 64, 1, [st.x, qam, qbm, scm, nlm * mt, K])
+        rt.launch("nvfp4_decode_stream_m", 1, 1, [tab_m, nlm, rows, K, 0, 0, 0, status, qam, qbm, scm, 0.05, mt, N, 0])
+        g = rt.graph_end()
+        us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nlm
+        rt.graph_free(g)
+        out["nvfp4_m4_stream"] = {"us_per_layer": round(us, 3), "gb_per_s": round(NVFP4_LAYER_BYTES * frac / us / 1e3, 1)}
+        for ptr in (tab_m, qam, qbm, scm):
+            rt.free(ptr)
     if int(rt.download(status, 1, np.int32)[0]) != 0:
         raise RuntimeError("a bounded wait ran out in a stream kernel")
     for p in (aq, asc4, qa, qb, sc16, nvs, table, status, ae, ao, sc8, su8, aq4, sc4):
