@@ -442,8 +442,20 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nlm
         rt.graph_free(g)
         out["w4a8_m4_stream"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
-        for ptr in (tab_m, aem, aom, scm, sum_):
+        for ptr in (aem, aom, scm, sum_):
             rt.free(ptr)
+        if rt.has("w4a4_decode_stream_m"):
+            aqm, scm = rt.alloc(nlm * mt * K // 2), rt.alloc(nlm * mt * (K // 32) * 4)
+            rt.graph_begin()
+            rt.launch2d("quant_act4", K // 32, nlm * mt, 32, 1, [st.x, aqm, scm, nlm * mt, K])
+            rt.launch("w4a4_decode_stream_m", 1, 1, [tab_m, nlm, rows, K, 0, 0, 0, status, aqm, scm, mt, N, 0])
+            g = rt.graph_end()
+            us = time_graph(rt, g, reps, 3, lambda: None) * 1e3 / nlm
+            rt.graph_free(g)
+            out["w4a4_m4_stream"] = {"us_per_layer": round(us, 3), "gb_per_s": round(LAYER_BYTES * frac / us / 1e3, 1)}
+            rt.free(aqm)
+            rt.free(scm)
+        rt.free(tab_m)
     # the same for NVFP4: four tokens per layer on the tcgen05 consumer (12 columns of B per token)
     nlm = min(nv_layers, st.layers) // mt
     if nlm > 0 and rt.has("nvfp4_decode_stream_m"):

@@ -185,7 +185,7 @@ struct W4A8Mma {
             }
             for (int jst = jf; jst < c.nst; jst += NGROUPS, cg++) {
                 const int cc = c0 + jst, s = cc % STAGES;
-                if (!cta_wait(c, &c.bars->full[s], (cc / STAGES) & 1, 3)) return;
+                if (!stage_wait<W4A8Mma>(c, cc)) return;
                 const uint8_t* st = c.ring + (size_t)s * STAGE;
                 const uint8_t* ab = AIS ? st + OFF_ACT : tile;
                 uint4 xa[GPW], xb[GPW];                  // packed words of rows g and g + 8
@@ -280,7 +280,7 @@ struct W4A8ReadCeiling {
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;
             for (int jst = jf; jst < c.nst; jst += NGROUPS) {
                 const int cc = c0 + jst, s = cc % STAGES;
-                if (!cta_wait(c, &c.bars->full[s], (cc / STAGES) & 1, 3)) return;
+                if (!stage_wait<W4A8ReadCeiling>(c, cc)) return;
                 __syncwarp();
                 if (c.lane == 0) mbar_arrive(&c.bars->empty[s]);
             }
@@ -299,31 +299,44 @@ struct W4A8ReadCeiling {
 // Both operands are formed as 16 x their value with one or two logic instructions per register (a two's-
 // complement nibble in the upper half of a byte is the signed byte 16 * v): J = acc >> 8, exactly, with no
 // correction term.  The four lanes of a row then add their sub-groups with two shuffles.
-template <int STAGES_, int NGROUPS_, bool DUMP, int NPROD_ = 1>
+// Several tokens (M_ = 2..4): accumulator column 2t + 1, which lane t owns as well, takes a second token of the same
+// sub-group (column g carries token g & 1 in the k slots of lane g >> 1), so two tokens cost what one does; tokens
+// 2 and 3 are a second set of MMAs over the same A registers.  The code tile of a layer is [M][K/2] nibbles, then
+// [M][K/32] scales (a 2-D quant_act4 launch with grid y = layer * M + token).
+template <int STAGES_, int NGROUPS_, bool DUMP, int NPROD_ = 1, int M_ = 1>
 struct W4A4Mma {
     using Params = PlainParams;
-    static constexpr int M = 1, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = 1;
+    static constexpr int M = M_, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = 1;
     static constexpr bool ACT_IN_STAGE = true;
     static constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
     static constexpr int ROWB = K / 2, SCB = NG * 2, PITCH = ROWB;
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB;
-    static constexpr int ACT = K / 2 + (K / 32) * 4;            // packed nibbles, sub-group scales
+    static constexpr int ACT = M * (K / 2 + (K / 32) * 4);      // packed nibbles, sub-group scales
     static constexpr int STAGE = (OFF_ACT + ACT + 127) & ~127;
-    static constexpr int RED = CW * ROWS, EXTRA = 0;
+    static constexpr int RED = CW * ROWS * M, EXTRA = 0;
     static constexpr int NPROD = NPROD_;
     static constexpr int kThreads = (NGROUPS * CW + 1 + NPROD) * 32;
+    static constexpr int NSET = (M + 1) / 2;                    // MMA sets of two tokens
 
     __device__ static void init_extra(const Params&, uint8_t*) {}
     __device__ static void copy_act(const Params& pp, int l, uint8_t* dst, uint64_t* bar) {
         const StreamParams& p = pp.s;
-        bulk_g2s(dst, p.ae + (size_t)l * (K / 2), K / 2, bar);                               // aq
-        bulk_g2s(dst + K / 2, p.asc + (size_t)l * (K / 32 * 4), K / 32 * 4, bar);
+        bulk_g2s(dst, p.ae + (size_t)l * M * (K / 2), M * (K / 2), bar);                     // aq
+        bulk_g2s(dst + M * (K / 2), p.asc + (size_t)l * M * (K / 32 * 4), M * (K / 32 * 4), bar);
     }
 
     __device__ static void consume(const Cta& c, const Params& pp, int grp, int w) {
         const StreamParams& p = pp.s;
         const int lane = c.lane, g = lane >> 2, t = lane & 3;
-        const uint32_t bmask = g == 2 * t ? 0xF0F0F0F0u : 0u;   // this lane's B registers carry column 2t (or nothing)
+        // this lane's B registers carry column g: token (g & 1) of a set, in the k slots that lane g >> 1 feeds
+        uint32_t bmask[NSET];
+        int btok[NSET];
+#pragma unroll
+        for (int si = 0; si < NSET; si++) {
+            const int tok = 2 * si + (g & 1);
+            bmask[si] = ((g >> 1) == t && tok < M) ? 0xF0F0F0F0u : 0u;
+            btok[si] = tok < M ? tok : M - 1;
+        }
         int cg = 0;
         for (int l = 0; l < p.nlayers; l++) {
             const int c0 = l * c.nst;
@@ -333,7 +346,7 @@ struct W4A4Mma {
             if (!layer_enter<W4A4Mma>(c, l)) return;
             for (int jst = jf; jst < c.nst; jst += NGROUPS, cg++) {
                 const int cc = c0 + jst, s = cc % STAGES;
-                if (!cta_wait(c, &c.bars->full[s], (cc / STAGES) & 1, 3)) return;
+                if (!stage_wait<W4A4Mma>(c, cc)) return;
                 const uint8_t* st = c.ring + (size_t)s * STAGE;
                 const uint8_t* ab = st + OFF_ACT;
                 uint4 xa[GPW], xb[GPW];
@@ -346,40 +359,66 @@ struct W4A4Mma {
                     swa[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + g * SCB + gg * 2));
                     swb[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + (g + 8) * SCB + gg * 2));
                 }
-                float fa = 0.f, fb = 0.f;
+                float fa[2 * NSET], fb[2 * NSET];                // rows g, g + 8 x tokens 2*set, 2*set + 1 (this lane's sub-groups)
+#pragma unroll
+                for (int k = 0; k < 2 * NSET; k++) fa[k] = fb[k] = 0.f;
 #pragma unroll
                 for (int j = 0; j < GPW; j++) {
                     const int gg = j * CW + w;
-                    const uint4 a = *reinterpret_cast<const uint4*>(ab + gg * 64 + t * 16);   // the sub-group's 32 codes
-                    const float sa = *reinterpret_cast<const float*>(ab + K / 2 + (gg * 4 + t) * 4);
                     const uint32_t m_hi = 0xF0F0F0F0u;
-                    int acc[4] = {0, 0, 0, 0};
                     // even k: low nibbles moved to the upper half of their bytes; odd k: high nibbles in place
-                    mma_s8(acc, (xa[j].x << 4) & m_hi, (xb[j].x << 4) & m_hi, (xa[j].y << 4) & m_hi, (xb[j].y << 4) & m_hi,
-                           (a.x << 4) & bmask, (a.y << 4) & bmask);
-                    mma_s8(acc, (xa[j].z << 4) & m_hi, (xb[j].z << 4) & m_hi, (xa[j].w << 4) & m_hi, (xb[j].w << 4) & m_hi,
-                           (a.z << 4) & bmask, (a.w << 4) & bmask);
-                    mma_s8(acc, xa[j].x & m_hi, xb[j].x & m_hi, xa[j].y & m_hi, xb[j].y & m_hi, a.x & bmask, a.y & bmask);
-                    mma_s8(acc, xa[j].z & m_hi, xb[j].z & m_hi, xa[j].w & m_hi, xb[j].w & m_hi, a.z & bmask, a.w & bmask);
-                    const int ia = acc[0] >> 8, ib = acc[2] >> 8;      // rows g, g + 8, column 2t: 256 * J exactly
-                    fa += (swa[j] * sa) * (float)ia;
-                    fb += (swb[j] * sa) * (float)ib;
-                    if (DUMP) {
-                        const int ra = c.r0 + jst * ROWS + g, rb = ra + 8, sg = gg * 4 + t;
-                        if (ra < c.r1) p.iacc[((size_t)l * p.rows + ra) * (K / 32) + sg] = ia;
-                        if (rb < c.r1) p.iacc[((size_t)l * p.rows + rb) * (K / 32) + sg] = ib;
+                    const uint32_t ea0 = (xa[j].x << 4) & m_hi, eb0 = (xb[j].x << 4) & m_hi, ea1 = (xa[j].y << 4) & m_hi, eb1 = (xb[j].y << 4) & m_hi;
+                    const uint32_t ea2 = (xa[j].z << 4) & m_hi, eb2 = (xb[j].z << 4) & m_hi, ea3 = (xa[j].w << 4) & m_hi, eb3 = (xb[j].w << 4) & m_hi;
+                    const uint32_t oa0 = xa[j].x & m_hi, ob0 = xb[j].x & m_hi, oa1 = xa[j].y & m_hi, ob1 = xb[j].y & m_hi;
+                    const uint32_t oa2 = xa[j].z & m_hi, ob2 = xb[j].z & m_hi, oa3 = xa[j].w & m_hi, ob3 = xb[j].w & m_hi;
+#pragma unroll
+                    for (int si = 0; si < NSET; si++) {
+                        // the 32 codes of sub-group t of this lane's column token
+                        const uint4 a = *reinterpret_cast<const uint4*>(ab + btok[si] * (K / 2) + gg * 64 + t * 16);
+                        const uint32_t bm = bmask[si];
+                        int acc[4] = {0, 0, 0, 0};
+                        mma_s8(acc, ea0, eb0, ea1, eb1, (a.x << 4) & bm, (a.y << 4) & bm);
+                        mma_s8(acc, ea2, eb2, ea3, eb3, (a.z << 4) & bm, (a.w << 4) & bm);
+                        mma_s8(acc, oa0, ob0, oa1, ob1, a.x & bm, a.y & bm);
+                        mma_s8(acc, oa2, ob2, oa3, ob3, a.z & bm, a.w & bm);
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {            // accumulator columns 2t, 2t + 1: tokens 2*si, 2*si + 1
+                            const int tok = 2 * si + h;
+                            if (tok >= M) continue;
+                            const float sa = *reinterpret_cast<const float*>(ab + M * (K / 2) + (tok * (K / 32) + gg * 4 + t) * 4);
+                            const int ia = acc[h] >> 8, ib = acc[2 + h] >> 8;      // rows g, g + 8: 256 * J exactly
+                            fa[tok] += (swa[j] * sa) * (float)ia;
+                            fb[tok] += (swb[j] * sa) * (float)ib;
+                            if (DUMP) {
+                                const int ra = c.r0 + jst * ROWS + g, rb = ra + 8, sg = gg * 4 + t;
+                                int* d = p.iacc + ((size_t)l * M + tok) * p.rows * (K / 32) + sg;
+                                if (ra < c.r1) d[(size_t)ra * (K / 32)] = ia;
+                                if (rb < c.r1) d[(size_t)rb * (K / 32)] = ib;
+                            }
+                        }
                     }
                 }
-                consumed(fa + fb);                       // release only after the loaded data has been used
+                float chk = 0.f;
+#pragma unroll
+                for (int k = 0; k < M; k++) chk += fa[k] + fb[k];
+                consumed(chk);                           // release only after the loaded data has been used
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&c.bars->empty[s]);
                 // the four lanes of a row hold the sums over their own sub-groups
-                fa += __shfl_xor_sync(0xffffffffu, fa, 1);
-                fb += __shfl_xor_sync(0xffffffffu, fb, 1);
-                fa += __shfl_xor_sync(0xffffffffu, fa, 2);
-                fb += __shfl_xor_sync(0xffffffffu, fb, 2);
-                const float vals[2] = {fa, fb};
-                const int idx[2] = {t == 0 ? g : -1, t == 0 ? g + 8 : -1};
+                float vals[2 * M];
+                int idx[2 * M];
+#pragma unroll
+                for (int k = 0; k < M; k++) {
+                    float va = fa[k], vb = fb[k];
+                    va += __shfl_xor_sync(0xffffffffu, va, 1);
+                    vb += __shfl_xor_sync(0xffffffffu, vb, 1);
+                    va += __shfl_xor_sync(0xffffffffu, va, 2);
+                    vb += __shfl_xor_sync(0xffffffffu, vb, 2);
+                    vals[2 * k] = va;
+                    vals[2 * k + 1] = vb;
+                    idx[2 * k] = t == 0 ? g * M + k : -1;
+                    idx[2 * k + 1] = t == 0 ? (g + 8) * M + k : -1;
+                }
                 if (!reduce_and_emit<W4A4Mma>(c, grp, w, cg, vals, idx, yt, y, c.r0 + jst * ROWS)) return;
             }
             layer_done(c, l);
@@ -460,7 +499,7 @@ struct W4Dp4a {
             }
             for (int j = 0; j < c.nst; j++, cc++) {
                 const int s = cc % STAGES;
-                if (!cta_wait(c, &c.bars->full[s], (cc / STAGES) & 1, 3)) return;
+                if (!stage_wait<W4Dp4a>(c, cc)) return;
                 const int row = c.r0 + j * CW + w;
                 const bool live = row < c.r1;
                 const uint8_t* st = c.ring + (size_t)s * STAGE;
@@ -592,7 +631,7 @@ struct Nvfp4Mma {
             }
             for (int jst = jf; jst < c.nst; jst += NGROUPS, cg++) {
                 const int cc = c0 + jst, s = cc % STAGES;
-                if (!cta_wait(c, &c.bars->full[s], (cc / STAGES) & 1, 3)) return;
+                if (!stage_wait<Nvfp4Mma>(c, cc)) return;
                 const uint8_t* st = c.ring + (size_t)s * STAGE;
                 uint4 xa[GPW], xb[GPW];
                 uint32_t sba[GPW], sbb[GPW];             // E4M3 bytes of the lane's two blocks, rows g and g + 8
@@ -708,7 +747,7 @@ struct Nvfp4Dp4a {
             }
             for (int j = 0; j < c.nst; j++, cc++) {
                 const int s = cc % STAGES;
-                if (!cta_wait(c, &c.bars->full[s], (cc / STAGES) & 1, 3)) return;
+                if (!stage_wait<Nvfp4Dp4a>(c, cc)) return;
                 const int row = c.r0 + j * CW + w;
                 const bool live = row < c.r1;
                 const uint8_t* st = c.ring + (size_t)s * STAGE;
@@ -826,7 +865,7 @@ struct W4A16Mma {
             }
             for (int jst = jf; jst < c.nst; jst += NGROUPS, cg++) {
                 const int cc0 = c0 + jst, s = cc0 % STAGES;
-                if (!cta_wait(c, &c.bars->full[s], (cc0 / STAGES) & 1, 3)) return;
+                if (!stage_wait<W4A16Mma>(c, cc0)) return;
                 const uint8_t* st = c.ring + (size_t)s * STAGE;
                 uint4 xa[GPW], xb[GPW];
                 float swa[GPW], swb[GPW];
@@ -1180,6 +1219,47 @@ int launch_w4a8_stream_m(const LaunchCtx& c, const uint64_t* a) {
     }
 }
 
+// w4a4_decode_stream_m(common..., aq, asc, M, ystride, flags): M = 2..4 tokens per layer on the W4A4 tensor-core
+// consumer.  aq / asc hold [nlayers * M] tokens (one 2-D quant_act4 launch with grid y = nlayers * M over
+// x[nlayers][M][K]); y and the table's row_base argument as for w4a8_decode_stream_m.
+// w4a4_decode_stream_m_iacc(..., flags, iacc): iacc int32 [nlayers][M][rows][K/32].
+template <bool DUMP>
+int launch_w4a4_stream_m(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = DUMP ? "w4a4_decode_stream_m_iacc" : "w4a4_decode_stream_m";
+    PlainParams pp = {};
+    StreamParams& p = pp.s;
+    const int M = arg_i32(a[10]);
+    FM_REQUIRE(M >= 2 && M <= 4, kn, "M=%d: this kernel takes 2..4 tokens (w4a4_decode_stream takes one)", M);
+    const int rc = parse_common(kn, c, a, a[12], p, M);
+    if (rc) return rc < 0 ? rc : FM_OK;
+    p.ae = arg_ptr<const uint8_t>(a[8]);
+    p.asc = arg_ptr<const uint8_t>(a[9]);
+    p.ystride = arg_i32(a[11]);
+    FM_REQUIRE(p.ystride >= p.row_base + p.rows && (long long)(p.M - 1) * p.ystride + p.row_base < (1LL << 31), kn,
+               "ystride=%d must be at least row_base + rows = %d", p.ystride, p.row_base + p.rows);
+    const int vbase = p.row_base + (p.M - 1) * p.ystride;
+    FM_REQUIRE(stream_table_ok(p.layers, p.nlayers, p.rows, p.K, vbase, p.peer_delta, p.npeers, true), kn,
+               "the layer table at %p was not filled by fm_stream_table for nlayers=%d rows=%d K=%d and the row_base "
+               "argument row_base + (M - 1) * ystride = %d (or was overwritten, or a buffer it points into was freed since), "
+               "or the peer offsets do not come from fm_stream_peers for its outputs", (const void*)p.layers, p.nlayers,
+               p.rows, p.K, vbase);
+    FM_REQUIRE(aligned(p.ae, 16) && aligned(p.asc, 16), kn, "the activation code arrays must be 16-byte aligned");
+    const size_t tokens = (size_t)p.nlayers * p.M;
+    FM_RANGE(p.ae, tokens * (p.K / 2), kn, "aq");
+    FM_RANGE(p.asc, tokens * (p.K / 32) * 4, kn, "asc");
+    if (DUMP) {
+        p.iacc = arg_ptr<int>(a[13]);
+        FM_REQUIRE(aligned(p.iacc, 4), kn, "misaligned accumulator dump");
+        FM_RANGE(p.iacc, tokens * p.rows * (p.K / 32) * 4, kn, "iacc");
+    }
+    // four stages where they fit beside the tokens' codes (3200 bytes per token and stage), three at M = 4
+    switch (p.M) {
+        case 2: return run_policy<W4A4Mma<4, 2, DUMP, 2, 2>>(kn, c, pp);
+        case 3: return run_policy<W4A4Mma<4, 2, DUMP, 2, 3>>(kn, c, pp);
+        default: return run_policy<W4A4Mma<3, 2, DUMP, 1, 4>>(kn, c, pp);
+    }
+}
+
 // nvfp4_decode_stream(common..., qa, qb, sc, gscale, flags): the layer table's ws entries are the E4M3 block scales
 // [rows][K/16] (the table must have been validated with room for them: fm_stream_table records how many bytes follow
 // every ws pointer inside its allocation); qa / qb / sc are nvfp4_quant_act's outputs for all layers: [nlayers][K/2],
@@ -1325,11 +1405,13 @@ const KernelEntry kStream[] = {
     {"w4a8_decode_stream", 13, launch_w4_stream<false, false>, "piiiiippppppp"},
     {"w4a4_decode_stream", 11, launch_w4_stream<true, false>, "piiiiippppp"},
     {"w4a8_decode_stream_m", 15, launch_w4a8_stream_m<false>, "piiiiippppppiip"},
+    {"w4a4_decode_stream_m", 13, launch_w4a4_stream_m<false>, "piiiiippppiip"},
     {"nvfp4_decode_stream", 13, launch_nvfp4_stream<false>, "piiiiipppppfp"},
     {"w4a16_decode_stream", 9, launch_w4a16_stream, "piiiiippp"},
     {"w4a8_decode_stream_iacc", 14, launch_w4_stream<false, true>, "piiiiipppppppp"},
     {"w4a4_decode_stream_iacc", 12, launch_w4_stream<true, true>, "piiiiipppppp"},
     {"w4a8_decode_stream_m_iacc", 16, launch_w4a8_stream_m<true>, "piiiiippppppiipp"},
+    {"w4a4_decode_stream_m_iacc", 14, launch_w4a4_stream_m<true>, "piiiiippppiipp"},
     {"nvfp4_decode_stream_iacc", 14, launch_nvfp4_stream<true>, "piiiiipppppfpp"},
     {"stream_flag_wait", 5, launch_flag_wait, "piipi"},
     {"w4a8_stream_read_ceiling", 13, launch_w4a8_read_ceiling, "piiiiippppppp"},

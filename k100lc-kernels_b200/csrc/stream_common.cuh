@@ -79,6 +79,7 @@ struct Bars {
     uint64_t red_full[4], red_free[4]; // partial-sum tiles of the tensor-core consumers (two per group)
     uint64_t ydone[kYBufs], yfree[kYBufs];   // output tile complete / written out
     volatile int abort;
+    uint32_t seen[kMaxStages];         // fills of a slot that some consumer has seen land (stage_wait)
 };
 static_assert(sizeof(Bars) <= kHeader, "barrier block");
 
@@ -148,6 +149,37 @@ __device__ __forceinline__ bool cta_wait(const Cta& c, uint64_t* bar, uint32_t p
     atomicCAS(c.p->status, 0, code);
     return false;
 }
+// A consumer group waits until stage `cc` (counted over the whole launch) has landed in its ring slot.  A parity wait
+// tells "this fill has landed" from "the fill before it has not landed yet" only for a waiter that knows that the fill
+// before has landed.  The groups take the stages in turn, so when STAGES is not a multiple of NGROUPS the fill before
+// was another group's: whoever sees a fill land writes its number beside the barrier, and a group reads that number
+// before it trusts the parity (the fill it waits for cannot be issued before that group released the slot, so this
+// adds no dependence).
+template <class P>
+__device__ __forceinline__ bool stage_wait(const Cta& c, int cc) {
+    const int s = cc % P::STAGES, ph = cc / P::STAGES;
+    constexpr bool kShared = P::STAGES % P::NGROUPS != 0;
+    if constexpr (kShared) {
+        const uint32_t addr = smem_u32(&c.bars->seen[s]);
+        for (int i = 0; ph > 0; i++) {
+            uint32_t v;
+            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+            if (v >= (uint32_t)ph) break;
+            if ((i & 7) == 7 && c.bars->abort) return false;
+            if (i >= kSpinLimit) {
+                c.bars->abort = 1;
+                atomicCAS(c.p->status, 0, 3);
+                return false;
+            }
+        }
+    }
+    if (!cta_wait(c, &c.bars->full[s], ph & 1, 3)) return false;
+    if constexpr (kShared) {
+        if (c.lane == 0 && c.warp % P::CW == 0)            // one warp of the group speaks for it
+            asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&c.bars->seen[s])), "r"((uint32_t)ph + 1u) : "memory");
+    }
+    return true;
+}
 // the same without a report: used on the way out, for copies that are still in flight
 __device__ __forceinline__ void quiet_wait(uint64_t* bar, uint32_t parity) {
     for (int i = 0; i < kSpinLimit && !mbar_try_wait(bar, parity, 1000u); i++) {}
@@ -183,6 +215,8 @@ __device__ __forceinline__ void run_producer(const Cta& cta, const typename P::P
     const StreamParams& p = *c.p;
     Bars* B = c.bars;
     static_assert(P::NPROD == 1 || P::ACT_IN_STAGE, "several producer lanes need self-contained stages");
+    // a ring slot belongs to one lane: a lane that met a slot only every other round could not tell its phases apart
+    static_assert(P::STAGES % P::NPROD == 0, "the producer lanes must divide the ring");
     int issued = 0, acts = 0;          // stages armed by any lane up to this lane's last one / activation tiles armed
     bool ok = true;
     auto copy_tile = [&](int l) -> bool {          // layer l's codes -> tile l % NACT
@@ -412,6 +446,7 @@ stream_kernel(const typename P::Params pp) {
             mbar_init(&c.bars->yfree[b], 1);
         }
         c.bars->abort = 0;
+        for (int s = 0; s < P::STAGES; s++) c.bars->seen[s] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     P::init_extra(pp, c.extra);

@@ -434,12 +434,60 @@ def test_stream_accumulators_several_tokens(rt, m, rows):
         assert O.rel_err(got[i, :, :rows], ref["y"]) < REL
 
 
+@pytest.mark.parametrize("m,rows,row_base,nl", [(2, 600, 0, 3), (3, 148, 0, 5), (4, 17408, 0, 2), (4, 700, 300, 6), (3, 1001, 8, 7)])
+def test_w4a4_stream_several_tokens(rt, m, rows, row_base, nl):
+    """w4a4_decode_stream_m: 2..4 tokens per layer on the W4A4 tensor-core consumer (two tokens share an MMA: the
+    second one rides in the accumulator column that a lane owns beside its own).  The int32 of every
+    (token, row, 32-group) bit for bit; y against the oracle, also at a pinned host receiver; a one-token table is
+    refused."""
+    ystride = row_base + rows + 24
+    layers = [synth.rt4_layer(rows, K, m, seed=1350 + 10 * m + i) for i in range(nl)]
+    host = rt.pinned((nl, m, ystride), np.float32)
+    host[:] = np.nan
+    with Bufs(rt) as b:
+        x = b.put(np.stack([L["x"] for L in layers]))                       # [nl][m][K]
+        aq, asc = b.zeros(nl * m * K // 2, np.uint8), b.zeros(nl * m * K // 32)
+        y = b.zeros(nl * m * ystride, np.float32, np.nan)
+        ptrs = [(b.put(L["wq"]), b.put(L["ws"]), x + i * m * K * 4, y + i * m * ystride * 4) for i, L in enumerate(layers)]
+        table = rt.stream_table(ptrs, rows, K, row_base + (m - 1) * ystride)
+        deltas = rt.stream_peers([host.ctypes.data], y, nl * m * ystride * 4)
+        status = b.zeros(1, np.int32)
+        rt.launch2d("quant_act4", K // 32, nl * m, 32, 1, [x, aq, asc, nl * m, K])
+        pi = b.zeros(nl * m * rows * (K // 32), np.int32, -7)
+        rt.launch("w4a4_decode_stream_m_iacc", 1, 1, [table, nl, rows, K, row_base, 0, 0, status, aq, asc, m, ystride, 0, pi])
+        acc = b.get(pi, nl * m * rows * (K // 32), np.int32).reshape(nl, m, rows, -1)
+        dumped = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
+        rt.memset(y, 0xFF, nl * m * ystride * 4)
+        rt.launch("w4a4_decode_stream_m", 1, 1, [table, nl, rows, K, row_base, 1, deltas, status, aq, asc, m, ystride, 0])
+        got = b.get(y, nl * m * ystride).reshape(nl, m, ystride)
+        assert int(b.get(status, 1, np.int32)[0]) == 0
+        with pytest.raises(RuntimeError, match="2..4 tokens"):
+            rt.launch("w4a4_decode_stream_m", 1, 1, [table, nl, rows, K, row_base, 0, 0, status, aq, asc, 1, ystride, 0])
+        with pytest.raises(RuntimeError, match="rc=-4"):                    # a table validated for one token is refused
+            t1 = rt.stream_table(ptrs, rows, K, row_base)
+            try:
+                rt.launch("w4a4_decode_stream_m", 1, 1, [t1, nl, rows, K, row_base, 0, 0, status, aq, asc, m, ystride, 0])
+            finally:
+                rt.free(t1)
+        rt.free(table)
+        rt.free(deltas)
+    sl = slice(row_base, row_base + rows)
+    assert np.array_equal(got[:, :, sl].view(np.uint32), dumped[:, :, sl].view(np.uint32))
+    assert np.array_equal(host[:, :, sl].view(np.uint32), got[:, :, sl].view(np.uint32))
+    for i, L in enumerate(layers):
+        q = O.quant_act4(L["x"])
+        ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 32)
+        assert np.array_equal(acc[i], ref["acc"]), "W4A4 multi-token stream accumulators differ"
+        assert O.rel_err(got[i, :, sl], ref["y"]) < REL
+        assert np.isnan(got[i, :, :row_base]).all() and np.isnan(got[i, :, row_base + rows:]).all()
+        assert np.isnan(host[i, :, :row_base]).all() and np.isnan(host[i, :, row_base + rows:]).all()
+
+
 @pytest.mark.parametrize("cfg", [None, "3", "1", "0", "2"])
 @pytest.mark.parametrize("rows,nlayers", [(17408, 2), (520, 3)])
 def test_stream_accumulators_nvfp4(rt, monkeypatch, rows, nlayers, cfg):
     """nvfp4_decode_stream: the int32 of every (row, 16-block), bit for bit, from the default consumer (tcgen05
-    kind::f8f6f4: the integer is rebuilt from the exact fp32 block sums of the lo / hi halves of the activation
-    codes), the dp4a consumer ($FM_NVFP4_CFG=1) and the mma.sync consumer (0; 2 = two groups, same arithmetic)."""
+    kind::mxf4: the integer is rebuilt from the exact fp32 block sums of the base-7 digits of the activation codes), the dp4a consumer ($FM_NVFP4_CFG=1) and the mma.sync consumer (0; 2 = two groups, same arithmetic)."""
     if cfg is None:
         monkeypatch.delenv("FM_NVFP4_CFG", raising=False)
     else:
