@@ -1479,6 +1479,30 @@ int stream_gemv_w4a8(const LaunchCtx& c, const char* kn, const void* wq, const v
     }
 }
 
+// The same for gemv_w4a4<2..4> and its r2 names: aq [M][K/2] packed nibbles, asc [M][K/32]; iacc [M][rows][K/32].
+int stream_gemv_w4a4(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* aq, const void* asc,
+                     float* y, int M, int ystride, int rows, int* iacc) {
+    PlainParams pp = {};
+    one_layer(pp.s, wq, ws, y, rows, M, ystride);
+    FM_REQUIRE(pp.s.status != nullptr, kn, "the status word of the ring kernels is not addressable");
+    FM_REQUIRE(M >= 2 && M <= 4, kn, "M=%d: the ring takes 2..4 tokens here", M);
+    pp.s.ae = static_cast<const uint8_t*>(aq);
+    pp.s.asc = static_cast<const uint8_t*>(asc);
+    pp.s.iacc = iacc;
+    if (iacc) {
+        switch (M) {
+            case 2: return run_policy<W4A4Mma<4, 2, true, 2, 2>>(kn, c, pp);
+            case 3: return run_policy<W4A4Mma<4, 2, true, 2, 3>>(kn, c, pp);
+            default: return run_policy<W4A4Mma<3, 2, true, 1, 4>>(kn, c, pp);
+        }
+    }
+    switch (M) {
+        case 2: return run_policy<W4A4Mma<4, 2, false, 2, 2>>(kn, c, pp);
+        case 3: return run_policy<W4A4Mma<4, 2, false, 2, 3>>(kn, c, pp);
+        default: return run_policy<W4A4Mma<3, 2, false, 1, 4>>(kn, c, pp);
+    }
+}
+
 int stream_read_status(cudaStream_t stream) {
     int v = 0, zero = 0;
     if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;

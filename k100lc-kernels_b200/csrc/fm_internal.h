@@ -90,6 +90,9 @@ cudaError_t gemv_w4a8_raw(const uint32_t* wq, const void* ws_f16, const int8_t* 
 // accumulators [M][rows][K/128].
 int stream_gemv_w4a8(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* ae, const void* ao,
                      const void* asc, const void* asu, float* y, int M, int ystride, int rows, int* iacc);
+// The same behind gemv_w4a4<2..4> and its r2 names (aq [M][K/2], asc [M][K/32]; iacc [M][rows][K/32]).
+int stream_gemv_w4a4(const LaunchCtx& c, const char* kn, const void* wq, const void* ws, const void* aq, const void* asc,
+                     float* y, int M, int ystride, int rows, int* iacc);
 namespace stream { struct StreamParams; }
 // nvfp4_decode_stream on the tcgen05 path (nvfp4_tc_stream.cu).  FM_OK after enqueueing, negative after a rejection,
 // 1 when this path cannot take the launch and the caller should use another consumer.

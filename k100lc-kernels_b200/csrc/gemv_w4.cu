@@ -431,8 +431,9 @@ int run_variant(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
     return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
 }
 
-// Two to four tokens of int8 activations at K = 5120 with 16-byte aligned operands run on the bulk-copy ring of the
-// stream kernels (one layer): 15.1 us against 15.8 us for gemv_w4a8_mma_kernel at M = 4.  One token stays here: a ring
+// Two to four tokens at K = 5120 with 16-byte aligned operands run on the bulk-copy ring of the stream kernels (one
+// layer): int8 activations 15.1 us against 15.8 us for gemv_w4a8_mma_kernel at M = 4; int4 activations on the ring's
+// tensor-core consumer against 20.8 us for the dp4a kernel of this file.  One token stays here: a ring
 // that is launched for a single layer pays its fill and drain on every launch (11.4 us against 10.3 us for the GEMV
 // alone; likewise W4A4 13.6 / 12.2 and NVFP4 15.9 / 14.4 us with the quantiser).  $FM_GEMV_CFG=2 keeps the kernels of
 // this file for every shape.
@@ -447,6 +448,8 @@ int dispatch(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
     const int kiter = (p.K % 1024 == 0) ? p.K / 1024 : 0;
     if (!A4 && M > 1 && ring_ok(p, false) && (!DUMP || p.rows == p.N))
         return stream_gemv_w4a8(c, kn, p.wq, p.ws, p.a0, p.a1, p.asc, p.asu, p.y, M, p.N, p.rows, DUMP ? p.iacc : nullptr);
+    if (A4 && M > 1 && ring_ok(p, true) && (!DUMP || p.rows == p.N))
+        return stream_gemv_w4a4(c, kn, p.wq, p.ws, p.a0, p.asc, p.y, M, p.N, p.rows, DUMP ? p.iacc : nullptr);
     if (DUMP) {
         // the dump comes from the kernel that the by-name entry of this M runs: the tensor-core one for
         // int8 activations and 2..4 tokens, the dp4a one otherwise
