@@ -107,12 +107,15 @@ __device__ __forceinline__ bool reduce_and_emit(const Cta& c, int grp, int w, in
 //           loads fall into different banks; the rows are then copied one by one)
 //   DUMP    also store the integer accumulators
 //   VAR     the layers have shapes of their own (StreamParams::var): rows per layer, row pitch, chunks of longer rows
-template <int M_, int STAGES_, int NGROUPS_, bool AIS, int NACT_, bool BREG, int PAD, bool DUMP, int NPROD_ = 1, bool VAR_ = false>
+//   ROT     whole stages are dealt out to the CTAs, from a position that moves with the layer (stream_common.cuh: var_rows)
+template <int M_, int STAGES_, int NGROUPS_, bool AIS, int NACT_, bool BREG, int PAD, bool DUMP, int NPROD_ = 1, bool VAR_ = false,
+          bool ROT_ = false>
 struct W4A8Mma {
     using Params = PlainParams;
     static constexpr int M = M_, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = AIS ? 1 : NACT_;
-    static constexpr bool ACT_IN_STAGE = AIS, VAR = VAR_;
+    static constexpr bool ACT_IN_STAGE = AIS, VAR = VAR_, ROT = ROT_;
     static_assert(!VAR || (AIS && M_ == 1 && !DUMP && PAD == 0), "per-layer shapes: one token, codes inside the stage");
+    static_assert(!ROT || (AIS && !VAR && !BREG), "moving row ranges: no per-layer state outside the stages");
     static constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
     static constexpr int ROWB = K / 2, SCB = NG * 2, PITCH = ROWB + PAD;
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB;
@@ -259,12 +262,12 @@ struct W4A8Mma {
 // token's codes inside every stage) of the default W4A8 schedule, with consumers that release every stage as soon as it
 // has landed — no shared-memory read, no arithmetic, no output.  What this kernel takes per token is what the memory
 // system allows this access pattern; the distance of w4a8_decode_stream from it is what its arithmetic costs.
-template <int STAGES_, int NPROD_>
+template <int STAGES_, int NPROD_, bool ROT_ = false>
 struct W4A8ReadCeiling {
     using Params = PlainParams;
     using Base = W4A8Mma<1, STAGES_, 2, true, 1, false, 0, false, NPROD_>;
     static constexpr int M = 1, STAGES = STAGES_, NGROUPS = 2, NACT = 1;
-    static constexpr bool ACT_IN_STAGE = true, NO_OUTPUT = true;
+    static constexpr bool ACT_IN_STAGE = true, NO_OUTPUT = true, ROT = ROT_;
     static constexpr int K = Base::K, NG = Base::NG, CW = Base::CW, ROWS = Base::ROWS;
     static constexpr int ROWB = Base::ROWB, SCB = Base::SCB, PITCH = Base::PITCH;
     static constexpr int STAGE_W = Base::STAGE_W, OFF_ACT = Base::OFF_ACT, ACT = Base::ACT, STAGE = Base::STAGE;
@@ -273,10 +276,12 @@ struct W4A8ReadCeiling {
 
     __device__ static void init_extra(const Params&, uint8_t*) {}
     __device__ static void copy_act(const Params& pp, int l, uint8_t* dst, uint64_t* bar) { Base::copy_act(pp, l, dst, bar); }
-    __device__ static void consume(const Cta& c, const Params& pp, int grp, int w) {
+    __device__ static void consume(const Cta& cta, const Params& pp, int grp, int w) {
+        Cta c = cta;
         const StreamParams& p = pp.s;
-        for (int l = 0; l < p.nlayers; l++) {
-            const int c0 = l * c.nst;
+        int c0 = 0;
+        for (int l = 0; l < p.nlayers; c0 += c.nst, l++) {
+            set_geom<W4A8ReadCeiling>(c, l);
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;
             for (int jst = jf; jst < c.nst; jst += NGROUPS) {
                 const int cc = c0 + jst, s = cc % STAGES;
@@ -1001,7 +1006,7 @@ int parse_common(const char* kn, const LaunchCtx& c, const uint64_t* a, uint64_t
         const int grid = c.sm_count < p.rows ? c.sm_count : p.rows;
         FM_REQUIRE(aligned(p.flags, 4), kn, "misaligned flags");
         FM_RANGE(p.flags, (size_t)p.nlayers * 4, kn, "flags");
-        FM_REQUIRE((long long)((p.rows + grid - 1) / grid) * M <= kOutCap, kn,
+        FM_REQUIRE((long long)(((p.rows + 15) / 16 + grid - 1) / grid * 16) * M <= kOutCap, kn,
                    "completion counters need at most %d y values per CTA and layer (rows=%d on %d CTAs, M=%d)", kOutCap,
                    p.rows, grid, M);
         FM_REQUIRE(p.npeers == 0 || peer_window_ok(p.peer_delta, p.npeers, p.flags, (size_t)p.nlayers * 4), kn,
@@ -1009,6 +1014,9 @@ int parse_common(const char* kn, const LaunchCtx& c, const uint64_t* a, uint64_t
     }
     return 0;
 }
+
+// the default W4A8 schedule deals out whole 16-row stages (instead of rows / grid) when a CTA gets three or more per layer
+static bool whole_stages(int rows, int grid) { return (rows + 15) / 16 >= 3 * grid; }
 
 // w4a8_decode_stream(common..., ae, ao, asc, asu, flags)
 //   ae, ao, asc, asu   outputs of quant_act launched with grid y = nlayers over x [nlayers][K]:
@@ -1074,8 +1082,15 @@ int launch_w4_stream(const LaunchCtx& c, const uint64_t* a) {
         case 2: return run_policy<W4A8Mma<1, 4, 1, false, 5, true, 0, false>>(kn, c, pp);    // deeper ring of code tiles
         case 4: return run_policy<W4A8Mma<1, 4, 1, true, 1, false, 0, false>>(kn, c, pp);    // codes inside every stage, one group
         case 7: return run_policy<W4A8Mma<1, 4, 1, false, 2, true, 64, false>>(kn, c, pp);   // padded row pitch (no bank conflicts): slower
-        case 3: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);    // the default with one producer lane
-        default: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false, 2>>(kn, c, pp);
+        case 3: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false>>(kn, c, pp);    // one producer lane, rows / grid per CTA
+        case 5: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false, 2>>(kn, c, pp); // two producer lanes, rows / grid per CTA
+        case 6: return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false, 2, false, true>>(kn, c, pp);   // whole stages per CTA
+        default:
+            // Whole stages per CTA pay when a CTA has three or more per layer (17408 rows: 2.59 against 2.64 ms per
+            // token, 8704 rows: 1.29 against 1.31); with one stage per CTA and layer — the shard of eight GPUs — a
+            // full stage on 136 CTAs is slower than 14.7 rows on each of 148 (0.40 against 0.36 ms).
+            if (whole_stages(p.rows, grid)) return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false, 2, false, true>>(kn, c, pp);
+            return run_policy<W4A8Mma<1, 4, 2, true, 1, false, 0, false, 2>>(kn, c, pp);
     }
 }
 
@@ -1102,14 +1117,17 @@ int launch_w4a8_read_ceiling(const LaunchCtx& c, const uint64_t* a) {
     FM_RANGE(p.ao, (size_t)p.nlayers * (p.K / 2), kn, "ao");
     FM_RANGE(p.asc, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asc");
     FM_RANGE(p.asu, (size_t)p.nlayers * (p.K / 128) * 4, kn, "asu");
-    return run_policy<W4A8ReadCeiling<4, 2>>(kn, c, pp);
+    const int grid = c.sm_count < p.rows ? c.sm_count : p.rows;
+    const int cfg = env_or("FM_STREAM_CFG", -1);
+    if (cfg == 5 || (cfg != 6 && !whole_stages(p.rows, grid))) return run_policy<W4A8ReadCeiling<4, 2>>(kn, c, pp);
+    return run_policy<W4A8ReadCeiling<4, 2, true>>(kn, c, pp);
 }
 
 // w4a8_layers_stream(layers, shapes, nlayers, npeers, peer_delta, status, flags): W4A8, one token, layers of different
 // shapes in one launch.  `layers` / `shapes` are the two device arrays filled by fm_stream_table_var (a layer = 5120 k of
 // a set of rows; longer rows are consecutive layers that add to the same y); npeers, peer_delta, status and flags as for
 // the other stream kernels (flags: one counter per table entry, each reaching min(SM count, rows of the largest layer)).
-// Every CTA takes an equal share of the rows of every layer.
+// Every CTA takes an equal share of the 16-row stages of every layer (stream_common.cuh: var_rows).
 int launch_w4a8_layers_stream(const LaunchCtx& c, const uint64_t* a) {
     const char* kn = "w4a8_layers_stream";
     PlainParams pp = {};
@@ -1140,8 +1158,9 @@ int launch_w4a8_layers_stream(const LaunchCtx& c, const uint64_t* a) {
     // in the layer's hand-overs (and counts in its completion counter)
     const int grid = c.sm_count < max_rows ? c.sm_count : max_rows;
     (void)min_rows;
-    FM_REQUIRE((max_rows + grid - 1) / grid <= kOutCap, kn,
-               "a CTA would own %d rows of the largest layer (%d rows on %d CTAs); the output tile holds %d", (max_rows + grid - 1) / grid,
+    const int cta_rows = ((max_rows + 15) / 16 + grid - 1) / grid * 16;      // whole 16-row stages are dealt out
+    FM_REQUIRE(cta_rows <= kOutCap, kn,
+               "a CTA would own %d rows of the largest layer (%d rows on %d CTAs); the output tile holds %d", cta_rows,
                max_rows, grid, kOutCap);
     if (p.flags) {
         FM_REQUIRE(aligned(p.flags, 4), kn, "misaligned flags");

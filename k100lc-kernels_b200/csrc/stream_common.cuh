@@ -193,12 +193,34 @@ __device__ __forceinline__ void quiet_wait(uint64_t* bar, uint32_t parity) {
 template <class P, class = void> struct is_var : std::false_type {};
 template <class P> struct is_var<P, std::void_t<decltype(P::VAR)>> : std::bool_constant<P::VAR> {};
 
+// Rows of a layer with a shape of its own that this CTA takes.  Whole stages are dealt out, not rows: with rows / grid
+// a CTA's last stage of every layer is a partial one, and a stage costs its hand-overs however few rows it holds
+// (5120 rows on 148 CTAs: 2.16 stages per CTA instead of three).  The CTAs that get one stage more than the others
+// start at a position that moves with the weight matrix (`first`: the table index of its first chunk, so that all
+// chunks of a matrix — which add to the same y — are split alike), which spreads those stages evenly over the launch.
+template <int ROWS>
+__device__ __forceinline__ void var_rows(int rows, int first, int& r0, int& r1) {
+    const int G = (int)gridDim.x, S = (rows + ROWS - 1) / ROWS;
+    const int base = S / G, extra = S - base * G;
+    const int rot = (int)(((uint32_t)first * 2654435761u >> 12) % (uint32_t)G);
+    int b = (int)blockIdx.x - rot;
+    b += b < 0 ? G : 0;
+    const int s0 = b * base + min(b, extra), s1 = s0 + base + (b < extra ? 1 : 0);
+    r0 = min(rows, s0 * ROWS);
+    r1 = min(rows, s1 * ROWS);
+}
+// A policy may also declare `static constexpr bool ROT = true`: all layers have the table's one shape, and the CTA's
+// rows are dealt out per layer as above (the position moves with the layer).
+template <class P, class = void> struct is_rot : std::false_type {};
+template <class P> struct is_rot<P, std::void_t<decltype(P::ROT)>> : std::bool_constant<P::ROT> {};
 template <class P>
 __device__ __forceinline__ void set_geom(Cta& c, int l) {
     if constexpr (is_var<P>::value) {
-        const int rows = c.p->var[l].rows;
-        c.r0 = (int)((long long)rows * blockIdx.x / gridDim.x);
-        c.r1 = (int)((long long)rows * (blockIdx.x + 1) / gridDim.x);
+        const VarLayer& v = c.p->var[l];
+        var_rows<P::ROWS>(v.rows, l - v.chunk, c.r0, c.r1);
+        c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
+    } else if constexpr (is_rot<P>::value) {
+        var_rows<P::ROWS>(c.p->rows, l, c.r0, c.r1);
         c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
     }
 }
@@ -243,9 +265,10 @@ __device__ __forceinline__ void run_producer(const Cta& cta, const typename P::P
         if constexpr (is_var<P>::value) {                  // this layer's shape was requested a layer ago
             vl = vnext;
             vnext = p.var[min(l + 1, p.nlayers - 1)];
-            c.r0 = (int)((long long)vl.rows * blockIdx.x / gridDim.x);
-            c.r1 = (int)((long long)vl.rows * (blockIdx.x + 1) / gridDim.x);
+            var_rows<P::ROWS>(vl.rows, l - vl.chunk, c.r0, c.r1);
             c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
+        } else if constexpr (is_rot<P>::value) {
+            set_geom<P>(c, l);
         }
         if (!P::ACT_IN_STAGE && !copy_tile(l)) { ok = false; break; }
         for (int j = 0; j < c.nst; j++, cc++) {
@@ -464,6 +487,10 @@ stream_kernel(const typename P::Params pp) {
     c.r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
     c.nst = (c.r1 - c.r0 + P::ROWS - 1) / P::ROWS;
     c.tiled = !no_output<P>::value && (is_var<P>::value || (c.r1 - c.r0) * P::M <= kOutCap);   // (the launcher of a VAR policy checks the tile)
+    if constexpr (is_rot<P>::value) {                    // the most rows a layer can give this CTA
+        const int most = ((p.rows + P::ROWS - 1) / P::ROWS + (int)gridDim.x - 1) / (int)gridDim.x * P::ROWS;
+        c.tiled = !no_output<P>::value && most * P::M <= kOutCap;
+    }
 
     if (c.warp >= NCW && c.warp < NCW + P::NPROD) {
         if (c.lane == 0) run_producer<P>(c, pp, c.warp - NCW);
