@@ -126,10 +126,13 @@ def test_w4a4_stream_matches_oracle(rt):
         assert O.rel_err(y, O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 32)["y"][0]) < REL
 
 
-@pytest.mark.parametrize("kernel", ["w4a8_decode_stream", "w4a4_decode_stream"])
-def test_stream_delivers_y_to_pinned_host_memory(rt, kernel):
+@pytest.mark.parametrize("kernel,cfg", [("w4a8_decode_stream", None), ("w4a4_decode_stream", None), ("w4a8_decode_stream", "6")])
+def test_stream_delivers_y_to_pinned_host_memory(rt, monkeypatch, kernel, cfg):
     """A pinned host buffer registered through fm_stream_peers is one more receiver of y: after
-    fm_sync it holds the bits of the device copy, rows outside the shard untouched."""
+    fm_sync it holds the bits of the device copy, rows outside the shard untouched.  ($FM_STREAM_CFG=6: whole stages
+    per CTA from a position that moves with the layer, here with CTAs that have no row in a layer.)"""
+    if cfg is not None:
+        monkeypatch.setenv("FM_STREAM_CFG", cfg)
     rows, base, n_out, nl = 1500, 500, 2500, 5
     a4 = kernel.startswith("w4a4")
     layers = [synth.rt4_layer(rows, K, 1, seed=870 + i) for i in range(nl)]
@@ -706,9 +709,12 @@ def test_layers_of_different_shapes_in_one_launch(rt):
     rt.free_pinned(host)
 
 
-def test_read_ceiling_kernel_copies_and_writes_nothing(rt):
+@pytest.mark.parametrize("cfg", [None, "6"])
+def test_read_ceiling_kernel_copies_and_writes_nothing(rt, monkeypatch, cfg):
     """w4a8_stream_read_ceiling takes the arguments of w4a8_decode_stream, walks all stages (status 0) and leaves y as
-    it was; a table of another shape is refused."""
+    it was; a table of another shape is refused.  (6: the whole-stage split of the rows.)"""
+    if cfg is not None:
+        monkeypatch.setenv("FM_STREAM_CFG", cfg)
     rows, nl = 2176, 6
     layers = [synth.rt4_layer(rows, K, 1, seed=1900 + i) for i in range(nl)]
     with Bufs(rt) as b:
@@ -729,13 +735,16 @@ def test_read_ceiling_kernel_copies_and_writes_nothing(rt):
 def test_stream_schedules_give_identical_bits(rt, monkeypatch):
     """Every schedule of the W4A8 stream kernel ($FM_STREAM_CFG, with and without a suspend hint on the
     barrier waits) leaves the bits of gemv_w4a8<1,false,1> in y, on a shape with many stages per CTA and
-    layer and on one with a single (partial) stage; the NVFP4 consumers agree with each other to 1e-6."""
+    layer, on one with a single (partial) stage, on fewer rows than CTAs and on a row count that is no multiple of
+    the stage."""
     runner = W4Runner(rt)
-    for rows, nl in ((17408, 2), (2176, 6), (100, 9)):
+    for rows, nl in ((17408, 2), (2176, 6), (100, 9), (7111, 3)):
         layers = [synth.rt4_layer(rows, K, 1, seed=1500 + i) for i in range(nl)]
         with Bufs(rt) as b:
             want = None
-            for cfg in (None, 0, 1, 2, 3, 4, 7):
+            # (5 / 6: rows / grid per CTA / whole 16-row stages per CTA from a position that moves with the layer —
+            #  the default picks between them by the row count; 7111 rows end in a partial stage under both)
+            for cfg in (None, 0, 1, 2, 3, 4, 5, 6, 7):
                 for hint in ((0, 2000) if cfg is None else (0,)):
                     if cfg is None:
                         monkeypatch.delenv("FM_STREAM_CFG", raising=False)
