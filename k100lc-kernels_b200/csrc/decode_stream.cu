@@ -115,7 +115,7 @@ struct W4A8Mma {
     static constexpr int M = M_, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = AIS ? 1 : NACT_;
     static constexpr bool ACT_IN_STAGE = AIS, VAR = VAR_, ROT = ROT_;
     static_assert(!VAR || (AIS && M_ == 1 && !DUMP && PAD == 0), "per-layer shapes: one token, codes inside the stage");
-    static_assert(!ROT || (AIS && !VAR && !BREG), "moving row ranges: no per-layer state outside the stages");
+    static_assert(!ROT || (!VAR && !BREG), "moving row ranges: the shapes are the table's, no fragments held over a layer");
     static constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
     static constexpr int ROWB = K / 2, SCB = NG * 2, PITCH = ROWB + PAD;
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB;
@@ -308,11 +308,12 @@ struct W4A8ReadCeiling {
 // sub-group (column g carries token g & 1 in the k slots of lane g >> 1), so two tokens cost what one does; tokens
 // 2 and 3 are a second set of MMAs over the same A registers.  The code tile of a layer is [M][K/2] nibbles, then
 // [M][K/32] scales (a 2-D quant_act4 launch with grid y = layer * M + token).
-template <int STAGES_, int NGROUPS_, bool DUMP, int NPROD_ = 1, int M_ = 1>
+// ROT_: whole stages are dealt out to the CTAs, from a position that moves with the layer (stream_common.cuh: var_rows).
+template <int STAGES_, int NGROUPS_, bool DUMP, int NPROD_ = 1, int M_ = 1, bool ROT_ = false>
 struct W4A4Mma {
     using Params = PlainParams;
     static constexpr int M = M_, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = 1;
-    static constexpr bool ACT_IN_STAGE = true;
+    static constexpr bool ACT_IN_STAGE = true, ROT = ROT_;
     static constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
     static constexpr int ROWB = K / 2, SCB = NG * 2, PITCH = ROWB;
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB;
@@ -330,7 +331,8 @@ struct W4A4Mma {
         bulk_g2s(dst + M * (K / 2), p.asc + (size_t)l * M * (K / 32 * 4), M * (K / 32 * 4), bar);
     }
 
-    __device__ static void consume(const Cta& c, const Params& pp, int grp, int w) {
+    __device__ static void consume(const Cta& cta, const Params& pp, int grp, int w) {
+        Cta c = cta;                                     // (rows and stages of the CTA follow the layer when ROT)
         const StreamParams& p = pp.s;
         const int lane = c.lane, g = lane >> 2, t = lane & 3;
         // this lane's B registers carry column g: token (g & 1) of a set, in the k slots that lane g >> 1 feeds
@@ -343,8 +345,9 @@ struct W4A4Mma {
             btok[si] = tok < M ? tok : M - 1;
         }
         int cg = 0;
-        for (int l = 0; l < p.nlayers; l++) {
-            const int c0 = l * c.nst;
+        int c0 = 0;                                      // stages of the layers before this one
+        for (int l = 0; l < p.nlayers; c0 += c.nst, l++) {
+            set_geom<W4A4Mma>(c, l);
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;
             float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + p.row_base;
@@ -824,11 +827,13 @@ struct W4a16Params {
 //   NGROUPS consumer groups that take the stages in turn (2: a group has two stage times for its own stage)
 //   BREG    a warp keeps the B fragments of its blocks in registers for the whole layer (80 registers: one group only);
 //           otherwise they are read from the layer's tile with every stage
-template <int STAGES_, int NGROUPS_, int NACT_, bool BREG>
+//   ROT_    whole stages are dealt out to the CTAs, from a position that moves with the layer (stream_common.cuh: var_rows)
+template <int STAGES_, int NGROUPS_, int NACT_, bool BREG, bool ROT_ = false>
 struct W4A16Mma {
     using Params = W4a16Params;
     static constexpr int M = 1, STAGES = STAGES_, NGROUPS = NGROUPS_, NACT = NACT_;
-    static constexpr bool ACT_IN_STAGE = false;
+    static constexpr bool ACT_IN_STAGE = false, ROT = ROT_;
+    static_assert(!ROT || !BREG, "moving row ranges: no fragments held over a layer");
     static constexpr int K = 5120, NG = 40, CW = 8, GPW = NG / CW, ROWS = 16;
     static constexpr int ROWB = K / 2, SCB = NG * 2, PITCH = ROWB;
     static constexpr int STAGE_W = ROWS * PITCH, OFF_ACT = STAGE_W + ROWS * SCB, STAGE = OFF_ACT;
@@ -848,12 +853,14 @@ struct W4A16Mma {
         return reinterpret_cast<const uint4*>(ft + ((size_t)(b * 3 + g) * 4 + t) * 16)[q];
     }
 
-    __device__ static void consume(const Cta& c, const Params& pp, int grp, int w) {
+    __device__ static void consume(const Cta& cta, const Params& pp, int grp, int w) {
+        Cta c = cta;                                     // (rows and stages of the CTA follow the layer when ROT)
         const StreamParams& p = pp.s;
         const int lane = c.lane, g = lane >> 2, t = lane & 3;
         int cg = 0;                                      // stages this group has taken so far
-        for (int l = 0; l < p.nlayers; l++) {
-            const int c0 = l * c.nst;
+        int c0 = 0;                                      // stages of the layers before this one
+        for (int l = 0; l < p.nlayers; c0 += c.nst, l++) {
+            set_geom<W4A16Mma>(c, l);
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;     // this group's first stage of the layer
             if (!layer_enter<W4A16Mma>(c, l)) return;
             const uint32_t* ft = reinterpret_cast<const uint32_t*>(c.act + (size_t)(l % NACT) * ACT);
@@ -1224,7 +1231,15 @@ int launch_w4a8_stream_m(const LaunchCtx& c, const uint64_t* a) {
     // Default: two consumer groups that read the B fragments from the layer's tile.  Measured per layer (64 layers per
     // launch, burst): 7.3 / 8.3 / 8.1 us at M = 2 / 3 / 4 against 7.8 / 9.1 / 9.0 for one group with the fragments in
     // registers ($FM_STREAM_M_CFG=0, and the kernel the accumulator dump runs).
-    if (!DUMP && env_or("FM_STREAM_M_CFG", 1) == 1) {
+    const int grid = c.sm_count < p.rows ? c.sm_count : p.rows;
+    if (!DUMP && env_or("FM_STREAM_M_CFG", 1) == 1 && whole_stages(p.rows, grid)) {
+        switch (p.M) {                                   // + whole stages per CTA
+            case 2: return run_policy<W4A8Mma<2, 4, 2, false, 2, false, 0, false, 1, false, true>>(kn, c, pp);
+            case 3: return run_policy<W4A8Mma<3, 4, 2, false, 2, false, 0, false, 1, false, true>>(kn, c, pp);
+            default: return run_policy<W4A8Mma<4, 4, 2, false, 2, false, 0, false, 1, false, true>>(kn, c, pp);
+        }
+    }
+    if (!DUMP && env_or("FM_STREAM_M_CFG", 1) != 0) {    // (5: rows / grid per CTA whatever the row count)
         switch (p.M) {
             case 2: return run_policy<W4A8Mma<2, 4, 2, false, 2, false, 0, false>>(kn, c, pp);
             case 3: return run_policy<W4A8Mma<3, 4, 2, false, 2, false, 0, false>>(kn, c, pp);
@@ -1272,6 +1287,14 @@ int launch_w4a4_stream_m(const LaunchCtx& c, const uint64_t* a) {
         FM_RANGE(p.iacc, tokens * p.rows * (p.K / 32) * 4, kn, "iacc");
     }
     // four stages where they fit beside the tokens' codes (3200 bytes per token and stage), three at M = 4
+    const int grid = c.sm_count < p.rows ? c.sm_count : p.rows;
+    if (!DUMP && whole_stages(p.rows, grid) && env_or("FM_STREAM_M_CFG", 1) != 5) {
+        switch (p.M) {
+            case 2: return run_policy<W4A4Mma<4, 2, false, 2, 2, true>>(kn, c, pp);
+            case 3: return run_policy<W4A4Mma<4, 2, false, 2, 3, true>>(kn, c, pp);
+            default: return run_policy<W4A4Mma<3, 2, false, 1, 4, true>>(kn, c, pp);
+        }
+    }
     switch (p.M) {
         case 2: return run_policy<W4A4Mma<4, 2, DUMP, 2, 2>>(kn, c, pp);
         case 3: return run_policy<W4A4Mma<4, 2, DUMP, 2, 3>>(kn, c, pp);
@@ -1400,6 +1423,8 @@ int launch_w4a16_stream(const LaunchCtx& c, const uint64_t* a) {
     // Two consumer groups reading the fragments from the layer's tile; $FM_W4A16_CFG=0: one group with the fragments
     // of the layer in registers.
     if (env_or("FM_W4A16_CFG", 1) == 0) return run_policy<W4A16Mma<3, 1, 2, true>>(kn, c, pp);
+    const int grid = c.sm_count < p.rows ? c.sm_count : p.rows;
+    if (whole_stages(p.rows, grid) && env_or("FM_W4A16_CFG", 1) != 5) return run_policy<W4A16Mma<3, 2, 2, false, true>>(kn, c, pp);
     return run_policy<W4A16Mma<3, 2, 2, false>>(kn, c, pp);
 }
 
