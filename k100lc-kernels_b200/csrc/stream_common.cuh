@@ -202,7 +202,9 @@ template <int ROWS>
 __device__ __forceinline__ void var_rows(int rows, int first, int& r0, int& r1) {
     const int G = (int)gridDim.x, S = (rows + ROWS - 1) / ROWS;
     const int base = S / G, extra = S - base * G;
-    const int rot = (int)(((uint32_t)first * 2654435761u >> 12) % (uint32_t)G);
+    // the fractional part of first / golden ratio, scaled to the grid: consecutive matrices start far apart and the
+    // starts of any run of them cover the grid evenly
+    const int rot = (int)((((uint32_t)first * 2654435769u) >> 16) * (uint32_t)G >> 16);
     int b = (int)blockIdx.x - rot;
     b += b < 0 ? G : 0;
     const int s0 = b * base + min(b, extra), s1 = s0 + base + (b < extra ? 1 : 0);
