@@ -170,6 +170,10 @@ struct W4A8Mma {
         int c0 = 0;                                      // stages of the layers before this one
         for (int l = 0; l < p.nlayers; c0 += c.nst, l++) {
             set_geom<W4A8Mma>(c, l);
+            // a short chunk (the end of a row that is no multiple of 5120 k) has fewer 128-groups: the others would
+            // multiply zeros by zeros, so a warp skips them
+            int ngr = NG;
+            if (VAR) ngr = p.var[l].wbytes >> 6;
             const int jf = ((grp - c0) % NGROUPS + NGROUPS) % NGROUPS;     // this group's first stage of the layer
             float* yt = c.ytile + (l % kYBufs) * kOutCap;
             float* y = get_layer(p, l).y + (VAR ? 0 : p.row_base);      // (VAR: always through the tile, the writer adds the base)
@@ -196,6 +200,7 @@ struct W4A8Mma {
 #pragma unroll
                 for (int j = 0; j < GPW; j++) {
                     const int gg = j * CW + w;           // this warp's groups: w, w + 8, ...
+                    if (VAR && gg >= ngr) continue;
                     xa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * PITCH + gg * 64 + t * 16);
                     xb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * PITCH + gg * 64 + t * 16);
                     swa[j] = __half2float(*reinterpret_cast<const __half*>(st + STAGE_W + g * SCB + gg * 2));
@@ -205,6 +210,7 @@ struct W4A8Mma {
 #pragma unroll
                 for (int j = 0; j < GPW; j++) {
                     const int gg = j * CW + w;
+                    if (VAR && gg >= ngr) continue;
                     const Frag f = BREG ? fr[j] : load_frag(ab, gg, g, t);
                     int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
                     const uint32_t m_lo = 0x0F0F0F0Fu, x_lo = 0x08080808u, m_hi = 0xF0F0F0F0u, x_hi = 0x80808080u;
