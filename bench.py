@@ -305,9 +305,18 @@ def path_timings(rt, st: Stream, reps: int) -> dict:
         rt.launch("gemv_w4a8<1,false,1>", rows // 4, 256,
                   [st.wq_l(l), st.ws_l(l), st.ae, st.ao, st.asc, st.asu, st.y + l * N * 4, rows, K])
 
+    def w4a8_one(l):                                    # the quantiser inside the GEMV: one launch per layer
+        rt.launch("quant_gemv_w4a8", rows // 4, 256, [st.wq_l(l), st.ws_l(l), st.x + l * K * 4, st.y + l * N * 4, rows, K])
+
+    def w4a4_one(l):
+        rt.launch("quant_gemv_w4a4", rows // 4, 256, [st.wq_l(l), st.ws_l(l), st.x + l * K * 4, st.y + l * N * 4, rows, K])
+
     frac = rows / N
-    for name, fn, nbytes in (("w4a8_m1", w4a8, LAYER_BYTES), ("w4a4_m1", w4a4, LAYER_BYTES),
-                             ("nvfp4_m1", nvfp4, NVFP4_LAYER_BYTES), ("w4a8_m1_gemv_only", w4a8_only, LAYER_BYTES)):
+    paths = [("w4a8_m1", w4a8, LAYER_BYTES), ("w4a4_m1", w4a4, LAYER_BYTES), ("nvfp4_m1", nvfp4, NVFP4_LAYER_BYTES),
+             ("w4a8_m1_gemv_only", w4a8_only, LAYER_BYTES)]
+    if rt.has("quant_gemv_w4a8"):
+        paths += [("w4a8_m1_one_launch", w4a8_one, LAYER_BYTES), ("w4a4_m1_one_launch", w4a4_one, LAYER_BYTES)]
+    for name, fn, nbytes in paths:
         g = graph_of(fn, nl)
         ms = time_graph(rt, g, reps, 3, lambda: None)
         rt.graph_free(g)

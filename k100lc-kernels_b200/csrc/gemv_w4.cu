@@ -45,6 +45,7 @@ struct GemvW4Params {
     const float* asc;        // A8: [M][K/128]; A4: [M][K/32]
     const int* asu;          // A8: [M][K/128] group sums; A4: unused
     float* y;                // [M][N]
+    const float* x;          // FUSEQ kernels: the token itself, fp32 [K]; the codes above are then unused
     int* iacc;               // optional dump of the integer accumulators, [M][N][K/128 or K/32]
     int N, K;
     int rows;                // rows to compute: min(N, rows covered by the caller's grid)
@@ -95,9 +96,14 @@ __device__ __forceinline__ int dot32(const uint4& w, const uint4& e, const uint4
 // KITER  : K / 1024 when K is a multiple of 1024 (fully unrolled, no tail), else 0
 // AREG   : hold the activations in registers (needs KITER > 0 and M == 1)
 // DUMP   : also store the integer accumulators
-template <bool A4, int M, int R, int KITER, bool AREG, bool DUMP>
+// FUSEQ  : (one token, AREG) the CTA quantises x itself into shared memory in front of the rows — the arithmetic of
+//          quant_act / quant_act4 (reference kernels/gemv_w4a8_core.h:34-66, gemv_w4a4_core.h:26-45), so the codes,
+//          scales and sums are the bits the separate quantiser launch would have written — while its first weight
+//          loads are in flight: one launch and one round trip of the codes less per layer
+template <bool A4, int M, int R, int KITER, bool AREG, bool DUMP, bool FUSEQ = false>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_w4_kernel(const GemvW4Params p) {
+    static_assert(!FUSEQ || (M == 1 && AREG && !DUMP), "the fused quantiser serves the one-token register path");
     extern __shared__ __align__(16) uint32_t smem[];
     const int KD = p.K >> 3;                     // 32-bit words per weight row
     const int NG = p.K >> 7;                     // weight-scale groups per row
@@ -141,17 +147,75 @@ gemv_w4_kernel(const GemvW4Params p) {
     uint4 areg_e[AREG ? UN : 1], areg_o[AREG ? UN : 1];
     float areg_sc[AREG ? UN : 1];
     int areg_su[AREG ? UN : 1];
+    if constexpr (FUSEQ) {
+        // (all loads of x first: a warp's groups one after the other would pay the trip to L2 once per group)
+        if (A4) {                                           // quant_act4: a thread owns 8 elements = one packed word
+            constexpr int NW = (UN * 128 + kThreads - 1) / kThreads;           // words per thread (KD = KITER * 128)
+            float4 a[NW], b[NW];
+#pragma unroll
+            for (int i = 0; i < NW; i++) {
+                const int w = i * kThreads + threadIdx.x;
+                const bool live = (i * kThreads + (threadIdx.x & ~31)) < KD;    // whole warps: the shuffles need every lane
+                const float4* src = reinterpret_cast<const float4*>(p.x + (size_t)(live ? w : 0) * 8);
+                a[i] = src[0];
+                b[i] = src[1];
+            }
+#pragma unroll
+            for (int i = 0; i < NW; i++) {
+                const int w = i * kThreads + threadIdx.x;
+                if ((i * kThreads + (threadIdx.x & ~31)) >= KD) break;
+                float amax = fmaxf(fmaxf(fmaxf(fabsf(a[i].x), fabsf(a[i].y)), fmaxf(fabsf(a[i].z), fabsf(a[i].w))),
+                                   fmaxf(fmaxf(fabsf(b[i].x), fabsf(b[i].y)), fmaxf(fabsf(b[i].z), fabsf(b[i].w))));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                const float sc = absmax_scale(amax, 7.f);
+                const float e[8] = {a[i].x, a[i].y, a[i].z, a[i].w, b[i].x, b[i].y, b[i].z, b[i].w};
+                uint32_t word = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) word |= (uint32_t)(quant_rne(e[j], sc, -8, 7) & 0xF) << (4 * j);
+                s_e[w] = word;
+                if ((w & 3) == 0) s_sc[w >> 2] = sc;
+            }
+        } else {                                            // quant_act: a warp owns a 128-group, a lane 4 elements
+            float4 v[UN];                                   // NG = 8 * KITER groups, KITER per warp
+#pragma unroll
+            for (int i = 0; i < UN; i++)
+                v[i] = *reinterpret_cast<const float4*>(p.x + (size_t)(i * kWarps + (threadIdx.x >> 5)) * 128 + lane * 4);
+#pragma unroll
+            for (int i = 0; i < UN; i++) {
+                const int g = i * kWarps + (threadIdx.x >> 5);
+                float amax = fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+#pragma unroll
+                for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                const float sc = absmax_scale(amax, 127.f);
+                const int q0 = quant_rne(v[i].x, sc, -128, 127), q1 = quant_rne(v[i].y, sc, -128, 127);
+                const int q2 = quant_rne(v[i].z, sc, -128, 127), q3 = quant_rne(v[i].w, sc, -128, 127);
+                reinterpret_cast<char2*>(s_e)[g * 32 + lane] = make_char2((signed char)q0, (signed char)q2);
+                reinterpret_cast<char2*>(s_o)[g * 32 + lane] = make_char2((signed char)q1, (signed char)q3);
+                const int sum = warp_sum(q0 + q1 + q2 + q3);
+                if (lane == 0) {
+                    s_sc[g] = sc;
+                    s_su[g] = sum;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    const uint32_t* src_e = FUSEQ ? s_e : p.a0;
+    const uint32_t* src_o = FUSEQ ? s_o : p.a1;
+    const float* src_sc = FUSEQ ? s_sc : p.asc;
+    const int* src_su = FUSEQ ? s_su : p.asu;
     if (AREG) {
 #pragma unroll
         for (int it = 0; it < UN; it++) {
             const int d0 = it * 128 + lane * 4;
             if (A4) {                                       // 32 nibbles = one 32-sub-group per lane and step
-                const uint4 a = *reinterpret_cast<const uint4*>(p.a0 + d0);
+                const uint4 a = *reinterpret_cast<const uint4*>(src_e + d0);
                 areg_e[it] = make_uint4(sext_nibbles(a.x & 0x0F0F0F0Fu), sext_nibbles(a.y & 0x0F0F0F0Fu),
                                         sext_nibbles(a.z & 0x0F0F0F0Fu), sext_nibbles(a.w & 0x0F0F0F0Fu));
                 areg_o[it] = make_uint4(sext_nibbles((a.x >> 4) & 0x0F0F0F0Fu), sext_nibbles((a.y >> 4) & 0x0F0F0F0Fu),
                                         sext_nibbles((a.z >> 4) & 0x0F0F0F0Fu), sext_nibbles((a.w >> 4) & 0x0F0F0F0Fu));
-                areg_sc[it] = p.asc[d0 >> 2];
+                areg_sc[it] = src_sc[d0 >> 2];
                 int su = 0;
                 su = dot4(areg_e[it].x, 0x01010101u, su); su = dot4(areg_o[it].x, 0x01010101u, su);
                 su = dot4(areg_e[it].y, 0x01010101u, su); su = dot4(areg_o[it].y, 0x01010101u, su);
@@ -159,10 +223,10 @@ gemv_w4_kernel(const GemvW4Params p) {
                 su = dot4(areg_e[it].w, 0x01010101u, su); su = dot4(areg_o[it].w, 0x01010101u, su);
                 areg_su[it] = su;
             } else {
-                areg_e[it] = *reinterpret_cast<const uint4*>(p.a0 + d0);
-                areg_o[it] = *reinterpret_cast<const uint4*>(p.a1 + d0);
-                areg_sc[it] = p.asc[d0 >> 4];
-                areg_su[it] = p.asu[d0 >> 4];
+                areg_e[it] = *reinterpret_cast<const uint4*>(src_e + d0);
+                areg_o[it] = *reinterpret_cast<const uint4*>(src_o + d0);
+                areg_sc[it] = src_sc[d0 >> 4];
+                areg_su[it] = src_su[d0 >> 4];
             }
         }
     } else {
@@ -543,6 +607,52 @@ int launch_w4a4(const LaunchCtx& c, const uint64_t* a) {
     return dispatch<true, M, false>(kn, c, p);
 }
 
+// quant_gemv_w4a8(wq, ws, x, y, N, K) / quant_gemv_w4a4(wq, ws, x, y, N, K): one token, the activation quantiser inside
+// the GEMV (x fp32 [K]); K = 5120 or 6144 (the shapes whose row loop keeps the token's codes in registers).  Grid and
+// work-group as for gemv_w4a8<1,*,1> / gemv_w4a4<1>: 256 threads, rows < min(N, 4 * grid).  y has the bits of the
+// quantiser launch followed by the GEMV launch.
+template <bool A4, int KITER>
+int run_fused(const char* kn, const LaunchCtx& c, const GemvW4Params& p) {
+    auto kern = gemv_w4_kernel<A4, 1, 1, KITER, true, false, true>;
+    const int KD = p.K / 8, nsc = A4 ? p.K / 32 : p.K / 128;
+    const size_t smem = (size_t)2 * KD * 4 + (size_t)nsc * 8;
+    const int blocks_needed = (p.rows + kWarps - 1) / kWarps;
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
+    if (e != cudaSuccess) return cuda_fail(kn, e);
+    if (per_sm < 1) per_sm = 1;
+    int grid = c.sm_count * per_sm;
+    if (grid > blocks_needed) grid = blocks_needed;
+    e = launch_kernel(kern, dim3(grid), dim3(kThreads), smem, c.stream, pdl_enabled(), p);
+    return e == cudaSuccess ? after_launch(kn) : cuda_fail(kn, e);
+}
+
+template <bool A4>
+int launch_fused(const LaunchCtx& c, const uint64_t* a) {
+    const char* kn = A4 ? "quant_gemv_w4a4" : "quant_gemv_w4a8";
+    GemvW4Params p = {};
+    p.wq = arg_ptr<const uint32_t>(a[0]);
+    p.ws = arg_ptr<const __half>(a[1]);
+    p.x = arg_ptr<const float>(a[2]);
+    p.y = arg_ptr<float>(a[3]);
+    p.N = arg_i32(a[4]);
+    p.K = arg_i32(a[5]);
+    FM_REQUIRE(c.wx == 256 && c.wy == 1 && c.gy == 1, kn, "work-group must be 256x1 threads on a 1-D grid; got %ux%u, grid y=%u",
+               c.wx, c.wy, c.gy);
+    FM_REQUIRE(p.N > 0 && (p.K == 5120 || p.K == 6144), kn,
+               "N=%d K=%d: this entry takes K = 5120 or 6144; launch the quantiser and the GEMV for other shapes", p.N, p.K);
+    const long long covered = (long long)c.gx * 4;
+    p.rows = (int)(covered < p.N ? covered : p.N);
+    FM_REQUIRE(aligned(p.wq, 16) && aligned(p.ws, 2) && aligned(p.x, 16) && aligned(p.y, 4), kn,
+               "misaligned pointer (weights and x need 16 bytes, scales 2, y 4)");
+    if (p.rows == 0) return FM_OK;
+    FM_RANGE(p.wq, (size_t)p.rows * (p.K / 2), kn, "wq");
+    FM_RANGE(p.ws, (size_t)p.rows * (p.K / 128) * 2, kn, "ws");
+    FM_RANGE(p.x, (size_t)p.K * 4, kn, "x");
+    FM_RANGE(p.y, (size_t)p.rows * 4, kn, "y");
+    return p.K == 5120 ? run_fused<A4, 5>(kn, c, p) : run_fused<A4, 6>(kn, c, p);
+}
+
 // Accumulator dumps (extensions, used by the parity tests):
 //   gemv_w4a8_iacc(wq, ws, ae, ao, asc, asu, y, N, K, iacc, M)   iacc int32 [M][N][K/128]
 //   gemv_w4a4_iacc(wq, ws, aq, asc, y, N, K, iacc, M)            iacc int32 [M][N][K/32]
@@ -591,6 +701,8 @@ const KernelEntry kGemvW4[] = {
     {"gemv_w4a4<4>", 7, launch_w4a4<4, 1>, "pppppii"},
     {"gemv_w4a4_r2_k", 7, launch_w4a4<4, 2>, "pppppii"},
     {"gemv_w4a4_r2_m3_k", 7, launch_w4a4<3, 2>, "pppppii"},
+    {"quant_gemv_w4a8", 6, launch_fused<false>, "ppppii"},
+    {"quant_gemv_w4a4", 6, launch_fused<true>, "ppppii"},
     {"gemv_w4a8_iacc", 11, launch_iacc<false>, "pppppppiipi"},
     {"gemv_w4a4_iacc", 9, launch_iacc<true>, "pppppiipi"},
 };

@@ -105,6 +105,31 @@ def test_w4_two_row_names_and_partial_grid(rt):
 
 
 @pytest.mark.parametrize("kind", ["w4a8", "w4a4"])
+@pytest.mark.parametrize("n,k", [(1000, 5120), (333, 6144), (17408, 5120)])
+def test_quantiser_inside_the_gemv_leaves_the_same_bits(rt, kind, n, k):
+    """quant_gemv_w4a8 / quant_gemv_w4a4 (one token, x fp32 in, the CTA quantises x itself): the bits of the quantiser
+    launch followed by the GEMV launch, within 1e-5 of the oracle; a grid that covers fewer rows leaves the others
+    alone; another K is refused."""
+    L = synth.rt4_layer(n, k, 1, seed=4100 + n % 7)
+    q = O.quant_act(L["x"]) if kind == "w4a8" else O.quant_act4(L["x"])
+    ref = O.gemv_w4(L["wq"], L["ws"], q["q"], q["scale"], 128 if kind == "w4a8" else 32)["y"][0]
+    two, _, _ = (w4a8_device if kind == "w4a8" else w4a4_device)(rt, L["wq"], L["ws"], L["x"])
+    with Bufs(rt) as b:
+        pwq, pws, px = b.put(L["wq"]), b.put(L["ws"]), b.put(L["x"][0])
+        py = b.zeros(n, np.float32, np.nan)
+        rt.launch(f"quant_gemv_{kind}", -(-n // 4), 256, [pwq, pws, px, py, n, k])
+        one = b.get(py, n)
+        part = b.zeros(n, np.float32, np.nan)
+        rt.launch(f"quant_gemv_{kind}", 10, 256, [pwq, pws, px, part, n, k])       # 40 rows
+        some = b.get(part, n)
+        with pytest.raises(RuntimeError, match="rc=-4"):
+            rt.launch(f"quant_gemv_{kind}", -(-n // 4), 256, [pwq, pws, px, py, n, 4096])
+    assert np.array_equal(one.view(np.uint32), two[0].view(np.uint32))
+    assert O.rel_err(one, ref) < REL
+    assert np.array_equal(some[:40].view(np.uint32), one[:40].view(np.uint32)) and np.isnan(some[40:]).all()
+
+
+@pytest.mark.parametrize("kind", ["w4a8", "w4a4"])
 def test_w4_full_size(rt, kind):
     """The benchmark shape 17408 x 5120 at M=1 (seed 1): accumulators and y."""
     L = synth.rt4_layer(m=1, seed=1)
