@@ -234,3 +234,57 @@ def test_int4_manifest_round_trip(tmp_path):
         f.write(b"x")
     with pytest.raises(ValueError, match="regenerate"):
         im.read_manifest(tmp_path / "m.tsv", tmp_path)
+
+
+class _RecordingRuntime:
+    """Stands in for Runtime where only the sequence of launches matters (no device)."""
+
+    def __init__(self, kernels):
+        self.kernels, self.launches, self._next = set(kernels), [], 4096
+
+    def alloc(self, nbytes):
+        self._next += 4096 + int(nbytes)
+        return self._next
+
+    def free(self, ptr):
+        pass
+
+    def has(self, name):
+        return name in self.kernels
+
+    def launch(self, name, grid, threads, argv):
+        self.launches.append((name, grid, threads, len(argv)))
+
+    def launch2d(self, name, gx, gy, wx, wy, argv):
+        self.launches.append((name, (gx, gy), (wx, wy), len(argv)))
+
+    def sync(self):
+        pass
+
+
+def test_runner_picks_the_one_launch_entry_only_where_it_applies():
+    """W4Runner.gemv_device: one W4A8 token at K = 5120 / 6144 is the single launch quant_gemv_w4a8 when the library
+    has it; every other case (more tokens, another K, W4A4, an older library, fused=False) keeps the reference's
+    quantiser + GEMV pair; asking for the single launch on a shape it does not take is an error."""
+    from k100lc_kernels.rt4 import W4Runner
+    full = {"quant_gemv_w4a8", "quant_gemv_w4a4"}
+
+    def names(kernels, kind, m, k, **kw):
+        rt = _RecordingRuntime(kernels)
+        W4Runner(rt).gemv_device(kind, 1, 2, None, 1000, k, x_dev=64, y_dev=128, m=m, sync=False, **kw)
+        return [l[0] for l in rt.launches]
+
+    assert names(full, "w4a8", 1, 5120) == ["quant_gemv_w4a8"]
+    assert names(full, "w4a8", 1, 6144) == ["quant_gemv_w4a8"]
+    assert names(full, "w4a8", 1, 5120, fused=False) == ["quant_act", "gemv_w4a8<1,false,1>"]
+    assert names(set(), "w4a8", 1, 5120) == ["quant_act", "gemv_w4a8<1,false,1>"]
+    assert names(full, "w4a8", 2, 5120) == ["quant_act", "gemv_w4a8<2,false,2>"]
+    assert names(full, "w4a8", 1, 4096) == ["quant_act", "gemv_w4a8<1,false,1>"]
+    assert names(full, "w4a4", 1, 5120) == ["quant_act4", "gemv_w4a4<1>"]
+    assert names(full, "w4a4", 1, 5120, fused=True) == ["quant_gemv_w4a4"]
+    with pytest.raises(ValueError, match="one token"):
+        names(full, "w4a8", 3, 5120, fused=True)
+    with pytest.raises(ValueError, match="one token"):
+        names(full, "w4a8", 1, 1024, fused=True)
+    with pytest.raises(ValueError, match="unknown W4 path"):
+        names(full, "w8a8", 1, 5120)
