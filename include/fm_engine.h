@@ -131,6 +131,11 @@ int   fm_stream_table(void* dev_table, const uint64_t* host_layers, int nlayers,
  * Every range is checked against the live allocations; dev_table receives nlayers*32 bytes, dev_shapes nlayers*64.
  * 0 ok, -4 a pointer or a shape fails the check, -1 other errors. */
 int   fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_layers, int nlayers);
+/* Which rows [*r0, *r1) of a layer of `rows` rows CTA `cta` of a grid of `grid` CTAs computes in the stream kernels that
+ * deal out whole 16-row stages ("w4a8_layers_stream", and the uniform streams when a CTA has three or more stages per
+ * layer): `first` is the table index of the layer — of the first chunk of its weight matrix in a table of
+ * fm_stream_table_var.  The same function the kernels call; needs no device.  0 ok, -1 arguments out of range. */
+int   fm_stream_rows(int rows, int first, int grid, int cta, int* r0, int* r1);
 
 /* Peer memory for the row-sharded stream (one process per GPU).  fm_ipc_export gives the
  * 64-byte CUDA IPC handle of the fm_alloc allocation that contains `dev`, the offset of

@@ -28,6 +28,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "stage_split.h"
 #include "fm_internal.h"
 
 namespace fm {
@@ -1019,6 +1020,15 @@ int fm_stream_table_var(void* dev_table, void* dev_shapes, const uint64_t* host_
             if (dev) cudaFree(dev);
         }
     }
+    return 0;
+}
+
+int fm_stream_rows(int rows, int first, int grid, int cta, int* r0, int* r1) {
+    if (rows <= 0 || first < 0 || grid <= 0 || cta < 0 || cta >= grid || !r0 || !r1) {
+        set_errorf("fm_stream_rows: rows=%d first=%d grid=%d cta=%d out of range", rows, first, grid, cta);
+        return -1;
+    }
+    fm::stage_split(rows, first, grid, cta, 16, r0, r1);
     return 0;
 }
 

@@ -18,6 +18,7 @@
 // producer first waits (bounded again) for the copies it has already issued, so that no bulk copy is
 // still landing in this CTA's shared memory when the CTA gives it up.
 #pragma once
+#include "stage_split.h"
 #include <stdint.h>
 
 #include <type_traits>
@@ -200,16 +201,7 @@ template <class P> struct is_var<P, std::void_t<decltype(P::VAR)>> : std::bool_c
 // chunks of a matrix — which add to the same y — are split alike), which spreads those stages evenly over the launch.
 template <int ROWS>
 __device__ __forceinline__ void var_rows(int rows, int first, int& r0, int& r1) {
-    const int G = (int)gridDim.x, S = (rows + ROWS - 1) / ROWS;
-    const int base = S / G, extra = S - base * G;
-    // the fractional part of first / golden ratio, scaled to the grid: consecutive matrices start far apart and the
-    // starts of any run of them cover the grid evenly
-    const int rot = (int)((((uint32_t)first * 2654435769u) >> 16) * (uint32_t)G >> 16);
-    int b = (int)blockIdx.x - rot;
-    b += b < 0 ? G : 0;
-    const int s0 = b * base + min(b, extra), s1 = s0 + base + (b < extra ? 1 : 0);
-    r0 = min(rows, s0 * ROWS);
-    r1 = min(rows, s1 * ROWS);
+    stage_split(rows, first, (int)gridDim.x, (int)blockIdx.x, ROWS, &r0, &r1);     // stage_split.h
 }
 // A policy may also declare `static constexpr bool ROT = true`: all layers have the table's one shape, and the CTA's
 // rows are dealt out per layer as above (the position moves with the layer).

@@ -87,6 +87,7 @@ def load_library(path=None) -> ctypes.CDLL:
         "fm_download_beside": (c.c_int, [c.c_void_p, c.c_size_t, c.c_void_p, c.c_size_t, c.c_size_t, c.c_size_t]),
         "fm_download_join": (c.c_int, [c.c_int]),
         "fm_stream_table_var": (c.c_int, [c.c_void_p, c.c_void_p, c.POINTER(c.c_uint64), c.c_int]),
+        "fm_stream_rows": (c.c_int, [c.c_int, c.c_int, c.c_int, c.c_int, c.POINTER(c.c_int), c.POINTER(c.c_int)]),
         "fm_event_create": (c.c_int, []),
         "fm_event_record": (c.c_int, [c.c_int]),
         "fm_event_elapsed_ms": (c.c_float, [c.c_int, c.c_int]),
@@ -469,6 +470,14 @@ class Runtime:
             self.free(shapes)
             self._fail("fm_stream_table_var")
         return table, shapes
+
+    def stream_rows(self, rows: int, first: int, grid: int, cta: int) -> tuple[int, int]:
+        """Rows ``[r0, r1)`` of a layer that CTA ``cta`` of ``grid`` computes where whole 16-row stages are dealt out
+        (``first``: table index of the layer, or of the first chunk of its weight matrix)."""
+        r0, r1 = ctypes.c_int(), ctypes.c_int()
+        if self._lib.fm_stream_rows(int(rows), int(first), int(grid), int(cta), ctypes.byref(r0), ctypes.byref(r1)) != 0:
+            self._fail("fm_stream_rows")
+        return r0.value, r1.value
 
     def gemm_status(self) -> int:
         """Sync, then 0 or the code of a bounded wait that ran out in a GEMM kernel."""

@@ -288,3 +288,40 @@ def test_runner_picks_the_one_launch_entry_only_where_it_applies():
         names(full, "w4a8", 1, 1024, fused=True)
     with pytest.raises(ValueError, match="unknown W4 path"):
         names(full, "w8a8", 1, 5120)
+
+
+def test_stage_split_deals_out_every_row_once():
+    """fm_stream_rows (the function the stream kernels call with their own block index): for every layer the CTAs'
+    ranges are disjoint and cover [0, rows); every range is whole 16-row stages except the end of the layer; stage
+    counts of two CTAs differ by at most one; the chunks of a weight matrix (same `first`) are split alike; over a
+    run of layers the extra stages are spread evenly over the CTAs."""
+    lib = load_library()
+    r0, r1 = ctypes.c_int(), ctypes.c_int()
+
+    def split(rows, first, grid):
+        out = []
+        for cta in range(grid):
+            assert lib.fm_stream_rows(rows, first, grid, cta, ctypes.byref(r0), ctypes.byref(r1)) == 0
+            out.append((r0.value, r1.value))
+        return out
+
+    for rows, grid in ((17408, 148), (5120, 148), (2176, 148), (1024, 148), (7111, 148), (37, 37), (1, 1), (300, 148),
+                       (8704, 132), (100000, 148), (16, 148), (17, 2)):
+        for first in (0, 1, 2, 5, 77, 399, 655, 10_000):
+            parts = split(rows, first, grid)
+            covered = sorted(p for p in parts if p[1] > p[0])
+            assert covered[0][0] == 0 and covered[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(covered, covered[1:])), (rows, grid, first)
+            assert all((a % 16 == 0 or a == rows) and (b % 16 == 0 or b == rows) for a, b in parts)   # (empty ranges sit at `rows`)
+            stages = [-(-(b - a) // 16) for a, b in parts]
+            assert max(stages) - min(stages) <= 1 and sum(stages) == -(-rows // 16)
+            assert parts == split(rows, first, grid)                                    # the chunks of a matrix: same ranges
+    # 400 layers of 17408 rows on 148 CTAs: 1088 stages per layer, 52 CTAs get one more than the others; over the
+    # launch every CTA ends within a fraction of a per cent of the mean
+    total = np.zeros(148, np.int64)
+    for layer in range(400):
+        total += np.array([-(-(b - a) // 16) for a, b in split(17408, layer, 148)])
+    assert total.sum() == 400 * 1088 and (total.max() - total.min()) <= 0.01 * total.mean()
+    # arguments out of range
+    for bad in ((0, 0, 148, 0), (100, -1, 148, 0), (100, 0, 0, 0), (100, 0, 148, 148), (100, 0, 148, -1)):
+        assert lib.fm_stream_rows(*bad, ctypes.byref(r0), ctypes.byref(r1)) == -1
